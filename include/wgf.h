@@ -1,0 +1,264 @@
+/*
+ * wgf.h -- C ABI of the B200 (sm_100a) backend for the lazy, kernel-fusing tensor runtime
+ * whose behaviour is defined by the Rust crate `wgpu-compute`.
+ *
+ * The crate has no FFI layer of its own: its only contact with a GPU is five wgpu seams
+ * (device creation, buffer allocation/upload, kernel dispatch, queue submit, download and
+ * timestamp queries).  This header places one plain-C entry point at each of those seams
+ * ("kernel-level" section) and, above them, restates the crate's public `Tensor` API as
+ * opaque-handle calls ("graph-level" section) so that a host written in any language gets
+ * the lazy graph and the fusion resolver as well.  Every declaration cites the crate item it
+ * replaces as `path:line` relative to the crate root.
+ *
+ * Conventions
+ *   - every function returns a status (WGF_OK == 0); on failure `wgf_last_error()` gives a
+ *     thread-local message.  Nothing aborts, nothing throws across this boundary.
+ *   - handles are reference counted; `*_release` drops one reference.
+ *   - shapes, strides and offsets are in ELEMENTS and 64-bit (the crate passes u32 to its
+ *     shaders, src/kernel.rs:326-333).
+ *   - one CUDA stream per device handle; all work on a device is ordered on that stream.
+ *   - there is no CPU fallback: a call that needs the GPU fails with WGF_ERR_CUDA without one.
+ */
+#ifndef WGF_H
+#define WGF_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WGF_MAX_RANK 8
+
+/* ---- status codes ------------------------------------------------------------------ */
+enum {
+    WGF_OK = 0,
+    WGF_ERR_SHAPE = 1,          /* the crate panics: src/pair_wise.rs:92, src/matmul.rs:194 */
+    WGF_ERR_DTYPE = 2,
+    WGF_ERR_RANK = 3,           /* src/visit_tiled.rs:71 */
+    WGF_ERR_OOM = 4,
+    WGF_ERR_CUDA = 5,           /* RequestDeviceError / BufferAsyncError: src/device.rs:14, src/tensor.rs:551 */
+    WGF_ERR_NCCL = 6,
+    WGF_ERR_TIMEOUT = 7,
+    WGF_ERR_INVALID_HANDLE = 8,
+    WGF_ERR_INVALID_ARGUMENT = 9,
+    WGF_ERR_COMPILE = 10,       /* run-time kernel compilation failed (create_shader_module, src/kernel.rs:244-272) */
+    WGF_ERR_UNSUPPORTED = 11
+};
+
+/* ---- element types: DataTypeEnum, src/tensor.rs:67-72 (bf16 is an addition) ---------- */
+enum { WGF_F32 = 0, WGF_F16 = 1, WGF_BF16 = 2 };
+
+/* ---- opcodes ------------------------------------------------------------------------
+ * Unary functions: src/element_wise.rs:678-1380.  Scalar forms: src/element_wise.rs:197-651.
+ * Binary: src/pair_wise.rs:205-528.  Reductions: src/reduce.rs:433-815. */
+enum {
+    WGF_OP_EXP = 0, WGF_OP_EXP2, WGF_OP_LOG, WGF_OP_LOG2, WGF_OP_SQR, WGF_OP_SQRT,
+    WGF_OP_SIN, WGF_OP_COS, WGF_OP_TAN, WGF_OP_ASIN, WGF_OP_ACOS, WGF_OP_ATAN,
+    WGF_OP_SINH, WGF_OP_COSH, WGF_OP_TANH, WGF_OP_ASINH, WGF_OP_ACOSH, WGF_OP_ATANH,
+    WGF_OP_ABS, WGF_OP_NEG,
+    WGF_OP_ADD_C = 32,  /* x + c */
+    WGF_OP_SUB_C,       /* x - c */
+    WGF_OP_RSUB_C,      /* c - x */
+    WGF_OP_MUL_C,       /* x * c */
+    WGF_OP_DIV_C,       /* x / c */
+    WGF_OP_RDIV_C,      /* c / x */
+    WGF_OP_CAST = 48,   /* to out_dtype: src/element_wise.rs:1408-1471 */
+    WGF_OP_ADD = 64, WGF_OP_SUB, WGF_OP_MUL, WGF_OP_DIV, WGF_OP_POW,
+    WGF_OP_SUM = 96, WGF_OP_MAX, WGF_OP_MIN, WGF_OP_PRODUCT
+};
+
+typedef struct wgf_device wgf_device;
+typedef struct wgf_buffer wgf_buffer;
+typedef struct wgf_tensor wgf_tensor;
+typedef struct wgf_comm wgf_comm;
+
+const char* wgf_last_error(void);
+/* Version of this ABI; bumped on any incompatible change. */
+int32_t wgf_abi_version(void);
+
+/* ======================================================================================
+ * Device  (replaces Device::new / Clone / wgpu_device().poll, src/device.rs:8-52)
+ * ==================================================================================== */
+int32_t wgf_device_create(int32_t ordinal, wgf_device** out);
+int32_t wgf_device_retain(wgf_device* dev);
+int32_t wgf_device_release(wgf_device* dev);
+/* Blocks until all work queued on the device's stream has finished. */
+int32_t wgf_device_sync(wgf_device* dev);
+/* No-op kept so callers that spawn the crate's `device.poll(Wait)` loop still link. */
+int32_t wgf_device_poll(wgf_device* dev);
+/* Per-kernel CUDA-event timing on/off (default on, like the crate's timestamp queries). */
+int32_t wgf_device_set_timing(wgf_device* dev, int32_t enabled);
+/* Number of kernels this library has launched on the device since creation. */
+int32_t wgf_device_launch_count(wgf_device* dev, uint64_t* out);
+/* Number of run-time kernel compilations so far (cache misses). */
+int32_t wgf_device_compile_count(wgf_device* dev, uint64_t* out);
+/* Bytes held from the driver / bytes handed out to live buffers. */
+int32_t wgf_device_memory(wgf_device* dev, uint64_t* reserved, uint64_t* in_use);
+/* Number of SMs and the raw cudaStream_t (as void*) for interop with the caller's runtime. */
+int32_t wgf_device_info(wgf_device* dev, int32_t* sm_count, void** stream);
+
+/* ======================================================================================
+ * Buffers  (replaces TensorData::new_for_shape/new_inner/owned, src/tensor.rs:331-415,
+ *           and the download in src/tensor.rs:533-549)
+ * ==================================================================================== */
+int32_t wgf_buffer_alloc(wgf_device* dev, uint64_t bytes, int32_t zero, wgf_buffer** out);
+int32_t wgf_buffer_retain(wgf_buffer* buf);
+int32_t wgf_buffer_release(wgf_buffer* buf);
+/* Arc::strong_count analogue that gates in-place reuse, src/tensor.rs:413-415. */
+int32_t wgf_buffer_use_count(wgf_buffer* buf, int64_t* out);
+int32_t wgf_buffer_upload(wgf_buffer* buf, uint64_t offset_bytes, const void* src, uint64_t bytes);
+int32_t wgf_buffer_download(wgf_buffer* buf, uint64_t offset_bytes, void* dst, uint64_t bytes);
+int32_t wgf_buffer_device_ptr(wgf_buffer* buf, void** ptr, uint64_t* bytes);
+
+/* ======================================================================================
+ * Kernel-level launches  (replace Untyped*Kernel::run_with_query)
+ * ==================================================================================== */
+/* Layout {offset, shape, strides} + DataTypeEnum + buffer: src/layout.rs:33-38, src/tensor.rs:300-306 */
+typedef struct wgf_tensor_desc {
+    wgf_buffer* buf;
+    uint32_t dtype;
+    uint32_t rank;
+    int64_t offset;
+    int64_t shape[WGF_MAX_RANK];
+    int64_t stride[WGF_MAX_RANK];
+} wgf_tensor_desc;
+
+/* ElementWiseFunction, src/element_wise.rs:167-172; `chain[0]` is applied first. */
+typedef struct wgf_ew_op {
+    uint16_t opcode;
+    uint16_t out_dtype;   /* only read for WGF_OP_CAST */
+    float imm;            /* only read for the scalar forms */
+} wgf_ew_op;
+
+/* UntypedElementWiseKernel::run_with_query, src/element_wise.rs:89-164.
+ * `inplace_ok` != 0 lets the result reuse `in`'s buffer when the dtype width is unchanged
+ * (the crate decides this from the buffer's reference count, src/element_wise.rs:98-99).
+ * `out->buf` is a new reference the caller must release.  `elapsed_ns` may be NULL; when
+ * given, the call waits for the kernel and stores its device time. */
+int32_t wgf_launch_elementwise(wgf_device* dev, const wgf_tensor_desc* in, const wgf_ew_op* chain,
+                               uint32_t n_ops, int32_t inplace_ok, wgf_tensor_desc* out,
+                               uint64_t* elapsed_ns);
+/* UntypedPairWiseKernel::run_with_query, src/pair_wise.rs:85-176: out = post(op(preA(a), preB(b))). */
+int32_t wgf_launch_pairwise(wgf_device* dev, const wgf_tensor_desc* a, const wgf_tensor_desc* b,
+                            const wgf_ew_op* pre_a, uint32_t n_pre_a, const wgf_ew_op* pre_b,
+                            uint32_t n_pre_b, uint32_t opcode, const wgf_ew_op* post, uint32_t n_post,
+                            wgf_tensor_desc* out, uint64_t* elapsed_ns);
+/* UntypedReduceKernel::run_with_query, src/reduce.rs:283-386: out = post(reduce_axis(pre(in))). */
+int32_t wgf_launch_reduce(wgf_device* dev, const wgf_tensor_desc* in, uint32_t axis,
+                          const wgf_ew_op* pre, uint32_t n_pre, uint32_t reduce_opcode,
+                          const wgf_ew_op* post, uint32_t n_post, wgf_tensor_desc* out,
+                          uint64_t* elapsed_ns);
+/* UntypedMatMul::run_with_query, src/matmul.rs:157-214.  Rank 2, or rank 3 = batched.
+ * Strides and offsets are honoured; accumulation is fp32 for every dtype. */
+int32_t wgf_launch_matmul(wgf_device* dev, const wgf_tensor_desc* a, const wgf_tensor_desc* b,
+                          wgf_tensor_desc* out, uint64_t* elapsed_ns);
+/* UntypedResizeKernel::run_with_query, src/resize.rs:90-118: copy `in` into the leading
+ * `fill_shape` box of a zero-filled tensor of `new_shape`. */
+int32_t wgf_launch_resize(wgf_device* dev, const wgf_tensor_desc* in, uint32_t new_rank,
+                          const int64_t* new_shape, const int64_t* fill_shape, wgf_tensor_desc* out,
+                          uint64_t* elapsed_ns);
+/* UntypedSliceAssignKernel::run_with_query, src/slice_assign.rs:39-74: writes `value` into
+ * target[starts..ends) IN PLACE on the target's buffer. */
+int32_t wgf_launch_slice_assign(wgf_device* dev, const wgf_tensor_desc* target, const int64_t* starts,
+                                const int64_t* ends, const wgf_tensor_desc* value,
+                                uint64_t* elapsed_ns);
+
+/* ======================================================================================
+ * Graph-level API: the crate's `Tensor<R, D>` (src/tensor.rs:418-644).  A wgf_tensor is a
+ * handle on a node of the lazy compute graph (src/compute_graph/mod.rs:152-276); nothing
+ * runs until wgf_tensor_materialize / wgf_tensor_download.
+ * ==================================================================================== */
+/* Tensor::new, src/tensor.rs:518-531 (row-major host data of `dtype`). */
+int32_t wgf_tensor_from_host(wgf_device* dev, uint32_t dtype, uint32_t rank, const int64_t* shape,
+                             const void* data, wgf_tensor** out);
+/* Wraps an existing buffer + layout as a graph leaf (TensorData::new_from_parts). */
+int32_t wgf_tensor_from_desc(wgf_device* dev, const wgf_tensor_desc* desc, wgf_tensor** out);
+/* Tensor::arange / arange_step, src/composite/arange.rs:4-23 (host loop + upload). */
+int32_t wgf_tensor_arange(wgf_device* dev, uint32_t dtype, float start, float end, float step,
+                          wgf_tensor** out);
+/* Clone, src/tensor.rs:432-439: a second handle on the same node. */
+int32_t wgf_tensor_clone(wgf_tensor* t, wgf_tensor** out);
+int32_t wgf_tensor_release(wgf_tensor* t);
+/* shape() / rank() / datatype(), src/tensor.rs:629-639 */
+int32_t wgf_tensor_info(wgf_tensor* t, uint32_t* dtype, uint32_t* rank, int64_t* shape);
+
+/* 19 unary functions + Neg, src/element_wise.rs:678-1380 */
+int32_t wgf_tensor_unary(wgf_tensor* t, uint32_t opcode, wgf_tensor** out);
+/* t+c, t-c, c-t, t*c, t/c, c/t, src/element_wise.rs:197-651 */
+int32_t wgf_tensor_scalar(wgf_tensor* t, uint32_t opcode, float c, wgf_tensor** out);
+/* CastTensor::cast, src/element_wise.rs:1408-1471 */
+int32_t wgf_tensor_cast(wgf_tensor* t, uint32_t dtype, wgf_tensor** out);
+/* + - * / pow on equal shapes and dtypes, src/pair_wise.rs:205-528 */
+int32_t wgf_tensor_binary(wgf_tensor* a, wgf_tensor* b, uint32_t opcode, wgf_tensor** out);
+/* sum / max / min / product over one axis, src/reduce.rs:433-815 */
+int32_t wgf_tensor_reduce(wgf_tensor* t, uint32_t opcode, uint32_t axis, wgf_tensor** out);
+/* mat_mul, src/matmul.rs:25-29 (rank 2; rank 3 = batched, an addition) */
+int32_t wgf_tensor_matmul(wgf_tensor* a, wgf_tensor* b, wgf_tensor** out);
+/* slice / transpose / broadcast, src/map_layout.rs:41-98 */
+int32_t wgf_tensor_slice(wgf_tensor* t, const int64_t* starts, const int64_t* ends, wgf_tensor** out);
+int32_t wgf_tensor_transpose(wgf_tensor* t, uint32_t axis_a, uint32_t axis_b, wgf_tensor** out);
+/* Inserts ONE stride-0 axis; its position is the length of the common leading-dims prefix
+ * of the two shapes (src/map_layout.rs:73-77). */
+int32_t wgf_tensor_broadcast(wgf_tensor* t, uint32_t out_rank, const int64_t* out_shape,
+                             wgf_tensor** out);
+/* Same, with the position of the new axis stated (no counterpart in the crate). */
+int32_t wgf_tensor_broadcast_axis(wgf_tensor* t, uint32_t axis, int64_t size, wgf_tensor** out);
+/* Stride-0 expansion of size-1 axes to `out_shape` (no counterpart in the crate). */
+int32_t wgf_tensor_expand(wgf_tensor* t, const int64_t* out_shape, wgf_tensor** out);
+/* resize / reshape, src/resize.rs:121-144 */
+int32_t wgf_tensor_resize(wgf_tensor* t, const int64_t* new_shape, wgf_tensor** out);
+int32_t wgf_tensor_reshape(wgf_tensor* t, uint32_t new_rank, const int64_t* new_shape, wgf_tensor** out);
+/* slice_assign, src/slice_assign.rs:76-79 */
+int32_t wgf_tensor_slice_assign(wgf_tensor* target, const int64_t* starts, const int64_t* ends,
+                                wgf_tensor* value, wgf_tensor** out);
+/* Composites (graph recipes, no kernels of their own), src/composite/ */
+int32_t wgf_tensor_cat(wgf_tensor* const* parts, uint32_t n_parts, uint32_t dim, wgf_tensor** out); /* cat.rs:4-40 */
+int32_t wgf_tensor_narrow(wgf_tensor* t, uint32_t axis, int64_t start, int64_t length, wgf_tensor** out); /* narrow.rs:4-15 */
+int32_t wgf_tensor_unsqueeze(wgf_tensor* t, uint32_t axis, wgf_tensor** out);                       /* unsqueeze.rs:16-53 */
+int32_t wgf_tensor_silu(wgf_tensor* t, wgf_tensor** out);                                           /* silu.rs:4-7 */
+int32_t wgf_tensor_layer_norm(wgf_tensor* t, wgf_tensor* weight, float eps, wgf_tensor** out);      /* rms_norm.rs:8-15 */
+int32_t wgf_tensor_softmax(wgf_tensor* t, wgf_tensor** out);                                        /* softmax.rs:4-10, rank 1, no max-subtract */
+/* Max-subtracted softmax over the last axis of any rank (no counterpart in the crate). */
+int32_t wgf_tensor_softmax_last_dim(wgf_tensor* t, wgf_tensor** out);
+int32_t wgf_tensor_rope(wgf_tensor* t, wgf_tensor* cos, wgf_tensor* sin, wgf_tensor** out);         /* rope.rs:13-22 */
+
+/* LazyTensorData::materialize, src/tensor.rs:286-288: resolves the graph below `t`
+ * (src/compute_graph/resolve.rs:16-248) and queues its kernels; does not wait. */
+int32_t wgf_tensor_materialize(wgf_tensor* t);
+/* The layout and buffer of the materialised result (TensorData, src/tensor.rs:300-306).
+ * `out->buf` is a new reference. */
+int32_t wgf_tensor_desc_of(wgf_tensor* t, wgf_tensor_desc* out);
+/* Tensor::as_slice, src/tensor.rs:551-554, compacted: materialises, waits, and copies the
+ * logical elements in row-major order to `dst` (`bytes` must equal numel * sizeof(dtype)). */
+int32_t wgf_tensor_download(wgf_tensor* t, void* dst, uint64_t bytes);
+/* Tensor::all_timing_information, src/tensor.rs:556-558: device time in ns of each kernel
+ * launched while resolving `t`'s graph.  Call with out_ns == NULL to get the count. */
+int32_t wgf_tensor_timing(wgf_tensor* t, uint64_t* out_ns, uint32_t capacity, uint32_t* count);
+/* Graphviz DOT text of the graph below `t` (Tensor::graphvis, src/tensor.rs:641-643). */
+int32_t wgf_tensor_graphviz(wgf_tensor* t, char* dst, uint64_t capacity, uint64_t* needed);
+/* Number of live graph nodes reachable from the graph `t` belongs to (debug aid). */
+int32_t wgf_tensor_graph_size(wgf_tensor* t, uint64_t* nodes);
+
+/* ======================================================================================
+ * Multi-GPU (no counterpart in the crate, which drives one device): one process per GPU;
+ * rows or batches are sharded by the caller; the only exchange is the all-reduce that
+ * closes a full-tensor reduction.
+ * ==================================================================================== */
+/* Contiguous block partition of `n_units` over `world` ranks: the first n_units % world
+ * ranks get one extra unit. */
+int32_t wgf_shard_range(int64_t n_units, int32_t world, int32_t rank, int64_t* begin, int64_t* end);
+#define WGF_COMM_ID_BYTES 128
+int32_t wgf_comm_unique_id(uint8_t id[WGF_COMM_ID_BYTES]);
+int32_t wgf_comm_create(wgf_device* dev, int32_t world, int32_t rank,
+                        const uint8_t id[WGF_COMM_ID_BYTES], wgf_comm** out);
+int32_t wgf_comm_release(wgf_comm* comm);
+/* Lazy node: all-reduce (WGF_OP_SUM / MAX / MIN / PRODUCT) of `t` over the communicator,
+ * queued on the device stream directly behind the kernel that produces `t`. */
+int32_t wgf_tensor_all_reduce(wgf_tensor* t, wgf_comm* comm, uint32_t opcode, wgf_tensor** out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WGF_H */

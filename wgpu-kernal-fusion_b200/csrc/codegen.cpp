@@ -1,0 +1,663 @@
+// Turns a fused Program into CUDA source around the hand-written templates, compiles it on
+// first use (cached per device) and launches it.  Replaces the WGSL text generation of
+// src/element_wise.rs:64-130, src/pair_wise.rs:112-159, src/reduce.rs:83-281 and the launch
+// arithmetic of src/visit_tiled.rs:149-193 / src/reduce.rs:321-386.
+#include <algorithm>
+#include <sstream>
+
+#include "jit_templates.hpp"
+#include "launch.hpp"
+
+namespace wgf {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// expression text
+// ---------------------------------------------------------------------------------------
+const char* unary_fn(uint16_t op) {
+    switch (op) {
+        case WGF_OP_EXP: return "op_exp";
+        case WGF_OP_EXP2: return "op_exp2";
+        case WGF_OP_LOG: return "op_log";
+        case WGF_OP_LOG2: return "op_log2";
+        case WGF_OP_SQRT: return "op_sqrt";
+        case WGF_OP_SIN: return "op_sin";
+        case WGF_OP_COS: return "op_cos";
+        case WGF_OP_TAN: return "op_tan";
+        case WGF_OP_ASIN: return "op_asin";
+        case WGF_OP_ACOS: return "op_acos";
+        case WGF_OP_ATAN: return "op_atan";
+        case WGF_OP_SINH: return "op_sinh";
+        case WGF_OP_COSH: return "op_cosh";
+        case WGF_OP_TANH: return "op_tanh";
+        case WGF_OP_ASINH: return "op_asinh";
+        case WGF_OP_ACOSH: return "op_acosh";
+        case WGF_OP_ATANH: return "op_atanh";
+        case WGF_OP_ABS: return "fabsf";
+        default: return nullptr;
+    }
+}
+
+std::string rounded(DType dt, const std::string& e) {
+    if (dt == DType::F16) return "rh(" + e + ")";
+    if (dt == DType::BF16) return "rb(" + e + ")";
+    return e;
+}
+
+// Text of instruction `in` given the text of its operands.
+std::string instr_expr(const Instr& in, const std::string& a, const std::string& b) {
+    switch (in.kind) {
+        case IKind::Unary:
+            if (in.op == WGF_OP_SQR) return rounded(in.dtype, "(" + a + " * " + a + ")");
+            if (in.op == WGF_OP_NEG) return "(-" + a + ")";
+            if (in.op == WGF_OP_ABS) return "fabsf(" + a + ")";
+            return rounded(in.dtype, std::string(unary_fn(in.op)) + "(" + a + ")");
+        case IKind::Scalar: {
+            std::string c = "imm[" + std::to_string(in.slot) + "]";
+            switch (in.op) {
+                case WGF_OP_ADD_C: return rounded(in.dtype, "(" + a + " + " + c + ")");
+                case WGF_OP_SUB_C: return rounded(in.dtype, "(" + a + " - " + c + ")");
+                case WGF_OP_RSUB_C: return rounded(in.dtype, "(" + c + " - " + a + ")");
+                case WGF_OP_MUL_C: return rounded(in.dtype, "(" + a + " * " + c + ")");
+                case WGF_OP_DIV_C: return rounded(in.dtype, "(" + a + " / " + c + ")");
+                default: return rounded(in.dtype, "(" + c + " / " + a + ")");
+            }
+        }
+        case IKind::Cast: return rounded(in.dtype, a);
+        case IKind::Binary:
+            switch (in.op) {
+                case WGF_OP_ADD: return rounded(in.dtype, "(" + a + " + " + b + ")");
+                case WGF_OP_SUB: return rounded(in.dtype, "(" + a + " - " + b + ")");
+                case WGF_OP_MUL: return rounded(in.dtype, "(" + a + " * " + b + ")");
+                case WGF_OP_DIV: return rounded(in.dtype, "(" + a + " / " + b + ")");
+                default: return rounded(in.dtype, "op_pow(" + a + ", " + b + ")");
+            }
+        default: return "";
+    }
+}
+
+const char* red_name(uint16_t op) {
+    switch (op) {
+        case WGF_OP_SUM: return "RED_SUM";
+        case WGF_OP_MAX: return "RED_MAX";
+        case WGF_OP_MIN: return "RED_MIN";
+        default: return "RED_PROD";
+    }
+}
+
+std::string vn(int i) { return "v" + std::to_string(i); }
+
+// ---------------------------------------------------------------------------------------
+// host-side parameter block, laid out like the `Params` struct of the templates
+// ---------------------------------------------------------------------------------------
+struct ParamWriter {
+    std::vector<unsigned char> bytes;
+    template <typename T> void put(T v) {
+        size_t at = bytes.size();
+        bytes.resize(at + sizeof(T));
+        std::memcpy(bytes.data() + at, &v, sizeof(T));
+    }
+    void finish() {
+        while (bytes.size() % 8) bytes.push_back(0);
+    }
+};
+
+void magic_for(uint32_t d, uint32_t& m, uint32_t& s) {
+    if (d <= 1) {
+        m = 0;
+        s = 0;
+        return;
+    }
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) lg++;  // ceil(log2 d)
+    uint32_t p = 31 + lg;
+    m = (uint32_t)(((1ull << p) + d - 1) / d);
+    s = p - 32;
+}
+
+int pow2_at_least(int64_t v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+// Canonical index space: extent-1 axes dropped, adjacent axes merged where every tensor
+// allows it.  `strides[t]` are the strides of tensor t over `shape`.
+void collapse(std::vector<int64_t>& shape, std::vector<std::vector<int64_t>>& strides) {
+    std::vector<int64_t> ns;
+    std::vector<std::vector<int64_t>> nst(strides.size());
+    for (size_t d = 0; d < shape.size(); ++d) {
+        if (shape[d] == 1) continue;
+        if (!ns.empty()) {
+            bool merge = true;
+            for (size_t t = 0; t < strides.size(); ++t)
+                if (nst[t].back() != strides[t][d] * shape[d]) merge = false;
+            if (merge) {
+                ns.back() *= shape[d];
+                for (size_t t = 0; t < strides.size(); ++t) nst[t].back() = strides[t][d];
+                continue;
+            }
+        }
+        ns.push_back(shape[d]);
+        for (size_t t = 0; t < strides.size(); ++t) nst[t].push_back(strides[t][d]);
+    }
+    if (ns.empty()) {
+        ns.push_back(1);
+        for (auto& s : nst) s.push_back(0);
+    }
+    shape = ns;
+    strides = nst;
+}
+
+bool aligned_to(const TensorData& td, int64_t bytes) {
+    return ((uintptr_t)td.base_ptr() % (uintptr_t)bytes) == 0;
+}
+
+bool can_alias(const TensorData& td, const std::vector<int64_t>& shape, DType out_dt) {
+    if (dtype_size(td.dtype) != dtype_size(out_dt)) return false;
+    if (td.layout.shape != shape) return false;
+    if (!td.layout.is_dense() || td.layout.allocation_overlaps()) return false;
+    return td.buf.use_count() <= 1;  // 0: a non-owning alias whose owner allowed the overwrite
+}
+
+// ---------------------------------------------------------------------------------------
+// element-wise kernel
+// ---------------------------------------------------------------------------------------
+std::string ew_prog_text(const Program& prog) {
+    std::ostringstream s;
+    s << "DEV float prog(const float (&x)[NIN][C], int j, const float* imm) {\n";
+    for (int i = 0; i < (int)prog.ins.size(); ++i) {
+        const Instr& in = prog.ins[i];
+        if (in.kind == IKind::Load)
+            s << "    float " << vn(i) << " = x[" << in.slot << "][j];\n";
+        else
+            s << "    float " << vn(i) << " = "
+              << instr_expr(in, vn(in.a), in.b >= 0 ? vn(in.b) : std::string()) << ";\n";
+    }
+    s << "    return " << vn(prog.result) << ";\n}\n";
+    return s.str();
+}
+
+struct EwConfig {
+    int R, C, U, idx64, out_mode;
+    std::vector<int> mode;  // per input slot
+};
+
+std::string ew_source(const Program& prog, const EwConfig& c) {
+    std::ostringstream s;
+    s << JIT_PRELUDE;
+    s << "#define R " << c.R << "\n#define NIN " << prog.n_slots() << "\n#define C " << c.C
+      << "\n#define U " << c.U << "\n#define IDX64 " << c.idx64 << "\n#define NIMM "
+      << prog.imms.size() << "\n#define OUT_DT " << (int)prog.out_dtype() << "\n#define OUT_MODE "
+      << c.out_mode << "\n";
+    s << ew_prog_text(prog);
+    s << "#define LOAD_INPUTS(off, nvalid, X) \\\n";
+    for (int t = 0; t < prog.n_slots(); ++t)
+        s << "    load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << c.mode[t]
+          << ">((const void*)p.ptr[" << t << "], off[" << t << "], p.stride[" << t
+          << " * R + R - 1], nvalid, X[" << t << "]); \\\n";
+    s << "\n";
+    s << JIT_EW_KERNEL;
+    return s.str();
+}
+
+}  // namespace
+
+std::string debug_ew_source(const Program& prog, int rank, int chunk) {
+    EwConfig c{rank, chunk, 2, 0, chunk > 1 ? 0 : 1, std::vector<int>(prog.n_slots(), chunk > 1 ? 0 : 1)};
+    return ew_source(prog, c);
+}
+
+TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<TensorData>& in,
+                           const std::vector<int64_t>& shape, int inplace_slot) {
+    const int nin = prog.n_slots();
+    WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
+    WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
+    const DType out_dt = prog.out_dtype();
+    int64_t n = 1;
+    for (auto v : shape) n *= v;
+
+    // output: reuse an input's buffer when allowed, else a fresh contiguous buffer
+    TensorData out;
+    if (inplace_slot >= 0 && can_alias(in[inplace_slot], shape, out_dt)) {
+        out = in[inplace_slot];
+        out.dtype = out_dt;
+    } else {
+        out.buf = dev.alloc((size_t)std::max<int64_t>(n, 1) * dtype_size(out_dt), false);
+        out.layout = Layout::contiguous(shape);
+        out.dtype = out_dt;
+    }
+    if (n == 0) return out;
+
+    std::vector<int64_t> cshape = shape;
+    std::vector<std::vector<int64_t>> st(nin + 1);
+    for (int t = 0; t < nin; ++t) {
+        WGF_CHECK(in[t].layout.shape == shape, WGF_ERR_SHAPE, "fused input shape differs from the index space");
+        st[t] = in[t].layout.strides;
+    }
+    st[nin] = Layout::contiguous_strides(shape);  // dense output (also when aliased)
+    collapse(cshape, st);
+    const int R = (int)cshape.size();
+    WGF_CHECK(R <= WGF_MAX_RANK, WGF_ERR_RANK, "rank above 8");
+
+    bool any16 = dtype_size(out_dt) == 2;
+    for (int t = 0; t < nin; ++t) any16 |= dtype_size(in[t].dtype) == 2;
+    EwConfig cfg;
+    cfg.R = R;
+    cfg.C = any16 ? 8 : 4;
+    if (R > 1 && cshape[R - 1] % cfg.C != 0) cfg.C = (any16 && cshape[R - 1] % 4 == 0) ? 4 : 1;
+    cfg.idx64 = n >= (1ll << 31);
+    auto classify = [&](const TensorData& td, const std::vector<int64_t>& s) {
+        int64_t inner = s[R - 1];
+        if (inner == 0) return 2;
+        if (inner != 1) return 3;
+        if (cfg.C == 1) return 1;
+        int64_t need = std::min<int64_t>(16, cfg.C * (int64_t)dtype_size(td.dtype));
+        if (!aligned_to(td, need)) return 1;
+        for (int d = 0; d < R - 1; ++d)
+            if ((s[d] * (int64_t)dtype_size(td.dtype)) % need) return 1;
+        return 0;
+    };
+    cfg.mode.resize(nin);
+    for (int t = 0; t < nin; ++t) cfg.mode[t] = classify(in[t], st[t]);
+    cfg.out_mode = classify(out, st[nin]);
+    const int64_t nchunks = (n + cfg.C - 1) / cfg.C;
+    int umax = std::max(1, std::min(4, 64 / (nin * cfg.C)));
+    int64_t want = nchunks / (256ll * 4 * dev.sm_count);
+    cfg.U = (int)std::max<int64_t>(1, std::min<int64_t>(umax, want));
+
+    std::ostringstream key;
+    key << "ew|" << R << "|" << cfg.C << "|" << cfg.U << "|" << cfg.idx64 << "|" << cfg.out_mode << "|";
+    for (int m : cfg.mode) key << m;
+    key << "|" << prog.signature();
+    const JitKernel& k = dev.kernel(key.str(), [&] { return ew_source(prog, cfg); });
+
+    ParamWriter w;
+    w.put<uint64_t>((uint64_t)n);
+    for (int t = 0; t < nin; ++t) w.put<uint64_t>((uint64_t)(uintptr_t)in[t].base_ptr());
+    w.put<uint64_t>((uint64_t)(uintptr_t)out.base_ptr());
+    for (int t = 0; t < nin; ++t)
+        for (int d = 0; d < R; ++d) w.put<int64_t>(st[t][d]);
+    for (int d = 0; d < R; ++d) w.put<uint32_t>((uint32_t)cshape[d]);
+    std::vector<uint32_t> mm(R), ms(R);
+    for (int d = 0; d < R; ++d) magic_for((uint32_t)std::min<int64_t>(cshape[d], 0x7fffffff), mm[d], ms[d]);
+    for (int d = 0; d < R; ++d) w.put<uint32_t>(mm[d]);
+    for (int d = 0; d < R; ++d) w.put<uint32_t>(ms[d]);
+    for (float f : prog.imms) w.put<float>(f);
+    if (prog.imms.empty()) w.put<float>(0.f);
+    w.finish();
+
+    int64_t blocks = (nchunks + 256ll * cfg.U - 1) / (256ll * cfg.U);
+    WGF_CHECK(blocks < (1ll << 31), WGF_ERR_UNSUPPORTED, "tensor too large for one launch");
+    dev.launch(k, dim3((unsigned)blocks), dim3(256), 0, w.bytes.data(), "elementwise");
+    return out;
+}
+
+// ---------------------------------------------------------------------------------------
+// row kernels
+// ---------------------------------------------------------------------------------------
+namespace {
+
+struct RowConfig {
+    int RO, C, NCH, GROUP, RPC, out_mode;
+    bool out_has_h;
+    std::vector<int> mode;       // per slot: 0 vec, 1 scalar, 3 strided; 2 = row value (cstride 0)
+};
+
+std::string row_source(const Program& prog, const RowConfig& c) {
+    std::ostringstream s;
+    s << JIT_PRELUDE;
+    s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define C " << c.C
+      << "\n#define NCH " << c.NCH << "\n#define GROUP " << c.GROUP << "\n#define RPC " << c.RPC
+      << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM " << prog.imms.size() << "\n";
+    std::ostringstream b;
+    int red_idx = 0;
+    auto operand = [&](int i, const char* idx) {
+        return prog.ins[i].vk == VKind::Row ? vn(i) : vn(i) + "[" + idx + "]";
+    };
+    for (int i = 0; i < (int)prog.ins.size(); ++i) {
+        const Instr& in = prog.ins[i];
+        if (in.kind == IKind::Load) {
+            int t = in.slot;
+            if (in.vk == VKind::Row) {
+                b << "float " << vn(i) << " = rv ? load1<" << (int)prog.slot_dtype[t]
+                  << ">((const void*)p.ptr[" << t << "], roff[" << t << "]) : 0.f;\n";
+            } else {
+                b << "float " << vn(i) << "[EPT];\n\n#pragma unroll\n for (int k = 0; k < NCH; ++k) {\n"
+                  << "  if (kv[k]) load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << c.mode[t]
+                  << ">((const void*)p.ptr[" << t << "], roff[" << t << "] + (i64)((k * GROUP + t) * C) * "
+                  << (c.mode[t] == 3 ? "p.cstride[" + std::to_string(t) + "]" : std::string("1"))
+                  << ", p.cstride[" << t << "], C, &" << vn(i) << "[k * C]);\n"
+                  << "  else { \n#pragma unroll\n for (int j = 0; j < C; ++j) " << vn(i) << "[k * C + j] = 0.f; }\n}\n";
+            }
+        } else if (in.kind == IKind::RowReduce) {
+            const char* op = red_name(in.op);
+            b << "float " << vn(i) << ";\n{ float a_ = red_ident<" << op << ">();\n"
+              << "\n#pragma unroll\n for (int k = 0; k < NCH; ++k) if (kv[k]) {\n"
+              << "  \n#pragma unroll\n for (int j = 0; j < C; ++j) a_ = red_comb<" << op << ">(a_, "
+              << operand(in.a, "k * C + j") << "); }\n";
+            if (c.GROUP > 32)
+                b << vn(i) << " = group_reduce<" << op << ", GROUP>(a_, red_smem[" << red_idx << "][g], t); }\n";
+            else
+                b << vn(i) << " = group_reduce<" << op << ", GROUP>(a_, (float*)0, t); }\n";
+            if (in.dtype != DType::F32) b << vn(i) << " = " << rounded(in.dtype, vn(i)) << ";\n";
+            red_idx++;
+        } else if (in.vk == VKind::Row) {
+            b << "float " << vn(i) << " = " << instr_expr(in, vn(in.a), in.b >= 0 ? vn(in.b) : std::string())
+              << ";\n";
+        } else {
+            b << "float " << vn(i) << "[EPT];\n\n#pragma unroll\n for (int e = 0; e < EPT; ++e) " << vn(i)
+              << "[e] = " << instr_expr(in, operand(in.a, "e"), in.b >= 0 ? operand(in.b, "e") : std::string())
+              << ";\n";
+        }
+    }
+    const int res = prog.result;
+    const int odt = (int)prog.out_dtype();
+    if (c.out_has_h) {
+        b << "\n#pragma unroll\n for (int k = 0; k < NCH; ++k) if (kv[k]) {\n";
+        if (prog.ins[res].vk == VKind::Row) {
+            b << "  float y_[C]; \n#pragma unroll\n for (int j = 0; j < C; ++j) y_[j] = " << vn(res) << ";\n"
+              << "  store_chunk<" << odt << ", C, " << c.out_mode << ">((void*)p.ptr[NIN], roff[NIN] + (i64)((k * GROUP + t) * C), C, y_);\n";
+        } else {
+            b << "  store_chunk<" << odt << ", C, " << c.out_mode
+              << ">((void*)p.ptr[NIN], roff[NIN] + (i64)((k * GROUP + t) * C), C, &" << vn(res) << "[k * C]);\n";
+        }
+        b << "}\n";
+    } else {
+        b << "if (rv && t == 0) store1<" << odt << ">((void*)p.ptr[NIN], roff[NIN], " << vn(res) << ");\n";
+    }
+    // splice the generated body into the template
+    std::string tmpl = JIT_ROW_KERNEL;
+    const std::string marker = "ROW_BODY";
+    size_t at = tmpl.rfind(marker);
+    tmpl.replace(at, marker.size(), b.str());
+    s << tmpl;
+    return s.str();
+}
+
+struct StreamConfig {
+    int RO, C, U;
+    std::vector<int> mode;
+};
+
+std::string stream_source(const Program& prog, const StreamConfig& c) {
+    const int n = (int)prog.ins.size();
+    std::vector<char> dep(n, 0);
+    for (int i = 0; i < n; ++i) {
+        const Instr& in = prog.ins[i];
+        char d = in.kind == IKind::RowReduce;
+        if (in.a >= 0) d |= dep[in.a];
+        if (in.b >= 0) d |= dep[in.b];
+        dep[i] = d;
+    }
+    // slots read per element, in slot order
+    std::vector<int> eslot(prog.n_slots(), -1);
+    int nine = 0;
+    for (auto& in : prog.ins)
+        if (in.kind == IKind::Load && in.vk == VKind::Elem) eslot[in.slot] = 0;
+    for (int t = 0; t < prog.n_slots(); ++t)
+        if (eslot[t] == 0) eslot[t] = nine++;
+    std::vector<int> rowv_index(n, -1);
+    int nrowv = 0;
+    std::ostringstream pre, elem, post, init, comb, blk, load;
+    int red_idx = 0;
+    std::vector<int> red_of(n, -1);
+    for (int i = 0; i < n; ++i) {
+        const Instr& in = prog.ins[i];
+        std::string a = in.a >= 0 ? vn(in.a) : "", bb = in.b >= 0 ? vn(in.b) : "";
+        if (in.kind == IKind::RowReduce) {
+            const char* op = red_name(in.op);
+            red_of[i] = red_idx;
+            // accumulate inside the element loop
+            std::string src = prog.ins[in.a].vk == VKind::Row && !dep[in.a]
+                                  ? "rowv[" + std::to_string(rowv_index[in.a]) + "]" : vn(in.a);
+            elem << "        acc[" << red_idx << "] = red_comb<" << op << ">(acc[" << red_idx << "], " << src << ");\n";
+            init << "acc[" << red_idx << "] = red_ident<" << op << ">(); ";
+            comb << "acc[" << red_idx << "] = red_comb<" << op << ">(acc[" << red_idx << "], __ldcg((PP) + "
+                 << red_idx << ")); ";
+            blk << "acc[" << red_idx << "] = group_reduce<" << op << ", THREADS>(acc[" << red_idx << "], red_smem["
+                << red_idx << "], t); ";
+            post << "float " << vn(i) << " = " << rounded(in.dtype, "acc[" + std::to_string(red_idx) + "]") << "; ";
+            red_idx++;
+        } else if (in.vk == VKind::Row && !dep[i]) {
+            if (in.kind == IKind::Load)
+                pre << "float " << vn(i) << " = load1<" << (int)prog.slot_dtype[in.slot] << ">((const void*)p.ptr["
+                    << in.slot << "], roff[" << in.slot << "]); ";
+            else
+                pre << "float " << vn(i) << " = " << instr_expr(in, a, bb) << "; ";
+            rowv_index[i] = nrowv++;
+        } else if (in.vk == VKind::Row) {
+            post << "float " << vn(i) << " = " << instr_expr(in, a, bb) << "; ";
+        } else {
+            auto opnd = [&](int j) {
+                if (prog.ins[j].vk == VKind::Row) return "rowv[" + std::to_string(rowv_index[j]) + "]";
+                return vn(j);
+            };
+            if (in.kind == IKind::Load)
+                elem << "        float " << vn(i) << " = x[" << eslot[in.slot] << "][j];\n";
+            else
+                elem << "        float " << vn(i) << " = "
+                     << instr_expr(in, opnd(in.a), in.b >= 0 ? opnd(in.b) : std::string()) << ";\n";
+        }
+    }
+    for (int t = 0; t < prog.n_slots(); ++t)
+        if (eslot[t] >= 0)
+            load << "load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << c.mode[t] << ">((const void*)p.ptr[" << t
+                 << "], roff[" << t << "] + (i64)(COL) * " << (c.mode[t] == 3 ? "p.cstride[" + std::to_string(t) + "]" : std::string("1"))
+                 << ", p.cstride[" << t << "], NV, X[" << eslot[t] << "]); ";
+
+    std::ostringstream s;
+    s << JIT_PRELUDE;
+    s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define NINE " << nine
+      << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces()
+      << "\n#define NIMM " << prog.imms.size() << "\n";
+    s << "DEV void elem_phase(const float (&x)[NINE > 0 ? NINE : 1][C], const float* rowv, const float* imm, int nvalid, float* acc) {\n"
+      << "#pragma unroll\n    for (int j = 0; j < C; ++j) {\n      if (j < nvalid) {\n"
+      << elem.str() << "      }\n    }\n}\n";
+    s << "#define STREAM_PRE " << pre.str() << " float rowv[" << std::max(nrowv, 1) << "]; ";
+    if (nrowv == 0) s << "rowv[0] = 0.f; ";
+    for (int i = 0; i < n; ++i)
+        if (rowv_index[i] >= 0) s << "rowv[" << rowv_index[i] << "] = " << vn(i) << "; ";
+    s << "\n#define STREAM_INIT " << init.str() << "\n";
+    s << "#define STREAM_COMBINE_PARTIAL(PP) " << comb.str() << "\n";
+    s << "#define STREAM_BLOCK_REDUCE " << blk.str() << "\n";
+    s << "#define STREAM_LOAD(COL, NV, X) " << load.str() << "\n";
+    s << "#define STREAM_POST " << post.str() << " if (t == 0) store1<" << (int)prog.out_dtype()
+      << ">((void*)p.ptr[NIN], roff[NIN], " << vn(prog.result) << ");\n";
+    s << JIT_STREAM_KERNEL;
+    return s.str();
+}
+
+}  // namespace
+
+int64_t max_resident_row(bool) { return 32768; }
+
+TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
+                    const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot) {
+    const int nin = prog.n_slots();
+    WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
+    WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
+    WGF_CHECK(!shape.empty(), WGF_ERR_RANK, "row kernel needs rank >= 1");
+    WGF_CHECK(out_has_h || prog.out_kind() == VKind::Row, WGF_ERR_INVALID_ARGUMENT,
+              "a per-element result needs an output with the row axis");
+    const DType out_dt = prog.out_dtype();
+    const int rank = (int)shape.size();
+    const int64_t H = shape[rank - 1];
+    std::vector<int64_t> oshape(shape.begin(), shape.end() - 1);
+    int64_t rows = 1;
+    for (auto v : oshape) rows *= v;
+    const std::vector<int64_t>& out_shape = out_has_h ? shape : oshape;
+    int64_t n_out = out_has_h ? rows * H : rows;
+
+    TensorData out;
+    if (out_has_h && inplace_slot >= 0 && can_alias(in[inplace_slot], shape, out_dt)) {
+        out = in[inplace_slot];
+        out.dtype = out_dt;
+    } else {
+        out.buf = dev.alloc((size_t)std::max<int64_t>(n_out, 1) * dtype_size(out_dt), false);
+        out.layout = Layout::contiguous(out_shape);
+        out.dtype = out_dt;
+    }
+    if (n_out == 0) return out;
+    WGF_CHECK(rows < (1ll << 31), WGF_ERR_UNSUPPORTED, "too many rows for one launch");
+
+    // outer strides per tensor (+ output), collapsed; column strides kept apart
+    std::vector<std::vector<int64_t>> st(nin + 1);
+    std::vector<int64_t> cs(nin + 1);
+    for (int t = 0; t < nin; ++t) {
+        WGF_CHECK(in[t].layout.shape == shape, WGF_ERR_SHAPE, "fused input shape differs from the index space");
+        st[t].assign(in[t].layout.strides.begin(), in[t].layout.strides.end() - 1);
+        cs[t] = H == 1 ? 0 : in[t].layout.strides[rank - 1];
+    }
+    {
+        std::vector<int64_t> os = Layout::contiguous_strides(out_shape);
+        st[nin].assign(os.begin(), os.begin() + (rank - 1));
+        cs[nin] = out_has_h ? 1 : 0;
+    }
+    std::vector<int64_t> coshape = oshape;
+    collapse(coshape, st);
+    const int RO = (int)coshape.size();
+
+    // which slots are per-row values
+    std::vector<char> slot_row(nin, 0);
+    for (auto& i : prog.ins)
+        if (i.kind == IKind::Load) slot_row[i.slot] = i.vk == VKind::Row;
+    for (int t = 0; t < nin; ++t)
+        WGF_CHECK(!slot_row[t] || cs[t] == 0 || H == 1, WGF_ERR_INVALID_ARGUMENT, "row-kind slot varies along the row");
+
+    bool any16 = dtype_size(out_dt) == 2;
+    for (int t = 0; t < nin; ++t) any16 |= dtype_size(in[t].dtype) == 2;
+    auto vec_ok = [&](const void* base, DType dt, const std::vector<int64_t>& s, int C) {
+        int64_t need = std::min<int64_t>(16, C * (int64_t)dtype_size(dt));
+        if ((uintptr_t)base % (uintptr_t)need) return false;
+        for (int d = 0; d < RO; ++d)
+            if (coshape[d] > 1 && (s[d] * (int64_t)dtype_size(dt)) % need) return false;
+        return true;
+    };
+    auto pick_modes = [&](int C, std::vector<int>& mode, int& out_mode, bool need_divisible) {
+        bool all_vec = C > 1 && (!need_divisible || H % C == 0);
+        mode.assign(nin, 1);
+        for (int t = 0; t < nin; ++t) {
+            if (slot_row[t] || cs[t] == 0) mode[t] = 2;
+            else if (cs[t] != 1) mode[t] = 3;
+            else if (all_vec && vec_ok(in[t].base_ptr(), in[t].dtype, st[t], C)) mode[t] = 0;
+            else { mode[t] = 1; all_vec = false; }
+        }
+        out_mode = 1;
+        if (out_has_h) {
+            if (all_vec && vec_ok(out.base_ptr(), out_dt, st[nin], C)) out_mode = 0;
+            else all_vec = false;
+        }
+        return all_vec;
+    };
+
+    const bool single_phase = !prog.multi_phase() && !out_has_h;
+    bool use_stream = false;
+    if (single_phase) {
+        // enough rows to fill the machine and a row short enough for registers -> resident
+        bool resident_ok = H >= 1 && H <= 8192 && rows >= 4ll * dev.sm_count;
+        use_stream = !resident_ok;
+    } else {
+        WGF_CHECK(H <= max_resident_row(any16), WGF_ERR_UNSUPPORTED, "row too long for a row-fused kernel");
+    }
+
+    auto put_common = [&](ParamWriter& w) {
+        w.put<uint64_t>((uint64_t)rows);
+        for (int t = 0; t < nin; ++t) w.put<uint64_t>((uint64_t)(uintptr_t)in[t].base_ptr());
+        w.put<uint64_t>((uint64_t)(uintptr_t)out.base_ptr());
+        for (int t = 0; t <= nin; ++t)
+            for (int d = 0; d < RO; ++d) w.put<int64_t>(st[t][d]);
+        for (int t = 0; t <= nin; ++t) w.put<int64_t>(cs[t]);
+    };
+    auto put_tail = [&](ParamWriter& w) {
+        for (int d = 0; d < RO; ++d) w.put<uint32_t>((uint32_t)coshape[d]);
+        for (int d = 0; d < RO; ++d) {
+            uint32_t m, s;
+            magic_for((uint32_t)coshape[d], m, s);
+            w.put<uint32_t>(m);
+        }
+        for (int d = 0; d < RO; ++d) {
+            uint32_t m, s;
+            magic_for((uint32_t)coshape[d], m, s);
+            w.put<uint32_t>(s);
+        }
+        for (float f : prog.imms) w.put<float>(f);
+        if (prog.imms.empty()) w.put<float>(0.f);
+        w.finish();
+    };
+
+    if (!use_stream) {
+        RowConfig cfg;
+        cfg.RO = RO;
+        cfg.out_has_h = out_has_h;
+        cfg.C = any16 ? 8 : 4;
+        if (!pick_modes(cfg.C, cfg.mode, cfg.out_mode, true)) {
+            // some tensor cannot be vectorised: fall back to one element per access so that
+            // consecutive threads still touch consecutive addresses
+            cfg.C = 1;
+            pick_modes(1, cfg.mode, cfg.out_mode, true);
+        }
+        const int64_t chunks = (H + cfg.C - 1) / cfg.C;
+        const int target = cfg.C == 1 ? 16 : (cfg.C == 4 ? 4 : 2);
+        cfg.GROUP = std::min(1024, std::max(32, pow2_at_least((chunks + target - 1) / target)));
+        cfg.NCH = (int)((chunks + cfg.GROUP - 1) / cfg.GROUP);
+        WGF_CHECK(cfg.NCH * cfg.C <= 64, WGF_ERR_UNSUPPORTED, "row too long for a row-fused kernel");
+        int threads = std::max(cfg.GROUP, 128);
+        cfg.RPC = threads / cfg.GROUP;
+        std::ostringstream key;
+        key << "row|" << RO << "|" << cfg.C << "|" << cfg.NCH << "|" << cfg.GROUP << "|" << cfg.RPC << "|"
+            << cfg.out_mode << "|" << out_has_h << "|";
+        for (int m : cfg.mode) key << m;
+        key << "|" << prog.signature();
+        const JitKernel& k = dev.kernel(key.str(), [&] { return row_source(prog, cfg); });
+        ParamWriter w;
+        put_common(w);
+        w.put<uint32_t>((uint32_t)H);
+        w.put<uint32_t>(0);
+        put_tail(w);
+        int64_t blocks = (rows + cfg.RPC - 1) / cfg.RPC;
+        dev.launch(k, dim3((unsigned)blocks), dim3(cfg.GROUP * cfg.RPC), 0, w.bytes.data(), "rows");
+        return out;
+    }
+
+    // streaming reduce
+    StreamConfig cfg;
+    cfg.RO = RO;
+    cfg.C = any16 ? 8 : 4;
+    int dummy;
+    if (!pick_modes(cfg.C, cfg.mode, dummy, false)) {
+        cfg.C = 1;
+        pick_modes(1, cfg.mode, dummy, false);
+    }
+    int nine = 0;
+    for (int t = 0; t < nin; ++t) nine += !(slot_row[t] || cs[t] == 0);
+    // a slot with column stride 0 that the program loads per element is read as broadcast
+    cfg.U = std::max(1, std::min(4, 64 / (std::max(nine, 1) * cfg.C)));
+    const int64_t nch = (H + cfg.C - 1) / cfg.C;
+    const int64_t per_cta = 256ll * cfg.U;
+    int64_t max_split = std::max<int64_t>(1, (nch + per_cta - 1) / per_cta);
+    int64_t split = std::max<int64_t>(1, (8ll * dev.sm_count + rows - 1) / rows);
+    split = std::min<int64_t>({split, max_split, 2048});
+    if (rows > 65536) split = 1;
+    std::ostringstream key;
+    key << "stream|" << RO << "|" << cfg.C << "|" << cfg.U << "|";
+    for (int m : cfg.mode) key << m;
+    key << "|" << prog.signature();
+    const JitKernel& k = dev.kernel(key.str(), [&] { return stream_source(prog, cfg); });
+    BufferRef partials;
+    if (split > 1)
+        partials = dev.alloc((size_t)(rows * split * std::max(prog.n_reduces(), 1)) * sizeof(float), false);
+    ParamWriter w;
+    put_common(w);
+    w.put<uint64_t>(partials ? (uint64_t)(uintptr_t)partials->ptr : 0);
+    w.put<uint64_t>((uint64_t)(uintptr_t)dev.counters());
+    w.put<uint64_t>((uint64_t)H);
+    w.put<uint32_t>((uint32_t)split);
+    w.put<uint32_t>(0);
+    put_tail(w);
+    dev.launch(k, dim3((unsigned)(rows * split)), dim3(256), 0, w.bytes.data(), "stream_reduce");
+    return out;
+}
+
+}  // namespace wgf

@@ -1,0 +1,138 @@
+// Fused-kernel IR.  A Program is a straight-line SSA list over two kinds of values:
+//   Elem - one value per element of the kernel's index space [outer..., H]
+//   Row  - one value per row (uniform along the last axis H): results of reductions over H,
+//          operands broadcast along H, and arithmetic between such values.
+// The resolver lowers a region of the lazy graph (chains of the crate's ElementWise /
+// PairWise / Reduce nodes, src/compute_graph/resolve.rs:49-196) to one Program; codegen.cpp
+// turns a Program into CUDA source built around hand-written kernel templates.
+#pragma once
+#include <sstream>
+
+#include "common.hpp"
+
+namespace wgf {
+
+enum class VKind : uint8_t { Elem = 0, Row = 1 };
+enum class IKind : uint8_t { Load = 0, Unary, Scalar, Cast, Binary, RowReduce };
+
+struct Instr {
+    IKind kind;
+    uint16_t op = 0;   // WGF_OP_*
+    int a = -1, b = -1;
+    int slot = -1;     // Load: input slot; Scalar: index into imms
+    DType dtype = DType::F32;
+    VKind vk = VKind::Elem;
+};
+
+struct Program {
+    std::vector<Instr> ins;
+    std::vector<DType> slot_dtype;  // element type of each input slot
+    std::vector<float> imms;
+    int result = -1;
+
+    int n_slots() const { return (int)slot_dtype.size(); }
+    DType out_dtype() const { return ins[result].dtype; }
+    VKind out_kind() const { return ins[result].vk; }
+    int n_reduces() const {
+        int n = 0;
+        for (auto& i : ins) n += i.kind == IKind::RowReduce;
+        return n;
+    }
+
+    int load(int slot, DType dt, VKind vk) {
+        for (int i = 0; i < (int)ins.size(); ++i)
+            if (ins[i].kind == IKind::Load && ins[i].slot == slot) return i;
+        Instr in{IKind::Load};
+        in.slot = slot;
+        in.dtype = dt;
+        in.vk = vk;
+        ins.push_back(in);
+        return (int)ins.size() - 1;
+    }
+    int new_slot(DType dt) {
+        slot_dtype.push_back(dt);
+        return (int)slot_dtype.size() - 1;
+    }
+    int unary(uint16_t op, int a) {
+        Instr in{IKind::Unary};
+        in.op = op;
+        in.a = a;
+        in.dtype = ins[a].dtype;
+        in.vk = ins[a].vk;
+        ins.push_back(in);
+        return (int)ins.size() - 1;
+    }
+    int scalar(uint16_t op, int a, float c) {
+        Instr in{IKind::Scalar};
+        in.op = op;
+        in.a = a;
+        in.slot = (int)imms.size();
+        imms.push_back(c);
+        in.dtype = ins[a].dtype;
+        in.vk = ins[a].vk;
+        ins.push_back(in);
+        return (int)ins.size() - 1;
+    }
+    int cast(int a, DType to) {
+        Instr in{IKind::Cast};
+        in.op = WGF_OP_CAST;
+        in.a = a;
+        in.dtype = to;
+        in.vk = ins[a].vk;
+        ins.push_back(in);
+        return (int)ins.size() - 1;
+    }
+    int binary(uint16_t op, int a, int b) {
+        Instr in{IKind::Binary};
+        in.op = op;
+        in.a = a;
+        in.b = b;
+        in.dtype = ins[a].dtype;
+        in.vk = (ins[a].vk == VKind::Row && ins[b].vk == VKind::Row) ? VKind::Row : VKind::Elem;
+        ins.push_back(in);
+        return (int)ins.size() - 1;
+    }
+    int row_reduce(uint16_t op, int a) {
+        Instr in{IKind::RowReduce};
+        in.op = op;
+        in.a = a;
+        in.dtype = ins[a].dtype;
+        in.vk = VKind::Row;
+        ins.push_back(in);
+        return (int)ins.size() - 1;
+    }
+
+    // True if some Elem value depends on the result of a RowReduce, i.e. the row has to be
+    // kept (in registers) across a reduction.
+    bool multi_phase() const {
+        std::vector<char> dep(ins.size(), 0);
+        for (size_t i = 0; i < ins.size(); ++i) {
+            const Instr& in = ins[i];
+            char d = 0;
+            if (in.a >= 0) d |= dep[in.a];
+            if (in.b >= 0) d |= dep[in.b];
+            if (in.kind == IKind::RowReduce) {
+                if (d) return true;  // a reduction of something that depends on a reduction
+                d = 1;
+            } else if (d && in.vk == VKind::Elem) {
+                return true;
+            }
+            dep[i] = d;
+        }
+        return false;
+    }
+
+    // Text form; immediates are kernel parameters, so their values are not part of it.
+    std::string signature() const {
+        std::ostringstream s;
+        for (auto d : slot_dtype) s << "s" << (int)d;
+        s << "|";
+        for (auto& in : ins)
+            s << (int)in.kind << "." << in.op << "." << in.a << "." << in.b << "." << in.slot << "."
+              << (int)in.dtype << "." << (int)in.vk << ";";
+        s << "->" << result;
+        return s.str();
+    }
+};
+
+}  // namespace wgf

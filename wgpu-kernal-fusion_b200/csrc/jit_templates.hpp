@@ -1,0 +1,411 @@
+// Hand-written CUDA kernel templates for the fused element-wise / pair-wise / reduce family.
+// codegen.cpp prepends `#define`s and the generated per-program functions, then hands the
+// text to NVRTC (the analogue of the crate's WGSL assembly in src/kernel.rs:391-495 and
+// src/visit_tiled.rs:63-147, but the kernels themselves are written for sm_100a: 128-bit
+// coalesced accesses along the innermost stride-1 axis, rows kept in registers across
+// reductions, warp-shuffle + shared-memory block reductions).
+#pragma once
+
+namespace wgf {
+
+// Common device helpers.  No CUDA headers are included: conversions use PTX directly.
+static const char* const JIT_PRELUDE = R"CUDA(
+typedef unsigned short u16;
+typedef unsigned int u32;
+typedef long long i64;
+typedef unsigned long long u64;
+#define DEV __device__ __forceinline__
+
+DEV float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
+DEV u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+DEV float b2f(u16 b) { return __uint_as_float(((u32)b) << 16); }
+DEV u16 f2b(float f) { u16 b; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(b) : "f"(f)); return b; }
+// round a float to the nearest f16 / bf16 value (every op of a 16-bit tensor rounds once)
+DEV float rh(float x) { return h2f(f2h(x)); }
+DEV float rb(float x) { return b2f(f2b(x)); }
+
+// Unary functions.  Single-precision CUDA functions documented at <= 2 ulp are used as they
+// are; the ones documented above that (tan, sinh, asinh, acosh, atanh, pow) go through double.
+DEV float op_exp(float x) { return expf(x); }
+DEV float op_exp2(float x) { return exp2f(x); }
+DEV float op_log(float x) { return logf(x); }
+DEV float op_log2(float x) { return log2f(x); }
+DEV float op_sqrt(float x) { return sqrtf(x); }
+DEV float op_sin(float x) { return sinf(x); }
+DEV float op_cos(float x) { return cosf(x); }
+DEV float op_tan(float x) { return (float)tan((double)x); }
+DEV float op_asin(float x) { return asinf(x); }
+DEV float op_acos(float x) { return acosf(x); }
+DEV float op_atan(float x) { return atanf(x); }
+DEV float op_sinh(float x) { return (float)sinh((double)x); }
+DEV float op_cosh(float x) { return coshf(x); }
+DEV float op_tanh(float x) { return tanhf(x); }
+DEV float op_asinh(float x) { return (float)asinh((double)x); }
+DEV float op_acosh(float x) { return (float)acosh((double)x); }
+DEV float op_atanh(float x) { return (float)atanh((double)x); }
+DEV float op_pow(float a, float b) { return (float)pow((double)a, (double)b); }
+
+// n / d for n < 2^31 with a precomputed multiplier (m == 0 encodes d == 1)
+DEV u32 fastdiv(u32 n, u32 m, u32 s) { return m ? (__umulhi(n, m) >> s) : n; }
+
+template <int DT> DEV float load1(const void* base, i64 i) {
+    if (DT == 0) return ((const float*)base)[i];
+    u16 v = ((const u16*)base)[i];
+    return DT == 1 ? h2f(v) : b2f(v);
+}
+template <int DT> DEV void store1(void* base, i64 i, float v) {
+    if (DT == 0) ((float*)base)[i] = v;
+    else ((u16*)base)[i] = DT == 1 ? f2h(v) : f2b(v);
+}
+template <int DT> DEV float cvt16(u16 v) { return DT == 1 ? h2f(v) : b2f(v); }
+template <int DT> DEV u32 pack16(float lo, float hi) {
+    u32 a = DT == 1 ? f2h(lo) : f2b(lo), b = DT == 1 ? f2h(hi) : f2b(hi);
+    return a | (b << 16);
+}
+
+// C consecutive elements starting at element index i; (base + i) is aligned to the vector.
+template <int DT, int C> DEV void load_vec(const void* base, i64 i, float* out) {
+    if (DT == 0) {
+        if (C % 4 == 0) {
+            const float4* p = (const float4*)((const float*)base + i);
+#pragma unroll
+            for (int q = 0; q < C / 4; ++q) {
+                float4 t = p[q];
+                out[4 * q] = t.x; out[4 * q + 1] = t.y; out[4 * q + 2] = t.z; out[4 * q + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < C; ++j) out[j] = ((const float*)base)[i + j];
+        }
+    } else {
+        if (C == 8) {
+            uint4 t = *(const uint4*)((const u16*)base + i);
+            u32 w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                out[2 * q] = cvt16<DT>((u16)(w[q] & 0xffff));
+                out[2 * q + 1] = cvt16<DT>((u16)(w[q] >> 16));
+            }
+        } else if (C == 4) {
+            uint2 t = *(const uint2*)((const u16*)base + i);
+            out[0] = cvt16<DT>((u16)(t.x & 0xffff)); out[1] = cvt16<DT>((u16)(t.x >> 16));
+            out[2] = cvt16<DT>((u16)(t.y & 0xffff)); out[3] = cvt16<DT>((u16)(t.y >> 16));
+        } else {
+#pragma unroll
+            for (int j = 0; j < C; ++j) out[j] = cvt16<DT>(((const u16*)base)[i + j]);
+        }
+    }
+}
+template <int DT, int C> DEV void store_vec(void* base, i64 i, const float* v) {
+    if (DT == 0) {
+        if (C % 4 == 0) {
+            float4* p = (float4*)((float*)base + i);
+#pragma unroll
+            for (int q = 0; q < C / 4; ++q) p[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < C; ++j) ((float*)base)[i + j] = v[j];
+        }
+    } else {
+        if (C == 8) {
+            uint4 t;
+            t.x = pack16<DT>(v[0], v[1]); t.y = pack16<DT>(v[2], v[3]);
+            t.z = pack16<DT>(v[4], v[5]); t.w = pack16<DT>(v[6], v[7]);
+            *(uint4*)((u16*)base + i) = t;
+        } else if (C == 4) {
+            uint2 t;
+            t.x = pack16<DT>(v[0], v[1]); t.y = pack16<DT>(v[2], v[3]);
+            *(uint2*)((u16*)base + i) = t;
+        } else {
+#pragma unroll
+            for (int j = 0; j < C; ++j) store1<DT>(base, i + j, v[j]);
+        }
+    }
+}
+
+// MODE 0: aligned vector, 1: contiguous scalars, 2: one element broadcast, 3: strided.
+template <int DT, int C, int MODE>
+DEV void load_chunk(const void* base, i64 off, i64 cs, int nvalid, float* out) {
+    if (MODE == 2) {
+        float v = load1<DT>(base, off);
+#pragma unroll
+        for (int j = 0; j < C; ++j) out[j] = v;
+    } else if (MODE == 0 && C > 1) {
+        if (nvalid == C) {
+            load_vec<DT, C>(base, off, out);
+        } else {
+#pragma unroll
+            for (int j = 0; j < C; ++j) out[j] = j < nvalid ? load1<DT>(base, off + j) : 0.f;
+        }
+    } else {
+        const i64 st = MODE == 3 ? cs : 1;
+#pragma unroll
+        for (int j = 0; j < C; ++j) out[j] = j < nvalid ? load1<DT>(base, off + j * st) : 0.f;
+    }
+}
+template <int DT, int C, int MODE>
+DEV void store_chunk(void* base, i64 off, int nvalid, const float* v) {
+    if (MODE == 0 && C > 1 && nvalid == C) {
+        store_vec<DT, C>(base, off, v);
+    } else {
+#pragma unroll
+        for (int j = 0; j < C; ++j)
+            if (j < nvalid) store1<DT>(base, off + j, v[j]);
+    }
+}
+
+// Reductions (identities follow src/reduce.rs:444, 638-642, 711-715, 784).
+#define RED_SUM 0
+#define RED_MAX 1
+#define RED_MIN 2
+#define RED_PROD 3
+template <int OP> DEV float red_ident() {
+    return OP == RED_SUM ? 0.f : OP == RED_PROD ? 1.f : OP == RED_MAX ? -3.40282e+38f : 3.40282e+38f;
+}
+template <int OP> DEV float red_comb(float a, float b) {
+    return OP == RED_SUM ? a + b : OP == RED_PROD ? a * b : OP == RED_MAX ? fmaxf(a, b) : fminf(a, b);
+}
+// All-lanes reduction over the `GROUP` consecutive threads that share a row.  `slot` points
+// at GROUP/32 floats of shared memory private to this (reduction, row) pair.
+template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v = red_comb<OP>(v, __shfl_xor_sync(0xffffffffu, v, m));
+    if (GROUP > 32) {
+        if ((t & 31) == 0) slot[t >> 5] = v;
+        __syncthreads();
+        v = slot[0];
+#pragma unroll
+        for (int w = 1; w < GROUP / 32; ++w) v = red_comb<OP>(v, slot[w]);
+    }
+    return v;
+}
+)CUDA";
+
+// ---------------------------------------------------------------------------------------
+// Element-wise template.  Defines expected: R NIN C U IDX64 NIMM OUT_DT OUT_MODE, macro
+// LOAD_INPUTS(off, nvalid, x) and function prog(x, j, imm).
+// ---------------------------------------------------------------------------------------
+static const char* const JIT_EW_KERNEL = R"CUDA(
+struct Params {
+    u64 n;
+    u64 ptr[NIN + 1];
+    i64 stride[NIN * R];
+    u32 shape[R];
+    u32 mm[R];
+    u32 ms[R];
+    float imm[NIMM > 0 ? NIMM : 1];
+};
+
+DEV void offsets(const Params& p, u64 e, i64* off) {
+#if R == 1
+#pragma unroll
+    for (int s = 0; s < NIN; ++s) off[s] = (i64)e * p.stride[s];
+#else
+#pragma unroll
+    for (int s = 0; s < NIN; ++s) off[s] = 0;
+#if IDX64
+    u64 rem = e;
+#pragma unroll
+    for (int d = R - 1; d >= 1; --d) {
+        u64 q = rem / p.shape[d];
+        i64 c = (i64)(rem - q * p.shape[d]);
+        rem = q;
+#pragma unroll
+        for (int s = 0; s < NIN; ++s) off[s] += c * p.stride[s * R + d];
+    }
+#else
+    u32 rem = (u32)e;
+#pragma unroll
+    for (int d = R - 1; d >= 1; --d) {
+        u32 q = fastdiv(rem, p.mm[d], p.ms[d]);
+        i64 c = (i64)(rem - q * p.shape[d]);
+        rem = q;
+#pragma unroll
+        for (int s = 0; s < NIN; ++s) off[s] += c * p.stride[s * R + d];
+    }
+#endif
+#pragma unroll
+    for (int s = 0; s < NIN; ++s) off[s] += (i64)rem * p.stride[s * R];
+#endif
+}
+
+extern "C" __global__ void __launch_bounds__(256) wgf_kernel(const __grid_constant__ Params p) {
+    const u64 nchunks = (p.n + C - 1) / C;
+    const u64 chunk0 = (u64)blockIdx.x * (256 * U) + threadIdx.x;
+    float x[U][NIN][C];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const u64 chunk = chunk0 + (u64)u * 256;
+        if (chunk < nchunks) {
+            const u64 e = chunk * C;
+            const u64 left = p.n - e;
+            const int nvalid = left < (u64)C ? (int)left : C;
+            i64 off[NIN];
+            offsets(p, e, off);
+            LOAD_INPUTS(off, nvalid, x[u])
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const u64 chunk = chunk0 + (u64)u * 256;
+        if (chunk < nchunks) {
+            const u64 e = chunk * C;
+            const u64 left = p.n - e;
+            const int nvalid = left < (u64)C ? (int)left : C;
+            float y[C];
+#pragma unroll
+            for (int j = 0; j < C; ++j) y[j] = prog(x[u], j, p.imm);
+            store_chunk<OUT_DT, C, OUT_MODE>((void*)p.ptr[NIN], (i64)e, nvalid, y);
+        }
+    }
+}
+)CUDA";
+
+// ---------------------------------------------------------------------------------------
+// Row template: index space [outer..., H]; GROUP threads share a row, RPC rows per CTA;
+// each thread keeps EPT = NCH*C elements of the row in registers across all reductions.
+// Defines expected: RO NIN C NCH GROUP RPC NRED NIMM and macro ROW_BODY.
+// ---------------------------------------------------------------------------------------
+static const char* const JIT_ROW_KERNEL = R"CUDA(
+#define THREADS (GROUP * RPC)
+#define EPT (NCH * C)
+struct Params {
+    u64 rows;
+    u64 ptr[NIN + 1];
+    i64 rstride[(NIN + 1) * RO];
+    i64 cstride[NIN + 1];
+    u32 H;
+    u32 pad_;
+    u32 oshape[RO];
+    u32 mm[RO];
+    u32 ms[RO];
+    float imm[NIMM > 0 ? NIMM : 1];
+};
+
+extern "C" __global__ void __launch_bounds__(THREADS) wgf_kernel(const __grid_constant__ Params p) {
+#if GROUP > 32 && NRED > 0
+    __shared__ float red_smem[NRED][RPC][GROUP / 32];
+#endif
+    const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
+    const u64 row = (u64)blockIdx.x * RPC + g;
+    const bool rv = row < p.rows;
+    i64 roff[NIN + 1];
+#pragma unroll
+    for (int s = 0; s <= NIN; ++s) roff[s] = 0;
+    if (rv) {
+        u32 rem = (u32)row;
+#pragma unroll
+        for (int d = RO - 1; d >= 1; --d) {
+            u32 q = fastdiv(rem, p.mm[d], p.ms[d]);
+            i64 c = (i64)(rem - q * p.oshape[d]);
+            rem = q;
+#pragma unroll
+            for (int s = 0; s <= NIN; ++s) roff[s] += c * p.rstride[s * RO + d];
+        }
+#pragma unroll
+        for (int s = 0; s <= NIN; ++s) roff[s] += (i64)rem * p.rstride[s * RO];
+    }
+    bool kv[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) kv[k] = rv && (u32)((k * GROUP + t) * C) < p.H;
+    const float* imm = p.imm;
+    ROW_BODY
+}
+)CUDA";
+
+// ---------------------------------------------------------------------------------------
+// Streaming reduce template: single-phase programs with a Row result, any row length.
+// A row is split over SPLIT CTAs (p.split); partials go to scratch and the last CTA to
+// arrive for a row combines them in a fixed order, runs the row phase and stores.
+// Defines expected: RO NIN NINE C U NRED NIMM, macros STREAM_PRE, STREAM_LOAD(u),
+// STREAM_POST and function elem_phase(x, rowv, imm, nvalid, acc).
+// ---------------------------------------------------------------------------------------
+static const char* const JIT_STREAM_KERNEL = R"CUDA(
+#define THREADS 256
+struct Params {
+    u64 rows;
+    u64 ptr[NIN + 1];
+    i64 rstride[(NIN + 1) * RO];
+    i64 cstride[NIN + 1];
+    u64 partials;   // float [rows][split][NRED]
+    u64 counters;   // u32 [rows], zero on entry, zero again on exit
+    u64 H;
+    u32 split;
+    u32 pad_;
+    u32 oshape[RO];
+    u32 mm[RO];
+    u32 ms[RO];
+    float imm[NIMM > 0 ? NIMM : 1];
+};
+
+extern "C" __global__ void __launch_bounds__(THREADS) wgf_kernel(const __grid_constant__ Params p) {
+    __shared__ float red_smem[NRED][THREADS / 32];
+    __shared__ u32 is_last;
+    const int t = threadIdx.x;
+    const u32 sp = blockIdx.x % p.split;
+    const u64 row = blockIdx.x / p.split;
+    i64 roff[NIN + 1];
+#pragma unroll
+    for (int s = 0; s <= NIN; ++s) roff[s] = 0;
+    {
+        u32 rem = (u32)row;
+#pragma unroll
+        for (int d = RO - 1; d >= 1; --d) {
+            u32 q = fastdiv(rem, p.mm[d], p.ms[d]);
+            i64 c = (i64)(rem - q * p.oshape[d]);
+            rem = q;
+#pragma unroll
+            for (int s = 0; s <= NIN; ++s) roff[s] += c * p.rstride[s * RO + d];
+        }
+#pragma unroll
+        for (int s = 0; s <= NIN; ++s) roff[s] += (i64)rem * p.rstride[s * RO];
+    }
+    const float* imm = p.imm;
+    const bool rv = true;
+    STREAM_PRE
+    float acc[NRED];
+    STREAM_INIT
+    const u64 nch = (p.H + C - 1) / C;
+    for (u64 base = (u64)sp * (THREADS * U); base < nch; base += (u64)p.split * (THREADS * U)) {
+        float x[U][NINE > 0 ? NINE : 1][C];
+        int nval[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const u64 chunk = base + (u64)u * THREADS + t;
+            nval[u] = 0;
+            if (chunk < nch) {
+                const u64 col = chunk * C;
+                const u64 left = p.H - col;
+                nval[u] = left < (u64)C ? (int)left : C;
+                STREAM_LOAD(col, nval[u], x[u])
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) elem_phase(x[u], rowv, imm, nval[u], acc);
+    }
+    STREAM_BLOCK_REDUCE
+    if (p.split > 1) {
+        float* part = (float*)p.partials + (row * p.split) * NRED;
+        if (t == 0) {
+#pragma unroll
+            for (int r = 0; r < NRED; ++r) part[(u64)sp * NRED + r] = acc[r];
+            __threadfence();
+            u32 ticket = atomicAdd((u32*)p.counters + row, 1u);
+            is_last = ticket == p.split - 1;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        STREAM_INIT
+        for (u32 s2 = t; s2 < p.split; s2 += THREADS) {
+            STREAM_COMBINE_PARTIAL(part + (u64)s2 * NRED)
+        }
+        __syncthreads();
+        STREAM_BLOCK_REDUCE
+        if (t == 0) ((u32*)p.counters)[row] = 0;
+    }
+    STREAM_POST
+}
+)CUDA";
+
+}  // namespace wgf

@@ -1,0 +1,35 @@
+// Launchers of the fused kernel family (run-time compiled) and of the precompiled kernels.
+#pragma once
+#include "ir.hpp"
+#include "runtime.hpp"
+
+namespace wgf {
+
+// Every input's layout must have the rank of `shape` (stride 0 where it is broadcast).
+// `inplace_slot` >= 0 names an input whose buffer the caller allows to be overwritten; it
+// is used only if its layout is dense, non-overlapping, covers the index space one-to-one
+// and its element width equals the result's.  Otherwise a new contiguous buffer is made.
+TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<TensorData>& in,
+                           const std::vector<int64_t>& shape, int inplace_slot);
+
+// Index space `shape` = [outer..., H]; reductions run over the last axis.  An Elem result
+// has shape `shape`, a Row result has shape `shape` without its last axis.
+// `out_has_h` says whether the result keeps the last axis (a Row-kind result is then written
+// to every column of its row).
+TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
+                    const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot);
+
+// Longest row the register-resident row kernel accepts, for the given element width mix.
+int64_t max_resident_row(bool any_16bit);
+
+// Source text of the kernel `run_*` would compile (for tests and inspection without a GPU).
+std::string debug_ew_source(const Program& prog, int rank, int chunk);
+
+// ---- precompiled kernels (move_kernels.cu, matmul*.cu) ----
+// dst[idx] = src[idx] for every index of the common shape; element bits are moved unchanged.
+void run_copy(Device& dev, const TensorData& dst, const TensorData& src);
+// A dense row-major copy of `src` (a new buffer).
+TensorData run_compact(Device& dev, const TensorData& src);
+TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b);
+
+}  // namespace wgf

@@ -1,0 +1,131 @@
+// Bit-exact data movement between strided views: the one kernel behind resize, reshape of
+// non-row-major inputs, slice_assign, cat and the compaction done before a download
+// (src/resize.rs:43-118, src/slice_assign.rs:39-74, src/composite/cat.rs:4-40 of the crate).
+// Threads run along the innermost axis of the collapsed index space; when both views are
+// stride-1 there and 16-byte aligned, each thread moves 16 bytes.
+#include <algorithm>
+
+#include "launch.hpp"
+
+namespace wgf {
+
+namespace {
+
+struct CopyParams {
+    long long n;       // number of units (elements or vectors)
+    int rank;
+    long long shape[WGF_MAX_RANK];   // in units along the innermost axis
+    long long dstride[WGF_MAX_RANK]; // in elements
+    long long sstride[WGF_MAX_RANK];
+};
+
+template <typename T, typename IDX>
+__global__ void __launch_bounds__(256) copy_kernel(T* __restrict__ dst, const T* __restrict__ src,
+                                                   const __grid_constant__ CopyParams p) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += stride) {
+        IDX rem = (IDX)i;
+        long long doff = 0, soff = 0;
+#pragma unroll 1
+        for (int d = p.rank - 1; d >= 1; --d) {
+            IDX q = rem / (IDX)p.shape[d];
+            long long c = (long long)(rem - q * (IDX)p.shape[d]);
+            rem = q;
+            doff += c * p.dstride[d];
+            soff += c * p.sstride[d];
+        }
+        doff += (long long)rem * p.dstride[0];
+        soff += (long long)rem * p.sstride[0];
+        dst[doff] = src[soff];
+    }
+}
+
+template <typename T>
+void launch_copy(Device& dev, void* dst, const void* src, const CopyParams& p) {
+    long long blocks = std::min<long long>((p.n + 255) / 256, (long long)dev.sm_count * 32);
+    dev.begin_launch("copy");
+    if (dev.dry) {
+        dev.end_launch();
+        return;
+    }
+    if (p.n < (1ll << 31))
+        copy_kernel<T, unsigned><<<(unsigned)blocks, 256, 0, dev.stream>>>((T*)dst, (const T*)src, p);
+    else
+        copy_kernel<T, unsigned long long><<<(unsigned)blocks, 256, 0, dev.stream>>>((T*)dst, (const T*)src, p);
+    dev.end_launch();
+}
+
+}  // namespace
+
+void run_copy(Device& dev, const TensorData& dst, const TensorData& src) {
+    WGF_CHECK(dst.layout.shape == src.layout.shape, WGF_ERR_SHAPE, "copy between different shapes");
+    WGF_CHECK(dst.dtype == src.dtype, WGF_ERR_DTYPE, "copy between different element types");
+    WGF_CHECK(!dst.layout.allocation_overlaps(), WGF_ERR_INVALID_ARGUMENT, "copy into an overlapping view");
+    const int64_t n = src.layout.numel();
+    if (n == 0) return;
+    dev.make_current();
+    const int64_t esize = (int64_t)dtype_size(src.dtype);
+    // collapse
+    std::vector<int64_t> shape, ds, ss;
+    for (int d = 0; d < src.layout.rank(); ++d) {
+        int64_t e = src.layout.shape[d];
+        if (e == 1) continue;
+        int64_t a = dst.layout.strides[d], b = src.layout.strides[d];
+        if (!shape.empty() && ds.back() == a * e && ss.back() == b * e) {
+            shape.back() *= e;
+            ds.back() = a;
+            ss.back() = b;
+        } else {
+            shape.push_back(e);
+            ds.push_back(a);
+            ss.push_back(b);
+        }
+    }
+    if (shape.empty()) {
+        shape.push_back(1);
+        ds.push_back(1);
+        ss.push_back(1);
+    }
+    const int R = (int)shape.size();
+    // vector width: 16, 8 or 4 bytes per thread when the innermost axis allows it
+    int64_t vec = 1;
+    if (ds[R - 1] == 1 && ss[R - 1] == 1) {
+        for (int64_t v = 16 / esize; v > 1; v /= 2) {
+            bool ok = shape[R - 1] % v == 0 && (uintptr_t)dst.base_ptr() % (v * esize) == 0 &&
+                      (uintptr_t)src.base_ptr() % (v * esize) == 0;
+            for (int d = 0; d < R - 1 && ok; ++d) ok = ds[d] % v == 0 && ss[d] % v == 0;
+            if (ok) {
+                vec = v;
+                break;
+            }
+        }
+    }
+    CopyParams p{};
+    p.rank = R;
+    p.n = n / vec;
+    for (int d = 0; d < R; ++d) {
+        p.shape[d] = d == R - 1 ? shape[d] / vec : shape[d];
+        p.dstride[d] = d == R - 1 ? 1 : ds[d] / vec;
+        p.sstride[d] = d == R - 1 ? 1 : ss[d] / vec;
+    }
+    if (vec == 1) {
+        p.dstride[R - 1] = ds[R - 1];
+        p.sstride[R - 1] = ss[R - 1];
+    }
+    const int64_t unit = vec * esize;
+    if (unit == 16) launch_copy<uint4>(dev, dst.base_ptr(), src.base_ptr(), p);
+    else if (unit == 8) launch_copy<uint2>(dev, dst.base_ptr(), src.base_ptr(), p);
+    else if (unit == 4) launch_copy<uint32_t>(dev, dst.base_ptr(), src.base_ptr(), p);
+    else launch_copy<uint16_t>(dev, dst.base_ptr(), src.base_ptr(), p);
+}
+
+TensorData run_compact(Device& dev, const TensorData& src) {
+    TensorData out;
+    out.dtype = src.dtype;
+    out.layout = Layout::contiguous(src.layout.shape);
+    out.buf = dev.alloc((size_t)std::max<int64_t>(out.layout.numel(), 1) * dtype_size(src.dtype), false);
+    run_copy(dev, out, src);
+    return out;
+}
+
+}  // namespace wgf

@@ -1,0 +1,415 @@
+#include "runtime.hpp"
+
+#include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cstdlib>
+#include <fstream>
+
+namespace wgf {
+
+// ---------------------------------------------------------------------------------------
+// Driver entry points
+// ---------------------------------------------------------------------------------------
+static void* driver_symbol(const char* name) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+        fail(WGF_ERR_CUDA, std::string("driver entry point not found: ") + name + " (" +
+                               cudaGetErrorString(e) + ")");
+    return fn;
+}
+
+const DriverApi& DriverApi::get() {
+    static DriverApi api = [] {
+        DriverApi a;
+        a.ModuleLoadData = (decltype(a.ModuleLoadData))driver_symbol("cuModuleLoadData");
+        a.ModuleUnload = (decltype(a.ModuleUnload))driver_symbol("cuModuleUnload");
+        a.ModuleGetFunction = (decltype(a.ModuleGetFunction))driver_symbol("cuModuleGetFunction");
+        a.LaunchKernel = (decltype(a.LaunchKernel))driver_symbol("cuLaunchKernel");
+        a.FuncSetAttribute = (decltype(a.FuncSetAttribute))driver_symbol("cuFuncSetAttribute");
+        a.FuncGetAttribute = (decltype(a.FuncGetAttribute))driver_symbol("cuFuncGetAttribute");
+        a.GetErrorString = (decltype(a.GetErrorString))driver_symbol("cuGetErrorString");
+        a.TensorMapEncodeTiled = driver_symbol("cuTensorMapEncodeTiled");
+        return a;
+    }();
+    return api;
+}
+
+static void cu_check(CUresult r, const char* what) {
+    if (r == CUDA_SUCCESS) return;
+    const char* s = nullptr;
+    DriverApi::get().GetErrorString(r, &s);
+    fail(WGF_ERR_CUDA, std::string(what) + ": " + (s ? s : "unknown driver error"));
+}
+
+// ---------------------------------------------------------------------------------------
+// NVRTC, loaded at run time so the library itself loads on machines without it
+// ---------------------------------------------------------------------------------------
+namespace {
+struct Nvrtc {
+    typedef void* Program;
+    int (*CreateProgram)(Program*, const char*, const char*, int, const char* const*, const char* const*);
+    int (*CompileProgram)(Program, int, const char* const*);
+    int (*GetProgramLogSize)(Program, size_t*);
+    int (*GetProgramLog)(Program, char*);
+    int (*GetCUBINSize)(Program, size_t*);
+    int (*GetCUBIN)(Program, char*);
+    int (*DestroyProgram)(Program*);
+    const char* (*GetErrorString)(int);
+    std::string include_dir;
+
+    static Nvrtc& get() {
+        static Nvrtc n = [] {
+            Nvrtc v{};
+            std::vector<std::string> names;
+            if (const char* p = getenv("WGF_NVRTC_PATH")) names.push_back(p);
+            names.push_back("libnvrtc.so.12");
+            names.push_back("/usr/local/cuda/lib64/libnvrtc.so.12");
+            names.push_back("libnvrtc.so");
+            void* h = nullptr;
+            std::string tried;
+            for (auto& nm : names) {
+                h = dlopen(nm.c_str(), RTLD_NOW | RTLD_LOCAL);
+                if (h) break;
+                tried += nm + " ";
+            }
+            if (!h) fail(WGF_ERR_COMPILE, "cannot load NVRTC (tried: " + tried + ")");
+            auto sym = [&](const char* s) {
+                void* p = dlsym(h, s);
+                if (!p) fail(WGF_ERR_COMPILE, std::string("NVRTC symbol missing: ") + s);
+                return p;
+            };
+            v.CreateProgram = (decltype(v.CreateProgram))sym("nvrtcCreateProgram");
+            v.CompileProgram = (decltype(v.CompileProgram))sym("nvrtcCompileProgram");
+            v.GetProgramLogSize = (decltype(v.GetProgramLogSize))sym("nvrtcGetProgramLogSize");
+            v.GetProgramLog = (decltype(v.GetProgramLog))sym("nvrtcGetProgramLog");
+            v.GetCUBINSize = (decltype(v.GetCUBINSize))sym("nvrtcGetCUBINSize");
+            v.GetCUBIN = (decltype(v.GetCUBIN))sym("nvrtcGetCUBIN");
+            v.DestroyProgram = (decltype(v.DestroyProgram))sym("nvrtcDestroyProgram");
+            v.GetErrorString = (decltype(v.GetErrorString))sym("nvrtcGetErrorString");
+            return v;
+        }();
+        return n;
+    }
+};
+
+uint64_t fnv1a(const std::string& s) {
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) {
+        h ^= c;
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+std::string cache_dir() {
+    const char* d = getenv("WGF_KERNEL_CACHE");
+    return d ? std::string(d) : std::string();
+}
+}  // namespace
+
+std::vector<char> compile_to_cubin(const std::string& source, const std::string& name) {
+    // On-disk cache of compiled kernels, keyed by a hash of the complete source text.
+    std::string dir = cache_dir(), path;
+    if (!dir.empty()) {
+        char buf[64];
+        snprintf(buf, sizeof buf, "/%016llx_%zu.cubin", (unsigned long long)fnv1a(source), source.size());
+        path = dir + buf;
+        std::ifstream f(path, std::ios::binary);
+        if (f) {
+            std::vector<char> data((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+            if (!data.empty()) return data;
+        }
+    }
+    Nvrtc& n = Nvrtc::get();
+    Nvrtc::Program prog = nullptr;
+    int r = n.CreateProgram(&prog, source.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr);
+    if (r != 0) fail(WGF_ERR_COMPILE, std::string("nvrtcCreateProgram: ") + n.GetErrorString(r));
+    // --fmad=false: every op of a fused chain rounds on its own, as separate shader functions do.
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17",
+                          "-default-device", "--extra-device-vectorization"};
+    r = n.CompileProgram(prog, 5, opts);
+    if (r != 0) {
+        size_t ls = 0;
+        n.GetProgramLogSize(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) n.GetProgramLog(prog, &log[0]);
+        n.DestroyProgram(&prog);
+        if (getenv("WGF_DUMP_SOURCE")) fprintf(stderr, "---- %s ----\n%s\n", name.c_str(), source.c_str());
+        fail(WGF_ERR_COMPILE, "kernel '" + name + "' failed to compile:\n" + log);
+    }
+    size_t cs = 0;
+    n.GetCUBINSize(prog, &cs);
+    std::vector<char> cubin(cs);
+    n.GetCUBIN(prog, cubin.data());
+    n.DestroyProgram(&prog);
+    if (!path.empty()) {
+        mkdir(dir.c_str(), 0755);
+        std::string tmp = path + ".tmp" + std::to_string((long)getpid());
+        std::ofstream f(tmp, std::ios::binary);
+        if (f) {
+            f.write(cubin.data(), (std::streamsize)cubin.size());
+            f.close();
+            rename(tmp.c_str(), path.c_str());
+        }
+    }
+    return cubin;
+}
+
+// ---------------------------------------------------------------------------------------
+// Buffer / Device
+// ---------------------------------------------------------------------------------------
+Buffer::~Buffer() {
+    if (ptr && dev) dev->release_block(ptr, block);
+}
+
+std::shared_ptr<Device> Device::create(int ordinal) {
+    if (ordinal == -1) {
+        auto d = std::make_shared<Device>();
+        d->ordinal = -1;
+        d->dry = true;
+        d->timing = false;
+        d->sm_count = 148;
+        return d;
+    }
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess)
+        fail(WGF_ERR_CUDA, std::string("no CUDA device available: ") + cudaGetErrorString(e));
+    WGF_CHECK(ordinal >= 0 && ordinal < count, WGF_ERR_INVALID_ARGUMENT,
+              "device ordinal " + std::to_string(ordinal) + " out of range (" + std::to_string(count) + " devices)");
+    auto d = std::make_shared<Device>();
+    d->ordinal = ordinal;
+    WGF_CUDA(cudaSetDevice(ordinal));
+    WGF_CUDA(cudaFree(nullptr));  // establish the primary context
+    cudaDeviceProp prop;
+    WGF_CUDA(cudaGetDeviceProperties(&prop, ordinal));
+    WGF_CHECK(prop.major == 10, WGF_ERR_UNSUPPORTED,
+              std::string("this library is built for sm_100a only; device is sm_") +
+                  std::to_string(prop.major) + std::to_string(prop.minor));
+    d->sm_count = prop.multiProcessorCount;
+    WGF_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+    DriverApi::get();
+    return d;
+}
+
+Device::~Device() {
+    if (dry) {
+        for (auto& kv : free_) free(kv.second);
+        return;
+    }
+    cudaSetDevice(ordinal);
+    if (stream) cudaStreamSynchronize(stream);
+    for (auto& kv : kernels_)
+        if (kv.second.module) DriverApi::get().ModuleUnload(kv.second.module);
+    for (auto& kv : free_) cudaFree(kv.second);
+    for (auto e : event_pool_) cudaEventDestroy(e);
+    if (counters_) cudaFree(counters_);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+void Device::make_current() const {
+    if (!dry) WGF_CUDA(cudaSetDevice(ordinal));
+}
+
+void Device::sync() {
+    if (dry) return;
+    make_current();
+    WGF_CUDA(cudaStreamSynchronize(stream));
+}
+
+static size_t round_block(size_t bytes) {
+    if (bytes < 512) return 512;
+    if (bytes < (1u << 20)) return (bytes + 511) & ~size_t(511);
+    return (bytes + ((1u << 20) - 1)) & ~size_t((1u << 20) - 1);
+}
+
+void* Device::raw_alloc(size_t block) {
+    if (dry) {
+        void* h = aligned_alloc(512, block);
+        if (!h) fail(WGF_ERR_OOM, "host allocation failed");
+        reserved_ += block;
+        return h;
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, block);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        // give cached blocks back to the driver and retry once
+        WGF_CUDA(cudaStreamSynchronize(stream));
+        for (auto& kv : free_) {
+            cudaFree(kv.second);
+            reserved_ -= kv.first;
+        }
+        free_.clear();
+        e = cudaMalloc(&p, block);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fail(e == cudaErrorMemoryAllocation ? WGF_ERR_OOM : WGF_ERR_CUDA,
+             "device allocation of " + std::to_string(block) + " bytes failed: " + cudaGetErrorString(e));
+    }
+    reserved_ += block;
+    return p;
+}
+
+BufferRef Device::alloc(size_t bytes, bool zero) {
+    make_current();
+    size_t block = round_block(bytes);
+    void* p = nullptr;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = free_.lower_bound(block);
+        // reuse a cached block unless it would waste more than a quarter of itself
+        if (it != free_.end() && it->first <= block + block / 4 + 4096) {
+            p = it->second;
+            block = it->first;
+            free_.erase(it);
+        } else {
+            p = raw_alloc(block);
+        }
+        in_use_ += block;
+    }
+    auto b = std::make_shared<Buffer>();
+    b->dev = shared_from_this();
+    b->ptr = p;
+    b->bytes = bytes;
+    b->block = block;
+    if (zero && bytes && !dry) WGF_CUDA(cudaMemsetAsync(p, 0, bytes, stream));
+    return b;
+}
+
+void Device::release_block(void* p, size_t block) {
+    // All work that touches the block was queued on `stream`; any later user of the block
+    // queues on the same stream, so handing it out again needs no wait.
+    std::lock_guard<std::mutex> g(mu_);
+    free_.emplace(block, p);
+    in_use_ -= block;
+}
+
+void Device::trim() {
+    if (dry) return;
+    make_current();
+    WGF_CUDA(cudaStreamSynchronize(stream));
+    std::lock_guard<std::mutex> g(mu_);
+    for (auto& kv : free_) {
+        cudaFree(kv.second);
+        reserved_ -= kv.first;
+    }
+    free_.clear();
+}
+
+void Device::upload(const Buffer& b, size_t off, const void* src, size_t n) {
+    WGF_CHECK(off + n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "upload past the end of the buffer");
+    if (!n || dry) return;
+    make_current();
+    WGF_CUDA(cudaMemcpyAsync((char*)b.ptr + off, src, n, cudaMemcpyHostToDevice, stream));
+    // The source may be pageable and reused by the caller right away.
+    WGF_CUDA(cudaStreamSynchronize(stream));
+}
+
+void Device::download(const Buffer& b, size_t off, void* dst, size_t n) {
+    WGF_CHECK(off + n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "download past the end of the buffer");
+    WGF_CHECK(!dry, WGF_ERR_CUDA, "compile-only device: nothing was executed, there is nothing to download");
+    make_current();
+    if (n) WGF_CUDA(cudaMemcpyAsync(dst, (const char*)b.ptr + off, n, cudaMemcpyDeviceToHost, stream));
+    WGF_CUDA(cudaStreamSynchronize(stream));
+}
+
+void* Device::counters() {
+    if (dry) return nullptr;
+    if (!counters_) {
+        make_current();
+        WGF_CUDA(cudaMalloc(&counters_, kCounters * sizeof(uint32_t)));
+        WGF_CUDA(cudaMemsetAsync(counters_, 0, kCounters * sizeof(uint32_t), stream));
+    }
+    return counters_;
+}
+
+cudaEvent_t Device::event() {
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        if (!event_pool_.empty()) {
+            cudaEvent_t e = event_pool_.back();
+            event_pool_.pop_back();
+            return e;
+        }
+    }
+    cudaEvent_t e;
+    WGF_CUDA(cudaEventCreate(&e));
+    return e;
+}
+
+void Device::recycle(cudaEvent_t e) {
+    std::lock_guard<std::mutex> g(mu_);
+    event_pool_.push_back(e);
+}
+
+const JitKernel& Device::kernel(const std::string& key, const std::function<std::string()>& source) {
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = kernels_.find(key);
+        if (it != kernels_.end()) return it->second;
+    }
+    make_current();
+    std::string src = source();
+    std::vector<char> cubin = compile_to_cubin(src, "wgf_kernel");
+    compiles++;
+    if (dry) {
+        std::lock_guard<std::mutex> g(mu_);
+        return kernels_.emplace(key, JitKernel{}).first->second;
+    }
+    const DriverApi& api = DriverApi::get();
+    JitKernel k;
+    cu_check(api.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData");
+    cu_check(api.ModuleGetFunction(&k.fn, k.module, "wgf_kernel"), "cuModuleGetFunction");
+    api.FuncGetAttribute(&k.regs, CU_FUNC_ATTRIBUTE_NUM_REGS, k.fn);
+    std::lock_guard<std::mutex> g(mu_);
+    auto ins = kernels_.emplace(key, k);
+    if (!ins.second) api.ModuleUnload(k.module);  // another thread won the race
+    return ins.first->second;
+}
+
+void Device::begin_launch(const char* what) {
+    launches++;
+    if (timing && sink && !dry) {
+        pending_.start = event();
+        pending_.stop = event();
+        pending_.what = what;
+        WGF_CUDA(cudaEventRecord(pending_.start, stream));
+    }
+}
+
+void Device::end_launch() {
+    if (pending_.start) {
+        WGF_CUDA(cudaEventRecord(pending_.stop, stream));
+        if (sink) sink->push_back(pending_);
+        pending_ = TimingRecord{};
+    }
+    if (dry) return;
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fail(WGF_ERR_CUDA, std::string("kernel launch failed: ") + cudaGetErrorString(e));
+    }
+}
+
+void Device::launch(const JitKernel& k, dim3 grid, dim3 block, size_t smem, const void* params,
+                    const char* what) {
+    make_current();
+    begin_launch(what);
+    if (dry) {
+        end_launch();
+        return;
+    }
+    void* args[] = {const_cast<void*>(params)};
+    CUresult r = DriverApi::get().LaunchKernel(k.fn, grid.x, grid.y, grid.z, block.x, block.y, block.z,
+                                               (unsigned)smem, (CUstream)stream, args, nullptr);
+    cu_check(r, what);
+    end_launch();
+}
+
+}  // namespace wgf

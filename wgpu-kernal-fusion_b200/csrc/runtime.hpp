@@ -1,0 +1,134 @@
+// Device runtime: CUDA context + stream, caching device allocator, CUDA-event timing,
+// run-time kernel compilation (NVRTC -> cubin -> module) with a per-device kernel cache.
+// Takes the place of src/device.rs, the buffer half of src/tensor.rs, src/query.rs and the
+// pipeline/bind-group half of src/kernel.rs in the crate.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.hpp"
+
+namespace wgf {
+
+#define WGF_CUDA(expr)                                                                      \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            ::wgf::fail(_e == cudaErrorMemoryAllocation ? WGF_ERR_OOM : WGF_ERR_CUDA,       \
+                        std::string(#expr) + ": " + cudaGetErrorString(_e));                \
+    } while (0)
+
+struct Device;
+
+struct Buffer {
+    std::shared_ptr<Device> dev;
+    void* ptr = nullptr;
+    size_t bytes = 0;       // requested
+    size_t block = 0;       // size of the pool block backing it
+    ~Buffer();
+};
+using BufferRef = std::shared_ptr<Buffer>;
+
+// TensorData of the crate (src/tensor.rs:300-306): buffer + layout + dtype.
+struct TensorData {
+    BufferRef buf;
+    Layout layout;
+    DType dtype = DType::F32;
+    void* base_ptr() const { return (char*)buf->ptr + layout.offset * (int64_t)dtype_size(dtype); }
+    explicit operator bool() const { return (bool)buf; }
+};
+
+struct TimingRecord {
+    cudaEvent_t start = nullptr, stop = nullptr;
+    const char* what = "";
+};
+
+struct JitKernel {
+    CUmodule module = nullptr;
+    CUfunction fn = nullptr;
+    int regs = 0;
+};
+
+struct Device : std::enable_shared_from_this<Device> {
+    int ordinal = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    bool timing = true;
+    // Compile-only device (ordinal -1): builds and compiles every kernel a graph needs but
+    // owns no GPU and executes nothing; downloads fail.  Lets the resolver and the generated
+    // CUDA source be checked on a machine without a GPU.
+    bool dry = false;
+    std::atomic<uint64_t> launches{0}, compiles{0};
+
+    static std::shared_ptr<Device> create(int ordinal);
+    ~Device();
+
+    void make_current() const;
+    void sync();
+
+    // ---- memory ----
+    BufferRef alloc(size_t bytes, bool zero);
+    void upload(const Buffer& b, size_t off, const void* src, size_t n);
+    void download(const Buffer& b, size_t off, void* dst, size_t n);
+    // 65536 zero-initialised u32 tickets for kernels that elect a last-arriving CTA; every
+    // such kernel leaves them zero again.
+    void* counters();
+    static constexpr int kCounters = 65536;
+    uint64_t reserved_bytes() const { return reserved_; }
+    uint64_t in_use_bytes() const { return in_use_; }
+    void release_block(void* p, size_t block);
+    void trim();
+
+    // ---- kernels ----
+    // Looks `key` up in the cache; on a miss calls `source()` and compiles it.  The kernel
+    // entry point must be `extern "C" __global__ void wgf_kernel(Params)`.
+    const JitKernel& kernel(const std::string& key, const std::function<std::string()>& source);
+    // Launch a run-time compiled kernel taking ONE by-value struct parameter.
+    void launch(const JitKernel& k, dim3 grid, dim3 block, size_t smem, const void* params,
+                const char* what);
+    // Book-keeping for kernels launched with <<<>>> from this library's own .cu files.
+    void begin_launch(const char* what);
+    void end_launch();
+
+    // Timing sink: while set, every launch appends an event pair to it.
+    std::vector<TimingRecord>* sink = nullptr;
+    cudaEvent_t event();
+    void recycle(cudaEvent_t e);
+
+   private:
+    std::mutex mu_;
+    std::multimap<size_t, void*> free_;
+    uint64_t reserved_ = 0, in_use_ = 0;
+    std::unordered_map<std::string, JitKernel> kernels_;
+    std::vector<cudaEvent_t> event_pool_;
+    TimingRecord pending_;
+    void* counters_ = nullptr;
+    void* raw_alloc(size_t block);
+};
+using DeviceRef = std::shared_ptr<Device>;
+
+// Compile CUDA C++ to an sm_100a cubin with NVRTC (no GPU needed).  Throws WGF_ERR_COMPILE
+// with the compiler log on failure.
+std::vector<char> compile_to_cubin(const std::string& source, const std::string& name);
+
+// Driver entry points fetched through the runtime (the library does not link libcuda).
+struct DriverApi {
+    CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*ModuleUnload)(CUmodule) = nullptr;
+    CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                             unsigned, CUstream, void**, void**) = nullptr;
+    CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*FuncGetAttribute)(int*, CUfunction_attribute, CUfunction) = nullptr;
+    CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    void* TensorMapEncodeTiled = nullptr;
+    static const DriverApi& get();
+};
+
+}  // namespace wgf
