@@ -1,0 +1,338 @@
+"""Benchmark of the fused element-wise -> reduce hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (one step, per GPU): x = f32 [8192, 4096] N(0,1) resident in HBM, w = f32 [4096] N(1, 0.1);
+  y = softmax_rows(rms_norm(x, w, eps 1e-5))      one fused row kernel, 268 451 840 algorithmic bytes
+  s = sum(exp(x)) over the whole tensor            one streaming reduce, 134 217 728 bytes
+      (+ an NCCL all-reduce of the per-GPU scalar when N > 1: rows are sharded, weak scaling)
+Inputs are synthetic (seeded PCG64).  Four input buffers are rotated so that every step reads x
+from HBM, not from L2.  `value` = algorithmic bytes of all ranks / device time (CUDA events on the
+library's stream, max over ranks).  `e2e` = the same metric through the public C ABI with HOST
+buffers: upload of x from pinned memory, both kernels, download of y and s, every step.
+
+`--impl reference` times the CPU restatement of the reference's math (oracle/oracle.c, fast mode:
+float + libm, one memory pass per kernel the reference's resolver would launch, all host threads).
+"""
+import argparse
+import ctypes
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+ROWS, H = 8192, 4096
+BYTES_CHAIN = ROWS * H * 4 * 2 + H * 4          # read x, read w, write y
+BYTES_SUM = ROWS * H * 4                        # read x (+ 4 bytes out)
+BYTES_STEP = BYTES_CHAIN + BYTES_SUM
+NBUF = 4
+
+
+def load(name, path):
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        self.lines = []
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def make_inputs(rank, k):
+    g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 2 + 64 * rank + k))
+    return g.standard_normal((ROWS, H), dtype=np.float32)
+
+
+def make_weight():
+    g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 2 + 1))
+    return (1.0 + 0.1 * g.standard_normal(H)).astype(np.float32)
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arm: the oracle's fast mode
+# --------------------------------------------------------------------------------------------
+class CpuWorkload:
+    """The workload (or its first `rows` rows) on the host cores."""
+
+    def __init__(self, rows=ROWS):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import oracle
+        self.lib = oracle.lib()
+        self.cores = int(self.lib.orc_threads())
+        self.rows = rows
+        self.x = make_inputs(0, 0)[:rows].copy()
+        self.w = make_weight()
+        f = np.float32
+        self.norm, self.m, self.s = np.empty(rows, f), np.empty(rows, f), np.empty(rows, f)
+        self.tmp, self.normed = np.empty((rows, H), f), np.empty((rows, H), f)
+        self.t1, self.t2, self.out = np.empty((rows, H), f), np.empty((rows, H), f), np.empty((rows, H), f)
+        self.col = np.empty(H, f)
+        self.bytes_step = rows * H * 4 * 3 + H * 4
+
+    def step(self):
+        p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        L, R = self.lib, ctypes.c_int64(self.rows)
+        L.orc_fast_rms_norm(p(self.x), p(self.w), ctypes.c_float(1e-5), p(self.norm), p(self.tmp), p(self.normed),
+                            R, ctypes.c_int64(H))
+        L.orc_fast_softmax_rows(p(self.normed), p(self.m), p(self.t1), p(self.t2), p(self.s), p(self.out),
+                                R, ctypes.c_int64(H))
+        return float(L.orc_fast_sum_exp(p(self.x), p(self.col), R, ctypes.c_int64(H)))
+
+    def time(self, steps, warmup):
+        for _ in range(warmup):
+            self.step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.step()
+        dt = time.perf_counter() - t0
+        return self.bytes_step * steps / dt / 1e9, dt / steps * 1e3
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # Each step is a bounded sample of the workload: as many leading rows as keep the whole
+    # run near one minute (never fewer than 256 rows = 4 MiB per array, beyond the core caches).
+    probe = CpuWorkload(256)
+    _, probe_ms = probe.time(2, 1)
+    budget_ms = 60e3 / max(args.steps + args.warmup, 1)
+    rows = int(min(ROWS, max(256, 256 * budget_ms / max(probe_ms, 1e-3))))
+    rows -= rows % 256
+    cpu = CpuWorkload(rows)
+    gbs, ms = cpu.time(args.steps, args.warmup)
+    sample = f"first {rows} of {ROWS} rows ({rows}x{H} f32) per step, {args.steps} steps after {args.warmup} warm-up"
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_chain_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "rmsnorm->softmax rows + sum(exp(x)), f32 [8192,4096]", "device": "host cpu"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+
+    wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
+    dev = wgf.Device(local)
+    sm_count, stream_ptr = dev.info()
+    stream = torch.cuda.ExternalStream(stream_ptr, device=torch.device("cuda", local))
+
+    comm = None
+    if world > 1:
+        ids = [wgf.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = wgf.Comm(dev, world, rank, ids[0])
+
+    w_host = make_weight()
+    w = dev.tensor(w_host)
+    xs = [dev.tensor(make_inputs(rank, k)) for k in range(NBUF)]
+
+    def step(i, keep=None):
+        x = xs[i % NBUF]
+        y = x.layer_norm(w, 1e-5).softmax_last_dim()
+        s = x.exp().sum(0).sum(0)
+        if comm is not None:
+            s = s.all_reduce(comm)
+        y.materialize()
+        s.materialize()
+        if keep is not None:
+            keep.append((y, s))
+
+    def barrier():
+        dev.sync()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing --------------------------------------------------------------
+    sampler = ClockSampler(local) if rank == 0 else None   # sampled from the warm-up on: the timed region is short
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    n_timing_before = len(xs[0].all_timing_information())
+    launches_before = dev.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = dev.launch_count - launches_before
+    clocks = sampler.stop() if sampler else None
+
+    # per-kernel device times of the timed region (event pair around every launch)
+    # (all inputs share one graph through w, so the records are in launch order:
+    #  rows, stream_reduce[, all_reduce] per step)
+    per_step = 3 if comm is not None else 2
+    recs = xs[0].all_timing_information()[n_timing_before:]
+    row_ns, sum_ns = recs[0::per_step], recs[1::per_step]
+    row_ms = float(np.mean(row_ns)) / 1e6 if row_ns else float("nan")
+    sum_ms = float(np.mean(sum_ns)) / 1e6 if sum_ns else float("nan")
+
+    # ---- end to end through the C ABI with host buffers ---------------------------------------
+    pin_x = wgf.PinnedArray((ROWS, H), np.float32)
+    pin_y = wgf.PinnedArray((ROWS, H), np.float32)
+    pin_s = wgf.PinnedArray((), np.float32)
+    pin_x.array[...] = make_inputs(rank, 0)
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        x = dev.tensor(pin_x.array)                  # H2D from pinned memory
+        y = x.layer_norm(w, 1e-5).softmax_last_dim()
+        s = x.exp().sum(0).sum(0)
+        if comm is not None:
+            s = s.all_reduce(comm)
+        y.download_into(pin_y.array)                 # D2H
+        s.download_into(pin_s.array)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+
+    # ---- max over ranks ---------------------------------------------------------------------
+    vals = torch.tensor([ms_total, e2e_ms, float(launches)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = vals.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = vals.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_total, e2e_ms, launches = float(mx[0]), float(mx[1]), int(sm[2])
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        ms_step = ms_total / args.steps
+        value = BYTES_STEP * world / (ms_step * 1e-3) / 1e9
+        achieved = BYTES_CHAIN / (row_ms * 1e-3) / 1e9
+        # CPU baseline on rank 0, N=1 only: the oracle's fast mode on the full workload
+        cpu_baseline = None
+        if world == 1 and not args.no_cpu:
+            cpu = CpuWorkload()
+            reps = 8
+            gbs, _ = cpu.time(reps, 1)
+            cpu_baseline = {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": "port",
+                            "sample": f"full workload ({ROWS}x{H} f32), {reps} repetitions after 1 warm-up"}
+        print(json.dumps({
+            "metric": "fused_chain_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "rmsnorm->softmax rows + sum(exp(x)), f32 [8192,4096] per GPU",
+                       "rows_per_gpu": ROWS, "row_len": H, "sharding": "rows" if world > 1 else "none",
+                       "l2": f"{NBUF} input buffers of 128 MiB rotated: inputs larger than L2",
+                       "bytes_per_step_per_gpu": BYTES_STEP},
+            "roofline": {"bound": "hbm", "kernel": "fused rmsnorm->softmax row kernel", "achieved": achieved,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "launch_ms": row_ms,
+                         "sum_exp_kernel": {"achieved": BYTES_SUM / (sum_ms * 1e-3) / 1e9, "launch_ms": sum_ms,
+                                            "frac": BYTES_SUM / (sum_ms * 1e-3) / 1e9 / peak}},
+            "cpu_baseline": cpu_baseline,
+            "e2e": {"value": BYTES_STEP * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "steps": e2e_steps, "h2d_bytes_per_step": ROWS * H * 4, "d2h_bytes_per_step": ROWS * H * 4 + 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--impl", default="wgf", choices=["wgf", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -111,6 +111,10 @@ int32_t wgf_buffer_use_count(wgf_buffer* buf, int64_t* out);
 int32_t wgf_buffer_upload(wgf_buffer* buf, uint64_t offset_bytes, const void* src, uint64_t bytes);
 int32_t wgf_buffer_download(wgf_buffer* buf, uint64_t offset_bytes, void* dst, uint64_t bytes);
 int32_t wgf_buffer_device_ptr(wgf_buffer* buf, void** ptr, uint64_t* bytes);
+/* Page-locked host memory, so that uploads and downloads run at full PCIe speed (the crate
+ * gets this from wgpu's mapped staging buffers, src/tensor.rs:345-381 and :533-549). */
+int32_t wgf_host_alloc(uint64_t bytes, void** out);
+int32_t wgf_host_free(void* ptr);
 
 /* ======================================================================================
  * Kernel-level launches  (replace Untyped*Kernel::run_with_query)

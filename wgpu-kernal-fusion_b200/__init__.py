@@ -363,6 +363,23 @@ for _i, _name in enumerate(UNARY_NAMES):
     setattr(Tensor, _name, (lambda op: lambda self: self.unary(op))(_i))
 
 
+class PinnedArray:
+    """numpy array over page-locked host memory (wgf_host_alloc)."""
+
+    def __init__(self, shape, dtype):
+        self.nbytes = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+        self.ptr = C.c_void_p()
+        check(lib().wgf_host_alloc(C.c_uint64(self.nbytes), C.byref(self.ptr)))
+        buf = (C.c_char * max(self.nbytes, 1)).from_address(self.ptr.value)
+        self.array = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape, dtype=np.int64))).reshape(shape)
+
+    def __del__(self):
+        if getattr(self, "ptr", None) and _lib is not None:
+            self.array = None
+            _lib.wgf_host_free(self.ptr)
+            self.ptr = None
+
+
 def shard_range(n_units, world, rank):
     b, e = C.c_int64(), C.c_int64()
     check(lib().wgf_shard_range(C.c_int64(n_units), C.c_int32(world), C.c_int32(rank), C.byref(b), C.byref(e)))

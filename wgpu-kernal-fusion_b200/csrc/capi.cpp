@@ -263,6 +263,18 @@ int32_t wgf_buffer_device_ptr(wgf_buffer* buf, void** ptr, uint64_t* bytes) {
     });
 }
 
+int32_t wgf_host_alloc(uint64_t bytes, void** out) {
+    return guard([&] {
+        REQUIRE(out);
+        WGF_CUDA(cudaHostAlloc(out, (size_t)std::max<uint64_t>(bytes, 1), cudaHostAllocDefault));
+    });
+}
+int32_t wgf_host_free(void* ptr) {
+    return guard([&] {
+        if (ptr) WGF_CUDA(cudaFreeHost(ptr));
+    });
+}
+
 // ---------------------------------------------------------------- kernel-level launches
 int32_t wgf_launch_elementwise(wgf_device* dev, const wgf_tensor_desc* in, const wgf_ew_op* chain,
                                uint32_t n_ops, int32_t inplace_ok, wgf_tensor_desc* out,

@@ -116,6 +116,13 @@ void magic_for(uint32_t d, uint32_t& m, uint32_t& s) {
     s = p - 32;
 }
 
+// Tuning overrides read from the environment (WGF_TUNE_<NAME>=int); absent = `dflt`.
+int tune(const char* name, int dflt) {
+    std::string key = std::string("WGF_TUNE_") + name;
+    const char* v = getenv(key.c_str());
+    return v ? atoi(v) : dflt;
+}
+
 int pow2_at_least(int64_t v) {
     int p = 1;
     while (p < v) p <<= 1;
@@ -271,7 +278,7 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
     key << "ew|" << R << "|" << cfg.C << "|" << cfg.U << "|" << cfg.idx64 << "|" << cfg.out_mode << "|";
     for (int m : cfg.mode) key << m;
     key << "|" << prog.signature();
-    const JitKernel& k = dev.kernel(key.str(), [&] { return ew_source(prog, cfg); });
+    const JitKernel& k = dev.kernel(key.str(), "wgf_elementwise", [&] { return ew_source(prog, cfg); });
 
     ParamWriter w;
     w.put<uint64_t>((uint64_t)n);
@@ -300,36 +307,67 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
 namespace {
 
 struct RowConfig {
-    int RO, C, NCH, GROUP, RPC, out_mode;
-    bool out_has_h;
+    int RO, C, NCH, GROUP, RPC, out_mode, minb;
+    bool out_has_h, prefetch;
     std::vector<int> mode;       // per slot: 0 vec, 1 scalar, 3 strided; 2 = row value (cstride 0)
+    std::vector<char> invariant; // per slot: does not depend on the row (all outer strides 0)
 };
+
+void replace_all(std::string& text, const std::string& marker, const std::string& with) {
+    size_t at = 0;
+    while ((at = text.find(marker, at)) != std::string::npos) {
+        text.replace(at, marker.size(), with);
+        at += with.size();
+    }
+}
 
 std::string row_source(const Program& prog, const RowConfig& c) {
     std::ostringstream s;
     s << JIT_PRELUDE;
     s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define C " << c.C
       << "\n#define NCH " << c.NCH << "\n#define GROUP " << c.GROUP << "\n#define RPC " << c.RPC
-      << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM " << prog.imms.size() << "\n";
-    std::ostringstream b;
+      << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM " << prog.imms.size()
+      << "\n#define MINB " << c.minb << "\n";
+    // inv: loaded once per CTA; decl/pre/take: double-buffered per-row loads; b: per-row body
+    std::ostringstream inv, decl, pre, take, b;
     int red_idx = 0;
     auto operand = [&](int i, const char* idx) {
         return prog.ins[i].vk == VKind::Row ? vn(i) : vn(i) + "[" + idx + "]";
+    };
+    // text of a whole-row load of slot t into array `dst`, guarded by `valid[k]`, row offset `off`
+    auto row_load = [&](std::ostringstream& o, int t, const std::string& dst, const char* valid, const std::string& off) {
+        o << "\n#pragma unroll\n for (int k = 0; k < NCH; ++k) {\n"
+          << "  if (" << valid << "[k]) load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << c.mode[t]
+          << ">((const void*)p.ptr[" << t << "], " << off << " + (i64)((k * GROUP + t) * C) * "
+          << (c.mode[t] == 3 ? "p.cstride[" + std::to_string(t) + "]" : std::string("1"))
+          << ", p.cstride[" << t << "], C, &" << dst << "[k * C]);\n"
+          << "  else { \n#pragma unroll\n for (int j = 0; j < C; ++j) " << dst << "[k * C + j] = 0.f; }\n}\n";
     };
     for (int i = 0; i < (int)prog.ins.size(); ++i) {
         const Instr& in = prog.ins[i];
         if (in.kind == IKind::Load) {
             int t = in.slot;
+            std::string dt = std::to_string((int)prog.slot_dtype[t]);
             if (in.vk == VKind::Row) {
-                b << "float " << vn(i) << " = rv ? load1<" << (int)prog.slot_dtype[t]
-                  << ">((const void*)p.ptr[" << t << "], roff[" << t << "]) : 0.f;\n";
+                if (c.invariant[t])
+                    inv << "const float " << vn(i) << " = load1<" << dt << ">((const void*)p.ptr[" << t << "], 0);\n";
+                else
+                    b << "float " << vn(i) << " = crv ? load1<" << dt << ">((const void*)p.ptr[" << t << "], coff["
+                      << t << "]) : 0.f;\n";
+            } else if (c.invariant[t]) {
+                inv << "float " << vn(i) << "[EPT];\n";
+                row_load(inv, t, vn(i), "cv", "(i64)0");
+            } else if (!c.prefetch) {
+                take << "float " << vn(i) << "[EPT];\n";
+                row_load(take, t, vn(i), "kv", "coff[" + std::to_string(t) + "]");
             } else {
-                b << "float " << vn(i) << "[EPT];\n\n#pragma unroll\n for (int k = 0; k < NCH; ++k) {\n"
-                  << "  if (kv[k]) load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << c.mode[t]
-                  << ">((const void*)p.ptr[" << t << "], roff[" << t << "] + (i64)((k * GROUP + t) * C) * "
-                  << (c.mode[t] == 3 ? "p.cstride[" + std::to_string(t) + "]" : std::string("1"))
-                  << ", p.cstride[" << t << "], C, &" << vn(i) << "[k * C]);\n"
-                  << "  else { \n#pragma unroll\n for (int j = 0; j < C; ++j) " << vn(i) << "[k * C + j] = 0.f; }\n}\n";
+                // next-row buffer n<i>, filled ahead of the reductions of the current row
+                decl << "float n" << i << "[EPT];\n";
+                pre << "if (rv) {";
+                row_load(pre, t, "n" + std::to_string(i), "cv", "roff[" + std::to_string(t) + "]");
+                pre << "}\n";
+                take << "float " << vn(i) << "[EPT];\n#pragma unroll\n for (int e = 0; e < EPT; ++e) " << vn(i)
+                     << "[e] = n" << i << "[e];\n";
             }
         } else if (in.kind == IKind::RowReduce) {
             const char* op = red_name(in.op);
@@ -346,6 +384,13 @@ std::string row_source(const Program& prog, const RowConfig& c) {
         } else if (in.vk == VKind::Row) {
             b << "float " << vn(i) << " = " << instr_expr(in, vn(in.a), in.b >= 0 ? vn(in.b) : std::string())
               << ";\n";
+        } else if (in.kind == IKind::Binary && in.op == WGF_OP_DIV && prog.ins[in.b].vk == VKind::Row) {
+            // a row of values divided by one per-row value: one correctly rounded reciprocal per
+            // row and a multiply per element (<= 2 ulp from the quotient) instead of an IEEE
+            // division per element, which would make the kernel instruction-bound
+            b << "const float q" << i << " = 1.0f / " << vn(in.b) << ";\nfloat " << vn(i)
+              << "[EPT];\n\n#pragma unroll\n for (int e = 0; e < EPT; ++e) " << vn(i) << "[e] = "
+              << rounded(in.dtype, "(" + operand(in.a, "e") + " * q" + std::to_string(i) + ")") << ";\n";
         } else {
             b << "float " << vn(i) << "[EPT];\n\n#pragma unroll\n for (int e = 0; e < EPT; ++e) " << vn(i)
               << "[e] = " << instr_expr(in, operand(in.a, "e"), in.b >= 0 ? operand(in.b, "e") : std::string())
@@ -358,26 +403,31 @@ std::string row_source(const Program& prog, const RowConfig& c) {
         b << "\n#pragma unroll\n for (int k = 0; k < NCH; ++k) if (kv[k]) {\n";
         if (prog.ins[res].vk == VKind::Row) {
             b << "  float y_[C]; \n#pragma unroll\n for (int j = 0; j < C; ++j) y_[j] = " << vn(res) << ";\n"
-              << "  store_chunk<" << odt << ", C, " << c.out_mode << ">((void*)p.ptr[NIN], roff[NIN] + (i64)((k * GROUP + t) * C), C, y_);\n";
+              << "  store_chunk<" << odt << ", C, " << c.out_mode << ">((void*)p.ptr[NIN], coff[NIN] + (i64)((k * GROUP + t) * C), C, y_);\n";
         } else {
             b << "  store_chunk<" << odt << ", C, " << c.out_mode
-              << ">((void*)p.ptr[NIN], roff[NIN] + (i64)((k * GROUP + t) * C), C, &" << vn(res) << "[k * C]);\n";
+              << ">((void*)p.ptr[NIN], coff[NIN] + (i64)((k * GROUP + t) * C), C, &" << vn(res) << "[k * C]);\n";
         }
         b << "}\n";
     } else {
-        b << "if (rv && t == 0) store1<" << odt << ">((void*)p.ptr[NIN], roff[NIN], " << vn(res) << ");\n";
+        b << "if (crv && t == 0) store1<" << odt << ">((void*)p.ptr[NIN], coff[NIN], " << vn(res) << ");\n";
     }
-    // splice the generated body into the template
+    // A group_reduce reuses its shared-memory slot in the next iteration: all reads of this
+    // iteration must be done before the next row writes.
+    // (with two or more reductions the barrier of the second one already orders that)
+    if (c.GROUP > 32 && prog.n_reduces() == 1) b << "__syncthreads();\n";
     std::string tmpl = JIT_ROW_KERNEL;
-    const std::string marker = "ROW_BODY";
-    size_t at = tmpl.rfind(marker);
-    tmpl.replace(at, marker.size(), b.str());
+    replace_all(tmpl, "ROW_INVARIANT", inv.str());
+    replace_all(tmpl, "ROW_NEXT_DECL", decl.str());
+    replace_all(tmpl, "ROW_PREFETCH", pre.str());
+    replace_all(tmpl, "ROW_TAKE", take.str());
+    replace_all(tmpl, "ROW_BODY", b.str());
     s << tmpl;
     return s.str();
 }
 
 struct StreamConfig {
-    int RO, C, U;
+    int RO, C, U, minb;
     std::vector<int> mode;
 };
 
@@ -451,7 +501,7 @@ std::string stream_source(const Program& prog, const StreamConfig& c) {
     s << JIT_PRELUDE;
     s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define NINE " << nine
       << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces()
-      << "\n#define NIMM " << prog.imms.size() << "\n";
+      << "\n#define NIMM " << prog.imms.size() << "\n#define MINB " << c.minb << "\n";
     s << "DEV void elem_phase(const float (&x)[NINE > 0 ? NINE : 1][C], const float* rowv, const float* imm, int nvalid, float* acc) {\n"
       << "#pragma unroll\n    for (int j = 0; j < C; ++j) {\n      if (j < nvalid) {\n"
       << elem.str() << "      }\n    }\n}\n";
@@ -599,24 +649,37 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             pick_modes(1, cfg.mode, cfg.out_mode, true);
         }
         const int64_t chunks = (H + cfg.C - 1) / cfg.C;
-        const int target = cfg.C == 1 ? 16 : (cfg.C == 4 ? 4 : 2);
+        const int target = std::max(1, tune("ROW_EPT", 16) / cfg.C);
         cfg.GROUP = std::min(1024, std::max(32, pow2_at_least((chunks + target - 1) / target)));
         cfg.NCH = (int)((chunks + cfg.GROUP - 1) / cfg.GROUP);
         WGF_CHECK(cfg.NCH * cfg.C <= 64, WGF_ERR_UNSUPPORTED, "row too long for a row-fused kernel");
         int threads = std::max(cfg.GROUP, 128);
         cfg.RPC = threads / cfg.GROUP;
+        cfg.minb = tune("ROW_MINB", std::max(1, std::min(4, 768 / threads)));
+        cfg.prefetch = tune("ROW_PREFETCH", 1) != 0;
+        cfg.invariant.assign(nin, 0);
+        for (int t = 0; t < nin; ++t) {
+            bool inv = true;
+            for (int d = 0; d < RO; ++d) inv = inv && (st[t][d] == 0 || coshape[d] == 1);
+            cfg.invariant[t] = inv;
+        }
         std::ostringstream key;
         key << "row|" << RO << "|" << cfg.C << "|" << cfg.NCH << "|" << cfg.GROUP << "|" << cfg.RPC << "|"
-            << cfg.out_mode << "|" << out_has_h << "|";
+            << cfg.out_mode << "|" << out_has_h << "|" << cfg.minb << cfg.prefetch << "|";
         for (int m : cfg.mode) key << m;
+        key << "|";
+        for (int v : cfg.invariant) key << v;
         key << "|" << prog.signature();
-        const JitKernel& k = dev.kernel(key.str(), [&] { return row_source(prog, cfg); });
+        const JitKernel& k = dev.kernel(key.str(), "wgf_rows", [&] { return row_source(prog, cfg); });
         ParamWriter w;
         put_common(w);
         w.put<uint32_t>((uint32_t)H);
         w.put<uint32_t>(0);
         put_tail(w);
+        // persistent CTAs: as many as fit on the machine at once, each walking several rows
         int64_t blocks = (rows + cfg.RPC - 1) / cfg.RPC;
+        if (tune("ROW_PERSIST", 1))
+            blocks = std::min<int64_t>(blocks, (int64_t)dev.sm_count * dev.max_blocks_per_sm(k, cfg.GROUP * cfg.RPC));
         dev.launch(k, dim3((unsigned)blocks), dim3(cfg.GROUP * cfg.RPC), 0, w.bytes.data(), "rows");
         return out;
     }
@@ -633,18 +696,21 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
     int nine = 0;
     for (int t = 0; t < nin; ++t) nine += !(slot_row[t] || cs[t] == 0);
     // a slot with column stride 0 that the program loads per element is read as broadcast
-    cfg.U = std::max(1, std::min(4, 64 / (std::max(nine, 1) * cfg.C)));
-    const int64_t nch = (H + cfg.C - 1) / cfg.C;
-    const int64_t per_cta = 256ll * cfg.U;
-    int64_t max_split = std::max<int64_t>(1, (nch + per_cta - 1) / per_cta);
-    int64_t split = std::max<int64_t>(1, (8ll * dev.sm_count + rows - 1) / rows);
-    split = std::min<int64_t>({split, max_split, 2048});
-    if (rows > 65536) split = 1;
+    cfg.U = std::max(1, std::min(tune("STREAM_U", 2), 64 / (std::max(nine, 1) * cfg.C)));
+    cfg.minb = tune("STREAM_MINB", 4);
     std::ostringstream key;
-    key << "stream|" << RO << "|" << cfg.C << "|" << cfg.U << "|";
+    key << "stream|" << RO << "|" << cfg.C << "|" << cfg.U << "|" << cfg.minb << "|";
     for (int m : cfg.mode) key << m;
     key << "|" << prog.signature();
-    const JitKernel& k = dev.kernel(key.str(), [&] { return stream_source(prog, cfg); });
+    const JitKernel& k = dev.kernel(key.str(), "wgf_stream_reduce", [&] { return stream_source(prog, cfg); });
+    // one wave of CTAs: every resident slot of the machine gets one share of the rows
+    const int64_t nch = (H + cfg.C - 1) / cfg.C;
+    const int64_t per_cta = 256ll * cfg.U;
+    const int64_t slots = (int64_t)dev.sm_count * dev.max_blocks_per_sm(k, 256);
+    int64_t max_split = std::max<int64_t>(1, (nch + per_cta - 1) / per_cta);
+    int64_t split = std::max<int64_t>(1, slots * tune("STREAM_WAVES", 1) / rows);
+    split = std::min<int64_t>({split, max_split, 2048});
+    if (rows > Device::kCounters) split = 1;
     BufferRef partials;
     if (split > 1)
         partials = dev.alloc((size_t)(rows * split * std::max(prog.n_reduces(), 1)) * sizeof(float), false);

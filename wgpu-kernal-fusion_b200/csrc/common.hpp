@@ -78,6 +78,7 @@ struct Layout {
     bool is_contiguous() const { return offset == 0 && is_dense(); }
     // True if two different indices can address the same element (src/layout.rs:86-90).
     bool allocation_overlaps() const {
+        if (numel() == 0) return false;
         for (int i = 0; i < rank(); ++i)
             if (strides[i] == 0 && shape[i] > 1) return true;
         return false;

@@ -229,7 +229,7 @@ DEV void offsets(const Params& p, u64 e, i64* off) {
 #endif
 }
 
-extern "C" __global__ void __launch_bounds__(256) wgf_kernel(const __grid_constant__ Params p) {
+extern "C" __global__ void __launch_bounds__(256) wgf_elementwise(const __grid_constant__ Params p) {
     const u64 nchunks = (p.n + C - 1) / C;
     const u64 chunk0 = (u64)blockIdx.x * (256 * U) + threadIdx.x;
     float x[U][NIN][C];
@@ -264,7 +264,11 @@ extern "C" __global__ void __launch_bounds__(256) wgf_kernel(const __grid_consta
 // ---------------------------------------------------------------------------------------
 // Row template: index space [outer..., H]; GROUP threads share a row, RPC rows per CTA;
 // each thread keeps EPT = NCH*C elements of the row in registers across all reductions.
-// Defines expected: RO NIN C NCH GROUP RPC NRED NIMM and macro ROW_BODY.
+// CTAs are persistent: each walks rows blockIdx.x*RPC + g, + gridDim.x*RPC, ... and loads
+// the next row's inputs before it reduces the current one, so HBM requests stay in flight
+// during the barrier phases.  Inputs that do not depend on the row are loaded once.
+// Defines expected: RO NIN C NCH GROUP RPC NRED NIMM MINB; text markers ROW_INVARIANT,
+// ROW_NEXT_DECL, ROW_PREFETCH, ROW_TAKE, ROW_BODY are replaced by generated code.
 // ---------------------------------------------------------------------------------------
 static const char* const JIT_ROW_KERNEL = R"CUDA(
 #define THREADS (GROUP * RPC)
@@ -282,14 +286,7 @@ struct Params {
     float imm[NIMM > 0 ? NIMM : 1];
 };
 
-extern "C" __global__ void __launch_bounds__(THREADS) wgf_kernel(const __grid_constant__ Params p) {
-#if GROUP > 32 && NRED > 0
-    __shared__ float red_smem[NRED][RPC][GROUP / 32];
-#endif
-    const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
-    const u64 row = (u64)blockIdx.x * RPC + g;
-    const bool rv = row < p.rows;
-    i64 roff[NIN + 1];
+DEV void row_offsets(const Params& p, u64 row, bool rv, i64* roff) {
 #pragma unroll
     for (int s = 0; s <= NIN; ++s) roff[s] = 0;
     if (rv) {
@@ -305,20 +302,53 @@ extern "C" __global__ void __launch_bounds__(THREADS) wgf_kernel(const __grid_co
 #pragma unroll
         for (int s = 0; s <= NIN; ++s) roff[s] += (i64)rem * p.rstride[s * RO];
     }
-    bool kv[NCH];
-#pragma unroll
-    for (int k = 0; k < NCH; ++k) kv[k] = rv && (u32)((k * GROUP + t) * C) < p.H;
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __grid_constant__ Params p) {
+#if GROUP > 32 && NRED > 0
+    __shared__ float red_smem[NRED][RPC][GROUP / 32];
+#endif
+    const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
     const float* imm = p.imm;
-    ROW_BODY
+    bool cv[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) cv[k] = (u32)((k * GROUP + t) * C) < p.H;
+    ROW_INVARIANT
+    const u64 row_step = (u64)gridDim.x * RPC;
+    u64 row0 = (u64)blockIdx.x * RPC;   // first row of this CTA in the current iteration
+    u64 row = row0 + g;
+    bool rv = row < p.rows;
+    i64 roff[NIN + 1];
+    row_offsets(p, row, rv, roff);
+    ROW_NEXT_DECL
+    ROW_PREFETCH
+    while (row0 < p.rows) {
+        const bool crv = rv;
+        i64 coff[NIN + 1];
+#pragma unroll
+        for (int s = 0; s <= NIN; ++s) coff[s] = roff[s];
+        bool kv[NCH];
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) kv[k] = crv && cv[k];
+        ROW_TAKE
+        row0 += row_step;
+        row += row_step;
+        rv = row < p.rows;
+        row_offsets(p, row, rv, roff);
+        ROW_PREFETCH
+        ROW_BODY
+    }
 }
 )CUDA";
 
 // ---------------------------------------------------------------------------------------
 // Streaming reduce template: single-phase programs with a Row result, any row length.
-// A row is split over SPLIT CTAs (p.split); partials go to scratch and the last CTA to
+// A row is split over p.split CTAs; each CTA streams its share with the next tile's loads
+// issued before the current tile is reduced; partials go to scratch and the last CTA to
 // arrive for a row combines them in a fixed order, runs the row phase and stores.
-// Defines expected: RO NIN NINE C U NRED NIMM, macros STREAM_PRE, STREAM_LOAD(u),
-// STREAM_POST and function elem_phase(x, rowv, imm, nvalid, acc).
+// Defines expected: RO NIN NINE C U NRED NIMM MINB, macros STREAM_PRE, STREAM_INIT,
+// STREAM_LOAD(COL, NV, X), STREAM_COMBINE_PARTIAL(PP), STREAM_BLOCK_REDUCE, STREAM_POST and
+// function elem_phase(x, rowv, imm, nvalid, acc).
 // ---------------------------------------------------------------------------------------
 static const char* const JIT_STREAM_KERNEL = R"CUDA(
 #define THREADS 256
@@ -338,7 +368,23 @@ struct Params {
     float imm[NIMM > 0 ? NIMM : 1];
 };
 
-extern "C" __global__ void __launch_bounds__(THREADS) wgf_kernel(const __grid_constant__ Params p) {
+typedef float Tile[U][NINE > 0 ? NINE : 1][C];
+
+DEV void load_tile(const Params& p, const i64* roff, u64 base, u64 nch, int t, Tile& x, int* nval) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const u64 chunk = base + (u64)u * THREADS + t;
+        nval[u] = 0;
+        if (chunk < nch) {
+            const u64 col = chunk * C;
+            const u64 left = p.H - col;
+            nval[u] = left < (u64)C ? (int)left : C;
+            STREAM_LOAD(col, nval[u], x[u])
+        }
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(const __grid_constant__ Params p) {
     __shared__ float red_smem[NRED][THREADS / 32];
     __shared__ u32 is_last;
     const int t = threadIdx.x;
@@ -361,27 +407,27 @@ extern "C" __global__ void __launch_bounds__(THREADS) wgf_kernel(const __grid_co
         for (int s = 0; s <= NIN; ++s) roff[s] += (i64)rem * p.rstride[s * RO];
     }
     const float* imm = p.imm;
-    const bool rv = true;
     STREAM_PRE
     float acc[NRED];
     STREAM_INIT
     const u64 nch = (p.H + C - 1) / C;
-    for (u64 base = (u64)sp * (THREADS * U); base < nch; base += (u64)p.split * (THREADS * U)) {
-        float x[U][NINE > 0 ? NINE : 1][C];
-        int nval[U];
+    const u64 step = (u64)p.split * (THREADS * U);
+    u64 base = (u64)sp * (THREADS * U);
+    Tile xa, xb;
+    int na[U], nb[U];
+    if (base < nch) load_tile(p, roff, base, nch, t, xa, na);
+    while (base < nch) {
+        // ping: fetch the next tile into b, reduce a
+        if (base + step < nch) load_tile(p, roff, base + step, nch, t, xb, nb);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const u64 chunk = base + (u64)u * THREADS + t;
-            nval[u] = 0;
-            if (chunk < nch) {
-                const u64 col = chunk * C;
-                const u64 left = p.H - col;
-                nval[u] = left < (u64)C ? (int)left : C;
-                STREAM_LOAD(col, nval[u], x[u])
-            }
-        }
+        for (int u = 0; u < U; ++u) elem_phase(xa[u], rowv, imm, na[u], acc);
+        base += step;
+        if (base >= nch) break;
+        // pong: fetch into a, reduce b
+        if (base + step < nch) load_tile(p, roff, base + step, nch, t, xa, na);
 #pragma unroll
-        for (int u = 0; u < U; ++u) elem_phase(x[u], rowv, imm, nval[u], acc);
+        for (int u = 0; u < U; ++u) elem_phase(xb[u], rowv, imm, nb[u], acc);
+        base += step;
     }
     STREAM_BLOCK_REDUCE
     if (p.split > 1) {

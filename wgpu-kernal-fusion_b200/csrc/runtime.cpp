@@ -32,6 +32,8 @@ const DriverApi& DriverApi::get() {
         a.FuncSetAttribute = (decltype(a.FuncSetAttribute))driver_symbol("cuFuncSetAttribute");
         a.FuncGetAttribute = (decltype(a.FuncGetAttribute))driver_symbol("cuFuncGetAttribute");
         a.GetErrorString = (decltype(a.GetErrorString))driver_symbol("cuGetErrorString");
+        a.OccupancyMaxActiveBlocksPerMultiprocessor = (decltype(a.OccupancyMaxActiveBlocksPerMultiprocessor))driver_symbol(
+            "cuOccupancyMaxActiveBlocksPerMultiprocessor");
         a.TensorMapEncodeTiled = driver_symbol("cuTensorMapEncodeTiled");
         return a;
     }();
@@ -129,9 +131,17 @@ std::vector<char> compile_to_cubin(const std::string& source, const std::string&
     int r = n.CreateProgram(&prog, source.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr);
     if (r != 0) fail(WGF_ERR_COMPILE, std::string("nvrtcCreateProgram: ") + n.GetErrorString(r));
     // --fmad=false: every op of a fused chain rounds on its own, as separate shader functions do.
+    const bool verbose = getenv("WGF_JIT_VERBOSE") != nullptr;  // print registers / spills per kernel
     const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17",
-                          "-default-device", "--extra-device-vectorization"};
-    r = n.CompileProgram(prog, 5, opts);
+                          "-default-device", "--extra-device-vectorization", "--ptxas-options=-v"};
+    r = n.CompileProgram(prog, verbose ? 6 : 5, opts);
+    if (verbose && r == 0) {
+        size_t ls = 0;
+        n.GetProgramLogSize(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) n.GetProgramLog(prog, &log[0]);
+        fprintf(stderr, "[wgf jit] %s", log.c_str());
+    }
     if (r != 0) {
         size_t ls = 0;
         n.GetProgramLogSize(prog, &ls);
@@ -348,7 +358,7 @@ void Device::recycle(cudaEvent_t e) {
     event_pool_.push_back(e);
 }
 
-const JitKernel& Device::kernel(const std::string& key, const std::function<std::string()>& source) {
+const JitKernel& Device::kernel(const std::string& key, const char* entry, const std::function<std::string()>& source) {
     {
         std::lock_guard<std::mutex> g(mu_);
         auto it = kernels_.find(key);
@@ -356,7 +366,7 @@ const JitKernel& Device::kernel(const std::string& key, const std::function<std:
     }
     make_current();
     std::string src = source();
-    std::vector<char> cubin = compile_to_cubin(src, "wgf_kernel");
+    std::vector<char> cubin = compile_to_cubin(src, entry);
     compiles++;
     if (dry) {
         std::lock_guard<std::mutex> g(mu_);
@@ -365,12 +375,20 @@ const JitKernel& Device::kernel(const std::string& key, const std::function<std:
     const DriverApi& api = DriverApi::get();
     JitKernel k;
     cu_check(api.ModuleLoadData(&k.module, cubin.data()), "cuModuleLoadData");
-    cu_check(api.ModuleGetFunction(&k.fn, k.module, "wgf_kernel"), "cuModuleGetFunction");
+    cu_check(api.ModuleGetFunction(&k.fn, k.module, entry), "cuModuleGetFunction");
     api.FuncGetAttribute(&k.regs, CU_FUNC_ATTRIBUTE_NUM_REGS, k.fn);
     std::lock_guard<std::mutex> g(mu_);
     auto ins = kernels_.emplace(key, k);
     if (!ins.second) api.ModuleUnload(k.module);  // another thread won the race
     return ins.first->second;
+}
+
+int Device::max_blocks_per_sm(const JitKernel& k, int threads) {
+    if (dry || !k.fn) return std::max(1, 2048 / threads);
+    int n = 0;
+    CUresult r = DriverApi::get().OccupancyMaxActiveBlocksPerMultiprocessor(&n, k.fn, threads, 0);
+    if (r != CUDA_SUCCESS || n < 1) n = 1;
+    return n;
 }
 
 void Device::begin_launch(const char* what) {

@@ -87,11 +87,13 @@ struct Device : std::enable_shared_from_this<Device> {
 
     // ---- kernels ----
     // Looks `key` up in the cache; on a miss calls `source()` and compiles it.  The kernel
-    // entry point must be `extern "C" __global__ void wgf_kernel(Params)`.
-    const JitKernel& kernel(const std::string& key, const std::function<std::string()>& source);
+    // `entry` names the `extern "C" __global__` function in that source.
+    const JitKernel& kernel(const std::string& key, const char* entry, const std::function<std::string()>& source);
     // Launch a run-time compiled kernel taking ONE by-value struct parameter.
     void launch(const JitKernel& k, dim3 grid, dim3 block, size_t smem, const void* params,
                 const char* what);
+    // Resident CTAs per SM for this kernel at the given block size (no dynamic shared memory).
+    int max_blocks_per_sm(const JitKernel& k, int threads);
     // Book-keeping for kernels launched with <<<>>> from this library's own .cu files.
     void begin_launch(const char* what);
     void end_launch();
@@ -127,6 +129,7 @@ struct DriverApi {
     CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
     CUresult (*FuncGetAttribute)(int*, CUfunction_attribute, CUfunction) = nullptr;
     CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
     void* TensorMapEncodeTiled = nullptr;
     static const DriverApi& get();
 };
