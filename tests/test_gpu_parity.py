@@ -147,7 +147,9 @@ def test_config3_pairwise_broadcast(wgf, dev, orc):
     np.testing.assert_array_equal(got_t, np.ascontiguousarray(got.transpose(1, 0, 2)))
     # inner-axis transpose: exercises the strided load path
     got_i = ((ta.transpose(1, 2) * 1.5).silu()).as_slice()
-    assert_ulp(orc, got_i, (ra.transpose(1, 2) * 1.5).silu().numpy())
+    # silu is five ops deep (mul, neg, exp, add, div); each is within 2 ulp on its own inputs and
+    # the 1-ulp difference of exp carries through the add and the division
+    assert_ulp(orc, got_i, (ra.transpose(1, 2) * 1.5).silu().numpy(), 4)
     # size-1 expansion form of the same broadcast
     got_e = ((ta * 1.5).silu() + tb.reshape((1, B, H)).expand((A, B, H)) * tc.reshape((A, 1, H)).expand((A, B, H))).as_slice()
     np.testing.assert_array_equal(got_e, got)

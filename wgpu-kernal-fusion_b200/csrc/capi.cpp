@@ -146,6 +146,10 @@ void timed(Device& dev, uint64_t* elapsed_ns, F&& f) {
 
 }  // namespace
 
+namespace wgf {
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+}  // namespace wgf
+
 extern "C" {
 
 const char* wgf_last_error(void) { return g_last_error.c_str(); }

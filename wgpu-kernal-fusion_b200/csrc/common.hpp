@@ -21,6 +21,9 @@ struct Error : std::exception {
 
 [[noreturn]] inline void fail(int code, const std::string& msg) { throw Error(code, msg); }
 
+// Sets the calling thread's message returned by wgf_last_error() (defined in capi.cpp).
+void set_last_error(const std::string& msg);
+
 #define WGF_CHECK(cond, code, msg)                                   \
     do {                                                             \
         if (!(cond)) ::wgf::fail((code), std::string(msg));          \
