@@ -262,6 +262,25 @@ int32_t wgf_comm_release(wgf_comm* comm);
  * queued on the device stream directly behind the kernel that produces `t`. */
 int32_t wgf_tensor_all_reduce(wgf_tensor* t, wgf_comm* comm, uint32_t opcode, wgf_tensor** out);
 
+/* ======================================================================================
+ * Reduction for callers that must not allocate.  (No counterpart in the crate: this entry
+ * point exists for hosts of THIS library that cannot let a compute call reach the device
+ * allocator -- code running inside a CUDA stream capture, real-time loops that rule out calls
+ * of unbounded latency, embedders with a device-memory budget fixed up front.)
+ *
+ * out[0] = reduce(pre(x[0..n))): x, out are DEVICE pointers owned by the caller, n <=
+ * 2^31 f32 elements (more is rejected with WGF_ERR_UNSUPPORTED); `pre_opcode` is WGF_OP_EXP,
+ * WGF_OP_SQR, WGF_OP_ABS or 0xFFFFFFFF for none; `reduce_opcode` is WGF_OP_SUM/MAX/MIN/PRODUCT;
+ * `cuda_stream` is a cudaStream_t (NULL = default stream) the work is queued on.
+ * Scratch (per-CTA partials and a ticket) is a fixed 16 KiB array inside the library image:
+ * each GPU that loads the library holds it until the process ends; all calls on a GPU share
+ * it, so calls that could overlap on the GPU race -- order them on one stream.  The first
+ * call on each GPU resolves the array's device address; issue it outside stream capture.
+ * Calls no cudaMalloc/cudaFree.
+ * ==================================================================================== */
+int32_t wgf_full_reduce_f32_noalloc(const float* x, uint64_t n, uint32_t pre_opcode,
+                                    uint32_t reduce_opcode, float* out, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
