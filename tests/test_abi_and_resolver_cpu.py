@@ -1,0 +1,181 @@
+"""CPU-only checks: the C ABI library loads and exports everything include/wgf.h declares; the
+graph, the fusion resolver and the generated kernels are exercised on the compile-only device
+(ordinal -1: every kernel is generated and compiled for sm_100a, nothing is executed)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "wgf.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(wgf_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(wgf):
+    lib = wgf.lib()
+    names = declared_functions()
+    assert len(names) >= 60
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, f"declared in wgf.h but not exported: {missing}"
+    assert lib.wgf_abi_version() == 1
+
+
+def test_no_gpu_means_error_not_fallback(wgf):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(wgf.WgfError) as e:
+        wgf.Device(0)
+    assert e.value.status == "CUDA"
+
+
+def test_compile_only_device_refuses_download(wgf, drydev):
+    t = drydev.tensor(np.ones((4, 4), np.float32)) + 1.0
+    t.materialize()
+    with pytest.raises(wgf.WgfError):
+        t.as_slice()
+
+
+def launches(dev, build):
+    before = dev.launch_count
+    t = build()
+    t.materialize()
+    return dev.launch_count - before
+
+
+def test_fusion_decisions(wgf, drydev):
+    d = drydev
+    x = d.tensor(np.zeros((64, 512), np.float32))
+    w = d.tensor(np.zeros((512,), np.float32))
+    y = d.tensor(np.zeros((64, 512), np.float32))
+    # chains and DAGs of element-wise / pair-wise nodes: one kernel (src/compute_graph/resolve.rs:63-136)
+    assert launches(d, lambda: (x + 1.0) * 2.0) == 1
+    assert launches(d, lambda: (x + 1.0) + (y * 2.0)) == 1
+    assert launches(d, lambda: ((x * 2.0 + 1.0).sin().cos() * 0.5) + (-(x * x)).exp()) == 1
+    assert launches(d, lambda: (x + y) * (x - y) / (y + 3.0)) == 1         # pair-wise of pair-wise
+    # reduce with prologue and epilogue (resolve.rs:164-196)
+    assert launches(d, lambda: (x + 1.0).sum(1) + 1.0) == 1
+    assert launches(d, lambda: (x + 1.0).sum(0) * 2.0) == 1
+    # reduce -> broadcast -> pair-wise patterns: one row kernel
+    assert launches(d, lambda: x.layer_norm(w, 1e-5)) == 1
+    assert launches(d, lambda: x.softmax_last_dim()) == 1
+    assert launches(d, lambda: x.layer_norm(w, 1e-5).softmax_last_dim()) == 1
+    # same-op reduce chain over all axes folds into one full reduction
+    assert launches(d, lambda: x.exp().sum(0).sum(0)) == 1
+    assert launches(d, lambda: x.max(1).max(0)) == 1
+    # different ops do not fold
+    assert launches(d, lambda: x.max(1).sum(0)) == 2
+    # matmul, resize, slice_assign never fuse (resolve.rs:138-154, 210-244)
+    assert launches(d, lambda: (x.mat_mul(y.transpose(0, 1)) + 1.0)) == 2
+    # views are free
+    assert launches(d, lambda: x.transpose(0, 1).slice([(0, 100), (3, 60)]) + 1.0) == 1
+    # a reshape of row-major data is a view; of a transposed view it is one gather
+    assert launches(d, lambda: x.reshape((128, 256))) == 0
+    assert launches(d, lambda: x.transpose(0, 1).reshape((128, 256))) == 1
+
+
+def test_memoisation_and_graph_growth(wgf, drydev):
+    d = drydev
+    x = d.tensor(np.zeros((32, 32), np.float32))
+    e = x.exp()
+    e.materialize()
+    before = d.launch_count
+    (e + 1.0).materialize()
+    (e * 2.0).materialize()
+    assert d.launch_count - before == 2          # e is not recomputed (the crate would re-run it)
+    # nodes die with their handles: the graph does not grow without bound
+    n0 = x.graph_size()
+    for _ in range(50):
+        t = (x + 1.0).sum(0)
+        t.materialize()
+        del t
+    assert x.graph_size() <= n0 + 2
+
+
+def test_kernel_cache_reuses_by_signature(wgf, drydev):
+    d = drydev
+    x = d.tensor(np.zeros((16, 128), np.float32))
+    (x * 3.0 + 7.0).materialize()
+    c0 = d.compile_count
+    (x * 5.0 + 9.0).materialize()                # other constants: same kernel (constants are parameters)
+    y = d.tensor(np.zeros((32, 128), np.float32))
+    (y * 5.0 + 9.0).materialize()                # other size: same kernel
+    assert d.compile_count == c0
+    (x * 5.0 - 9.0).materialize()                # other op: new kernel
+    assert d.compile_count == c0 + 1
+
+
+def test_shape_and_dtype_errors(wgf, drydev):
+    d = drydev
+    a = d.tensor(np.zeros((2, 3), np.float32))
+    b = d.tensor(np.zeros((3, 2), np.float32))
+    h = d.tensor(np.zeros((2, 3), np.float16))
+    for f, status in [(lambda: a + b, "SHAPE"), (lambda: a + h, "DTYPE"), (lambda: a.mat_mul(a), "SHAPE"),
+                      (lambda: a.sum(2), "INVALID_ARGUMENT"), (lambda: a.narrow(1, 2, 5), "SHAPE"),
+                      (lambda: a.reshape((7,)), "SHAPE"), (lambda: a.resize((1, 3)), "SHAPE"),
+                      (lambda: a.broadcast((2, 3)), "RANK"), (lambda: a.slice([(0, 3), (0, 3)]), "SHAPE"),
+                      (lambda: a.unary(wgf.OP_ADD), "INVALID_ARGUMENT"), (lambda: a.softmax(), "RANK"),
+                      (lambda: wgf.Tensor.cat([a, b], 0), "SHAPE")]:
+        with pytest.raises(wgf.WgfError) as e:
+            f()
+        assert e.value.status == status, (e.value, status)
+
+
+def test_views_shapes(wgf, drydev):
+    d = drydev
+    a = d.tensor(np.zeros((2, 3, 4), np.float32))
+    assert a.transpose(0, 2).shape == (4, 3, 2)
+    assert a.slice([(0, 1), (1, 3), (0, 4)]).shape == (1, 2, 4)
+    assert a.sum(1).shape == (2, 4)
+    assert a.sum(0).sum(0).sum(0).shape == ()
+    assert a.unsqueeze(1).shape == (2, 1, 3, 4)
+    assert a.resize((3, 3, 5)).shape == (3, 3, 5)
+    assert wgf.Tensor.cat([a, a], 2).shape == (2, 3, 8)
+    # broadcast puts the new axis where the common prefix of the shapes ends (src/map_layout.rs:73-77)
+    m = d.tensor(np.zeros((2, 2), np.float32))
+    assert m.broadcast((2, 2, 3)).shape == (2, 2, 3)
+    v = d.tensor(np.zeros((4,), np.float32))
+    assert v.broadcast((5, 4)).shape == (5, 4)
+    assert v.broadcast_axis(1, 7).shape == (4, 7)
+    assert d.arange(0.0, 10.0, 2.0).shape == (5,)
+    assert d.arange(5.0, 0.0, -1.0).shape == (5,)
+    assert "digraph" in (a + 1.0).graphvis()
+
+
+def test_shard_range(wgf):
+    for n in (0, 1, 7, 8, 8192, 8193):
+        for world in (1, 2, 3, 8):
+            covered = []
+            for r in range(world):
+                b, e = wgf.shard_range(n, world, r)
+                assert 0 <= b <= e <= n
+                covered += list(range(b, e))
+                assert (e - b) in (n // world, n // world + 1)
+            assert covered == list(range(n))
+
+
+def test_generated_kernels_compile_for_every_layout_class(wgf, drydev):
+    """Vector / scalar / broadcast / strided operand modes, ranks 1-4, 16-bit types, long rows."""
+    d = drydev
+    rng = np.random.default_rng(0)
+    for shape in [(7,), (1000,), (3, 5), (8, 256), (5, 7, 9), (4, 8, 16), (2, 3, 4, 5)]:
+        x = d.tensor(rng.standard_normal(shape).astype(np.float32))
+        ((x * 2.0).tanh() + x).materialize()
+        for ax in range(len(shape)):
+            (x.exp().sum(ax) + 1.0).materialize()
+            x.max(ax).materialize()
+        if len(shape) >= 2:
+            (x.transpose(0, len(shape) - 1) * 2.0).materialize()
+            x.softmax_last_dim().materialize()
+        h = x.cast(wgf.F16)
+        (h * 2.0 + h).sum(len(shape) - 1).materialize()
+        (x.cast(wgf.BF16).cast(wgf.F32) + 1.0).materialize()
+    big = d.tensor(np.zeros((2, 20000), np.float32))
+    big.softmax_last_dim().materialize()
+    d.tensor(np.zeros((3, 100000), np.float32)).sum(1).materialize()

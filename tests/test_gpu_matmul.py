@@ -1,0 +1,142 @@
+"""MatMul family vs the mathematical definition (double accumulation): f32 within 1e-4, f16 / bf16
+within 1e-2, both norm-wise (max |got - ref| / max |ref|).  The crate's own kernel is only right up
+to 8x8 (src/matmul.rs:31-39, 131-141) and ignores strides, so its output is not the oracle here."""
+import numpy as np
+import pytest
+
+from conftest import seeded
+
+pytestmark = pytest.mark.gpu
+
+
+def normwise(got, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.max(np.abs(np.asarray(got, dtype=np.float64) - ref)) / max(np.max(np.abs(ref)), 1e-30))
+
+
+def bf16_round(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return u.astype(np.uint16)
+
+
+def bf16_to_f32(u):
+    return (u.astype(np.uint32) << 16).view(np.float32)
+
+
+def make(dev, wgf, a, kind):
+    if kind == "f32":
+        return dev.tensor(a.astype(np.float32)), a.astype(np.float32).astype(np.float64)
+    if kind == "f16":
+        h = a.astype(np.float16)
+        return dev.tensor(h), h.astype(np.float64)
+    u = bf16_round(a)
+    return dev.tensor(u, dtype=wgf.BF16), bf16_to_f32(u).astype(np.float64)
+
+
+def result(t, kind):
+    out = t.as_slice()
+    return bf16_to_f32(out) if kind == "bf16" else out
+
+
+TOL = {"f32": 1e-4, "f16": 1e-2, "bf16": 1e-2}
+
+SHAPES = [(1, 1, 1), (3, 5, 7), (8, 8, 8), (9, 9, 9), (37, 50, 21), (64, 64, 64), (100, 100, 100), (128, 256, 64),
+          (129, 257, 72), (256, 512, 128), (300, 520, 200), (512, 1024, 256), (1024, 128, 1024)]
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_matmul_row_major(shape, kind, wgf, dev):
+    M, N, K = shape
+    g = seeded(4, 1)
+    a = (g.random((M, K)) * 2 - 1)
+    b = (g.random((K, N)) * 2 - 1)
+    ta, ra = make(dev, wgf, a, kind)
+    tb, rb = make(dev, wgf, b, kind)
+    got = result(ta.mat_mul(tb), kind)
+    assert got.shape == (M, N)
+    assert normwise(got, ra @ rb) <= TOL[kind]
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("shape", [(5, 6, 7), (128, 256, 64), (200, 392, 136), (512, 512, 512)])
+def test_matmul_transposed_and_sliced_operands(shape, kind, wgf, dev):
+    """Strides and offsets are honoured (the crate reads operands as if contiguous, src/matmul.rs:96-117)."""
+    M, N, K = shape
+    g = seeded(4, 2)
+    a = g.random((M, K)) * 2 - 1
+    bt = g.random((N, K)) * 2 - 1            # B given as its transpose: b = bt^T
+    ta, ra = make(dev, wgf, a, kind)
+    tbt, rbt = make(dev, wgf, bt, kind)
+    got = result(ta.mat_mul(tbt.transpose(0, 1)), kind)
+    assert normwise(got, ra @ rbt.T) <= TOL[kind]
+    at = np.ascontiguousarray(a.T)
+    tat, rat = make(dev, wgf, at, kind)
+    got = result(tat.transpose(0, 1).mat_mul(tbt.transpose(0, 1)), kind)   # A column-major
+    assert normwise(got, rat.T @ rbt.T) <= TOL[kind]
+    if M > 8 and K > 16:
+        sa = ta.slice([(3, M - 1), (8, K)])                                   # offset view of A
+        sb = tbt.transpose(0, 1).slice([(8, K), (0, N)])
+        got = result(sa.mat_mul(sb), kind)
+        assert normwise(got, ra[3:M - 1, 8:] @ rbt.T[8:, :]) <= TOL[kind]
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+def test_matmul_batched(kind, wgf, dev):
+    g = seeded(4, 3)
+    for (B, M, K, N) in [(3, 5, 7, 4), (4, 128, 64, 256), (5, 96, 40, 72)]:
+        a = g.random((B, M, K)) * 2 - 1
+        b = g.random((B, K, N)) * 2 - 1
+        ta, ra = make(dev, wgf, a, kind)
+        tb, rb = make(dev, wgf, b, kind)
+        got = result(ta.mat_mul(tb), kind)
+        assert got.shape == (B, M, N)
+        assert normwise(got, ra @ rb) <= TOL[kind]
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 3])
+def test_skinny_gemv(m, kind, wgf, dev):
+    g = seeded(4, 4)
+    K, N = 1024, 2752
+    a = g.random((m, K)) * 2 - 1
+    b = g.random((K, N)) * 2 - 1
+    ta, ra = make(dev, wgf, a, kind)
+    tb, rb = make(dev, wgf, b, kind)
+    assert normwise(result(ta.mat_mul(tb), kind), ra @ rb) <= TOL[kind]
+    bt = np.ascontiguousarray(b.T)
+    tbt, rbt = make(dev, wgf, bt, kind)
+    assert normwise(result(ta.mat_mul(tbt.transpose(0, 1)), kind), ra @ rbt.T) <= TOL[kind]
+
+
+def test_config4_full_sizes(wgf, dev):
+    """BASELINE sizes; checked on sampled rows against float64 (size-independent: any row is as good as another)."""
+    g = seeded(4, 0)
+    n = 4096
+    a = (g.random((n, n), dtype=np.float32) * 2 - 1)
+    b = (g.random((n, n), dtype=np.float32) * 2 - 1)
+    rows = [0, 1, 127, 128, 2047, 4095]
+    for kind in ("f32", "f16"):
+        ta, ra = make(dev, wgf, a, kind)
+        tb, rb = make(dev, wgf, b, kind)
+        got = result(ta.mat_mul(tb), kind)
+        ref = ra[rows] @ rb
+        assert normwise(got[rows], ref) <= TOL[kind]
+        # linearity: (2A)B == 2(AB) exactly in binary floating point
+        got2 = result((ta * 2.0).mat_mul(tb), kind)
+        np.testing.assert_array_equal(got2[rows], got[rows] * 2)
+    # batched f16 [32,1024,128] x [32,128,1024]
+    a3 = (g.random((32, 1024, 128), dtype=np.float32) * 2 - 1)
+    b3 = (g.random((32, 128, 1024), dtype=np.float32) * 2 - 1)
+    ta, ra = make(dev, wgf, a3, "f16")
+    tb, rb = make(dev, wgf, b3, "f16")
+    got = result(ta.mat_mul(tb), "f16")
+    for z in (0, 17, 31):
+        assert normwise(got[z], ra[z] @ rb[z]) <= 1e-2
+    # decode GEMV f16 [1,4096] x [4096,11008]
+    x = (g.random((1, 4096), dtype=np.float32) * 2 - 1)
+    w = (g.random((4096, 11008), dtype=np.float32) * 2 - 1)
+    tx, rx = make(dev, wgf, x, "f16")
+    tw, rw = make(dev, wgf, w, "f16")
+    assert normwise(result(tx.mat_mul(tw), "f16"), rx @ rw) <= 1e-2

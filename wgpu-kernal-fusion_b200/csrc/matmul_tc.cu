@@ -1,0 +1,424 @@
+// f16 / bf16 matmul on the 5th-generation tensor cores (sm_100a): tcgen05.mma with the
+// accumulator in tensor memory (TMEM), operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast), fp32 accumulation, one rounding.
+// Replaces the crate's scalar shared-memory kernel (src/matmul.rs:56-155) for 16-bit types.
+//
+// One persistent CTA per SM walks output tiles of 128 x 256.  Warp roles:
+//   warp 0      TMA producer   (one lane): fills a 4-stage ring of {A 128x64, B 256x64} k-blocks
+//   warp 1      MMA issuer     (one lane): 4 x tcgen05.mma (K = 16) per k-block into one of two
+//                               TMEM accumulators (2 x 256 columns = all 512 columns of the SM)
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (32 lanes x 32 columns per load),
+//                               convert, store to global; overlaps the next tile's main loop
+// Synchronisation is by mbarriers only; every wait is bounded and reports through an error
+// word instead of hanging.
+//
+// Layouts: A is [M,K] row-major (K-major).  B is either [N,K] row-major (a transposed view:
+// K-major) or [K,N] row-major (N-major); both go straight from global memory through TMA.
+// M, N, K need not divide the tile: TMA zero-fills out-of-range reads, stores are guarded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "matmul.hpp"
+
+namespace wgf {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;            // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int TC_THREADS = 192;
+constexpr unsigned SPIN_LIMIT = 1u << 22;             // bounded waits: ~seconds, then give up
+
+struct TcParams {
+    long long M, N, K, batch;
+    long long c_rs, c_bs;
+    int tiles_m, tiles_n;
+    int b_is_kn;       // 1: B stored [K,N] (N-major), 0: B stored [N,K] (K-major)
+    int is_bf16;
+    unsigned* error;   // device word: 0 = ok, else code of the wait that gave up
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Waits for the phase with the given parity; false if it did not complete within the bound.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    unsigned long long start = 0;
+    for (unsigned spin = 0; spin < SPIN_LIMIT; ++spin) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        // besides the iteration limit, never wait longer than two seconds of wall time
+        if ((spin & 63) == 63) {
+            const unsigned long long now = global_ns();
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) return false;
+        }
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                         unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier gets one arrival once every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(unsigned taddr, unsigned* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (64 bit): start address >> 4 in bits 0-13, leading byte
+// offset >> 4 in 16-29, stride byte offset >> 4 in 32-45, descriptor version 1 in 46-47,
+// layout type in 61-63 (2 = 128-byte swizzle).
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulator (bits 4-5 = 1), A/B format in bits
+// 7-9 / 10-12 (0 = f16, 1 = bf16), A/B major in bits 15 / 16 (0 = K-major, 1 = MN-major),
+// N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr unsigned instr_desc(bool bf16, bool b_mn_major) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+
+template <typename T> __device__ __forceinline__ unsigned pack2(float lo, float hi);
+template <> __device__ __forceinline__ unsigned pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&h);
+}
+template <> __device__ __forceinline__ unsigned pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&h);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, T* __restrict__ C,
+                 const __grid_constant__ TcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // stage buffers need 1024-byte alignment for the 128-byte swizzle atoms
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+    // bars[0..3] full, [4..7] empty, [8..9] accumulator full, [10..11] accumulator empty
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 12);
+    const unsigned bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 4);   // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+    const long long total_tiles = tiles_per_batch * p.batch;
+    const int k_blocks = (int)((p.K + BK - 1) / BK);
+    const unsigned smem_base = smem_u32(smem);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 1;   // a fresh "empty" barrier counts as already released
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int b = (int)(tile / tiles_per_batch);
+                const int r = (int)(tile % tiles_per_batch);
+                const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase)) {
+                        atomicExch(p.error, 1u);
+                        ok = false;
+                        break;
+                    }
+                    const unsigned sa = smem_base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    tma_load_3d(sa, &map_a, full_bar(stage), kb * BK, m0, b);
+                    if (p.b_is_kn) {
+                        // [K,N] storage: four boxes of 64 k-rows x 64 n (one 128-byte swizzle span each)
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_3d(sb + j * (BK * 128), &map_b, full_bar(stage), n0 + j * 64, kb * BK, b);
+                    } else {
+                        tma_load_3d(sb, &map_b, full_bar(stage), kb * BK, n0, b);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const unsigned idesc = p.b_is_kn ? instr_desc(false, true) | ((unsigned)p.is_bf16 << 7) | ((unsigned)p.is_bf16 << 10)
+                                             : instr_desc(false, false) | ((unsigned)p.is_bf16 << 7) | ((unsigned)p.is_bf16 << 10);
+            int stage = 0;
+            unsigned phase = 0;
+            int acc = 0;
+            unsigned acc_phase = 1;   // both accumulators start out free
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase)) {
+                    atomicExch(p.error, 2u);
+                    break;
+                }
+                tc_fence_after();
+                const unsigned tmem_d = tmem_base + (unsigned)acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) {
+                        atomicExch(p.error, 3u);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const unsigned sa = smem_base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // A, K-major: rows of 128 bytes, 8-row groups 1024 bytes apart; 32 bytes per K step
+                        const unsigned long long adesc = smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                        // B, K-major: same shape; N-major: 64-column panels 8192 bytes apart (leading),
+                        // 8-row k groups 1024 bytes apart (stride); 16 k-rows = 2048 bytes per K step
+                        const unsigned long long bdesc = p.b_is_kn ? smem_desc(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                                                                   : smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
+                        umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));          // frees the stage when these MMAs are done
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                umma_commit(acc_full_bar(acc));             // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31 belong to this warp
+        int acc = 0;
+        unsigned acc_phase = 0;
+        const bool vec_ok = (p.c_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.c_bs % 8 == 0);
+        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int b = (int)(tile / tiles_per_batch);
+            const int r = (int)(tile % tiles_per_batch);
+            const long long m0 = (long long)(r % p.tiles_m) * BM, n0 = (long long)(r / p.tiles_m) * BN;
+            if (!mbar_wait(acc_full_bar(acc), acc_phase)) {
+                if (lane == 0) atomicExch(p.error, 4u);
+                break;
+            }
+            tc_fence_after();
+            const long long m = m0 + quarter * 32 + lane;
+            T* crow = C + (long long)b * p.c_bs + m * p.c_rs;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                unsigned v[32];
+                tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c), v);
+                tmem_ld_wait();
+                const long long n = n0 + c;
+                if (m < p.M && n < p.N) {
+                    if (vec_ok && n + 31 < p.N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o;
+                            o.x = pack2<T>(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+                            o.y = pack2<T>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                            o.z = pack2<T>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                            o.w = pack2<T>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                            *reinterpret_cast<uint4*>(crow + n + 8 * q) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n + j < p.N) {
+                                unsigned pk = pack2<T>(__uint_as_float(v[j]), 0.f);
+                                reinterpret_cast<unsigned short*>(crow)[n + j] = (unsigned short)(pk & 0xffff);
+                            }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// cuTensorMapEncodeTiled through the driver entry point fetched by the runtime.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool encode_3d(CUtensorMap* map, bool bf16, const void* base, long long d0, long long d1, long long d2, long long stride1_elems,
+               long long stride2_elems, unsigned box0, unsigned box1) {
+    auto fn = (EncodeTiledFn)DriverApi::get().TensorMapEncodeTiled;
+    cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)d2};
+    cuuint64_t strides[2] = {(cuuint64_t)stride1_elems * 2, (cuuint64_t)(d2 > 1 ? stride2_elems : d1 * stride1_elems) * 2};
+    cuuint32_t box[3] = {box0, box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d) {
+    if (getenv("WGF_MATMUL_NO_TC")) return false;
+    if (dt != DType::F16 && dt != DType::BF16) return false;
+    // worth it only when a tile is reasonably full
+    if (d.M < 64 || d.N < 64 || d.K < 32) return false;
+    if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31) || d.batch >= (1ll << 31)) return false;
+    auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    // A must be K-major with 16-byte aligned rows
+    if (d.a_cs != 1 || d.a_rs % 8 || !a16(a) || (d.batch > 1 && d.a_bs % 8)) return false;
+    const bool b_kn = d.b_cs == 1 && d.b_rs % 8 == 0;   // [K,N] row-major
+    const bool b_nk = d.b_rs == 1 && d.b_cs % 8 == 0;   // [N,K] row-major (transposed view)
+    if ((!b_kn && !b_nk) || !a16(b) || (d.batch > 1 && d.b_bs % 8)) return false;
+    if (dev.dry) {
+        dev.begin_launch("matmul_tc");
+        dev.end_launch();
+        return true;
+    }
+    const bool bf16 = dt == DType::BF16;
+    CUtensorMap map_a, map_b;
+    if (!encode_3d(&map_a, bf16, a, d.K, d.M, d.batch, d.a_rs, d.a_bs, BK, BM)) return false;
+    const bool use_kn = b_kn;   // when both descriptions fit (a degenerate extent), either is right
+    if (use_kn) {
+        if (!encode_3d(&map_b, bf16, b, d.N, d.K, d.batch, d.b_rs, d.b_bs, 64, BK)) return false;
+    } else {
+        if (!encode_3d(&map_b, bf16, b, d.K, d.N, d.batch, d.b_cs, d.b_bs, BK, BN)) return false;
+    }
+    TcParams p{};
+    p.M = d.M;
+    p.N = d.N;
+    p.K = d.K;
+    p.batch = d.batch;
+    p.c_rs = d.c_rs;
+    p.c_bs = d.c_bs;
+    p.tiles_m = (int)((d.M + BM - 1) / BM);
+    p.tiles_n = (int)((d.N + BN - 1) / BN);
+    p.b_is_kn = use_kn ? 1 : 0;
+    p.is_bf16 = bf16 ? 1 : 0;
+    p.error = dev.error_word();
+    const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
+    const unsigned grid = (unsigned)std::min<long long>(total, dev.sm_count);
+    static bool attr_set[2] = {false, false};
+    if (bf16) {
+        if (!attr_set[1]) {
+            WGF_CUDA(cudaFuncSetAttribute(matmul_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            attr_set[1] = true;
+        }
+        dev.begin_launch("matmul_tc");
+        matmul_tc_kernel<__nv_bfloat16><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, (__nv_bfloat16*)c, p);
+        dev.end_launch();
+    } else {
+        if (!attr_set[0]) {
+            WGF_CUDA(cudaFuncSetAttribute(matmul_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            attr_set[0] = true;
+        }
+        dev.begin_launch("matmul_tc");
+        matmul_tc_kernel<__half><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, (__half*)c, p);
+        dev.end_launch();
+    }
+    return true;
+}
+
+}  // namespace wgf

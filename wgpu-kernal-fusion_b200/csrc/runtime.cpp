@@ -218,6 +218,7 @@ Device::~Device() {
     for (auto& kv : free_) cudaFree(kv.second);
     for (auto e : event_pool_) cudaEventDestroy(e);
     if (counters_) cudaFree(counters_);
+    if (error_word_) cudaFree(error_word_);
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -229,6 +230,29 @@ void Device::sync() {
     if (dry) return;
     make_current();
     WGF_CUDA(cudaStreamSynchronize(stream));
+    check_error_word();
+}
+
+unsigned* Device::error_word() {
+    if (dry) return nullptr;
+    if (!error_word_) {
+        make_current();
+        WGF_CUDA(cudaMalloc(&error_word_, 256));
+        WGF_CUDA(cudaMemsetAsync(error_word_, 0, 256, stream));
+    }
+    return error_word_;
+}
+
+// Called with the stream drained.
+void Device::check_error_word() {
+    if (!error_word_) return;
+    unsigned v = 0;
+    WGF_CUDA(cudaMemcpy(&v, error_word_, sizeof v, cudaMemcpyDeviceToHost));
+    if (v) {
+        cudaMemset(error_word_, 0, sizeof v);
+        fail(WGF_ERR_TIMEOUT, "a kernel gave up on a bounded wait (code " + std::to_string(v) +
+                                  "); its result is not valid");
+    }
 }
 
 static size_t round_block(size_t bytes) {
@@ -327,6 +351,7 @@ void Device::download(const Buffer& b, size_t off, void* dst, size_t n) {
     make_current();
     if (n) WGF_CUDA(cudaMemcpyAsync(dst, (const char*)b.ptr + off, n, cudaMemcpyDeviceToHost, stream));
     WGF_CUDA(cudaStreamSynchronize(stream));
+    check_error_word();
 }
 
 void* Device::counters() {

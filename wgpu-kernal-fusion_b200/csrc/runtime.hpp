@@ -80,6 +80,10 @@ struct Device : std::enable_shared_from_this<Device> {
     // such kernel leaves them zero again.
     void* counters();
     static constexpr int kCounters = 65536;
+    // A device word that kernels with bounded waits set when a wait gives up (0 = fine).
+    // sync() and download() read it after the stream has drained and raise WGF_ERR_TIMEOUT.
+    unsigned* error_word();
+    void check_error_word();
     uint64_t reserved_bytes() const { return reserved_; }
     uint64_t in_use_bytes() const { return in_use_; }
     void release_block(void* p, size_t block);
@@ -111,6 +115,7 @@ struct Device : std::enable_shared_from_this<Device> {
     std::vector<cudaEvent_t> event_pool_;
     TimingRecord pending_;
     void* counters_ = nullptr;
+    unsigned* error_word_ = nullptr;
     void* raw_alloc(size_t block);
 };
 using DeviceRef = std::shared_ptr<Device>;
