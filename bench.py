@@ -187,6 +187,10 @@ def run_gpu(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
+    # Libraries (NCCL) print to stdout; keep stdout for the one JSON line.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
 
@@ -227,27 +231,38 @@ def run_gpu(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
-    n_timing_before = len(xs[0].all_timing_information())
+    # Region A (the reported value): K steps bracketed by one event pair, per-kernel events off
+    # (an event pair around every launch costs the stream ~2.5 us per kernel).
+    dev.set_timing(False)
     launches_before = dev.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(stream)
+    host_t0 = time.perf_counter()
     for i in range(args.steps):
         step(i)
+    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps   # time the host needs to queue one step
     e1.record(stream)
     barrier()
     ms_total = e0.elapsed_time(e1)
     launches = dev.launch_count - launches_before
-    clocks = sampler.stop() if sampler else None
 
-    # per-kernel device times of the timed region (event pair around every launch)
-    # (all inputs share one graph through w, so the records are in launch order:
-    #  rows, stream_reduce[, all_reduce] per step)
+    # Region B (the roofline): the same K steps again with an event pair around every launch.
+    # All inputs share one graph through w, so the records are in launch order:
+    # rows, stream_reduce[, all_reduce] per step.
+    dev.set_timing(True)
+    n_timing_before = len(xs[0].all_timing_information())
+    for i in range(args.steps):
+        step(i)
+    barrier()
+    clocks = sampler.stop() if sampler else None
     per_step = 3 if comm is not None else 2
     recs = xs[0].all_timing_information()[n_timing_before:]
     row_ns, sum_ns = recs[0::per_step], recs[1::per_step]
     row_ms = float(np.mean(row_ns)) / 1e6 if row_ns else float("nan")
     sum_ms = float(np.mean(sum_ns)) / 1e6 if sum_ns else float("nan")
+    # what the all-reduce costs the device stream (a 4-byte copy; the collective itself runs beside it)
+    ar_ms = float(np.mean(recs[2::per_step])) / 1e6 if per_step == 3 and len(recs) >= 3 else None
 
     # ---- end to end through the C ABI with host buffers ---------------------------------------
     pin_x = wgf.PinnedArray((ROWS, H), np.float32)
@@ -296,6 +311,8 @@ def run_gpu(args):
             gbs, _ = cpu.time(reps, 1)
             cpu_baseline = {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": "port",
                             "sample": f"full workload ({ROWS}x{H} f32), {reps} repetitions after 1 warm-up"}
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
         print(json.dumps({
             "metric": "fused_chain_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -313,6 +330,8 @@ def run_gpu(args):
             "e2e": {"value": BYTES_STEP * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "steps": e2e_steps, "h2d_bytes_per_step": ROWS * H * 4, "d2h_bytes_per_step": ROWS * H * 4 + 4},
             "gpu_launches": launches,
+            "host_queue_ms_per_step": host_ms,
+            "all_reduce_on_device_stream_ms": ar_ms,
             "clocks": clocks,
         }))
     if world > 1:

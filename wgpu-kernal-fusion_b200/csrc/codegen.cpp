@@ -221,6 +221,7 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
     const int nin = prog.n_slots();
     WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
     WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
+    for (auto& t : in) dev.wait_for(*t.buf);   // inputs still owned by a collective
     const DType out_dt = prog.out_dtype();
     int64_t n = 1;
     for (auto v : shape) n *= v;
@@ -528,6 +529,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
     const int nin = prog.n_slots();
     WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
     WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
+    for (auto& t : in) dev.wait_for(*t.buf);   // inputs still owned by a collective
     WGF_CHECK(!shape.empty(), WGF_ERR_RANK, "row kernel needs rank >= 1");
     WGF_CHECK(out_has_h || prog.out_kind() == VKind::Row, WGF_ERR_INVALID_ARGUMENT,
               "a per-element result needs an output with the row axis");

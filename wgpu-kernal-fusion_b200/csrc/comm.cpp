@@ -75,14 +75,27 @@ std::shared_ptr<Comm> comm_create(const DeviceRef& dev, int world, int rank, con
     return c;
 }
 
-void comm_all_reduce(Comm& c, Device& dev, const void* send, void* recv, int64_t count, DType dt, uint16_t op) {
+void comm_all_reduce(Comm& c, Device& dev, Buffer& out, void* data, int64_t count, DType dt, uint16_t op) {
     int ndt = dt == DType::F32 ? 7 : dt == DType::F16 ? 6 : 9;
     int nop = op == WGF_OP_SUM ? 0 : op == WGF_OP_PRODUCT ? 1 : op == WGF_OP_MAX ? 2 : 3;
+    void* recv = data;
     dev.make_current();
+    dev.wait_for(out);
+    cudaStream_t cs = dev.collective_stream();
     dev.begin_launch("all_reduce");
-    int r = Nccl::get().AllReduce(send, recv, (size_t)count, ndt, nop, c.handle, dev.stream);
+    // The collective runs IN PLACE on the buffer that holds the partial result, on the
+    // collective stream, behind everything queued on the device stream so far; the kernels
+    // queued after it on the device stream overlap it.  The buffer carries the completion
+    // event: its next reader, and the pool when it is returned, wait for it (Buffer::pending).
+    cudaEvent_t produced = dev.event();
+    WGF_CUDA(cudaEventRecord(produced, dev.stream));
+    WGF_CUDA(cudaStreamWaitEvent(cs, produced, 0));
+    dev.recycle(produced);
+    int r = Nccl::get().AllReduce(recv, recv, (size_t)count, ndt, nop, c.handle, cs);
     dev.end_launch();
     nccl_check(r, "ncclAllReduce");
+    out.pending = dev.event();
+    WGF_CUDA(cudaEventRecord(out.pending, cs));
 }
 
 }  // namespace wgf

@@ -14,8 +14,9 @@ struct Comm {
 
 void comm_unique_id(uint8_t id[WGF_COMM_ID_BYTES]);
 std::shared_ptr<Comm> comm_create(const DeviceRef& dev, int world, int rank, const uint8_t id[WGF_COMM_ID_BYTES]);
-// Queued on the device stream; `send` and `recv` may be the same pointer.
-void comm_all_reduce(Comm& c, Device& dev, const void* send, void* recv, int64_t count, DType dt, uint16_t op);
+// In place on `data`, which lies in `out`.  The collective runs on the device's collective stream
+// behind everything queued on the device stream so far; `out.pending` is set to its completion event.
+void comm_all_reduce(Comm& c, Device& dev, Buffer& out, void* data, int64_t count, DType dt, uint16_t op);
 
 // Contiguous block partition: the first n % world ranks get one unit more.
 inline void shard_range(int64_t n, int world, int rank, int64_t& begin, int64_t& end) {

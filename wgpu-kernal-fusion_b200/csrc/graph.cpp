@@ -823,12 +823,23 @@ TensorData resolve_node(Node* n) {
             break;
         }
         case NodeKind::AllReduce: {
-            TensorData in = resolve_node(n->inputs[0].get());
-            TensorData dense = in.layout.is_dense() && !in.layout.allocation_overlaps() ? in : run_compact(dev, in);
-            out.buf = dev.alloc((size_t)std::max<int64_t>(dense.layout.numel(), 1) * dtype_size(n->dtype), false);
-            out.dtype = n->dtype;
-            out.layout = Layout::contiguous(n->shape);
-            comm_all_reduce(*n->comm, dev, dense.base_ptr(), out.base_ptr(), dense.layout.numel(), n->dtype, n->op);
+            Node* src = n->inputs[0].get();
+            TensorData in = resolve_node(src);
+            const bool dense_in = in.layout.is_dense() && !in.layout.allocation_overlaps();
+            // The collective runs in place.  If nothing else can read the partial result any
+            // more, its own buffer is used (no copy); otherwise a dense copy is reduced.
+            std::unordered_map<Node*, bool> memo;
+            bool own = dense_in && dies_with(src, n, memo);
+            if (own) {
+                src->cached = TensorData();
+                own = in.buf.use_count() == 1;
+                if (!own) src->cached = in;
+            }
+            out = own ? in : run_compact(dev, in);
+            out.layout.shape = n->shape;
+            if ((int)out.layout.strides.size() != n->rank()) out.layout.strides = Layout::contiguous_strides(n->shape);
+            dev.wait_for(*out.buf);
+            comm_all_reduce(*n->comm, dev, *out.buf, out.base_ptr(), out.layout.numel(), n->dtype, n->op);
             break;
         }
     }

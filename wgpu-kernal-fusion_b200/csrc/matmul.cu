@@ -114,6 +114,8 @@ TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b) {
     if (n_out == 0 || d.K == 0) return out;
     WGF_CHECK(d.batch <= 65535 && (d.M + 63) / 64 <= 65535, WGF_ERR_UNSUPPORTED, "matmul grid too large");
     dev.make_current();
+    dev.wait_for(*a.buf);
+    dev.wait_for(*b.buf);
 
     if (matmul_fast_path(dev, a.base_ptr(), b.base_ptr(), out.base_ptr(), a.dtype, d)) return out;
 

@@ -64,6 +64,8 @@ void run_copy(Device& dev, const TensorData& dst, const TensorData& src) {
     const int64_t n = src.layout.numel();
     if (n == 0) return;
     dev.make_current();
+    dev.wait_for(*dst.buf);
+    dev.wait_for(*src.buf);
     const int64_t esize = (int64_t)dtype_size(src.dtype);
     // collapse
     std::vector<int64_t> shape, ds, ss;

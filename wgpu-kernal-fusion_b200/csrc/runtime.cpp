@@ -173,7 +173,48 @@ std::vector<char> compile_to_cubin(const std::string& source, const std::string&
 // Buffer / Device
 // ---------------------------------------------------------------------------------------
 Buffer::~Buffer() {
-    if (ptr && dev) dev->release_block(ptr, block);
+    if (ptr && dev) {
+        // a collective may still touch the block: it goes back to the pool once that is over
+        if (pending) dev->release_block_after(ptr, block, pending);
+        else dev->release_block(ptr, block);
+    }
+}
+
+void Device::release_block_after(void* p, size_t block, cudaEvent_t ev) {
+    std::lock_guard<std::mutex> g(mu_);
+    deferred_.push_back({p, block, ev});
+}
+
+// Moves blocks whose collective has finished from the deferred list to the pool.  mu_ held.
+void Device::drain_deferred_locked() {
+    for (size_t i = 0; i < deferred_.size();) {
+        if (cudaEventQuery(deferred_[i].ev) == cudaSuccess) {
+            free_.emplace(deferred_[i].block, deferred_[i].ptr);
+            in_use_ -= deferred_[i].block;
+            event_pool_.push_back(deferred_[i].ev);
+            deferred_[i] = deferred_.back();
+            deferred_.pop_back();
+        } else {
+            cudaGetLastError();   // cudaErrorNotReady is not an error
+            ++i;
+        }
+    }
+}
+
+cudaStream_t Device::collective_stream() {
+    if (!collective_stream_ && !dry) {
+        make_current();
+        WGF_CUDA(cudaStreamCreateWithFlags(&collective_stream_, cudaStreamNonBlocking));
+    }
+    return collective_stream_;
+}
+
+void Device::wait_for(Buffer& b) {
+    if (!b.pending) return;
+    cudaSetDevice(ordinal);
+    cudaStreamWaitEvent(stream, b.pending, 0);
+    recycle(b.pending);
+    b.pending = nullptr;
 }
 
 std::shared_ptr<Device> Device::create(int ordinal) {
@@ -219,6 +260,14 @@ Device::~Device() {
     for (auto e : event_pool_) cudaEventDestroy(e);
     if (counters_) cudaFree(counters_);
     if (error_word_) cudaFree(error_word_);
+    if (collective_stream_) {
+        cudaStreamSynchronize(collective_stream_);
+        cudaStreamDestroy(collective_stream_);
+    }
+    for (auto& d : deferred_) {
+        cudaFree(d.ptr);
+        cudaEventDestroy(d.ev);
+    }
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -230,6 +279,11 @@ void Device::sync() {
     if (dry) return;
     make_current();
     WGF_CUDA(cudaStreamSynchronize(stream));
+    if (collective_stream_) WGF_CUDA(cudaStreamSynchronize(collective_stream_));
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        if (!deferred_.empty()) drain_deferred_locked();
+    }
     check_error_word();
 }
 
@@ -296,6 +350,7 @@ BufferRef Device::alloc(size_t bytes, bool zero) {
     void* p = nullptr;
     {
         std::lock_guard<std::mutex> g(mu_);
+        if (!deferred_.empty()) drain_deferred_locked();
         auto it = free_.lower_bound(block);
         // reuse a cached block unless it would waste more than a quarter of itself
         if (it != free_.end() && it->first <= block + block / 4 + 4096) {
@@ -349,6 +404,7 @@ void Device::download(const Buffer& b, size_t off, void* dst, size_t n) {
     WGF_CHECK(off + n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "download past the end of the buffer");
     WGF_CHECK(!dry, WGF_ERR_CUDA, "compile-only device: nothing was executed, there is nothing to download");
     make_current();
+    wait_for(const_cast<Buffer&>(b));
     if (n) WGF_CUDA(cudaMemcpyAsync(dst, (const char*)b.ptr + off, n, cudaMemcpyDeviceToHost, stream));
     WGF_CUDA(cudaStreamSynchronize(stream));
     check_error_word();

@@ -31,6 +31,10 @@ struct Buffer {
     void* ptr = nullptr;
     size_t bytes = 0;       // requested
     size_t block = 0;       // size of the pool block backing it
+    // Set while work on ANOTHER stream (the collective stream) still reads or writes the
+    // buffer.  The device stream waits for it before the next use of the buffer and before
+    // the block goes back to the pool (Device::wait_for, ~Buffer).
+    cudaEvent_t pending = nullptr;
     ~Buffer();
 };
 using BufferRef = std::shared_ptr<Buffer>;
@@ -84,9 +88,15 @@ struct Device : std::enable_shared_from_this<Device> {
     // sync() and download() read it after the stream has drained and raise WGF_ERR_TIMEOUT.
     unsigned* error_word();
     void check_error_word();
+    // Second stream for collectives, so that an all-reduce overlaps the kernels queued behind it.
+    cudaStream_t collective_stream();
+    // Orders the device stream behind any collective still using `b` (no-op otherwise).
+    void wait_for(Buffer& b);
     uint64_t reserved_bytes() const { return reserved_; }
     uint64_t in_use_bytes() const { return in_use_; }
     void release_block(void* p, size_t block);
+    // Same, but only once `ev` (recorded on the collective stream) has completed.
+    void release_block_after(void* p, size_t block, cudaEvent_t ev);
     void trim();
 
     // ---- kernels ----
@@ -116,6 +126,14 @@ struct Device : std::enable_shared_from_this<Device> {
     TimingRecord pending_;
     void* counters_ = nullptr;
     unsigned* error_word_ = nullptr;
+    cudaStream_t collective_stream_ = nullptr;
+    struct Deferred {
+        void* ptr;
+        size_t block;
+        cudaEvent_t ev;
+    };
+    std::vector<Deferred> deferred_;
+    void drain_deferred_locked();
     void* raw_alloc(size_t block);
 };
 using DeviceRef = std::shared_ptr<Device>;
