@@ -520,6 +520,90 @@ std::string stream_source(const Program& prog, const StreamConfig& c) {
     return s.str();
 }
 
+// ---- column reduce: reduced axis is not the innermost one --------------------------------
+struct ColConfig {
+    int C, U, out_mode;
+    std::vector<int> mode;      // per slot: 0 vector, 1 scalar, 2 one value for all columns
+    std::vector<char> is_row;   // per slot: does not vary along the reduced axis
+};
+
+std::string col_source(const Program& prog, const ColConfig& c) {
+    const int n = (int)prog.ins.size();
+    std::vector<char> dep(n, 0);
+    for (int i = 0; i < n; ++i) {
+        const Instr& in = prog.ins[i];
+        char d = in.kind == IKind::RowReduce;
+        if (in.a >= 0) d |= dep[in.a];
+        if (in.b >= 0) d |= dep[in.b];
+        dep[i] = d;
+    }
+    std::vector<int> eslot(prog.n_slots(), -1), rslot(prog.n_slots(), -1);
+    int nine = 0, nrowl = 0;
+    for (int t = 0; t < prog.n_slots(); ++t) {
+        if (c.is_row[t]) rslot[t] = nrowl++;
+        else eslot[t] = nine++;
+    }
+    std::vector<int> pre_index(n, -1);
+    int npre = 0, red_idx = 0;
+    std::ostringstream pre, elem, post, init, comb, sadd;
+    auto opnd_elem = [&](int j) {
+        return prog.ins[j].vk == VKind::Row ? "rv[" + std::to_string(pre_index[j]) + "]" : vn(j);
+    };
+    auto opnd_post = [&](int j) { return pre_index[j] >= 0 ? "rv[" + std::to_string(pre_index[j]) + "]" : vn(j); };
+    for (int i = 0; i < n; ++i) {
+        const Instr& in = prog.ins[i];
+        if (in.kind == IKind::RowReduce) {
+            const char* op = red_name(in.op);
+            elem << "    a[" << red_idx << "] = red_comb<" << op << ">(a[" << red_idx << "], " << opnd_elem(in.a) << ");\n";
+            init << "acc[" << red_idx << "][J] = red_ident<" << op << ">(); ";
+            comb << "acc[" << red_idx << "][J] = red_comb<" << op << ">(acc[" << red_idx << "][J], __ldcg((PP) + "
+                 << red_idx << " * (STRIDE) + J)); ";
+            sadd << "acc[" << red_idx << "][J] = red_comb<" << op << ">(acc[" << red_idx << "][J], red[" << red_idx
+                 << "][W][tx * C + J]); ";
+            post << "    float " << vn(i) << " = " << rounded(in.dtype, "a[" + std::to_string(red_idx) + "]") << ";\n";
+            red_idx++;
+        } else if (in.vk == VKind::Row && !dep[i]) {
+            if (in.kind == IKind::Load)
+                pre << "    float " << vn(i) << " = rl[" << rslot[in.slot] << "];\n";
+            else
+                pre << "    float " << vn(i) << " = " << instr_expr(in, vn(in.a), in.b >= 0 ? vn(in.b) : std::string()) << ";\n";
+            pre_index[i] = npre++;
+            pre << "    rv[" << pre_index[i] << "] = " << vn(i) << ";\n";
+        } else if (in.vk == VKind::Row) {
+            post << "    float " << vn(i) << " = "
+                 << instr_expr(in, opnd_post(in.a), in.b >= 0 ? opnd_post(in.b) : std::string()) << ";\n";
+        } else if (in.kind == IKind::Load) {
+            elem << "    float " << vn(i) << " = xe[" << eslot[in.slot] << "];\n";
+        } else {
+            elem << "    float " << vn(i) << " = "
+                 << instr_expr(in, opnd_elem(in.a), in.b >= 0 ? opnd_elem(in.b) : std::string()) << ";\n";
+        }
+    }
+    std::ostringstream le, lr;
+    for (int t = 0; t < prog.n_slots(); ++t) {
+        std::ostringstream& o = c.is_row[t] ? lr : le;
+        o << "load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << c.mode[t] << ">((const void*)p.ptr[" << t
+          << "], (i64)o * p.so[" << t << "] + " << (c.is_row[t] ? std::string("0") : "(i64)(KK) * p.sk[" + std::to_string(t) + "]")
+          << " + " << (c.mode[t] == 2 ? "0" : "(i64)col") << ", 1, C, X[" << (c.is_row[t] ? rslot[t] : eslot[t]) << "]); ";
+    }
+    std::ostringstream s;
+    s << JIT_PRELUDE;
+    s << "#define NIN " << prog.n_slots() << "\n#define NINE " << nine << "\n#define NROWL " << nrowl << "\n#define NPRE "
+      << npre << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM "
+      << prog.imms.size() << "\n#define OUT_DT " << (int)prog.out_dtype() << "\n#define OUT_MODE " << c.out_mode << "\n";
+    s << "DEV void pre_phase(const float* rl, const float* imm, float* rv) {\n" << pre.str() << "}\n";
+    s << "DEV void elem_phase(const float* xe, const float* rv, const float* imm, float* a) {\n" << elem.str() << "}\n";
+    s << "DEV float post_phase(const float* a, const float* rv, const float* imm) {\n" << post.str() << "    return "
+      << opnd_post(prog.result) << ";\n}\n";
+    s << "#define COL_INIT(J) " << init.str() << "\n";
+    s << "#define COL_COMB(J, PP, STRIDE) " << comb.str() << "\n";
+    s << "#define COL_SMEM_ADD(J, W) " << sadd.str() << "\n";
+    s << "#define COL_LOAD_ELEM(KK, X) " << le.str() << "\n";
+    s << "#define COL_LOAD_ROW(X) " << lr.str() << "\n";
+    s << JIT_COL_KERNEL;
+    return s.str();
+}
+
 }  // namespace
 
 int64_t max_resident_row(bool) { return 32768; }
@@ -605,6 +689,86 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
     };
 
     const bool single_phase = !prog.multi_phase() && !out_has_h;
+
+    // ---- column reduce: the reduced axis is strided and the last kept axis is the contiguous one
+    if (single_phase && (RO == 1 || RO == 2) && H >= 1 && tune("COL_REDUCE", 1)) {
+        const int64_t I = coshape[RO - 1], O = RO == 2 ? coshape[0] : 1;
+        bool ok = I >= 32 && O <= 65535, any_contig = false;
+        for (int t = 0; t < nin && ok; ++t) {
+            const int64_t si = st[t][RO - 1];
+            if (si != 0 && si != 1) ok = false;
+            if (!slot_row[t] && si == 1 && cs[t] != 1) any_contig = true;
+            if (!slot_row[t] && cs[t] == 1 && H > 1) ok = false;   // contiguous along the reduced axis: row kernels
+        }
+        if (ok && any_contig) {
+            ColConfig cfg;
+            cfg.is_row.assign(slot_row.begin(), slot_row.end());
+            cfg.C = any16 ? 8 : 4;
+            auto col_vec_ok = [&](const void* base, DType dt, int64_t so, int64_t sk, int C) {
+                const int64_t need = std::min<int64_t>(16, C * (int64_t)dtype_size(dt));
+                if ((uintptr_t)base % (uintptr_t)need) return false;
+                const int64_t es = (int64_t)dtype_size(dt);
+                return (O == 1 || (so * es) % need == 0) && (H == 1 || (sk * es) % need == 0);
+            };
+            auto pick = [&](int C) {
+                bool all_vec = C > 1 && I % C == 0;
+                cfg.mode.assign(nin, 1);
+                for (int t = 0; t < nin; ++t) {
+                    const int64_t si = st[t][RO - 1], so = RO == 2 ? st[t][0] : 0;
+                    if (si == 0) cfg.mode[t] = 2;
+                    else if (all_vec && col_vec_ok(in[t].base_ptr(), in[t].dtype, so, slot_row[t] ? 0 : cs[t], C)) cfg.mode[t] = 0;
+                    else all_vec = false;
+                }
+                cfg.out_mode = 1;
+                if (all_vec && col_vec_ok(out.base_ptr(), out_dt, I, 0, C)) cfg.out_mode = 0;
+                else all_vec = false;
+                return all_vec;
+            };
+            if (!pick(cfg.C)) {
+                cfg.C = 1;
+                pick(1);
+            }
+            int nine = 0;
+            for (int t = 0; t < nin; ++t) nine += !slot_row[t];
+            cfg.U = std::max(1, std::min(4, 32 / (std::max(nine, 1) * cfg.C)));
+            std::ostringstream key;
+            key << "col|" << cfg.C << "|" << cfg.U << "|" << cfg.out_mode << "|";
+            for (int m : cfg.mode) key << m;
+            key << "|";
+            for (int v : cfg.is_row) key << v;
+            key << "|" << prog.signature();
+            const JitKernel& k = dev.kernel(key.str(), "wgf_col_reduce", [&] { return col_source(prog, cfg); });
+            const int64_t tiles = (I + 32ll * cfg.C - 1) / (32ll * cfg.C);
+            int64_t split = std::max<int64_t>(1, ((int64_t)dev.sm_count * 4 + tiles * O - 1) / (tiles * O));
+            split = std::min<int64_t>(split, std::max<int64_t>(1, H / 64));
+            if (tiles * O > Device::kCounters || tiles > 65535 * 32768ll) split = 1;
+            split = std::min<int64_t>(split, 65535);
+            int64_t kper = (H + split - 1) / split;
+            kper = (kper + 7) / 8 * 8;
+            split = (H + kper - 1) / kper;
+            BufferRef partials;
+            if (split > 1)
+                partials = dev.alloc((size_t)(prog.n_reduces() * O * split * I) * sizeof(float), false);
+            ParamWriter w;
+            w.put<uint64_t>((uint64_t)O);
+            w.put<uint64_t>((uint64_t)H);
+            w.put<uint64_t>((uint64_t)I);
+            for (int t = 0; t < nin; ++t) w.put<uint64_t>((uint64_t)(uintptr_t)in[t].base_ptr());
+            w.put<uint64_t>((uint64_t)(uintptr_t)out.base_ptr());
+            for (int t = 0; t <= nin; ++t) w.put<int64_t>(RO == 2 ? st[t][0] : 0);
+            for (int t = 0; t <= nin; ++t) w.put<int64_t>(cs[t]);
+            w.put<uint64_t>(partials ? (uint64_t)(uintptr_t)partials->ptr : 0);
+            w.put<uint64_t>((uint64_t)(uintptr_t)dev.counters());
+            w.put<uint32_t>((uint32_t)split);
+            w.put<uint32_t>((uint32_t)kper);
+            for (float f : prog.imms) w.put<float>(f);
+            if (prog.imms.empty()) w.put<float>(0.f);
+            w.finish();
+            dev.launch(k, dim3((unsigned)tiles, (unsigned)split, (unsigned)O), dim3(32, 8), 0, w.bytes.data(), "col_reduce");
+            return out;
+        }
+    }
+
     bool use_stream = false;
     if (single_phase) {
         // enough rows to fill the machine and a row short enough for registers -> resident

@@ -454,4 +454,147 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(co
 }
 )CUDA";
 
+// ---------------------------------------------------------------------------------------
+// Column-reduce template: the reduced axis K is NOT the innermost one.  Index space
+// [O, K, I] with I contiguous in memory.  Threads run along I (C columns each, 16-byte
+// loads), the 8 thread rows of a CTA and p.split CTAs share K; per-column accumulators stay
+// in registers; partials of split CTAs go to scratch, the last CTA per column tile (ticket)
+// combines them in index order.  A reduction over axis 0 of a row-major matrix therefore
+// reads whole rows, where the crate walks one column per workgroup (src/reduce.rs:349-373).
+// Defines expected: NIN NINE NROWL NPRE C U NRED NIMM; macro COL_LOAD_ELEM(K, X),
+// COL_LOAD_ROW(X); functions pre_phase, elem_phase, post_phase; per-reduction macros
+// COL_INIT(j) COL_COMB(j, PP, STRIDE) COL_SMEM_ADD(j, w).
+// ---------------------------------------------------------------------------------------
+static const char* const JIT_COL_KERNEL = R"CUDA(
+struct Params {
+    u64 O, K, I;
+    u64 ptr[NIN + 1];
+    i64 so[NIN + 1];
+    i64 sk[NIN + 1];
+    u64 partials;   // float [NRED][O][split][I]
+    u64 counters;   // u32 [O * tiles], zero on entry, zero again on exit
+    u32 split;
+    u32 kper;       // K rows per split
+    float imm[NIMM > 0 ? NIMM : 1];
+};
+
+extern "C" __global__ void __launch_bounds__(256, 2) wgf_col_reduce(const __grid_constant__ Params p) {
+    __shared__ float red[NRED][8][32 * C + 1];
+    __shared__ u32 is_last;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const u64 o = blockIdx.z;
+    const u32 sp = blockIdx.y;
+    const u64 col = ((u64)blockIdx.x * 32 + tx) * C;
+    const bool cv = col < p.I;
+    const float* imm = p.imm;
+    // values that do not depend on k: per-column operands and arithmetic on them
+    float rowl[NROWL > 0 ? NROWL : 1][C];
+    float rowv[NPRE > 0 ? NPRE : 1][C];
+    if (cv) {
+        COL_LOAD_ROW(rowl)
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            float rl[NROWL > 0 ? NROWL : 1], rv[NPRE > 0 ? NPRE : 1];
+#pragma unroll
+            for (int s = 0; s < NROWL; ++s) rl[s] = rowl[s][j];
+            pre_phase(rl, imm, rv);
+#pragma unroll
+            for (int s = 0; s < NPRE; ++s) rowv[s][j] = rv[s];
+        }
+    }
+    float acc[NRED][C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) { COL_INIT(j) }
+    const u64 kbeg = (u64)sp * p.kper;
+    const u64 kend = kbeg + p.kper < p.K ? kbeg + p.kper : p.K;
+    if (cv) {
+        for (u64 k0 = kbeg + ty; k0 < kend; k0 += 8 * U) {
+            float x[U][NINE > 0 ? NINE : 1][C];
+            bool kv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const u64 k = k0 + (u64)u * 8;
+                kv[u] = k < kend;
+                if (kv[u]) { COL_LOAD_ELEM(k, x[u]) }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!kv[u]) continue;
+#pragma unroll
+                for (int j = 0; j < C; ++j) {
+                    float xe[NINE > 0 ? NINE : 1], rv[NPRE > 0 ? NPRE : 1], a[NRED];
+#pragma unroll
+                    for (int s = 0; s < NINE; ++s) xe[s] = x[u][s][j];
+#pragma unroll
+                    for (int s = 0; s < NPRE; ++s) rv[s] = rowv[s][j];
+#pragma unroll
+                    for (int r = 0; r < NRED; ++r) a[r] = acc[r][j];
+                    elem_phase(xe, rv, imm, a);
+#pragma unroll
+                    for (int r = 0; r < NRED; ++r) acc[r][j] = a[r];
+                }
+            }
+        }
+    }
+    // combine the 8 thread rows
+#pragma unroll
+    for (int r = 0; r < NRED; ++r)
+#pragma unroll
+        for (int j = 0; j < C; ++j) red[r][ty][tx * C + j] = acc[r][j];
+    __syncthreads();
+    if (ty == 0) {
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            COL_INIT(j)
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { COL_SMEM_ADD(j, w) }
+        }
+    }
+    const u64 tiles = gridDim.x;
+    if (p.split > 1) {
+        float* part = (float*)p.partials;
+        const u64 plane = p.O * p.split * p.I;               // one reduction's partials
+        const u64 base = (o * p.split + sp) * p.I + col;
+        if (ty == 0 && cv) {
+#pragma unroll
+            for (int r = 0; r < NRED; ++r)
+#pragma unroll
+                for (int j = 0; j < C; ++j) part[(u64)r * plane + base + j] = acc[r][j];
+        }
+        __threadfence();
+        __syncthreads();
+        if (tx == 0 && ty == 0) {
+            u32 ticket = atomicAdd((u32*)p.counters + o * tiles + blockIdx.x, 1u);
+            is_last = ticket == p.split - 1;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        if (ty == 0 && cv) {
+#pragma unroll
+            for (int j = 0; j < C; ++j) { COL_INIT(j) }
+            for (u32 s2 = 0; s2 < p.split; ++s2) {
+                const float* pp = part + (o * p.split + s2) * p.I + col;
+#pragma unroll
+                for (int j = 0; j < C; ++j) { COL_COMB(j, pp, plane) }
+            }
+        }
+        if (tx == 0 && ty == 0) ((u32*)p.counters)[o * tiles + blockIdx.x] = 0;
+    }
+    if (ty == 0 && cv) {
+        float y[C];
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            float rv[NPRE > 0 ? NPRE : 1], a[NRED];
+#pragma unroll
+            for (int s = 0; s < NPRE; ++s) rv[s] = rowv[s][j];
+#pragma unroll
+            for (int r = 0; r < NRED; ++r) a[r] = acc[r][j];
+            y[j] = post_phase(a, rv, imm);
+        }
+        store_chunk<OUT_DT, C, OUT_MODE>((void*)p.ptr[NIN], (i64)(o * p.I + col), C, y);
+    }
+}
+)CUDA";
+
 }  // namespace wgf
