@@ -1,0 +1,39 @@
+"""Builds the C++ mirror of the crate's API (include/wgf/tensor.hpp) against libwgf.so and runs the
+crate's tests restated in C++ (tests/cpp/facade_test.cpp): on the compile-only device without a GPU,
+for real with one."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "wgpu-kernal-fusion_b200")
+
+
+@pytest.fixture(scope="module")
+def facade_binary(tmp_path_factory, wgf):
+    wgf.lib()
+    exe = str(tmp_path_factory.mktemp("cpp") / "facade_test")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "facade_test.cpp"), "-o", exe, "-L", PKG, "-lwgf",
+                    f"-Wl,-rpath,{PKG}"], check=True)
+    return exe
+
+
+def _env():
+    env = dict(os.environ)
+    env.setdefault("WGF_KERNEL_CACHE", os.path.join(PKG, "_jit_cache"))
+    return env
+
+
+def test_facade_builds_and_resolves_without_gpu(facade_binary):
+    r = subprocess.run([facade_binary, "--compile-only-device"], capture_output=True, text=True, env=_env())
+    assert r.returncode == 0, r.stderr
+    assert "facade ok" in r.stdout
+
+
+@pytest.mark.gpu
+def test_facade_on_gpu(facade_binary):
+    r = subprocess.run([facade_binary], capture_output=True, text=True, env=_env())
+    assert r.returncode == 0, r.stderr
+    assert "facade ok" in r.stdout
