@@ -227,6 +227,16 @@ int32_t wgf_tensor_softmax(wgf_tensor* t, wgf_tensor** out);                    
 /* Max-subtracted softmax over the last axis of any rank (no counterpart in the crate). */
 int32_t wgf_tensor_softmax_last_dim(wgf_tensor* t, wgf_tensor** out);
 int32_t wgf_tensor_rope(wgf_tensor* t, wgf_tensor* cos, wgf_tensor* sin, wgf_tensor** out);         /* rope.rs:13-22 */
+/* Llama-style decoder block forward, composed from the primitives above (no counterpart in the
+ * crate; its README lists the ops such a block needs, README.md:24-38).
+ *   h = x + Wo.attn(rope(Wq.n1), rope(Wk.n1), Wv.n1), n1 = rms_norm(x, norm1);
+ *   out = h + Wd.(silu(Wg.n2) * (Wu.n2)),             n2 = rms_norm(h, norm2).
+ * x [batch, seq, hidden]; weights[7] = {Wq, Wk, Wv, Wo, Wg, Wu, Wd}, each stored
+ * [out_features, in_features]; norm1/norm2 [hidden]; cos/sin [>= seq, head_dim/2];
+ * mask [seq, seq] additive (0 where attended, -inf where not). */
+int32_t wgf_tensor_llama_block(wgf_tensor* x, wgf_tensor* const* weights, wgf_tensor* norm1, wgf_tensor* norm2,
+                               wgf_tensor* cos, wgf_tensor* sin, wgf_tensor* mask, uint32_t n_heads, float eps,
+                               wgf_tensor** out);
 
 /* LazyTensorData::materialize, src/tensor.rs:286-288: resolves the graph below `t`
  * (src/compute_graph/resolve.rs:16-248) and queues its kernels; does not wait. */

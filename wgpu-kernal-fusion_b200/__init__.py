@@ -311,6 +311,14 @@ class Tensor:
         check(lib().wgf_tensor_rope(self.h, cos.h, sin.h, C.byref(out)))
         return Tensor(self.dev, out)
 
+    def llama_block(self, weights, norm1, norm2, cos, sin, mask, n_heads, eps=1e-5):
+        """Llama-style decoder block forward; weights = [Wq, Wk, Wv, Wo, Wg, Wu, Wd], each [out, in]."""
+        arr = (C.c_void_p * 7)(*[w.h for w in weights])
+        out = C.c_void_p()
+        check(lib().wgf_tensor_llama_block(self.h, arr, norm1.h, norm2.h, cos.h, sin.h, mask.h, C.c_uint32(n_heads),
+                                           C.c_float(eps), C.byref(out)))
+        return Tensor(self.dev, out)
+
     def all_reduce(self, comm, op=OP_SUM):
         out = C.c_void_p()
         check(lib().wgf_tensor_all_reduce(self.h, comm.h, C.c_uint32(op), C.byref(out)))

@@ -697,6 +697,25 @@ int32_t wgf_tensor_rope(wgf_tensor* t, wgf_tensor* cos, wgf_tensor* sin, wgf_ten
     })
 }
 
+int32_t wgf_tensor_llama_block(wgf_tensor* x, wgf_tensor* const* weights, wgf_tensor* norm1, wgf_tensor* norm2,
+                               wgf_tensor* cos, wgf_tensor* sin, wgf_tensor* mask, uint32_t n_heads, float eps,
+                               wgf_tensor** out) {
+    GRAPH_GUARD({
+        REQUIRE(x);
+        REQUIRE(weights);
+        REQUIRE(norm1);
+        REQUIRE(norm2);
+        REQUIRE(cos);
+        REQUIRE(sin);
+        REQUIRE(mask);
+        REQUIRE(out);
+        for (int i = 0; i < 7; ++i) REQUIRE(weights[i]);
+        *out = wrap(op_llama_block(x->node, weights[0]->node, weights[1]->node, weights[2]->node, weights[3]->node,
+                                   weights[4]->node, weights[5]->node, weights[6]->node, norm1->node, norm2->node,
+                                   cos->node, sin->node, mask->node, (int)n_heads, eps));
+    })
+}
+
 int32_t wgf_tensor_materialize(wgf_tensor* t) {
     GRAPH_GUARD({
         REQUIRE(t);

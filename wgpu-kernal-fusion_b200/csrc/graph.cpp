@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <functional>
 #include <sstream>
 
@@ -381,6 +382,50 @@ NodeRef op_rope(const NodeRef& x, const NodeRef& cos, const NodeRef& sin) {
     NodeRef x1 = op_narrow(x, 2, 0, d / 2), x2 = op_narrow(x, 2, d / 2, d - d / 2);
     NodeRef rot = op_cat({make_unary(x2, WGF_OP_NEG), x1}, 2);
     return make_binary(make_binary(x, c, WGF_OP_MUL), make_binary(rot, s, WGF_OP_MUL), WGF_OP_ADD);
+}
+
+// Llama-style decoder block forward (no counterpart in the crate, whose README only lists the
+// ops such a block needs, README.md:24-38); a composition of the primitives above:
+//   h   = x + Wo . attention(rope(Wq . n1), rope(Wk . n1), Wv . n1),   n1 = rms_norm(x, norm1)
+//   out = h + Wd . (silu(Wg . n2) * (Wu . n2)),                        n2 = rms_norm(h, norm2)
+// x is [batch, seq, hidden]; weights are stored [out_features, in_features]; cos/sin are
+// [>= seq, head_dim / 2]; `mask` is the additive attention mask [seq, seq] (0 / -inf for causal).
+NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, const NodeRef& wv, const NodeRef& wo,
+                       const NodeRef& wg, const NodeRef& wu, const NodeRef& wd, const NodeRef& norm1,
+                       const NodeRef& norm2, const NodeRef& cos, const NodeRef& sin, const NodeRef& mask,
+                       int n_heads, float eps) {
+    WGF_CHECK(x->rank() == 3, WGF_ERR_RANK, "llama block input is [batch, seq, hidden]");
+    const int64_t B = x->shape[0], S = x->shape[1], Hd = x->shape[2];
+    WGF_CHECK(n_heads > 0 && Hd % n_heads == 0, WGF_ERR_SHAPE, "hidden size must divide into the heads");
+    const int64_t D = Hd / n_heads;
+    auto is2 = [](const NodeRef& w, int64_t o, int64_t i) { return w->rank() == 2 && w->shape[0] == o && w->shape[1] == i; };
+    WGF_CHECK(is2(wq, Hd, Hd) && is2(wk, Hd, Hd) && is2(wv, Hd, Hd) && is2(wo, Hd, Hd), WGF_ERR_SHAPE,
+              "attention weights must be [hidden, hidden]");
+    WGF_CHECK(wg->rank() == 2 && wg->shape[1] == Hd && wu->shape == wg->shape && is2(wd, Hd, wg->shape[0]), WGF_ERR_SHAPE,
+              "MLP weights must be [inter, hidden], [inter, hidden], [hidden, inter]");
+    WGF_CHECK(is2(mask, S, S), WGF_ERR_SHAPE, "attention mask must be [seq, seq]");
+    auto linear = [](const NodeRef& a, const NodeRef& w) { return make_matmul(a, view_transpose(w, 0, 1)); };
+    // [B*S, Hd] -> [B*heads, S, D]
+    auto split_heads = [&](const NodeRef& t) {
+        NodeRef r = op_reshape(t, {B, S, (int64_t)n_heads, D});
+        return op_reshape(view_transpose(r, 1, 2), {B * n_heads, S, D});
+    };
+    NodeRef x2 = op_reshape(x, {B * S, Hd});
+    NodeRef n1 = op_layer_norm(x2, norm1, eps);
+    NodeRef q = op_rope(split_heads(linear(n1, wq)), cos, sin);
+    NodeRef k = op_rope(split_heads(linear(n1, wk)), cos, sin);
+    NodeRef v = split_heads(linear(n1, wv));
+    NodeRef scores = make_matmul(q, view_transpose(k, 1, 2));                       // [B*heads, S, S]
+    NodeRef scaled = make_scalar(scores, WGF_OP_MUL_C, 1.0f / std::sqrt((float)D));
+    NodeRef masked = make_binary(scaled, view_broadcast_axis(mask, 0, B * n_heads), WGF_OP_ADD);
+    NodeRef probs = op_softmax_last_dim(masked);                                    // one fused row kernel
+    NodeRef ctx = make_matmul(probs, v);                                            // [B*heads, S, D]
+    NodeRef merged = op_reshape(view_transpose(op_reshape(ctx, {B, (int64_t)n_heads, S, D}), 1, 2), {B * S, Hd});
+    NodeRef h = make_binary(x2, linear(merged, wo), WGF_OP_ADD);
+    NodeRef n2 = op_layer_norm(h, norm2, eps);
+    NodeRef act = make_binary(op_silu(linear(n2, wg)), linear(n2, wu), WGF_OP_MUL);  // one fused kernel
+    NodeRef out = make_binary(h, linear(act, wd), WGF_OP_ADD);
+    return op_reshape(out, {B, S, Hd});
 }
 
 // ---------------------------------------------------------------------------------------

@@ -102,6 +102,10 @@ NodeRef op_layer_norm(const NodeRef& x, const NodeRef& weight, float eps);
 NodeRef op_softmax(const NodeRef& x);
 NodeRef op_softmax_last_dim(const NodeRef& x);
 NodeRef op_rope(const NodeRef& x, const NodeRef& cos, const NodeRef& sin);
+NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, const NodeRef& wv, const NodeRef& wo,
+                       const NodeRef& wg, const NodeRef& wu, const NodeRef& wd, const NodeRef& norm1,
+                       const NodeRef& norm2, const NodeRef& cos, const NodeRef& sin, const NodeRef& mask,
+                       int n_heads, float eps);
 
 // The resolver: returns the materialised result of `n` (cached in the node afterwards).
 // Kernels are queued on the device stream; nothing waits.
