@@ -339,16 +339,112 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------
+# Secondary workload (--workload llama_block): Llama-style decoder block forward, f16, random init,
+# hidden 4096, 32 heads x 128, MLP 11008, batch 8 x seq 2048 sharded by batch over the GPUs (strong
+# scaling: the global batch stays 8).  Metric: tokens/s.  No collective: the shards are independent.
+# --------------------------------------------------------------------------------------------
+def run_llama(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+    wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
+    dev = wgf.Device(local)
+    _, stream_ptr = dev.info()
+    stream = torch.cuda.ExternalStream(stream_ptr, device=torch.device("cuda", local))
+    Hd, heads, inter, S, Bg = 4096, 32, 11008, args.seq, 8
+    D = Hd // heads
+    b0, b1 = wgf.shard_range(Bg, world, rank)
+    B = b1 - b0
+    g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 5))
+    h16 = lambda a: a.astype(np.float16)
+    shapes = [(Hd, Hd)] * 4 + [(inter, Hd), (inter, Hd), (Hd, inter)]
+    W = [dev.tensor(h16(g.standard_normal(s, dtype=np.float32) * 0.02)) for s in shapes]
+    n1, n2 = dev.tensor(np.ones(Hd, np.float16)), dev.tensor(np.ones(Hd, np.float16))
+    pos = np.arange(S, dtype=np.float32)[:, None]
+    inv = (1.0 / (10000.0 ** (np.arange(0, D, 2, dtype=np.float32) / D)))[None, :]
+    cos, sin = dev.tensor(h16(np.cos(pos * inv))), dev.tensor(h16(np.sin(pos * inv)))
+    mask = dev.tensor(np.where(np.arange(S)[None, :] <= np.arange(S)[:, None], 0.0, -np.inf).astype(np.float16))
+    x_all = h16(np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 5 + 1)).standard_normal((Bg, S, Hd), dtype=np.float32))
+    x = dev.tensor(x_all[b0:b1]) if B > 0 else None
+    dev.set_timing(False)
+
+    def step():
+        if x is not None:
+            x.llama_block(W, n1, n2, cos, sin, mask, heads, 1e-5).materialize()
+
+    def barrier():
+        dev.sync()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    launches_before = dev.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = dev.launch_count - launches_before
+    clocks = sampler.stop() if sampler else None
+    vals = torch.tensor([ms, float(launches)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx, sm = vals.clone(), vals.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, launches = float(mx[0]), int(sm[1])
+    if rank == 0:
+        tokens = Bg * S
+        flop = tokens * (4 * 2 * Hd * Hd + 3 * 2 * Hd * inter + 4 * S * Hd)   # attention counted in full (masked half included)
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps({
+            "metric": "llama_block_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "llama-style decoder block forward", "hidden": Hd, "heads": heads, "head_dim": D,
+                       "mlp": inter, "global_batch": Bg, "seq_len": S, "sharding": f"batch/{world}"},
+            "tflops_executed": flop / (ms * 1e-3) / 1e12, "gpu_launches": launches, "clocks": clocks,
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="wgf", choices=["wgf", "reference"])
+    ap.add_argument("--workload", default="fused_chain", choices=["fused_chain", "llama_block"])
+    ap.add_argument("--seq", type=int, default=2048, help="sequence length of the llama_block workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
+    llama = args.workload == "llama_block"
+    if args.steps is None:
+        args.steps = 10 if llama else 2000
+    if args.warmup is None:
+        args.warmup = 3 if llama else 200
     if args.impl == "reference":
         run_reference(args)
+    elif llama:
+        run_llama(args)
     else:
         run_gpu(args)
 

@@ -250,6 +250,9 @@ int32_t wgf_tensor_download(wgf_tensor* t, void* dst, uint64_t bytes);
 /* Tensor::all_timing_information, src/tensor.rs:556-558: device time in ns of each kernel
  * launched while resolving `t`'s graph.  Call with out_ns == NULL to get the count. */
 int32_t wgf_tensor_timing(wgf_tensor* t, uint64_t* out_ns, uint32_t capacity, uint32_t* count);
+/* Kernel names matching wgf_tensor_timing, one per line (elementwise, rows, stream_reduce,
+ * col_reduce, copy, sgemm, matmul_tc, gemv_kn, ...).  Same size protocol as wgf_tensor_graphviz. */
+int32_t wgf_tensor_timing_labels(wgf_tensor* t, char* dst, uint64_t capacity, uint64_t* needed);
 /* Graphviz DOT text of the graph below `t` (Tensor::graphvis, src/tensor.rs:641-643). */
 int32_t wgf_tensor_graphviz(wgf_tensor* t, char* dst, uint64_t capacity, uint64_t* needed);
 /* Number of live graph nodes reachable from the graph `t` belongs to (debug aid). */

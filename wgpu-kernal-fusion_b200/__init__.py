@@ -352,6 +352,14 @@ class Tensor:
         check(lib().wgf_tensor_timing(self.h, arr, C.c_uint32(n.value), C.byref(n)))
         return [arr[i] for i in range(n.value)]
 
+    def timing_labels(self):
+        """Kernel names matching all_timing_information(), in launch order."""
+        need = C.c_uint64()
+        check(lib().wgf_tensor_timing_labels(self.h, None, C.c_uint64(0), C.byref(need)))
+        buf = C.create_string_buffer(need.value)
+        check(lib().wgf_tensor_timing_labels(self.h, buf, C.c_uint64(need.value), C.byref(need)))
+        return [s for s in buf.value.decode().split("\n") if s]
+
     def graphvis(self):
         need = C.c_uint64()
         check(lib().wgf_tensor_graphviz(self.h, None, C.c_uint64(0), C.byref(need)))

@@ -763,6 +763,23 @@ int32_t wgf_tensor_timing(wgf_tensor* t, uint64_t* out_ns, uint32_t capacity, ui
     })
 }
 
+int32_t wgf_tensor_timing_labels(wgf_tensor* t, char* dst, uint64_t capacity, uint64_t* needed) {
+    GRAPH_GUARD({
+        REQUIRE(t);
+        std::string s;
+        for (auto& r : graph_of(t->node)->timings) {
+            s += r.what;
+            s += '\n';
+        }
+        if (needed) *needed = s.size() + 1;
+        if (dst && capacity) {
+            size_t n = std::min<size_t>(s.size(), (size_t)capacity - 1);
+            std::memcpy(dst, s.data(), n);
+            dst[n] = 0;
+        }
+    })
+}
+
 int32_t wgf_tensor_graphviz(wgf_tensor* t, char* dst, uint64_t capacity, uint64_t* needed) {
     GRAPH_GUARD({
         REQUIRE(t);
