@@ -177,6 +177,12 @@ int32_t wgf_launch_slice_assign(wgf_device* dev, const wgf_tensor_desc* target, 
 /* Tensor::new, src/tensor.rs:518-531 (row-major host data of `dtype`). */
 int32_t wgf_tensor_from_host(wgf_device* dev, uint32_t dtype, uint32_t rank, const int64_t* shape,
                              const void* data, wgf_tensor** out);
+/* Same, from PAGE-LOCKED host memory (wgf_host_alloc) without waiting: the copy runs on a
+ * separate upload stream and overlaps kernels and downloads already queued; every consumer is
+ * ordered behind it.  `data` must stay unchanged until a synchronising call (wgf_device_sync,
+ * a download of a dependent tensor) has returned.  Pageable memory is rejected. */
+int32_t wgf_tensor_from_host_pinned(wgf_device* dev, uint32_t dtype, uint32_t rank, const int64_t* shape,
+                                    const void* data, wgf_tensor** out);
 /* Wraps an existing buffer + layout as a graph leaf (TensorData::new_from_parts). */
 int32_t wgf_tensor_from_desc(wgf_device* dev, const wgf_tensor_desc* desc, wgf_tensor** out);
 /* Tensor::arange / arange_step, src/composite/arange.rs:4-23 (host loop + upload). */

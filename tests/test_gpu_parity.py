@@ -312,6 +312,24 @@ def test_memoised_and_inplace(dev, orc):
     np.testing.assert_array_equal(cur.as_slice(), ((((x + 1) + 1) + 1) + 1) + 1)
 
 
+def test_pinned_async_upload(wgf, dev, orc):
+    x = seeded(0, 8).standard_normal((300, 1000)).astype(np.float32)
+    pins = [wgf.PinnedArray(x.shape, np.float32) for _ in range(2)]
+    outs = []
+    for k in range(4):                       # uploads overlap the previous round's kernels and downloads
+        pins[k % 2].array[...] = x + k
+        t = dev.tensor_pinned(pins[k % 2])
+        outs.append(((t * 2.0).sum(1), k))
+        got = outs[-1][0].as_slice()         # synchronises: the pinned array may be rewritten afterwards
+        ref = (orc.Ref(x + k) * 2.0).sum(1).numpy()
+        assert_rel(got, ref, 1e-5)
+    with pytest.raises(wgf.WgfError):        # pageable memory is refused, not copied synchronously
+        class Fake:
+            array = x
+            ptr = type("P", (), {"value": x.ctypes.data})()
+        dev.tensor_pinned(Fake())
+
+
 def test_timing_and_graphviz(dev):
     x = dev.tensor(np.ones((10, 10, 20), np.float32))
     y = x.sum(0).sum(0).sum(0)          # examples/hello.rs:15-22

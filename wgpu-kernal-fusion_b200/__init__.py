@@ -115,6 +115,17 @@ class Device:
     def tensor(self, data, dtype=None):
         return Tensor.new(self, data, dtype)
 
+    def tensor_pinned(self, pinned, dtype=None):
+        """Asynchronous upload from a PinnedArray: returns at once; keep the array unchanged until a
+        synchronising call has returned."""
+        a = pinned.array
+        if dtype is None:
+            dtype = F16 if a.dtype == np.float16 else F32
+        out = C.c_void_p()
+        check(lib().wgf_tensor_from_host_pinned(self.h, C.c_uint32(dtype), C.c_uint32(a.ndim), _i64(a.shape),
+                                                C.c_void_p(pinned.ptr.value), C.byref(out)))
+        return Tensor(self, out)
+
     def arange(self, start, end, step=1.0, dtype=F32):
         out = C.c_void_p()
         check(lib().wgf_tensor_arange(self.h, C.c_uint32(dtype), C.c_float(start), C.c_float(end),

@@ -444,6 +444,26 @@ int32_t wgf_tensor_from_host(wgf_device* dev, uint32_t dtype, uint32_t rank, con
     })
 }
 
+int32_t wgf_tensor_from_host_pinned(wgf_device* dev, uint32_t dtype, uint32_t rank, const int64_t* shape,
+                                    const void* data, wgf_tensor** out) {
+    GRAPH_GUARD({
+        REQUIRE(dev);
+        REQUIRE(out);
+        WGF_CHECK(valid_dtype(dtype), WGF_ERR_DTYPE, "unknown element type");
+        WGF_CHECK(rank <= WGF_MAX_RANK, WGF_ERR_RANK, "rank above 8");
+        WGF_CHECK(shape || !rank, WGF_ERR_INVALID_ARGUMENT, "null shape");
+        TensorData td;
+        td.dtype = (DType)dtype;
+        td.layout = Layout::contiguous(vec(shape, rank));
+        for (auto s : td.layout.shape) WGF_CHECK(s >= 0, WGF_ERR_SHAPE, "negative extent");
+        size_t bytes = (size_t)td.layout.numel() * dtype_size(td.dtype);
+        WGF_CHECK(data || !bytes, WGF_ERR_INVALID_ARGUMENT, "null data");
+        td.buf = dev->ref->alloc(std::max<size_t>(bytes, 1), false);
+        if (bytes) dev->ref->upload_async(*td.buf, data, bytes);
+        *out = wrap(make_tensor(dev->ref, td));
+    })
+}
+
 int32_t wgf_tensor_from_desc(wgf_device* dev, const wgf_tensor_desc* desc, wgf_tensor** out) {
     GRAPH_GUARD({
         REQUIRE(dev);

@@ -264,6 +264,10 @@ Device::~Device() {
         cudaStreamSynchronize(collective_stream_);
         cudaStreamDestroy(collective_stream_);
     }
+    if (upload_stream_) {
+        cudaStreamSynchronize(upload_stream_);
+        cudaStreamDestroy(upload_stream_);
+    }
     for (auto& d : deferred_) {
         cudaFree(d.ptr);
         cudaEventDestroy(d.ev);
@@ -280,6 +284,7 @@ void Device::sync() {
     make_current();
     WGF_CUDA(cudaStreamSynchronize(stream));
     if (collective_stream_) WGF_CUDA(cudaStreamSynchronize(collective_stream_));
+    if (upload_stream_) WGF_CUDA(cudaStreamSynchronize(upload_stream_));
     {
         std::lock_guard<std::mutex> g(mu_);
         if (!deferred_.empty()) drain_deferred_locked();
@@ -398,6 +403,31 @@ void Device::upload(const Buffer& b, size_t off, const void* src, size_t n) {
     WGF_CUDA(cudaMemcpyAsync((char*)b.ptr + off, src, n, cudaMemcpyHostToDevice, stream));
     // The source may be pageable and reused by the caller right away.
     WGF_CUDA(cudaStreamSynchronize(stream));
+}
+
+// Upload from PAGE-LOCKED host memory on the upload stream: returns at once, overlaps whatever the
+// device stream is doing (kernels, a download in the other PCIe direction).  The copy is ordered
+// behind everything queued on the device stream so far, because the pool may have handed out a block
+// that earlier kernels still use; the buffer carries the completion event (Buffer::pending).
+void Device::upload_async(Buffer& b, const void* src, size_t n) {
+    WGF_CHECK(n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "upload past the end of the buffer");
+    if (!n || dry) return;
+    make_current();
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, src);
+    if (e != cudaSuccess || attr.type != cudaMemoryTypeHost) {
+        cudaGetLastError();
+        fail(WGF_ERR_INVALID_ARGUMENT, "asynchronous upload needs page-locked host memory (wgf_host_alloc)");
+    }
+    if (!upload_stream_) WGF_CUDA(cudaStreamCreateWithFlags(&upload_stream_, cudaStreamNonBlocking));
+    wait_for(b);
+    cudaEvent_t before = event();
+    WGF_CUDA(cudaEventRecord(before, stream));
+    WGF_CUDA(cudaStreamWaitEvent(upload_stream_, before, 0));
+    recycle(before);
+    WGF_CUDA(cudaMemcpyAsync(b.ptr, src, n, cudaMemcpyHostToDevice, upload_stream_));
+    b.pending = event();
+    WGF_CUDA(cudaEventRecord(b.pending, upload_stream_));
 }
 
 void Device::download(const Buffer& b, size_t off, void* dst, size_t n) {

@@ -79,6 +79,7 @@ struct Device : std::enable_shared_from_this<Device> {
     // ---- memory ----
     BufferRef alloc(size_t bytes, bool zero);
     void upload(const Buffer& b, size_t off, const void* src, size_t n);
+    void upload_async(Buffer& b, const void* src, size_t n);   // src must be page-locked
     void download(const Buffer& b, size_t off, void* dst, size_t n);
     // 65536 zero-initialised u32 tickets for kernels that elect a last-arriving CTA; every
     // such kernel leaves them zero again.
@@ -127,6 +128,7 @@ struct Device : std::enable_shared_from_this<Device> {
     void* counters_ = nullptr;
     unsigned* error_word_ = nullptr;
     cudaStream_t collective_stream_ = nullptr;
+    cudaStream_t upload_stream_ = nullptr;
     struct Deferred {
         void* ptr;
         size_t block;
