@@ -313,8 +313,8 @@ def test_memoised_and_inplace(dev, orc):
 
 
 def test_pinned_async_upload(wgf, dev, orc):
-    x = seeded(0, 8).standard_normal((300, 1000)).astype(np.float32)
-    pins = [wgf.PinnedArray(x.shape, np.float32) for _ in range(2)]
+    x = np.abs(seeded(0, 8).standard_normal((300, 1000))).astype(np.float32)   # positive: no cancellation in the sums
+    pins =[wgf.PinnedArray(x.shape, np.float32) for _ in range(2)]
     outs = []
     for k in range(4):                       # uploads overlap the previous round's kernels and downloads
         pins[k % 2].array[...] = x + k

@@ -504,8 +504,10 @@ std::string stream_source(const Program& prog, const StreamConfig& c) {
       << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces()
       << "\n#define NIMM " << prog.imms.size() << "\n#define MINB " << c.minb << "\n";
     s << "DEV void elem_phase(const float (&x)[NINE > 0 ? NINE : 1][C], const float* rowv, const float* imm, int nvalid, float* acc) {\n"
+      // full chunks (all but the ragged end of a row) take a path without per-element predicates
+      << "  if (nvalid == C) {\n#pragma unroll\n    for (int j = 0; j < C; ++j) {\n" << elem.str() << "    }\n  } else {\n"
       << "#pragma unroll\n    for (int j = 0; j < C; ++j) {\n      if (j < nvalid) {\n"
-      << elem.str() << "      }\n    }\n}\n";
+      << elem.str() << "      }\n    }\n  }\n}\n";
     s << "#define STREAM_PRE " << pre.str() << " float rowv[" << std::max(nrowv, 1) << "]; ";
     if (nrowv == 0) s << "rowv[0] = 0.f; ";
     for (int i = 0; i < n; ++i)

@@ -29,7 +29,9 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;            // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_TILE_BYTES = 32 * 128;              // one warp's staging tile: 32 rows x 64 f16
+constexpr int EPI_BYTES = 4 * 2 * EPI_TILE_BYTES;     // 4 epilogue warps x 2 tiles = 32 KiB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int TC_THREADS = 192;
 constexpr unsigned SPIN_LIMIT = 1u << 22;             // bounded waits: ~seconds, then give up
 
@@ -39,6 +41,7 @@ struct TcParams {
     int tiles_m, tiles_n;
     int b_is_kn;       // 1: B stored [K,N] (N-major), 0: B stored [N,K] (K-major)
     int is_bf16;
+    int use_tma_store; // 1: epilogue stages through shared memory and stores by TMA (needs N % 8 == 0)
     unsigned* error;   // device word: 0 = ok, else code of the wait that gave up
 };
 
@@ -86,6 +89,18 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
+}
+
+// shared memory -> global through the tensor map (rows/columns outside the tensor are clipped)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, unsigned src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk stores still READ their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned cols) {
@@ -160,12 +175,13 @@ template <> __device__ __forceinline__ unsigned pack2<__nv_bfloat16>(float lo, f
 
 template <typename T>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, T* __restrict__ C,
-                 const __grid_constant__ TcParams p) {
+matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, T* __restrict__ C, const __grid_constant__ TcParams p) {
     extern __shared__ unsigned char smem_raw[];
     // stage buffers need 1024-byte alignment for the 128-byte swizzle atoms
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+    unsigned char* epi_smem = smem + STAGES * STAGE_BYTES;   // 1024-byte aligned (the stages are 48 KiB each)
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(epi_smem + EPI_BYTES);
     // bars[0..3] full, [4..7] empty, [8..9] accumulator full, [10..11] accumulator empty
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 12);
     const unsigned bar0 = smem_u32(bars);
@@ -284,6 +300,7 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31 belong to this warp
         int acc = 0;
         unsigned acc_phase = 0;
+        int epi_buf = 0;
         const bool vec_ok = (p.c_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.c_bs % 8 == 0);
         for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = (int)(tile / tiles_per_batch);
@@ -296,6 +313,42 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tc_fence_after();
             const long long m = m0 + quarter * 32 + lane;
             T* crow = C + (long long)b * p.c_bs + m * p.c_rs;
+            if (p.use_tma_store) {
+                // 64 columns at a time: TMEM -> registers -> this warp's staging tile in shared
+                // memory (32 rows x 128 bytes, 128-byte swizzle) -> one TMA store of full 128-byte
+                // rows.  Two staging tiles per warp alternate; out-of-range rows/columns are
+                // clipped by the tensor map.
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    unsigned char* tile_smem = epi_smem + ((warp - 2) * 2 + epi_buf) * EPI_TILE_BYTES;
+                    if (lane == 0) bulk_wait_read<1>();          // the tile used two stores ago has been read
+                    __syncwarp();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        unsigned v[32];
+                        tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c + half * 32), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o;
+                            o.x = pack2<T>(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+                            o.y = pack2<T>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                            o.z = pack2<T>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                            o.w = pack2<T>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                            const int chunk = (half * 4 + q) ^ (lane & 7);
+                            *reinterpret_cast<uint4*>(tile_smem + lane * 128 + chunk * 16) = o;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    const long long mrow = m0 + quarter * 32, ncol = n0 + c;
+                    if (lane == 0 && mrow < p.M && ncol < p.N) {
+                        tma_store_3d(&map_c, smem_u32(tile_smem), (int)ncol, (int)mrow, b);
+                        bulk_commit();
+                    }
+                    epi_buf ^= 1;
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 unsigned v[32];
@@ -331,6 +384,7 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 acc_phase ^= 1;
             }
         }
+        if (p.use_tma_store && lane == 0) bulk_wait_read<0>();   // shared memory stays valid until the stores have read it
     }
     tc_fence_before();
     __syncthreads();
@@ -397,6 +451,12 @@ bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt
     p.tiles_n = (int)((d.N + BN - 1) / BN);
     p.b_is_kn = use_kn ? 1 : 0;
     p.is_bf16 = bf16 ? 1 : 0;
+    // C through TMA when its rows are 16-byte aligned; otherwise guarded stores from registers
+    CUtensorMap map_c = map_a;
+    p.use_tma_store = 0;
+    if (!getenv("WGF_TC_NO_TMA_STORE") && d.c_rs % 8 == 0 && (d.batch == 1 || d.c_bs % 8 == 0) && a16(c) &&
+        encode_3d(&map_c, bf16, c, d.N, d.M, d.batch, d.c_rs, d.c_bs, 64, 32))
+        p.use_tma_store = 1;
     p.error = dev.error_word();
     const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
     const unsigned grid = (unsigned)std::min<long long>(total, dev.sm_count);
@@ -407,7 +467,7 @@ bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt
             attr_set[1] = true;
         }
         dev.begin_launch("matmul_tc");
-        matmul_tc_kernel<__nv_bfloat16><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, (__nv_bfloat16*)c, p);
+        matmul_tc_kernel<__nv_bfloat16><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__nv_bfloat16*)c, p);
         dev.end_launch();
     } else {
         if (!attr_set[0]) {
@@ -415,7 +475,7 @@ bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt
             attr_set[0] = true;
         }
         dev.begin_launch("matmul_tc");
-        matmul_tc_kernel<__half><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, (__half*)c, p);
+        matmul_tc_kernel<__half><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__half*)c, p);
         dev.end_launch();
     }
     return true;
