@@ -216,8 +216,36 @@ std::string debug_ew_source(const Program& prog, int rank, int chunk) {
     return ew_source(prog, c);
 }
 
+static TensorData run_elementwise_impl(Device& dev, const Program& prog, const std::vector<TensorData>& in,
+                                       const std::vector<int64_t>& shape, int inplace_slot);
+
+// Operands whose innermost axis is strided (a transposed view) would be read with adjacent
+// threads far apart.  When such an operand is contiguous along another axis it is first
+// brought into the kernel's index order by the tiled-transpose copy (both passes coalesced);
+// the private copy may then serve as the output buffer.
 TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<TensorData>& in,
                            const std::vector<int64_t>& shape, int inplace_slot) {
+    int64_t n = 1;
+    for (auto v : shape) n *= v;
+    if (n < 65536 || shape.empty() || !tune("EW_PRETRANSPOSE", 1)) return run_elementwise_impl(dev, prog, in, shape, inplace_slot);
+    std::vector<TensorData> ins;
+    for (size_t t = 0; t < in.size(); ++t) {
+        const Layout& l = in[t].layout;
+        const int r = l.rank();
+        bool strided_inner = r >= 2 && l.shape == shape && l.shape[r - 1] > 1 && l.strides[r - 1] != 0 && l.strides[r - 1] != 1;
+        bool other_contig = false;
+        for (int d = 0; strided_inner && d < r - 1; ++d) other_contig |= l.strides[d] == 1 && l.shape[d] >= 8;
+        if (strided_inner && other_contig) {
+            if (ins.empty()) ins = in;
+            ins[t] = run_compact(dev, in[t]);
+            if (inplace_slot < 0) inplace_slot = (int)t;
+        }
+    }
+    return run_elementwise_impl(dev, prog, ins.empty() ? in : ins, shape, inplace_slot);
+}
+
+static TensorData run_elementwise_impl(Device& dev, const Program& prog, const std::vector<TensorData>& in,
+                                       const std::vector<int64_t>& shape, int inplace_slot) {
     const int nin = prog.n_slots();
     WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
     WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");

@@ -40,6 +40,68 @@ __global__ void __launch_bounds__(256) copy_kernel(T* __restrict__ dst, const T*
     }
 }
 
+// Transposing copy: the destination is contiguous along the last axis, the source along axis
+// `pax`.  A CTA moves a 32 x 32 tile of the (pax, last) plane through shared memory so that
+// both its reads and its writes are coalesced (the crate's strided kernel walks the source
+// with adjacent threads a whole row apart, src/visit_tiled.rs:100-144).
+struct TransposeParams {
+    int rank, pax;
+    long long tiles_p, tiles_l, total_tiles;
+    long long shape[WGF_MAX_RANK];
+    long long dstride[WGF_MAX_RANK];
+    long long sstride[WGF_MAX_RANK];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_copy_kernel(T* __restrict__ dst, const T* __restrict__ src,
+                                                             const __grid_constant__ TransposeParams p) {
+    __shared__ T tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;   // 32 x 8
+    const int last = p.rank - 1;
+    for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+        long long rem = t;
+        const long long tl = rem % p.tiles_l;
+        rem /= p.tiles_l;
+        const long long tp = rem % p.tiles_p;
+        rem /= p.tiles_p;
+        long long doff = 0, soff = 0;
+#pragma unroll 1
+        for (int d = last - 1; d >= 0; --d) {
+            if (d == p.pax) continue;
+            const long long c = rem % p.shape[d];
+            rem /= p.shape[d];
+            doff += c * p.dstride[d];
+            soff += c * p.sstride[d];
+        }
+        const long long p0 = tp * 32, l0 = tl * 32;
+        // read: x along pax (source contiguous), rows along last
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            const long long pi = p0 + tx, li = l0 + ty + i;
+            if (pi < p.shape[p.pax] && li < p.shape[last])
+                tile[ty + i][tx] = src[soff + pi * p.sstride[p.pax] + li * p.sstride[last]];
+        }
+        __syncthreads();
+        // write: x along last (destination contiguous), rows along pax
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            const long long pi = p0 + ty + i, li = l0 + tx;
+            if (pi < p.shape[p.pax] && li < p.shape[last])
+                dst[doff + pi * p.dstride[p.pax] + li * p.dstride[last]] = tile[tx][ty + i];
+        }
+        __syncthreads();
+    }
+}
+
+template <typename T>
+void launch_transpose(Device& dev, void* dst, const void* src, const TransposeParams& p) {
+    long long blocks = std::min<long long>(p.total_tiles, (long long)dev.sm_count * 16);
+    dev.begin_launch("transpose_copy");
+    if (!dev.dry)
+        transpose_copy_kernel<T><<<(unsigned)blocks, dim3(32, 8), 0, dev.stream>>>((T*)dst, (const T*)src, p);
+    dev.end_launch();
+}
+
 template <typename T>
 void launch_copy(Device& dev, void* dst, const void* src, const CopyParams& p) {
     long long blocks = std::min<long long>((p.n + 255) / 256, (long long)dev.sm_count * 32);
@@ -89,6 +151,29 @@ void run_copy(Device& dev, const TensorData& dst, const TensorData& src) {
         ss.push_back(1);
     }
     const int R = (int)shape.size();
+    // transposed source: contiguous along another axis than the destination -> tiled transpose
+    if (R >= 2 && ds[R - 1] == 1 && ss[R - 1] != 1 && n >= 4096) {
+        int pax = -1;
+        for (int d = 0; d < R - 1; ++d)
+            if (ss[d] == 1 && shape[d] >= 8) pax = d;
+        if (pax >= 0) {
+            TransposeParams tp{};
+            tp.rank = R;
+            tp.pax = pax;
+            tp.tiles_p = (shape[pax] + 31) / 32;
+            tp.tiles_l = (shape[R - 1] + 31) / 32;
+            tp.total_tiles = tp.tiles_p * tp.tiles_l;
+            for (int d = 0; d < R; ++d) {
+                tp.shape[d] = shape[d];
+                tp.dstride[d] = ds[d];
+                tp.sstride[d] = ss[d];
+                if (d != pax && d != R - 1) tp.total_tiles *= shape[d];
+            }
+            if (esize == 4) launch_transpose<uint32_t>(dev, dst.base_ptr(), src.base_ptr(), tp);
+            else launch_transpose<uint16_t>(dev, dst.base_ptr(), src.base_ptr(), tp);
+            return;
+        }
+    }
     // vector width: 16, 8 or 4 bytes per thread when the innermost axis allows it
     int64_t vec = 1;
     if (ds[R - 1] == 1 && ss[R - 1] == 1) {
