@@ -45,6 +45,11 @@ def _p(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
+def _c(a, dtype=None):
+    """C-contiguous array that keeps rank 0 (np.ascontiguousarray would make it rank 1)."""
+    return np.asarray(a, dtype=dtype, order="C")
+
+
 def _code(a, bf16):
     if bf16:
         return BF16
@@ -74,23 +79,23 @@ class Ref:
         return Ref(a, bf16=(self.bf16 if code is None else code == BF16))
 
     def numpy(self):
-        return np.ascontiguousarray(self.a)
+        return _c(self.a)
 
     def _unary(self, op):
-        x = np.ascontiguousarray(self.a)
+        x = _c(self.a)
         out = np.empty_like(x)
         lib().orc_unary(op, self.code, _p(x), _p(out), C.c_int64(x.size))
         return self._like(out)
 
     def _scalar(self, op, c):
-        x = np.ascontiguousarray(self.a)
+        x = _c(self.a)
         out = np.empty_like(x)
         lib().orc_scalar(op, self.code, _p(x), C.c_float(c), _p(out), C.c_int64(x.size))
         return self._like(out)
 
     def _binary(self, o, op):
         assert self.shape == o.shape and self.code == o.code
-        x, y = np.ascontiguousarray(self.a), np.ascontiguousarray(o.a)
+        x, y = _c(self.a), _c(o.a)
         out = np.empty_like(x)
         lib().orc_binary(op, self.code, _p(x), _p(y), _p(out), C.c_int64(x.size))
         return self._like(out)
@@ -125,14 +130,14 @@ class Ref:
         return self._binary(o, OP_POW)
 
     def cast(self, code):
-        x = np.ascontiguousarray(self.a)
+        x = _c(self.a)
         out = np.empty(x.shape, dtype=np.float32 if code == F32 else (np.float16 if code == F16 else np.uint16))
         lib().orc_cast(self.code, code, _p(x), _p(out), C.c_int64(x.size))
         return Ref(out, bf16=code == BF16)
 
     # ---- reduce / matmul ----
     def reduce(self, op, axis):
-        x = np.ascontiguousarray(self.a)
+        x = _c(self.a)
         outer = int(np.prod(x.shape[:axis], dtype=np.int64))
         k = x.shape[axis]
         inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
@@ -153,7 +158,7 @@ class Ref:
         return self.reduce(OP_PRODUCT, axis)
 
     def mat_mul(self, o):
-        x, y = np.ascontiguousarray(self.a), np.ascontiguousarray(o.a)
+        x, y = _c(self.a), _c(o.a)
         batch = x.shape[0] if x.ndim == 3 else 1
         M, K, N = x.shape[-2], x.shape[-1], y.shape[-1]
         out = np.empty(x.shape[:-1] + (N,), dtype=x.dtype)
@@ -189,7 +194,7 @@ class Ref:
         return self._like(out)
 
     def reshape(self, new_shape):
-        return self._like(np.ascontiguousarray(self.a).reshape(new_shape))
+        return self._like(_c(self.a).reshape(new_shape))
 
     def slice_assign(self, ranges, value):
         out = np.array(self.a, copy=True)
@@ -204,7 +209,7 @@ class Ref:
         return self.slice([(start, start + length) if i == axis else (0, s) for i, s in enumerate(self.shape)])
 
     def unsqueeze(self, axis):
-        return self._like(np.expand_dims(np.ascontiguousarray(self.a), axis))
+        return self._like(np.expand_dims(_c(self.a), axis))
 
     # ---- composites: src/composite/*.rs ----
     def silu(self):
@@ -257,8 +262,8 @@ def arange(start, end, step=1.0, dtype=np.float32):
 
 def ulp_diff_f32(got, ref):
     """Elementwise distance in units in the last place (NaN matches NaN)."""
-    g = np.ascontiguousarray(got, dtype=np.float32).view(np.int32).astype(np.int64)
-    r = np.ascontiguousarray(ref, dtype=np.float32).view(np.int32).astype(np.int64)
+    g = _c(got, dtype=np.float32).view(np.int32).astype(np.int64)
+    r = _c(ref, dtype=np.float32).view(np.int32).astype(np.int64)
     g = np.where(g < 0, -(2 ** 31) - g, g)
     r = np.where(r < 0, -(2 ** 31) - r, r)
     d = np.abs(g - r)
@@ -270,8 +275,8 @@ def ulp_diff_f32(got, ref):
 
 
 def ulp_diff_f16(got, ref):
-    g = np.ascontiguousarray(got, dtype=np.float16).view(np.int16).astype(np.int64)
-    r = np.ascontiguousarray(ref, dtype=np.float16).view(np.int16).astype(np.int64)
+    g = _c(got, dtype=np.float16).view(np.int16).astype(np.int64)
+    r = _c(ref, dtype=np.float16).view(np.int16).astype(np.int64)
     g = np.where(g < 0, -(2 ** 15) - g, g)
     r = np.where(r < 0, -(2 ** 15) - r, r)
     d = np.abs(g - r)

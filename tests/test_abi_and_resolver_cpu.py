@@ -98,6 +98,40 @@ def test_memoisation_and_graph_growth(wgf, drydev):
     assert x.graph_size() <= n0 + 2
 
 
+def test_inplace_reuse_by_liveness(wgf, drydev):
+    """A tensor nobody can read any more donates its buffer (src/element_wise.rs:98-99,
+    src/pair_wise.rs:95-107); a held tensor never does (tests/inplace_clone.rs)."""
+    d = drydev
+    x = np.zeros((64, 64), np.float32)
+    cur = d.tensor(x)
+    base = d.memory()[0]
+    for _ in range(4):
+        nxt = cur + 1.0
+        cur.release()                       # `cur + 1.0` consumed cur
+        nxt.materialize()
+        cur = nxt
+    assert d.memory()[0] == base            # no second buffer was ever needed
+    held = d.tensor(x)
+    before = d.memory()[0]
+    y = held * 2.0
+    y.materialize()
+    assert d.memory()[0] > before           # held input: the result got its own buffer
+    # pair-wise: the dead operand donates, whichever side it is on
+    a, b = d.tensor(x), d.tensor(x)
+    before = d.memory()[0]
+    z = b - a
+    a.release()
+    z.materialize()
+    assert d.memory()[0] == before
+    # a cast to a narrower type cannot reuse the buffer
+    c = d.tensor(x)
+    before = d.memory()[0]
+    h = c.cast(wgf.F16)
+    c.release()
+    h.materialize()
+    assert d.memory()[0] > before
+
+
 def test_kernel_cache_reuses_by_signature(wgf, drydev):
     d = drydev
     x = d.tensor(np.zeros((16, 128), np.float32))

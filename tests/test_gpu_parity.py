@@ -289,7 +289,7 @@ def test_rope(dev, orc):
     np.testing.assert_allclose(got, x * c + rot * s, rtol=0, atol=1e-5)
 
 
-def test_memoised_and_inplace(dev, orc):
+def test_memoised_and_inplace(wgf, dev, orc):
     x = seeded(0, 7).standard_normal((64, 64)).astype(np.float32)
     t = dev.tensor(x)
     e = t.exp()
@@ -300,16 +300,32 @@ def test_memoised_and_inplace(dev, orc):
     assert_ulp(orc, b, (r * 2.0).numpy())
     np.testing.assert_array_equal(t.as_slice(), x)
     # a chain of materialised steps with dropped handles reuses buffers in place
+    import ctypes as C
+
+    def device_ptr(t):
+        d = t.desc()
+        p = C.c_void_p()
+        wgf.check(wgf.lib().wgf_buffer_device_ptr(C.c_void_p(d.buf), C.byref(p), None))
+        wgf.check(wgf.lib().wgf_buffer_release(C.c_void_p(d.buf)))   # drop the extra reference again
+        return p.value
+
     cur = dev.tensor(x)
     cur.materialize()
-    res0 = dev.memory()[1]
+    ptrs = [device_ptr(cur)]
     for _ in range(5):
         nxt = cur + 1.0
         cur.release()
         nxt.materialize()
         cur = nxt
-    assert dev.memory()[1] <= res0
+        ptrs.append(device_ptr(cur))
+    assert len(set(ptrs)) == 1, ptrs                  # every step wrote into the same buffer
     np.testing.assert_array_equal(cur.as_slice(), ((((x + 1) + 1) + 1) + 1) + 1)
+    # ... but never into a buffer whose tensor is still held
+    held = dev.tensor(x)
+    y = held + 1.0
+    y.materialize()
+    assert device_ptr(y) != device_ptr(held)
+    np.testing.assert_array_equal(held.as_slice(), x)
 
 
 def test_pinned_async_upload(wgf, dev, orc):

@@ -777,7 +777,10 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         }
     }
     if (donor) {
-        saved = std::move(donor->cached);
+        // The donor's cache lets go of the buffer, so that the slot holds the only reference
+        // (what the launcher checks).  Its layout is kept to put the cache back on failure.
+        saved.layout = donor->cached.layout;
+        saved.dtype = donor->cached.dtype;
         donor->cached = TensorData();
     }
     TensorData out;
@@ -786,7 +789,10 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace);
         else out = run_elementwise(dev, em.prog, em.slots, index_shape, inplace);
     } catch (...) {
-        if (donor) donor->cached = std::move(saved);
+        if (donor) {
+            saved.buf = em.slots[inplace].buf;
+            donor->cached = std::move(saved);
+        }
         throw;
     }
     out.layout.shape = root->shape;  // same element count and order; restores extent-1 axes
