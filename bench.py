@@ -332,7 +332,10 @@ def run_gpu(args):
                        "bytes_per_step_per_gpu": BYTES_STEP},
             "roofline": {"bound": "hbm", "kernel": "fused rmsnorm->softmax row kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "launch_ms": row_ms,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+                         # workload (ncu capture summarised under profiles/): 134.25 MB + 84.19 MB; the rest
+                         # of the 134 MB output is still dirty in L2 when the kernel ends
+                         "traffic": 218_444_800, "launch_ms": row_ms,
                          "sum_exp_kernel": {"achieved": BYTES_SUM / (sum_ms * 1e-3) / 1e9, "launch_ms": sum_ms,
                                             "frac": BYTES_SUM / (sum_ms * 1e-3) / 1e9 / peak}},
             "cpu_baseline": cpu_baseline,

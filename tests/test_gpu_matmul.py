@@ -111,7 +111,7 @@ def test_skinny_gemv(m, kind, wgf, dev):
 
 
 def test_config4_full_sizes(wgf, dev):
-    """BASELINE sizes; checked on sampled rows against float64 (size-independent: any row is as good as another)."""
+    """Full benchmark sizes; checked on sampled rows against float64 (size-independent: any row is as good as another)."""
     g = seeded(4, 0)
     n = 4096
     a = (g.random((n, n), dtype=np.float32) * 2 - 1)
