@@ -7,7 +7,9 @@
  * The crate has no CPU code for its ops: every op is a WGSL snippet evaluated by the GPU
  * driver's shader compiler, whose precision is implementation-defined.  This file restates
  * each snippet with these rules (the reference cannot be built or run here, so the values
- * are pinned by the known answers in the crate's own tests, see tests/test_reference_kats.py):
+ * are pinned by the known answers in the crate's own tests, see tests/test_reference_kats.py;
+ * past those answers and their tolerances -- the last bits a particular shader compiler gives
+ * a transcendental op -- PARITY IS UNPINNED, because no run of the crate exists to compare with):
  *   - element-wise / pair-wise: evaluate in double, round ONCE to the op's element type;
  *     chains apply op after op, each rounding on its own (src/element_wise.rs:64-79 emits one
  *     WGSL function per op, so no contraction across ops);
