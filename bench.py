@@ -3,9 +3,12 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Workload (one step, per GPU): x = f32 [8192, 4096] N(0,1) resident in HBM, w = f32 [4096] N(1, 0.1);
-  y = softmax_rows(rms_norm(x, w, eps 1e-5))      one fused row kernel, 268 451 840 algorithmic bytes
-  s = sum(exp(x)) over the whole tensor            one streaming reduce, 134 217 728 bytes
+  y = softmax_rows(rms_norm(x, w, eps 1e-5))      268 451 840 algorithmic bytes
+  s = sum(exp(x)) over the whole tensor            134 217 728 algorithmic bytes
       (+ an NCCL all-reduce of the per-GPU scalar when N > 1: rows are sharded, weak scaling)
+Both results are requested together, so one fused row kernel computes y and, from the same registers,
+the partial sums of s: x is read from HBM once.  --separate-kernels requests them one by one (row
+kernel, then a streaming reduce), which is all the reference's one-tensor-per-call API can express.
 Inputs are synthetic (seeded PCG64).  Four input buffers are rotated so that every step reads x
 from HBM, not from L2.  `value` = algorithmic bytes of all ranks / device time (CUDA events on the
 library's stream, max over ranks).  `e2e` = the same metric through the public C ABI with HOST
@@ -209,16 +212,24 @@ def run_gpu(args):
     w = dev.tensor(w_host)
     xs = [dev.tensor(make_inputs(rank, k)) for k in range(NBUF)]
 
-    def step(i, keep=None):
+    fused = not args.separate_kernels
+
+    def request(y, s):
+        # One request for both results: sum(exp(x)) rides along in the row kernel, which has every
+        # element of x in registers anyway (x is read from HBM once per step instead of twice).
+        if fused:
+            wgf.Tensor.materialize_all([y, s])
+        else:
+            y.materialize()
+            s.materialize()
+
+    def step(i):
         x = xs[i % NBUF]
         y = x.layer_norm(w, 1e-5).softmax_last_dim()
         s = x.exp().sum(0).sum(0)
         if comm is not None:
             s = s.all_reduce(comm)
-        y.materialize()
-        s.materialize()
-        if keep is not None:
-            keep.append((y, s))
+        request(y, s)
 
     def barrier():
         dev.sync()
@@ -256,13 +267,17 @@ def run_gpu(args):
         step(i)
     barrier()
     clocks = sampler.stop() if sampler else None
-    per_step = 3 if comm is not None else 2
+    kernels_per_step = 1 if fused else 2
+    per_step = kernels_per_step + (1 if comm is not None else 0)
     recs = xs[0].all_timing_information()[n_timing_before:]
-    row_ns, sum_ns = recs[0::per_step], recs[1::per_step]
+    row_ns = recs[0::per_step]
     row_ms = float(np.mean(row_ns)) / 1e6 if row_ns else float("nan")
-    sum_ms = float(np.mean(sum_ns)) / 1e6 if sum_ns else float("nan")
-    # what the all-reduce costs the device stream (a 4-byte copy; the collective itself runs beside it)
-    ar_ms = float(np.mean(recs[2::per_step])) / 1e6 if per_step == 3 and len(recs) >= 3 else None
+    sum_ms = None
+    if not fused:
+        sum_ns = recs[1::per_step]
+        sum_ms = float(np.mean(sum_ns)) / 1e6 if sum_ns else float("nan")
+    # what the all-reduce costs the device stream (the collective itself runs beside it)
+    ar_ms = float(np.mean(recs[kernels_per_step::per_step])) / 1e6 if comm is not None and len(recs) >= per_step else None
 
     # ---- end to end through the C ABI with host buffers ---------------------------------------
     # Every step uploads its own input from pinned host memory and downloads its results.  The
@@ -284,8 +299,7 @@ def run_gpu(args):
             s = x.exp().sum(0).sum(0)
             if comm is not None:
                 s = s.all_reduce(comm)
-            y.materialize()
-            s.materialize()
+            request(y, s)
             if i + 1 < n:
                 x_next = dev.tensor_pinned(pin_x[(i + 1) % 2])       # H2D of step i+1 ...
             y.download_into(pin_y.array)                             # ... beside the D2H of step i
@@ -311,7 +325,16 @@ def run_gpu(args):
         peak, peak_kind = measured_peak()
         ms_step = ms_total / args.steps
         value = BYTES_STEP * world / (ms_step * 1e-3) / 1e9
-        achieved = BYTES_CHAIN / (row_ms * 1e-3) / 1e9
+        # bytes the dominant kernel has to move per launch: x, w in, y out (+ the 4-byte scalar when
+        # the reduction rides along)
+        kernel_bytes = BYTES_CHAIN + (4 if fused else 0)
+        achieved = kernel_bytes / (row_ms * 1e-3) / 1e9
+        # ncu capture of one launch of this kernel on this workload (summary under profiles/)
+        traffic = None if fused else 218_444_800
+        sum_exp = None
+        if not fused:
+            sum_exp = {"achieved": BYTES_SUM / (sum_ms * 1e-3) / 1e9, "launch_ms": sum_ms,
+                       "frac": BYTES_SUM / (sum_ms * 1e-3) / 1e9 / peak}
         # CPU baseline on rank 0, N=1 only: the oracle's fast mode on the full workload
         cpu_baseline = None
         if world == 1 and not args.no_cpu:
@@ -329,15 +352,17 @@ def run_gpu(args):
             "config": {"workload": "rmsnorm->softmax rows + sum(exp(x)), f32 [8192,4096] per GPU",
                        "rows_per_gpu": ROWS, "row_len": H, "sharding": "rows" if world > 1 else "none",
                        "l2": f"{NBUF} input buffers of 128 MiB rotated: inputs larger than L2",
-                       "bytes_per_step_per_gpu": BYTES_STEP},
-            "roofline": {"bound": "hbm", "kernel": "fused rmsnorm->softmax row kernel", "achieved": achieved,
-                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
-                         # workload (ncu capture summarised under profiles/): 134.25 MB + 84.19 MB; the rest
-                         # of the 134 MB output is still dirty in L2 when the kernel ends
-                         "traffic": 218_444_800, "launch_ms": row_ms,
-                         "sum_exp_kernel": {"achieved": BYTES_SUM / (sum_ms * 1e-3) / 1e9, "launch_ms": sum_ms,
-                                            "frac": BYTES_SUM / (sum_ms * 1e-3) / 1e9 / peak}},
+                       "bytes_per_step_per_gpu": BYTES_STEP,
+                       "kernels_per_step": kernels_per_step,
+                       "note": ("value counts the algorithmic bytes of both results, x once for each "
+                                "(268 451 840 + 134 217 728); with both requested together one kernel reads x once "
+                                "and moves 268 451 844 bytes, which is what roofline.achieved counts"
+                                if fused else "two kernels per step: row kernel, then streaming reduce")},
+            "roofline": {"bound": "hbm",
+                         "kernel": "fused rmsnorm->softmax row kernel" + (" with sum(exp(x)) riding along" if fused else ""),
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "launch_ms": row_ms,
+                         "bytes_per_launch": kernel_bytes, "sum_exp_kernel": sum_exp},
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": BYTES_STEP * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "steps": e2e_steps, "h2d_bytes_per_step": ROWS * H * 4, "d2h_bytes_per_step": ROWS * H * 4 + 4},
@@ -438,23 +463,46 @@ def run_llama(args):
         dist.destroy_process_group()
 
 
+def run_configs(args):
+    """--workload configs: every benchmark configuration on one GPU, one JSON object per row
+    (the sweep itself is wgpu-kernal-fusion_b200/config_sweep.py)."""
+    wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
+    sweep = load("wgf_b200_config_sweep", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "config_sweep.py"))
+    peak_gbs, which = measured_peak()
+    peak_tf = 1590.0
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak_tf = float(json.load(f).get("bf16_tflops", peak_tf))
+    dev = wgf.Device(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler = ClockSampler(0)
+    rows = sweep.run(wgf, dev, peak_gbs, peak_tf, iters=args.steps, warmup=max(args.warmup, 3))
+    print(json.dumps({"workload": "configs", "rows": len(rows), "peak_hbm_gbs": peak_gbs, "peak_bf16_tflops": peak_tf,
+                      "peaks": which, "clocks": sampler.stop()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="wgf", choices=["wgf", "reference"])
-    ap.add_argument("--workload", default="fused_chain", choices=["fused_chain", "llama_block"])
+    ap.add_argument("--workload", default="fused_chain", choices=["fused_chain", "llama_block", "configs"])
     ap.add_argument("--seq", type=int, default=2048, help="sequence length of the llama_block workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--separate-kernels", action="store_true",
+                    help="fused_chain: request the two results one by one (row kernel, then streaming reduce)")
     args = ap.parse_args()
     llama = args.workload == "llama_block"
+    configs = args.workload == "configs"
     if args.steps is None:
-        args.steps = 10 if llama else 2000
+        args.steps = 10 if llama else 30 if configs else 2000
     if args.warmup is None:
-        args.warmup = 3 if llama else 200
+        args.warmup = 3 if llama else 5 if configs else 200
     if args.impl == "reference":
         run_reference(args)
+    elif configs:
+        run_configs(args)
     elif llama:
         run_llama(args)
     else:

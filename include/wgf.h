@@ -247,6 +247,14 @@ int32_t wgf_tensor_llama_block(wgf_tensor* x, wgf_tensor* const* weights, wgf_te
 /* LazyTensorData::materialize, src/tensor.rs:286-288: resolves the graph below `t`
  * (src/compute_graph/resolve.rs:16-248) and queues its kernels; does not wait. */
 int32_t wgf_tensor_materialize(wgf_tensor* t);
+/* Materialises `n` tensors as one request.  Same results as n calls of wgf_tensor_materialize;
+ * in addition, a reduction of a whole tensor to a scalar (e.g. t.sum(0).sum(0), also below
+ * wgf_tensor_all_reduce) that is requested together with a row-fused tensor over the same
+ * index space (layer_norm, softmax_last_dim, ...) is computed inside that tensor's kernel and
+ * reads nothing from memory a second time.  No counterpart in the crate, which resolves one
+ * tensor per call (src/tensor.rs:551-554) and names sibling-reduce fusion as future work
+ * (README.md:19-22). */
+int32_t wgf_tensor_materialize_many(wgf_tensor* const* tensors, uint32_t n);
 /* The layout and buffer of the materialised result (TensorData, src/tensor.rs:300-306).
  * `out->buf` is a new reference. */
 int32_t wgf_tensor_desc_of(wgf_tensor* t, wgf_tensor_desc* out);

@@ -80,6 +80,37 @@ def test_fusion_decisions(wgf, drydev):
     assert launches(d, lambda: x.transpose(0, 1).reshape((128, 256))) == 1
 
 
+def test_whole_tensor_reductions_ride_along_in_a_row_kernel(wgf, drydev):
+    """materialize_all: reductions of a whole tensor to a scalar requested together with a row-fused
+    tensor over the same index space cost no kernel of their own (the crate's README lists fusing
+    parallel reduce ops as an open item, README.md:20)."""
+    d = drydev
+    x = d.tensor(np.zeros((64, 512), np.float32))
+    w = d.tensor(np.zeros((512,), np.float32))
+    z = d.tensor(np.zeros((32, 512), np.float32))
+
+    def count(build):
+        before = d.launch_count
+        ts = build()
+        wgf.Tensor.materialize_all(ts)
+        again = d.launch_count
+        wgf.Tensor.materialize_all(ts)            # everything is cached now
+        assert d.launch_count == again
+        return again - before
+
+    assert count(lambda: [x.layer_norm(w, 1e-5).softmax_last_dim(), x.exp().sum(0).sum(0)]) == 1
+    assert count(lambda: [x.sum(1).sum(0), x.softmax_last_dim(), x.max(0).max(0), (x * x).sum(0).sum(0)]) == 1
+    assert count(lambda: [x.softmax_last_dim(), (x * w.broadcast((64, 512))).min(1).min(0)]) == 1
+    # no row kernel to ride in, another index space, or not a scalar: separate kernels as before
+    assert count(lambda: [x + 1.0, x.sum(0).sum(0)]) == 2
+    assert count(lambda: [x.softmax_last_dim(), z.sum(0).sum(0)]) == 2
+    assert count(lambda: [x.softmax_last_dim(), x.sum(0)]) == 2
+    # a reduction the row kernel itself depends on is computed first, not alongside
+    s = x.sum(0).sum(0)
+    y = x.softmax_last_dim() * s.broadcast((512,)).broadcast((64, 512))
+    assert count(lambda: [y, s]) == 2
+
+
 def test_memoisation_and_graph_growth(wgf, drydev):
     d = drydev
     x = d.tensor(np.zeros((32, 32), np.float32))

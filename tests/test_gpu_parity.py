@@ -370,3 +370,45 @@ def test_errors_do_not_abort(wgf, dev):
         a.narrow(1, 2, 5)
     with pytest.raises(wgf.WgfError):
         wgf.Device(99)
+
+
+@pytest.mark.parametrize("shape", [(300, 1000), (8192, 512), (7, 33), (5, 6, 64), (1, 4096)])
+def test_reductions_riding_along_match_the_oracle(shape, wgf, dev, orc):
+    """materialize_all: whole-tensor reductions computed inside the row kernel of a tensor requested
+    with them.  Same values as the separate kernels (reductions: 1e-5 relative)."""
+    g = seeded(2, 7)
+    x = g.standard_normal(shape, dtype=np.float32)
+    w = (1.0 + 0.1 * g.standard_normal(shape[-1])).astype(np.float32)
+    tx, tw = dev.tensor(x), dev.tensor(w)
+    y = tx.layer_norm(tw, 1e-5).softmax_last_dim() if len(shape) == 2 else tx.softmax_last_dim()
+    s, m, q = tx.exp(), tx, tx * tx
+    for _ in shape:
+        s, m, q = s.sum(0), m.max(0), q.sum(0)
+    before = dev.launch_count
+    wgf.Tensor.materialize_all([y, s, m, q])
+    assert dev.launch_count - before == 1
+    rx, rw = orc.Ref(x), orc.Ref(w)
+    ry = rx.layer_norm(rw, 1e-5).softmax_last_dim() if len(shape) == 2 else rx.softmax_last_dim()
+    assert_rel(y.as_slice(), ry.numpy(), 1e-4)
+    x64 = x.astype(np.float64)
+    assert_rel(s.as_slice(), np.float32(np.exp(x64).sum()), 1e-5)
+    assert float(m.as_slice()) == float(x.max())
+    assert_rel(q.as_slice(), np.float32((x64 * x64).sum()), 1e-5)
+    # the same requests one by one give the same answers
+    s2 = tx.exp()
+    for _ in shape:
+        s2 = s2.sum(0)
+    assert_rel(s2.as_slice(), s.as_slice(), 1e-5)
+
+
+def test_reduction_riding_along_f16_and_all_results_cached(wgf, dev, orc):
+    g = seeded(2, 8)
+    x = g.standard_normal((96, 256), dtype=np.float32).astype(np.float16)
+    tx = dev.tensor(x)
+    y, mx = tx.softmax_last_dim(), tx.max(1).max(0)
+    wgf.Tensor.materialize_all([mx, y])
+    before = dev.launch_count
+    assert float(mx.as_slice()) == float(x.max())
+    d = orc.ulp_diff_f16(y.as_slice(), orc.Ref(x).softmax_last_dim().numpy())
+    assert int(d.max()) <= 2
+    assert dev.launch_count == before          # both were computed by the one request

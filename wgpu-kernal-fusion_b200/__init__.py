@@ -340,6 +340,14 @@ class Tensor:
         check(lib().wgf_tensor_materialize(self.h))
         return self
 
+    @staticmethod
+    def materialize_all(tensors):
+        """One request for several tensors: a whole-tensor reduction among them rides along in the
+        row kernel of another one over the same index space (wgf_tensor_materialize_many)."""
+        arr = (C.c_void_p * len(tensors))(*[t.h for t in tensors])
+        check(lib().wgf_tensor_materialize_many(arr, C.c_uint32(len(tensors))))
+        return tensors
+
     def desc(self):
         d = TensorDesc()
         check(lib().wgf_tensor_desc_of(self.h, C.byref(d)))

@@ -1,0 +1,148 @@
+"""Times every benchmark configuration on one GPU and prints one JSON object per row.
+
+Run as  python bench.py --workload configs  (one GPU).  Each row builds its lazy graph afresh every
+iteration, materialises it with per-kernel timestamps on (the crate's own method: timestamp queries
+around each dispatch, benches/elementwise.rs:42-43) and reports, per iteration, the median over the
+iterations of the summed kernel times.  Inputs larger than the 126 MB L2 are reused as they are;
+smaller inputs rotate through enough copies to exceed L2 ("cold") and are also timed on one copy
+("warm").  `bytes` / `flop` are the algorithmic figures of the row, so GB/s and TFLOP/s are
+algorithmic too.
+"""
+import collections
+import json
+
+import numpy as np
+
+SEED = 0xB2000000
+
+
+def rng(config, index):
+    return np.random.Generator(np.random.PCG64(SEED + 16 * config + index))
+
+
+def uniform(g, shape, lo, hi):
+    return (g.random(shape, dtype=np.float32) * (hi - lo) + lo).astype(np.float32)
+
+
+def normal(g, shape, mu=0.0, sigma=1.0):
+    return (g.standard_normal(shape, dtype=np.float32) * sigma + mu).astype(np.float32)
+
+
+class Row:
+    def __init__(self, name, build, nbytes=None, flop=None, variants=1, note=""):
+        self.name, self.build, self.nbytes, self.flop, self.variants, self.note = name, build, nbytes, flop, variants, note
+
+
+def time_row(dev, row, iters, warmup):
+    # A tensor reports the timestamps of every kernel its (merged) graph has run so far, the
+    # inputs' earlier iterations included: one iteration's share is the growth of the total.
+    per_iter, labels = [], None
+    total_before, labels_before = 0, collections.Counter()
+    for i in range(warmup + iters):
+        t = row.build(i % row.variants)
+        if row.variants > 1:
+            probe = row.build(i % row.variants)
+            total_before = sum(probe.all_timing_information())
+            labels_before = collections.Counter(probe.timing_labels())
+            probe.release()
+        t.materialize()
+        dev.sync()
+        total = sum(t.all_timing_information())
+        names = collections.Counter(t.timing_labels())
+        if i >= warmup:
+            per_iter.append(total - total_before)
+            if labels is None:
+                labels = dict(names - labels_before)
+        total_before, labels_before = total, names
+        t.release()
+    per_iter.sort()
+    return per_iter[len(per_iter) // 2] * 1e-3, per_iter[0] * 1e-3, labels
+
+
+def rows_for(wgf, dev, peak_gbs):
+    out = []
+    F16 = wgf.F16
+
+    # C1: y = cos(sin(x*2+1))*0.5 + exp(-x*x) on [1024,1024] f32; 64 copies of x = 256 MiB for the cold run
+    x1 = [dev.tensor(uniform(rng(1, k), (1024, 1024), -1, 1)) for k in range(64)]
+
+    def c1(x):
+        return (x * 2.0 + 1.0).sin().cos() * 0.5 + (-(x * x)).exp()
+    out.append(Row("C1 chain f32 [1024,1024] cold", lambda k: c1(x1[k]), nbytes=8388608, variants=64))
+    out.append(Row("C1 chain f32 [1024,1024] warm", lambda k: c1(x1[0]), nbytes=8388608))
+    xb = dev.tensor(uniform(rng(1, 100), (8192, 4096), -1, 1))
+    out.append(Row("C1' chain f32 [8192,4096]", lambda k: c1(xb), nbytes=2 * 134217728))
+    out.append(Row("x*2+1 f32 [8192,4096]", lambda k: xb * 2.0 + 1.0, nbytes=2 * 134217728))
+
+    # C2
+    x2 = dev.tensor(normal(rng(2, 0), (8192, 4096)))
+    w2 = dev.tensor(normal(rng(2, 1), (4096,), 1.0, 0.1))
+    normed = x2.layer_norm(w2, 1e-5)
+    normed.materialize()
+    out.append(Row("C2a RmsNorm rows f32 [8192,4096]", lambda k: x2.layer_norm(w2, 1e-5), nbytes=268451840))
+    out.append(Row("C2b softmax rows f32 [8192,4096]", lambda k: normed.softmax_last_dim(), nbytes=268435456))
+    out.append(Row("C2ab RmsNorm->softmax f32 [8192,4096]", lambda k: x2.layer_norm(w2, 1e-5).softmax_last_dim(),
+                   nbytes=268451840))
+    out.append(Row("C2c sum(exp(x)) f32 [8192,4096]", lambda k: x2.exp().sum(0).sum(0), nbytes=134217728))
+    out.append(Row("sum(x) all f32 [8192,4096]", lambda k: x2.sum(0).sum(0), nbytes=134217728))
+    out.append(Row("sum(x, axis 1) f32 [8192,4096]", lambda k: x2.sum(1), nbytes=134217728 + 32768))
+    out.append(Row("max(x, axis 1) f32 [8192,4096]", lambda k: x2.max(1), nbytes=134217728 + 32768))
+    out.append(Row("sum(x, axis 0) f32 [8192,4096]", lambda k: x2.sum(0), nbytes=134217728 + 16384))
+
+    # C3
+    a = dev.tensor(normal(rng(3, 0), (64, 512, 1024)))
+    b = dev.tensor(uniform(rng(3, 1), (512, 1024), -1, 1))
+    c = dev.tensor(uniform(rng(3, 2), (64, 1024), 0, 1))
+    bv = b.broadcast((64, 512, 1024))
+    cv = c.broadcast_axis(1, 512)
+    out.append(Row("C3a silu(a*1.5)+b*c f32 [64,512,1024]", lambda k: (a * 1.5).silu() + bv * cv, nbytes=270794752))
+    at, bt, ct = a.transpose(0, 1), bv.transpose(0, 1), cv.transpose(0, 1)
+    out.append(Row("C3b same, operands permuted (1,0,2)", lambda k: (at * 1.5).silu() + bt * ct, nbytes=270794752))
+    a12, b12, c12 = a.transpose(1, 2), bv.transpose(1, 2), cv.transpose(1, 2)
+    out.append(Row("C3b' same, a.transpose(1,2): strided inner axis", lambda k: (a12 * 1.5).silu() + b12 * c12,
+                   nbytes=270794752))
+    out.append(Row("C3c cast f32->f16->f32 [64,512,1024]", lambda k: a.cast(F16).cast(wgf.F32), nbytes=268435456))
+    out.append(Row("cast f32->f16 [64,512,1024]", lambda k: a.cast(F16), nbytes=134217728 + 67108864))
+    out.append(Row("reshape of a.transpose(1,2) (gather) f32", lambda k: a12.reshape((64 * 1024, 512)), nbytes=268435456))
+
+    # C4
+    n = 4096
+    af = dev.tensor(uniform(rng(4, 0), (n, n), -1, 1))
+    bf = dev.tensor(uniform(rng(4, 1), (n, n), -1, 1))
+    ah, bh = af.cast(F16), bf.cast(F16)
+    ah.materialize(), bh.materialize()
+    out.append(Row("C4a matmul f32 4096^3", lambda k: af.mat_mul(bf), flop=2 * n ** 3))
+    out.append(Row("C4b matmul f16 4096^3", lambda k: ah.mat_mul(bh), flop=2 * n ** 3))
+    out.append(Row("C4b matmul f16 4096^3, B transposed view", lambda k: ah.mat_mul(bh.transpose(0, 1)), flop=2 * n ** 3))
+    a3 = dev.tensor(uniform(rng(4, 2), (32, 1024, 128), -1, 1).astype(np.float16))
+    b3 = dev.tensor(uniform(rng(4, 3), (32, 128, 1024), -1, 1).astype(np.float16))
+    out.append(Row("C4c batched f16 [32,1024,128]x[32,128,1024]", lambda k: a3.mat_mul(b3), nbytes=83886080, flop=8589934592))
+    xv = dev.tensor(uniform(rng(4, 4), (1, 4096), -1, 1).astype(np.float16))
+    wv = dev.tensor(uniform(rng(4, 5), (4096, 11008), -1, 1).astype(np.float16))
+    wt = dev.tensor(uniform(rng(4, 6), (11008, 4096), -1, 1).astype(np.float16))
+    out.append(Row("C4d GEMV f16 [1,4096]x[4096,11008]", lambda k: xv.mat_mul(wv), nbytes=90207744))
+    out.append(Row("C4d GEMV f16, weight stored [11008,4096]", lambda k: xv.mat_mul(wt.transpose(0, 1)), nbytes=90207744))
+    return out
+
+
+def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, emit=print):
+    dev.set_timing(True)
+    results = []
+    for row in rows_for(wgf, dev, peak_gbs):
+        med, best, labels = time_row(dev, row, iters, warmup)
+        med = max(med, 1e-9)          # the compile-only device records no time
+        r = {"row": row.name, "kernels": labels, "median_us": round(med, 2), "best_us": round(best, 2)}
+        if row.nbytes:
+            r["gbs"] = round(row.nbytes / med / 1e3, 1)
+            r["frac_hbm"] = round(row.nbytes / med / 1e3 / peak_gbs, 3)
+        if row.flop:
+            r["tflops"] = round(row.flop / med / 1e6, 1)
+            if not row.nbytes and "f32" in row.name:
+                # FFMA peak: 148 SMs x 128 lanes x 2 flop at the 1965 MHz maximum clock
+                r["frac_ffma_peak"] = round(row.flop / med / 1e6 / 74.5, 3)
+            elif not row.nbytes:
+                r["frac_bf16_peak"] = round(row.flop / med / 1e6 / peak_tflops, 3)
+        results.append(r)
+        emit(json.dumps(r))
+    dev.set_timing(False)
+    return results

@@ -743,6 +743,18 @@ int32_t wgf_tensor_materialize(wgf_tensor* t) {
     })
 }
 
+int32_t wgf_tensor_materialize_many(wgf_tensor* const* tensors, uint32_t n) {
+    GRAPH_GUARD({
+        if (n > 0) REQUIRE(tensors);
+        std::vector<NodeRef> nodes;
+        for (uint32_t i = 0; i < n; ++i) {
+            REQUIRE(tensors[i]);
+            nodes.push_back(tensors[i]->node);
+        }
+        resolve_many(nodes);
+    })
+}
+
 int32_t wgf_tensor_desc_of(wgf_tensor* t, wgf_tensor_desc* out) {
     GRAPH_GUARD({
         REQUIRE(t);

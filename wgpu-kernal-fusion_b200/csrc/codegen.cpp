@@ -123,6 +123,9 @@ int tune(const char* name, int dflt) {
     return v ? atoi(v) : dflt;
 }
 
+// The helpers every generated kernel starts with.
+std::string prelude() { return JIT_PRELUDE; }
+
 int pow2_at_least(int64_t v) {
     int p = 1;
     while (p < v) p <<= 1;
@@ -189,13 +192,14 @@ std::string ew_prog_text(const Program& prog) {
 struct EwConfig {
     int R, C, U, idx64, out_mode;
     std::vector<int> mode;  // per input slot
+    int minb = 1;
 };
 
 std::string ew_source(const Program& prog, const EwConfig& c) {
     std::ostringstream s;
-    s << JIT_PRELUDE;
+    s << prelude();
     s << "#define R " << c.R << "\n#define NIN " << prog.n_slots() << "\n#define C " << c.C
-      << "\n#define U " << c.U << "\n#define IDX64 " << c.idx64 << "\n#define NIMM "
+      << "\n#define U " << c.U << "\n#define MINB " << c.minb << "\n#define IDX64 " << c.idx64 << "\n#define NIMM "
       << prog.imms.size() << "\n#define OUT_DT " << (int)prog.out_dtype() << "\n#define OUT_MODE "
       << c.out_mode << "\n";
     s << ew_prog_text(prog);
@@ -237,8 +241,19 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
         for (int d = 0; strided_inner && d < r - 1; ++d) other_contig |= l.strides[d] == 1 && l.shape[d] >= 8;
         if (strided_inner && other_contig) {
             if (ins.empty()) ins = in;
-            ins[t] = run_compact(dev, in[t]);
-            if (inplace_slot < 0) inplace_slot = (int)t;
+            // only the distinct elements are moved: axes of stride 0 stay broadcast
+            TensorData core = in[t];
+            for (int d = 0; d < r; ++d)
+                if (l.strides[d] == 0) core.layout.shape[d] = 1;
+            ins[t] = run_compact(dev, core);
+            bool broadcast = false;
+            for (int d = 0; d < r; ++d)
+                if (l.strides[d] == 0 && l.shape[d] > 1) {
+                    ins[t].layout.shape[d] = l.shape[d];
+                    ins[t].layout.strides[d] = 0;
+                    broadcast = true;
+                }
+            if (inplace_slot < 0 && !broadcast) inplace_slot = (int)t;
         }
     }
     return run_elementwise_impl(dev, prog, ins.empty() ? in : ins, shape, inplace_slot);
@@ -299,12 +314,17 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
     for (int t = 0; t < nin; ++t) cfg.mode[t] = classify(in[t], st[t]);
     cfg.out_mode = classify(out, st[nin]);
     const int64_t nchunks = (n + cfg.C - 1) / cfg.C;
-    int umax = std::max(1, std::min(4, 64 / (nin * cfg.C)));
+    // U chunks per thread are loaded before the first is used, at most EW_BUDGET input values
+    // held as floats.  Measured on B200: 16 beats 32 and 64 on every chain with two or more
+    // inputs or 16-bit elements (f16 a+b 142 -> 83 us, f16 silu(a)*b 277 -> 120 us on
+    // [8192,11008]): residency of more CTAs hides latency better than deeper unrolling.
+    int umax = std::max(1, std::min(4, tune("EW_BUDGET", 16) / (nin * cfg.C)));
     int64_t want = nchunks / (256ll * 4 * dev.sm_count);
     cfg.U = (int)std::max<int64_t>(1, std::min<int64_t>(umax, want));
+    cfg.minb = tune("EW_MINB", 1);
 
     std::ostringstream key;
-    key << "ew|" << R << "|" << cfg.C << "|" << cfg.U << "|" << cfg.idx64 << "|" << cfg.out_mode << "|";
+    key << "ew|" << R << "|" << cfg.C << "|" << cfg.U << "|" << cfg.minb << "|" << cfg.idx64 << "|" << cfg.out_mode << "|";
     for (int m : cfg.mode) key << m;
     key << "|" << prog.signature();
     const JitKernel& k = dev.kernel(key.str(), "wgf_elementwise", [&] { return ew_source(prog, cfg); });
@@ -352,11 +372,11 @@ void replace_all(std::string& text, const std::string& marker, const std::string
 
 std::string row_source(const Program& prog, const RowConfig& c) {
     std::ostringstream s;
-    s << JIT_PRELUDE;
+    s << prelude();
     s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define C " << c.C
       << "\n#define NCH " << c.NCH << "\n#define GROUP " << c.GROUP << "\n#define RPC " << c.RPC
       << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM " << prog.imms.size()
-      << "\n#define MINB " << c.minb << "\n";
+      << "\n#define MINB " << c.minb << "\n#define NGRAND " << prog.grands.size() << "\n";
     // inv: loaded once per CTA; decl/pre/take: double-buffered per-row loads; b: per-row body
     std::ostringstream inv, decl, pre, take, b;
     int red_idx = 0;
@@ -441,11 +461,34 @@ std::string row_source(const Program& prog, const RowConfig& c) {
     } else {
         b << "if (crv && t == 0) store1<" << odt << ">((void*)p.ptr[NIN], coff[NIN], " << vn(res) << ");\n";
     }
+    // companion whole-tensor reductions: accumulated per thread over all its rows
+    std::ostringstream gblock, gput, gfinish;
+    for (int gi = 0; gi < (int)prog.grands.size(); ++gi) {
+        const Grand& gr = prog.grands[gi];
+        const char* op = red_name(gr.op);
+        const std::string id = std::to_string(gi);
+        inv << "float ga" << id << " = red_ident<" << op << ">();\n";
+        b << "\n#pragma unroll\n for (int k = 0; k < NCH; ++k) if (kv[k]) {\n"
+          << "  \n#pragma unroll\n for (int j = 0; j < C; ++j) ga" << id << " = red_comb<" << op << ">(ga" << id << ", "
+          << operand(gr.a, "k * C + j") << "); }\n";
+        gblock << "const float gp" << id << " = group_reduce<" << op << ", THREADS>(ga" << id << ", g_smem[" << id
+               << "], (int)threadIdx.x);\n";
+        gput << "gpart[(u64)blockIdx.x * NGRAND + " << id << "] = gp" << id << ";\n";
+        gfinish << "{ float a_ = red_ident<" << op << ">();\n"
+                << "  for (u32 b_ = threadIdx.x; b_ < gridDim.x; b_ += THREADS) a_ = red_comb<" << op
+                << ">(a_, __ldcg(gpart + (u64)b_ * NGRAND + " << id << "));\n"
+                << "  __syncthreads();\n  a_ = group_reduce<" << op << ", THREADS>(a_, g_smem[" << id
+                << "], (int)threadIdx.x);\n  if (threadIdx.x == 0) store1<" << (int)gr.dtype << ">((void*)p.gout[" << id
+                << "], 0, a_); }\n";
+    }
     // A group_reduce reuses its shared-memory slot in the next iteration: all reads of this
     // iteration must be done before the next row writes.
     // (with two or more reductions the barrier of the second one already orders that)
     if (c.GROUP > 32 && prog.n_reduces() == 1) b << "__syncthreads();\n";
     std::string tmpl = JIT_ROW_KERNEL;
+    replace_all(tmpl, "ROW_GRAND_BLOCK", gblock.str());
+    replace_all(tmpl, "ROW_GRAND_PUT", gput.str());
+    replace_all(tmpl, "ROW_GRAND_FINISH", gfinish.str());
     replace_all(tmpl, "ROW_INVARIANT", inv.str());
     replace_all(tmpl, "ROW_NEXT_DECL", decl.str());
     replace_all(tmpl, "ROW_PREFETCH", pre.str());
@@ -527,7 +570,7 @@ std::string stream_source(const Program& prog, const StreamConfig& c) {
                  << ", p.cstride[" << t << "], NV, X[" << eslot[t] << "]); ";
 
     std::ostringstream s;
-    s << JIT_PRELUDE;
+    s << prelude();
     s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define NINE " << nine
       << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces()
       << "\n#define NIMM " << prog.imms.size() << "\n#define MINB " << c.minb << "\n";
@@ -617,7 +660,7 @@ std::string col_source(const Program& prog, const ColConfig& c) {
           << " + " << (c.mode[t] == 2 ? "0" : "(i64)col") << ", 1, C, X[" << (c.is_row[t] ? rslot[t] : eslot[t]) << "]); ";
     }
     std::ostringstream s;
-    s << JIT_PRELUDE;
+    s << prelude();
     s << "#define NIN " << prog.n_slots() << "\n#define NINE " << nine << "\n#define NROWL " << nrowl << "\n#define NPRE "
       << npre << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM "
       << prog.imms.size() << "\n#define OUT_DT " << (int)prog.out_dtype() << "\n#define OUT_MODE " << c.out_mode << "\n";
@@ -639,12 +682,15 @@ std::string col_source(const Program& prog, const ColConfig& c) {
 int64_t max_resident_row(bool) { return 32768; }
 
 TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
-                    const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot) {
+                    const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot,
+                    std::vector<TensorData>* grand_out) {
     const int nin = prog.n_slots();
     WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
     WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
     for (auto& t : in) dev.wait_for(*t.buf);   // inputs still owned by a collective
     WGF_CHECK(!shape.empty(), WGF_ERR_RANK, "row kernel needs rank >= 1");
+    WGF_CHECK(prog.grands.empty() || (out_has_h && grand_out && prog.grands.size() <= 4), WGF_ERR_INVALID_ARGUMENT,
+              "companion reductions need a per-element result");
     WGF_CHECK(out_has_h || prog.out_kind() == VKind::Row, WGF_ERR_INVALID_ARGUMENT,
               "a per-element result needs an output with the row axis");
     const DType out_dt = prog.out_dtype();
@@ -665,6 +711,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
         out.layout = Layout::contiguous(out_shape);
         out.dtype = out_dt;
     }
+    WGF_CHECK(prog.grands.empty() || n_out > 0, WGF_ERR_INVALID_ARGUMENT, "companion reductions over an empty index space");
     if (n_out == 0) return out;
     WGF_CHECK(rows < (1ll << 31), WGF_ERR_UNSUPPORTED, "too many rows for one launch");
 
@@ -845,14 +892,18 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             pick_modes(1, cfg.mode, cfg.out_mode, true);
         }
         const int64_t chunks = (H + cfg.C - 1) / cfg.C;
-        const int target = std::max(1, tune("ROW_EPT", 16) / cfg.C);
+        // elements of the row per thread: 16 floats, or 32 values of a 16-bit type (the same 64
+        // bytes in flight per thread and row)
+        const int target = std::max(1, tune("ROW_EPT", any16 ? 32 : 16) / cfg.C);
         cfg.GROUP = std::min(1024, std::max(32, pow2_at_least((chunks + target - 1) / target)));
         cfg.NCH = (int)((chunks + cfg.GROUP - 1) / cfg.GROUP);
         WGF_CHECK(cfg.NCH * cfg.C <= 64, WGF_ERR_UNSUPPORTED, "row too long for a row-fused kernel");
         int threads = std::max(cfg.GROUP, 128);
         cfg.RPC = threads / cfg.GROUP;
         cfg.minb = tune("ROW_MINB", std::max(1, std::min(4, 768 / threads)));
-        cfg.prefetch = tune("ROW_PREFETCH", 1) != 0;
+        // the next row is loaded ahead in f32 kernels; with 16-bit rows the converted copy costs
+        // too many registers (measured: f16 softmax rows 333 us with, 245 us without)
+        cfg.prefetch = tune("ROW_PREFETCH", any16 ? 0 : 1) != 0;
         cfg.invariant.assign(nin, 0);
         for (int t = 0; t < nin; ++t) {
             bool inv = true;
@@ -867,15 +918,31 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
         for (int v : cfg.invariant) key << v;
         key << "|" << prog.signature();
         const JitKernel& k = dev.kernel(key.str(), "wgf_rows", [&] { return row_source(prog, cfg); });
-        ParamWriter w;
-        put_common(w);
-        w.put<uint32_t>((uint32_t)H);
-        w.put<uint32_t>(0);
-        put_tail(w);
         // persistent CTAs: as many as fit on the machine at once, each walking several rows
         int64_t blocks = (rows + cfg.RPC - 1) / cfg.RPC;
         if (tune("ROW_PERSIST", 1))
             blocks = std::min<int64_t>(blocks, (int64_t)dev.sm_count * dev.max_blocks_per_sm(k, cfg.GROUP * cfg.RPC));
+        ParamWriter w;
+        put_common(w);
+        w.put<uint32_t>((uint32_t)H);
+        w.put<uint32_t>(0);
+        BufferRef gpartials;
+        if (!prog.grands.empty()) {
+            const size_t ng = prog.grands.size();
+            gpartials = dev.alloc((size_t)blocks * ng * sizeof(float), false);
+            w.put<uint64_t>((uint64_t)(uintptr_t)gpartials->ptr);
+            w.put<uint64_t>((uint64_t)(uintptr_t)dev.counters());
+            grand_out->clear();
+            for (const Grand& gr : prog.grands) {
+                TensorData g;
+                g.buf = dev.alloc(dtype_size(gr.dtype), false);
+                g.layout = Layout::contiguous({});
+                g.dtype = gr.dtype;
+                w.put<uint64_t>((uint64_t)(uintptr_t)g.base_ptr());
+                grand_out->push_back(g);
+            }
+        }
+        put_tail(w);
         dev.launch(k, dim3((unsigned)blocks), dim3(cfg.GROUP * cfg.RPC), 0, w.bytes.data(), "rows");
         return out;
     }

@@ -729,16 +729,68 @@ void plan_region(Region& rg, bool allow_fold) {
     rg.fold_x = base;
 }
 
+// Nodes requested together with `g_companion_host` (resolve_many): whole-tensor reductions
+// that may ride along in the host's row kernel, which already has every element in registers.
+thread_local Node* g_companion_host = nullptr;
+thread_local std::vector<Node*>* g_companions = nullptr;
+
+// The per-element expression under a reduction (or folded chain of reductions) of a whole
+// tensor of shape `E` to a scalar; nullptr if `c` is not of that form.
+Node* companion_expr(Node* c, const std::vector<int64_t>& E) {
+    if (c->cached || c->kind != NodeKind::Reduce || c->rank() != 0) return nullptr;
+    Region cr;
+    cr.root = c;
+    plan_region(cr, true);
+    if (!cr.Rw.empty() || cr.E != E) return nullptr;
+    return cr.fold_top ? cr.fold_x : c->inputs[0].get();
+}
+
+// Adds the element-wise nodes under `n` to the host region `rg` (same index space); anything
+// else becomes an input of the kernel.
+void gather_companion(Node* n, Region& rg) {
+    if (rg.visited.count(n)) return;   // already computed by the host
+    if (!n->cached && is_ew(n) && n->shape == rg.E) {
+        rg.visited.insert(n);
+        rg.n_fused++;
+        for (auto& in : n->inputs) gather_companion(in.get(), rg);
+    } else if (rg.leaf_set.insert(n).second) {
+        rg.leaves.push_back(n);
+    }
+}
+
 TensorData run_region(Node* root, bool allow_fold = true) {
+    std::vector<Node*> candidates;
+    if (g_companions && root == g_companion_host) {
+        candidates = *g_companions;
+        g_companions = nullptr;   // leaves resolved below must not pick them up again
+    }
     Region rg;
     rg.root = root;
     plan_region(rg, allow_fold);
     rg.collect(root, rg.row_mode && !rg.out_has_h ? Region::Row : Region::Elem);
+    for (Node* l : rg.leaves) resolve_node(l);   // a candidate the host depends on is computed here
+    std::vector<std::pair<Node*, Node*>> companions;   // (reduction node, its per-element expression)
+    if (rg.row_mode && rg.out_has_h && root->numel() > 0) {
+        for (Node* c : candidates) {
+            if (c->dev != root->dev || companions.size() >= 4) continue;
+            Node* expr = companion_expr(c, rg.E);
+            if (!expr) continue;
+            Region trial = rg;
+            gather_companion(expr, trial);
+            if (trial.leaves.size() > 12 || trial.n_fused > 200) continue;
+            rg = std::move(trial);
+            companions.emplace_back(c, expr);
+        }
+    }
     for (Node* l : rg.leaves) resolve_node(l);
 
     Emitter em(rg);
     int res = em.emit(root, rg.row_mode && !rg.out_has_h ? Region::Row : Region::Elem);
     em.prog.result = res;
+    for (auto& ce : companions) {
+        int v = em.emit(ce.second, Region::Elem);
+        em.prog.grands.push_back(Grand{ce.first->op, v, ce.first->dtype});
+    }
     if (!em.ok) {
         WGF_CHECK(rg.fold_top != nullptr, WGF_ERR_UNSUPPORTED, "internal: unmergeable index space");
         return run_region(root, false);  // some input cannot be flattened: reduce axis by axis
@@ -784,9 +836,10 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         donor->cached = TensorData();
     }
     TensorData out;
+    std::vector<TensorData> grand_out;
     try {
         Device& dev = *root->dev;
-        if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace);
+        if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace, &grand_out);
         else out = run_elementwise(dev, em.prog, em.slots, index_shape, inplace);
     } catch (...) {
         if (donor) {
@@ -794,6 +847,11 @@ TensorData run_region(Node* root, bool allow_fold = true) {
             donor->cached = std::move(saved);
         }
         throw;
+    }
+    for (size_t i = 0; i < companions.size(); ++i) {
+        Node* c = companions[i].first;
+        c->cached = grand_out[i];
+        c->drop_inputs();
     }
     out.layout.shape = root->shape;  // same element count and order; restores extent-1 axes
     if ((int)out.layout.strides.size() != root->rank()) out.layout.strides = Layout::contiguous_strides(root->shape);
@@ -915,6 +973,38 @@ TensorData resolve(const NodeRef& n) {
         dev.sink = nullptr;
         throw;
     }
+}
+
+// Resolves several tensors as one request.  Whole-tensor reductions among them (also below a
+// requested all-reduce) are offered to the row kernels of the other requested tensors: where
+// both read the same index space, the reduction is computed by that kernel and costs no
+// second pass over memory.  The crate resolves one tensor per call (src/tensor.rs:551-554)
+// and lists fusing sibling reductions as future work (README.md:19-22).
+void resolve_many(const std::vector<NodeRef>& nodes) {
+    std::vector<NodeRef> keep;   // the candidates stay alive whatever the hosts resolve
+    for (auto& n : nodes) {
+        NodeRef c = n;
+        if (!c->cached && c->kind == NodeKind::AllReduce) c = c->inputs[0];
+        if (!c->cached && c->kind == NodeKind::Reduce && c->rank() == 0) keep.push_back(c);
+    }
+    std::vector<Node*> comps;
+    for (auto& c : keep) comps.push_back(c.get());
+    for (auto& n : nodes) {
+        if (n->cached || !is_ew(n.get()) || comps.empty()) continue;
+        g_companion_host = n.get();
+        g_companions = &comps;
+        try {
+            resolve(n);
+        } catch (...) {
+            g_companions = nullptr;
+            g_companion_host = nullptr;
+            throw;
+        }
+        g_companions = nullptr;
+        g_companion_host = nullptr;
+        comps.erase(std::remove_if(comps.begin(), comps.end(), [](Node* c) { return (bool)c->cached; }), comps.end());
+    }
+    for (auto& n : nodes) resolve(n);
 }
 
 // ---------------------------------------------------------------------------------------

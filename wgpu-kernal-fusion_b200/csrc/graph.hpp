@@ -58,6 +58,11 @@ struct Node {
     ~Node();
     void drop_inputs();
     int rank() const { return (int)shape.size(); }
+    int64_t numel() const {
+        int64_t n = 1;
+        for (auto v : shape) n *= v;
+        return n;
+    }
 };
 using NodeRef = std::shared_ptr<Node>;
 
@@ -110,6 +115,10 @@ NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, c
 // The resolver: returns the materialised result of `n` (cached in the node afterwards).
 // Kernels are queued on the device stream; nothing waits.
 TensorData resolve(const NodeRef& n);
+
+// Resolves all of `nodes` as one request: a whole-tensor reduction among them is computed
+// inside the row kernel of another requested tensor when both cover the same index space.
+void resolve_many(const std::vector<NodeRef>& nodes);
 
 std::string graphviz(const NodeRef& n);
 

@@ -24,10 +24,19 @@ struct Instr {
     VKind vk = VKind::Elem;
 };
 
+// A companion output of a row kernel: Elem value `a` reduced with `op` over the WHOLE index
+// space (all rows, all columns) to one scalar, computed while the rows pass through registers.
+struct Grand {
+    uint16_t op;
+    int a;
+    DType dtype;
+};
+
 struct Program {
     std::vector<Instr> ins;
     std::vector<DType> slot_dtype;  // element type of each input slot
     std::vector<float> imms;
+    std::vector<Grand> grands;
     int result = -1;
 
     int n_slots() const { return (int)slot_dtype.size(); }
@@ -131,6 +140,7 @@ struct Program {
             s << (int)in.kind << "." << in.op << "." << in.a << "." << in.b << "." << in.slot << "."
               << (int)in.dtype << "." << (int)in.vk << ";";
         s << "->" << result;
+        for (auto& g : grands) s << "|g" << g.op << "." << g.a << "." << (int)g.dtype;
         return s.str();
     }
 };

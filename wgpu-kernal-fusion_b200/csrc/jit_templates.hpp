@@ -17,8 +17,11 @@ typedef unsigned long long u64;
 #define DEV __device__ __forceinline__
 
 DEV float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
-DEV u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
 DEV float b2f(u16 b) { return __uint_as_float(((u32)b) << 16); }
+// two floats -> packed pair of 16-bit values (lo in bits 0-15), round to nearest even
+DEV u32 f2h2(float lo, float hi) { u32 r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+DEV u32 f2b2(float lo, float hi) { u32 r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+DEV u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
 DEV u16 f2b(float f) { u16 b; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(b) : "f"(f)); return b; }
 // round a float to the nearest f16 / bf16 value (every op of a 16-bit tensor rounds once)
 DEV float rh(float x) { return h2f(f2h(x)); }
@@ -59,8 +62,7 @@ template <int DT> DEV void store1(void* base, i64 i, float v) {
 }
 template <int DT> DEV float cvt16(u16 v) { return DT == 1 ? h2f(v) : b2f(v); }
 template <int DT> DEV u32 pack16(float lo, float hi) {
-    u32 a = DT == 1 ? f2h(lo) : f2b(lo), b = DT == 1 ? f2h(hi) : f2b(hi);
-    return a | (b << 16);
+    return DT == 1 ? f2h2(lo, hi) : f2b2(lo, hi);
 }
 
 // C consecutive elements starting at element index i; (base + i) is aligned to the vector.
@@ -229,7 +231,7 @@ DEV void offsets(const Params& p, u64 e, i64* off) {
 #endif
 }
 
-extern "C" __global__ void __launch_bounds__(256) wgf_elementwise(const __grid_constant__ Params p) {
+extern "C" __global__ void __launch_bounds__(256, MINB) wgf_elementwise(const __grid_constant__ Params p) {
     const u64 nchunks = (p.n + C - 1) / C;
     const u64 chunk0 = (u64)blockIdx.x * (256 * U) + threadIdx.x;
     float x[U][NIN][C];
@@ -280,6 +282,11 @@ struct Params {
     i64 cstride[NIN + 1];
     u32 H;
     u32 pad_;
+#if NGRAND > 0
+    u64 gpartials;      // float [gridDim.x][NGRAND]
+    u64 gcounter;       // u32, zero on entry, zero again on exit
+    u64 gout[NGRAND];   // one scalar each
+#endif
     u32 oshape[RO];
     u32 mm[RO];
     u32 ms[RO];
@@ -338,6 +345,25 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __gri
         ROW_PREFETCH
         ROW_BODY
     }
+#if NGRAND > 0
+    // Companion whole-tensor reductions: CTA partial -> scratch; the last CTA to arrive
+    // (ticket) combines all partials in index order and stores the scalars.
+    __shared__ float g_smem[NGRAND][THREADS / 32];
+    __shared__ u32 g_last;
+    float* gpart = (float*)p.gpartials;
+    ROW_GRAND_BLOCK
+    if (threadIdx.x == 0) {
+        ROW_GRAND_PUT
+        __threadfence();
+        const u32 ticket = atomicAdd((u32*)p.gcounter, 1u);
+        g_last = ticket == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!g_last) return;
+    __threadfence();
+    ROW_GRAND_FINISH
+    if (threadIdx.x == 0) *(u32*)p.gcounter = 0;
+#endif
 }
 )CUDA";
 

@@ -15,9 +15,11 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
 // Index space `shape` = [outer..., H]; reductions run over the last axis.  An Elem result
 // has shape `shape`, a Row result has shape `shape` without its last axis.
 // `out_has_h` says whether the result keeps the last axis (a Row-kind result is then written
-// to every column of its row).
+// to every column of its row).  A program with companion reductions (`prog.grands`) needs
+// `out_has_h` and a non-empty index space; their rank-0 results are returned in `grand_out`.
 TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
-                    const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot);
+                    const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot,
+                    std::vector<TensorData>* grand_out = nullptr);
 
 // Longest row the register-resident row kernel accepts, for the given element width mix.
 int64_t max_resident_row(bool any_16bit);

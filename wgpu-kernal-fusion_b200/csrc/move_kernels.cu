@@ -93,12 +93,80 @@ __global__ void __launch_bounds__(256) transpose_copy_kernel(T* __restrict__ dst
     }
 }
 
+// The same move on 64 x 64 tiles with 4-element vector accesses on both sides (16 bytes for
+// 4-byte elements, 8 for 2-byte): every thread has four vector loads in flight before it
+// touches shared memory.  Needs both extents, every other stride and both base addresses
+// to be multiples of 4 elements; tiles_p / tiles_l count 64-wide tiles here.
+template <typename T, typename V>
+__global__ void __launch_bounds__(256) transpose_copy_vec_kernel(T* __restrict__ dst, const T* __restrict__ src,
+                                                                 const __grid_constant__ TransposeParams p) {
+    constexpr int PAD = 4 / (int)sizeof(T);       // rows start one 32-bit bank further each
+    __shared__ T tile[64][64 + PAD];              // [pax index][last index]
+    const int c = threadIdx.x & 15, r = threadIdx.x >> 4;   // 16 vectors per 64-wide row, 16 rows per pass
+    const int last = p.rank - 1;
+    const long long P = p.shape[p.pax], L = p.shape[last];
+    const long long sl = p.sstride[last], dp = p.dstride[p.pax];
+    for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+        long long rem = t;
+        const long long tl = rem % p.tiles_l;
+        rem /= p.tiles_l;
+        const long long tp = rem % p.tiles_p;
+        rem /= p.tiles_p;
+        long long doff = 0, soff = 0;
+#pragma unroll 1
+        for (int d = last - 1; d >= 0; --d) {
+            if (d == p.pax) continue;
+            const long long q = rem % p.shape[d];
+            rem /= p.shape[d];
+            doff += q * p.dstride[d];
+            soff += q * p.sstride[d];
+        }
+        const long long p0 = tp * 64, l0 = tl * 64;
+        V v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long li = l0 + r + 16 * i, pi = p0 + 4 * c;
+            if (li < L && pi < P) v[i] = *(const V*)(src + soff + pi + li * sl);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const T* e = (const T*)&v[i];
+            if (l0 + r + 16 * i < L && p0 + 4 * c < P) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tile[4 * c + k][r + 16 * i] = e[k];
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long pi = p0 + r + 16 * i, li = l0 + 4 * c;
+            if (pi < P && li < L) {
+                V o;
+                T* e = (T*)&o;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) e[k] = tile[r + 16 * i][4 * c + k];
+                *(V*)(dst + doff + pi * dp + li) = o;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 template <typename T>
 void launch_transpose(Device& dev, void* dst, const void* src, const TransposeParams& p) {
     long long blocks = std::min<long long>(p.total_tiles, (long long)dev.sm_count * 16);
     dev.begin_launch("transpose_copy");
     if (!dev.dry)
         transpose_copy_kernel<T><<<(unsigned)blocks, dim3(32, 8), 0, dev.stream>>>((T*)dst, (const T*)src, p);
+    dev.end_launch();
+}
+
+template <typename T, typename V>
+void launch_transpose_vec(Device& dev, void* dst, const void* src, const TransposeParams& p) {
+    long long blocks = std::min<long long>(p.total_tiles, (long long)dev.sm_count * 8);
+    dev.begin_launch("transpose_copy");
+    if (!dev.dry)
+        transpose_copy_vec_kernel<T, V><<<(unsigned)blocks, 256, 0, dev.stream>>>((T*)dst, (const T*)src, p);
     dev.end_launch();
 }
 
@@ -168,6 +236,21 @@ void run_copy(Device& dev, const TensorData& dst, const TensorData& src) {
                 tp.dstride[d] = ds[d];
                 tp.sstride[d] = ss[d];
                 if (d != pax && d != R - 1) tp.total_tiles *= shape[d];
+            }
+            bool vec_ok = shape[pax] % 4 == 0 && shape[R - 1] % 4 == 0 && n >= (1 << 16) &&
+                          (uintptr_t)dst.base_ptr() % (4 * esize) == 0 && (uintptr_t)src.base_ptr() % (4 * esize) == 0;
+            for (int d = 0; d < R && vec_ok; ++d) {
+                if (d != pax && ss[d] % 4 != 0) vec_ok = false;
+                if (d != R - 1 && ds[d] % 4 != 0) vec_ok = false;
+            }
+            if (vec_ok) {
+                tp.total_tiles /= tp.tiles_p * tp.tiles_l;
+                tp.tiles_p = (shape[pax] + 63) / 64;
+                tp.tiles_l = (shape[R - 1] + 63) / 64;
+                tp.total_tiles *= tp.tiles_p * tp.tiles_l;
+                if (esize == 4) launch_transpose_vec<uint32_t, uint4>(dev, dst.base_ptr(), src.base_ptr(), tp);
+                else launch_transpose_vec<uint16_t, uint2>(dev, dst.base_ptr(), src.base_ptr(), tp);
+                return;
             }
             if (esize == 4) launch_transpose<uint32_t>(dev, dst.base_ptr(), src.base_ptr(), tp);
             else launch_transpose<uint16_t>(dev, dst.base_ptr(), src.base_ptr(), tp);
