@@ -233,13 +233,23 @@ int32_t wgf_tensor_softmax(wgf_tensor* t, wgf_tensor** out);                    
 /* Max-subtracted softmax over the last axis of any rank (no counterpart in the crate). */
 int32_t wgf_tensor_softmax_last_dim(wgf_tensor* t, wgf_tensor** out);
 int32_t wgf_tensor_rope(wgf_tensor* t, wgf_tensor* cos, wgf_tensor* sin, wgf_tensor** out);         /* rope.rs:13-22 */
+/* softmax(scale * q k^T + mask) v for q [n, seq_q, d], k and v [n, seq_k, d] (n = batch * heads).
+ * `mask` is an additive [seq_q, seq_k] tensor or NULL.  With mask == NULL, `causal` != 0 masks the
+ * keys after each query; for 16-bit elements, d == 128 and seq_q == seq_k a multiple of 128 this
+ * runs as ONE fused tensor-core kernel that keeps the scores in tensor memory.  Other shapes
+ * (and any explicit mask) run as mat_mul, scale, add, softmax_last_dim, mat_mul; a causal
+ * request that cannot be fused fails with WGF_ERR_UNSUPPORTED and asks for a mask.  No
+ * counterpart in the crate. */
+int32_t wgf_tensor_attention(wgf_tensor* q, wgf_tensor* k, wgf_tensor* v, wgf_tensor* mask, int32_t causal, float scale,
+                             wgf_tensor** out);
 /* Llama-style decoder block forward, composed from the primitives above (no counterpart in the
  * crate; its README lists the ops such a block needs, README.md:24-38).
  *   h = x + Wo.attn(rope(Wq.n1), rope(Wk.n1), Wv.n1), n1 = rms_norm(x, norm1);
  *   out = h + Wd.(silu(Wg.n2) * (Wu.n2)),             n2 = rms_norm(h, norm2).
  * x [batch, seq, hidden]; weights[7] = {Wq, Wk, Wv, Wo, Wg, Wu, Wd}, each stored
  * [out_features, in_features]; norm1/norm2 [hidden]; cos/sin [>= seq, head_dim/2];
- * mask [seq, seq] additive (0 where attended, -inf where not). */
+ * mask [seq, seq] additive (0 where attended, -inf where not), or NULL for causal attention
+ * through wgf_tensor_attention's fused kernel. */
 int32_t wgf_tensor_llama_block(wgf_tensor* x, wgf_tensor* const* weights, wgf_tensor* norm1, wgf_tensor* norm2,
                                wgf_tensor* cos, wgf_tensor* sin, wgf_tensor* mask, uint32_t n_heads, float eps,
                                wgf_tensor** out);

@@ -323,11 +323,21 @@ class Tensor:
         return Tensor(self.dev, out)
 
     def llama_block(self, weights, norm1, norm2, cos, sin, mask, n_heads, eps=1e-5):
-        """Llama-style decoder block forward; weights = [Wq, Wk, Wv, Wo, Wg, Wu, Wd], each [out, in]."""
+        """Llama-style decoder block forward; weights = [Wq, Wk, Wv, Wo, Wg, Wu, Wd], each [out, in].
+        mask: additive [seq, seq] tensor, or None for causal attention through the fused kernel."""
         arr = (C.c_void_p * 7)(*[w.h for w in weights])
         out = C.c_void_p()
-        check(lib().wgf_tensor_llama_block(self.h, arr, norm1.h, norm2.h, cos.h, sin.h, mask.h, C.c_uint32(n_heads),
-                                           C.c_float(eps), C.byref(out)))
+        check(lib().wgf_tensor_llama_block(self.h, arr, norm1.h, norm2.h, cos.h, sin.h, mask.h if mask is not None else None,
+                                           C.c_uint32(n_heads), C.c_float(eps), C.byref(out)))
+        return Tensor(self.dev, out)
+
+    def attention(self, k, v, mask=None, causal=False, scale=None):
+        """softmax(scale * self k^T + mask) v for [batch*heads, seq, head_dim] tensors (wgf_tensor_attention)."""
+        if scale is None:
+            scale = 1.0 / float(np.sqrt(self.shape[-1]))
+        out = C.c_void_p()
+        check(lib().wgf_tensor_attention(self.h, k.h, v.h, mask.h if mask is not None else None, C.c_int32(1 if causal else 0),
+                                         C.c_float(scale), C.byref(out)))
         return Tensor(self.dev, out)
 
     def all_reduce(self, comm, op=OP_SUM):

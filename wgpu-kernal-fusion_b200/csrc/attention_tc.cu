@@ -1,0 +1,430 @@
+// Fused softmax attention for 16-bit tensors with head dimension 128 on the tcgen05 tensor
+// cores (sm_100a):  O = softmax(scale * Q K^T  [causal])  V  per (batch * head).  The [S, S]
+// score matrix lives only in tensor memory; nothing but Q, K, V and O touches HBM.  The crate
+// has no attention op (its README lists the ops a Llama block needs, README.md:24-38); built
+// from its primitives the same result takes a batched matmul, a softmax kernel and a second
+// batched matmul with two round trips of the score matrix through memory.
+//
+// One persistent CTA per SM walks (batch*head, 128-row query tile) work items, heaviest first.
+// Key/value tiles are 128 rows.  Two passes over the keys of an item:
+//   pass 1   S = Q K_j^T (tensor cores)            -> row maxima m           (softmax warps)
+//   pass 2   S = Q K_j^T again, P = exp2((S - m) * scale * log2 e) as 16-bit -> shared memory,
+//            O += P V_j (tensor cores, accumulating in TMEM), l = row sums of P
+//   end      O / l -> global memory
+// Recomputing S costs a third more tensor work than the single-pass online softmax, but O is
+// never rescaled, so nothing has to be read back from and written again to tensor memory per
+// tile; the exponentials, not the tensor cores, bound this kernel either way.
+// Warp roles:
+//   warp 0     TMA producer (one lane): Q tile, then K / V tiles through a 4-stage ring
+//   warp 1     MMA issuer   (one lane): S into one of two TMEM buffers (2 x 128 columns), O in a
+//              third (128 columns)
+//   warps 2-5  softmax: thread r owns row r of the tile = TMEM lane r
+// Synchronisation is by mbarriers only; every wait is bounded and reports through the device
+// error word instead of hanging.
+#include <algorithm>
+#include <cmath>
+
+#include "attention.hpp"
+#include "tc_common.cuh"
+
+namespace wgf {
+
+using namespace tc;
+
+namespace {
+
+constexpr int AT_STAGES = 4;
+constexpr int AT_PANEL = 128 * 128;        // bytes of one 64-column panel: 128 rows x 128 bytes
+constexpr int AT_TILE = 2 * AT_PANEL;      // a [128 x 128] 16-bit tile: 32 KiB
+constexpr int AT_SMEM = (2 + AT_STAGES) * AT_TILE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int AT_THREADS = 192;
+constexpr unsigned AT_S_COLS = 128, AT_O_COL0 = 256;
+
+struct AtParams {
+    int n_q_tiles, n_k_tiles;
+    int bh;                  // batch * heads
+    int causal;
+    int is_bf16;
+    float scale_log2e;
+    long long o_rs, o_bs;    // output row / batch stride in elements
+    unsigned* error;         // device word: 0 = ok, else code of the wait that gave up
+};
+
+// kind::f16 instruction descriptor for M = 128, N = 128 (fields as in matmul_tc.cu)
+__device__ __forceinline__ unsigned at_idesc(unsigned bf16, unsigned b_mn_major) {
+    return (1u << 4) | (bf16 << 7) | (bf16 << 10) | (b_mn_major << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+enum {
+    Q_FULL = 0, Q_EMPTY, KV_FULL, KV_EMPTY = KV_FULL + AT_STAGES, S_FULL = KV_EMPTY + AT_STAGES, S_EMPTY = S_FULL + 2,
+    P_FULL = S_EMPTY + 2, P_EMPTY, O_FULL, O_EMPTY, N_BARS
+};
+
+template <typename T>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, T* __restrict__ O, const __grid_constant__ AtParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle atoms
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* p_tile = smem + AT_TILE;
+    const unsigned q_smem = smem_u32(smem), p_smem = q_smem + AT_TILE, ring = p_smem + AT_TILE;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (2 + AT_STAGES) * AT_TILE);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + N_BARS);
+    const unsigned bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (unsigned)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < N_BARS; ++i) {
+            const bool four = (i >= S_EMPTY && i < S_EMPTY + 2) || i == P_FULL || i == O_EMPTY;   // one arrival per softmax warp
+            mbar_init(bar(i), four ? 4 : 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const long long items = (long long)p.bh * p.n_q_tiles;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 1, q_phase = 1;   // fresh "empty" barriers count as already released
+            bool ok = true;
+            auto push = [&](const CUtensorMap* map, int row0, int b) -> bool {
+                if (!mbar_wait(bar(KV_EMPTY + stage), phase)) {
+                    atomicExch(p.error, 11u);
+                    return false;
+                }
+                const unsigned dst = ring + (unsigned)stage * AT_TILE;
+                mbar_expect_tx(bar(KV_FULL + stage), AT_TILE);
+                tma_load_3d(dst, map, bar(KV_FULL + stage), 0, row0, b);
+                tma_load_3d(dst + AT_PANEL, map, bar(KV_FULL + stage), 64, row0, b);
+                if (++stage == AT_STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                return true;
+            };
+            for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                const int qt = p.n_q_tiles - 1 - (int)(w / p.bh), b = (int)(w % p.bh);
+                const int n_kv = p.causal ? qt + 1 : p.n_k_tiles;
+                if (!mbar_wait(bar(Q_EMPTY), q_phase)) {
+                    atomicExch(p.error, 10u);
+                    break;
+                }
+                q_phase ^= 1;
+                mbar_expect_tx(bar(Q_FULL), AT_TILE);
+                tma_load_3d(q_smem, &map_q, bar(Q_FULL), 0, qt * 128, b);
+                tma_load_3d(q_smem + AT_PANEL, &map_q, bar(Q_FULL), 64, qt * 128, b);
+                // the order below is the order in which the MMA warp consumes the ring
+                for (int j = 0; j < n_kv && ok; ++j) ok = push(&map_k, j * 128, b);
+                for (int j = 0; j < n_kv && ok; ++j) {
+                    ok = push(&map_k, j * 128, b);
+                    if (ok && j > 0) ok = push(&map_v, (j - 1) * 128, b);
+                }
+                if (ok) ok = push(&map_v, (n_kv - 1) * 128, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const unsigned idesc_s = at_idesc((unsigned)p.is_bf16, 0u), idesc_pv = at_idesc((unsigned)p.is_bf16, 1u);
+            int stage = 0, sb = 0;
+            unsigned phase = 0, q_phase = 0, p_phase = 0, o_phase = 1;
+            unsigned s_phase[2] = {1, 1};      // both S buffers start out free
+            bool ok = true;
+            auto advance = [&]() {
+                if (++stage == AT_STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            };
+            // S[sb] = Q K^T for the K tile at the head of the ring
+            auto issue_s = [&]() -> bool {
+                if (!mbar_wait(bar(KV_FULL + stage), phase)) {
+                    atomicExch(p.error, 21u);
+                    return false;
+                }
+                if (!mbar_wait(bar(S_EMPTY + sb), s_phase[sb])) {
+                    atomicExch(p.error, 22u);
+                    return false;
+                }
+                s_phase[sb] ^= 1;
+                tc_fence_after();
+                const unsigned kt = ring + (unsigned)stage * AT_TILE;
+                const unsigned d = tmem_base + (unsigned)sb * AT_S_COLS;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    // both K-major: rows of 128 bytes, 8-row groups 1024 bytes apart, 32 bytes per
+                    // K step inside a 64-column panel, the second panel 16 KiB further
+                    const unsigned off = (unsigned)(kk >> 2) * AT_PANEL + (unsigned)(kk & 3) * 32u;
+                    umma_f16(d, smem_desc(q_smem + off, 16, 1024), smem_desc(kt + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                }
+                umma_commit(bar(KV_EMPTY + stage));
+                umma_commit(bar(S_FULL + sb));
+                advance();
+                sb ^= 1;
+                return true;
+            };
+            // O (+)= P V for the V tile at the head of the ring
+            auto issue_pv = [&](bool first) -> bool {
+                if (first) {
+                    if (!mbar_wait(bar(O_EMPTY), o_phase)) {
+                        atomicExch(p.error, 23u);
+                        return false;
+                    }
+                    o_phase ^= 1;
+                }
+                if (!mbar_wait(bar(P_FULL), p_phase)) {
+                    atomicExch(p.error, 24u);
+                    return false;
+                }
+                p_phase ^= 1;
+                if (!mbar_wait(bar(KV_FULL + stage), phase)) {
+                    atomicExch(p.error, 25u);
+                    return false;
+                }
+                tc_fence_after();
+                const unsigned vt = ring + (unsigned)stage * AT_TILE;
+                const unsigned d = tmem_base + AT_O_COL0;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    // A = P, K-major (keys along K).  B = V, N-major: 64-column panels 16 KiB apart
+                    // (leading), 8-key groups 1024 bytes apart (stride), 16 keys = 2048 bytes per K step
+                    const unsigned long long adesc =
+                        smem_desc(p_smem + (unsigned)(kk >> 2) * AT_PANEL + (unsigned)(kk & 3) * 32u, 16, 1024);
+                    const unsigned long long bdesc = smem_desc(vt + (unsigned)kk * 2048u, AT_PANEL, 1024);
+                    umma_f16(d, adesc, bdesc, idesc_pv, (first && kk == 0) ? 0u : 1u);
+                }
+                umma_commit(bar(KV_EMPTY + stage));
+                umma_commit(bar(P_EMPTY));
+                advance();
+                return true;
+            };
+            for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                const int qt = p.n_q_tiles - 1 - (int)(w / p.bh);
+                const int n_kv = p.causal ? qt + 1 : p.n_k_tiles;
+                if (!mbar_wait(bar(Q_FULL), q_phase)) {
+                    atomicExch(p.error, 20u);
+                    break;
+                }
+                q_phase ^= 1;
+                tc_fence_after();
+                for (int j = 0; j < n_kv && ok; ++j) ok = issue_s();          // pass 1
+                for (int j = 0; j < n_kv && ok; ++j) {                         // pass 2
+                    ok = issue_s();
+                    if (ok && j == n_kv - 1) umma_commit(bar(Q_EMPTY));        // Q is free once these MMAs are done
+                    if (ok && j > 0) ok = issue_pv(j == 1);
+                }
+                if (ok) ok = issue_pv(n_kv == 1);
+                if (ok) umma_commit(bar(O_FULL));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax (warps 2..5)
+        const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31 belong to this warp
+        const int r = quarter * 32 + lane;                  // row of the query tile
+        const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+        unsigned s_phase[2] = {0, 0};
+        unsigned pe_phase = 1, o_phase = 0;
+        int sb = 0;
+        bool ok = true;
+        auto wait_all = [&](int which, unsigned parity, unsigned code) -> bool {
+            bool got = mbar_wait(bar(which), parity);
+            got = __all_sync(0xffffffffu, got);
+            if (!got && lane == 0) atomicExch(p.error, code);
+            return got;
+        };
+        for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+            const int qt = p.n_q_tiles - 1 - (int)(w / p.bh), b = (int)(w % p.bh);
+            const int n_kv = p.causal ? qt + 1 : p.n_k_tiles;
+            // ---- pass 1: row maximum of the raw scores
+            float m = -INFINITY;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (!(ok = wait_all(S_FULL + sb, s_phase[sb], 31u))) break;
+                s_phase[sb] ^= 1;
+                tc_fence_after();
+                const bool diag = p.causal && j == qt;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    unsigned v[32];
+                    tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)c * 32u, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float s = __uint_as_float(v[i]);
+                        if (diag && c * 32 + i > r) s = -INFINITY;
+                        m = fmaxf(m, s);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(S_EMPTY + sb));
+                sb ^= 1;
+            }
+            if (!ok) break;
+            // ---- pass 2: P = exp2((S - m) * scale * log2 e) -> shared memory, row sums
+            const float mc = m * p.scale_log2e;
+            float l = 0.f;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (!(ok = wait_all(S_FULL + sb, s_phase[sb], 32u))) break;
+                s_phase[sb] ^= 1;
+                if (!(ok = wait_all(P_EMPTY, pe_phase, 33u))) break;     // the previous P V has read the P tile
+                pe_phase ^= 1;
+                tc_fence_after();
+                const bool diag = p.causal && j == qt;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    unsigned v[32];
+                    tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)c * 32u, v);
+                    tmem_ld_wait();
+                    float e[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float s = __uint_as_float(v[i]);
+                        if (diag && c * 32 + i > r) s = -INFINITY;
+                        e[i] = ex2_approx(fmaf(s, p.scale_log2e, -mc));
+                        l += e[i];
+                    }
+                    // A-operand layout (K-major, 128-byte swizzle): row r of panel c/2 is 128 bytes
+                    // at r * 128; its 16-byte chunk q sits at position q ^ (r % 8)
+                    unsigned char* row = p_tile + (c >> 1) * AT_PANEL + r * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 o;
+                        o.x = pack2<T>(e[8 * q + 0], e[8 * q + 1]);
+                        o.y = pack2<T>(e[8 * q + 2], e[8 * q + 3]);
+                        o.z = pack2<T>(e[8 * q + 4], e[8 * q + 5]);
+                        o.w = pack2<T>(e[8 * q + 6], e[8 * q + 7]);
+                        const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(row + chunk * 16) = o;
+                    }
+                }
+                tc_fence_before();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor cores
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar(P_FULL));
+                    mbar_arrive(bar(S_EMPTY + sb));
+                }
+                sb ^= 1;
+            }
+            if (!ok) break;
+            // ---- O / l -> global memory
+            if (!(ok = wait_all(O_FULL, o_phase, 34u))) break;
+            o_phase ^= 1;
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            T* orow = O + (long long)b * p.o_bs + ((long long)qt * 128 + r) * p.o_rs;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned v[32];
+                tmem_ld_32x32(lane_base + AT_O_COL0 + (unsigned)c * 32u, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = pack2<T>(__uint_as_float(v[8 * q + 0]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
+                    o.y = pack2<T>(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
+                    o.z = pack2<T>(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
+                    o.w = pack2<T>(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O_EMPTY));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+bool attention_supported(DType dt, int64_t seq_q, int64_t seq_k, int64_t head_dim) {
+    return (dt == DType::F16 || dt == DType::BF16) && head_dim == 128 && seq_q == seq_k && seq_q >= 128 && seq_q % 128 == 0 &&
+           seq_q < (1ll << 24);
+}
+
+TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& k_in, const TensorData& v_in, bool causal,
+                         float scale) {
+    WGF_CHECK(q_in.layout.rank() == 3 && k_in.layout.shape == q_in.layout.shape && v_in.layout.shape == q_in.layout.shape,
+              WGF_ERR_SHAPE, "attention takes q, k, v of one shape [batch*heads, seq, 128]");
+    WGF_CHECK(q_in.dtype == k_in.dtype && q_in.dtype == v_in.dtype, WGF_ERR_DTYPE, "attention operands differ in element type");
+    const int64_t BH = q_in.layout.shape[0], S = q_in.layout.shape[1], D = q_in.layout.shape[2];
+    WGF_CHECK(attention_supported(q_in.dtype, S, S, D) && BH >= 1 && BH < (1ll << 31), WGF_ERR_UNSUPPORTED,
+              "fused attention needs 16-bit elements, head dimension 128 and a sequence length that is a multiple of 128");
+    dev.make_current();
+    // rows must be contiguous and 16-byte aligned for TMA; anything else is gathered first
+    auto usable = [](const TensorData& t) {
+        const Layout& l = t.layout;
+        return l.strides[2] == 1 && l.strides[1] % 8 == 0 && l.strides[0] % 8 == 0 && ((uintptr_t)t.base_ptr() & 15) == 0 &&
+               l.strides[1] >= l.shape[2];
+    };
+    TensorData q = usable(q_in) ? q_in : run_compact(dev, q_in);
+    TensorData k = usable(k_in) ? k_in : run_compact(dev, k_in);
+    TensorData v = usable(v_in) ? v_in : run_compact(dev, v_in);
+    for (const TensorData* t : {&q, &k, &v}) dev.wait_for(*t->buf);
+    TensorData out;
+    out.dtype = q.dtype;
+    out.layout = Layout::contiguous({BH, S, D});
+    out.buf = dev.alloc((size_t)(BH * S * D) * 2, false);
+    if (dev.dry) {
+        dev.begin_launch("attention_tc");
+        dev.end_launch();
+        return out;
+    }
+    const bool bf16 = q.dtype == DType::BF16;
+    CUtensorMap mq, mk, mv;
+    const bool maps_ok = encode_3d(&mq, bf16, q.base_ptr(), D, S, BH, q.layout.strides[1], q.layout.strides[0], 64, 128) &&
+                         encode_3d(&mk, bf16, k.base_ptr(), D, S, BH, k.layout.strides[1], k.layout.strides[0], 64, 128) &&
+                         encode_3d(&mv, bf16, v.base_ptr(), D, S, BH, v.layout.strides[1], v.layout.strides[0], 64, 128);
+    WGF_CHECK(maps_ok, WGF_ERR_CUDA, "attention: tensor map creation failed");
+    AtParams p{};
+    p.n_q_tiles = p.n_k_tiles = (int)(S / 128);
+    p.bh = (int)BH;
+    p.causal = causal ? 1 : 0;
+    p.is_bf16 = bf16 ? 1 : 0;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.o_rs = D;
+    p.o_bs = S * D;
+    p.error = dev.error_word();
+    const long long items = BH * (S / 128);
+    const unsigned grid = (unsigned)std::min<long long>(items, dev.sm_count);
+    static bool attr_set[2] = {false, false};
+    dev.begin_launch("attention_tc");
+    if (bf16) {
+        if (!attr_set[1]) {
+            WGF_CUDA(cudaFuncSetAttribute(attention_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
+            attr_set[1] = true;
+        }
+        attention_tc_kernel<__nv_bfloat16><<<grid, AT_THREADS, AT_SMEM, dev.stream>>>(mq, mk, mv, (__nv_bfloat16*)out.base_ptr(), p);
+    } else {
+        if (!attr_set[0]) {
+            WGF_CUDA(cudaFuncSetAttribute(attention_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
+            attr_set[0] = true;
+        }
+        attention_tc_kernel<__half><<<grid, AT_THREADS, AT_SMEM, dev.stream>>>(mq, mk, mv, (__half*)out.base_ptr(), p);
+    }
+    dev.end_launch();
+    return out;
+}
+
+}  // namespace wgf

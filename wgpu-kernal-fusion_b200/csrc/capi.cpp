@@ -727,12 +727,22 @@ int32_t wgf_tensor_llama_block(wgf_tensor* x, wgf_tensor* const* weights, wgf_te
         REQUIRE(norm2);
         REQUIRE(cos);
         REQUIRE(sin);
-        REQUIRE(mask);
         REQUIRE(out);
         for (int i = 0; i < 7; ++i) REQUIRE(weights[i]);
         *out = wrap(op_llama_block(x->node, weights[0]->node, weights[1]->node, weights[2]->node, weights[3]->node,
                                    weights[4]->node, weights[5]->node, weights[6]->node, norm1->node, norm2->node,
-                                   cos->node, sin->node, mask->node, (int)n_heads, eps));
+                                   cos->node, sin->node, mask ? mask->node : NodeRef(), (int)n_heads, eps));
+    })
+}
+
+int32_t wgf_tensor_attention(wgf_tensor* q, wgf_tensor* k, wgf_tensor* v, wgf_tensor* mask, int32_t causal, float scale,
+                             wgf_tensor** out) {
+    GRAPH_GUARD({
+        REQUIRE(q);
+        REQUIRE(k);
+        REQUIRE(v);
+        REQUIRE(out);
+        *out = wrap(op_attention(q->node, k->node, v->node, mask ? mask->node : NodeRef(), causal != 0, scale));
     })
 }
 

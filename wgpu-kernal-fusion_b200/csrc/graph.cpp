@@ -6,6 +6,7 @@
 #include <functional>
 #include <sstream>
 
+#include "attention.hpp"
 #include "comm.hpp"
 #include "half.hpp"
 
@@ -384,12 +385,39 @@ NodeRef op_rope(const NodeRef& x, const NodeRef& cos, const NodeRef& sin) {
     return make_binary(make_binary(x, c, WGF_OP_MUL), make_binary(rot, s, WGF_OP_MUL), WGF_OP_ADD);
 }
 
+NodeRef op_attention(const NodeRef& q, const NodeRef& k, const NodeRef& v, const NodeRef& mask, bool causal, float scale) {
+    WGF_CHECK(q->rank() == 3 && k->rank() == 3 && v->rank() == 3, WGF_ERR_RANK, "attention takes [batch*heads, seq, head_dim] tensors");
+    WGF_CHECK(q->shape[0] == k->shape[0] && q->shape[2] == k->shape[2] && k->shape == v->shape, WGF_ERR_SHAPE,
+              "attention: q is [n, seq_q, d], k and v are [n, seq_k, d]");
+    WGF_CHECK(q->dtype == k->dtype && q->dtype == v->dtype, WGF_ERR_DTYPE, "attention operands differ in element type");
+    const int64_t n = q->shape[0], sq = q->shape[1], sk = k->shape[1], d = q->shape[2];
+    if (mask) {
+        WGF_CHECK(mask->rank() == 2 && mask->shape[0] == sq && mask->shape[1] == sk, WGF_ERR_SHAPE,
+                  "attention mask must be [seq_q, seq_k]");
+        WGF_CHECK(mask->dtype == q->dtype, WGF_ERR_DTYPE, "attention mask differs in element type");
+    }
+    if (!mask && attention_supported(q->dtype, sq, sk, d)) {
+        auto node = new_node(NodeKind::Attention, q->dev, q->shape, q->dtype, {q, k, v});
+        node->imm = scale;
+        node->axis = causal ? 1 : 0;
+        return node;
+    }
+    WGF_CHECK(mask || !causal, WGF_ERR_UNSUPPORTED,
+              "causal attention without a mask needs 16-bit elements, head_dim 128 and seq a multiple of 128; pass an additive mask");
+    NodeRef scores = make_matmul(q, view_transpose(k, 1, 2));                       // [n, seq_q, seq_k]
+    NodeRef scaled = make_scalar(scores, WGF_OP_MUL_C, scale);
+    NodeRef masked = mask ? make_binary(scaled, view_broadcast_axis(mask, 0, n), WGF_OP_ADD) : scaled;
+    NodeRef probs = op_softmax_last_dim(masked);                                    // one fused row kernel
+    return make_matmul(probs, v);
+}
+
 // Llama-style decoder block forward (no counterpart in the crate, whose README only lists the
 // ops such a block needs, README.md:24-38); a composition of the primitives above:
 //   h   = x + Wo . attention(rope(Wq . n1), rope(Wk . n1), Wv . n1),   n1 = rms_norm(x, norm1)
 //   out = h + Wd . (silu(Wg . n2) * (Wu . n2)),                        n2 = rms_norm(h, norm2)
 // x is [batch, seq, hidden]; weights are stored [out_features, in_features]; cos/sin are
-// [>= seq, head_dim / 2]; `mask` is the additive attention mask [seq, seq] (0 / -inf for causal).
+// [>= seq, head_dim / 2]; `mask` is the additive attention mask [seq, seq] (0 / -inf for causal),
+// or null for causal attention through the fused tensor-core kernel.
 NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, const NodeRef& wv, const NodeRef& wo,
                        const NodeRef& wg, const NodeRef& wu, const NodeRef& wd, const NodeRef& norm1,
                        const NodeRef& norm2, const NodeRef& cos, const NodeRef& sin, const NodeRef& mask,
@@ -403,7 +431,7 @@ NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, c
               "attention weights must be [hidden, hidden]");
     WGF_CHECK(wg->rank() == 2 && wg->shape[1] == Hd && wu->shape == wg->shape && is2(wd, Hd, wg->shape[0]), WGF_ERR_SHAPE,
               "MLP weights must be [inter, hidden], [inter, hidden], [hidden, inter]");
-    WGF_CHECK(is2(mask, S, S), WGF_ERR_SHAPE, "attention mask must be [seq, seq]");
+    WGF_CHECK(!mask || is2(mask, S, S), WGF_ERR_SHAPE, "attention mask must be [seq, seq]");
     auto linear = [](const NodeRef& a, const NodeRef& w) { return make_matmul(a, view_transpose(w, 0, 1)); };
     // [B*S, Hd] -> [B*heads, S, D]
     auto split_heads = [&](const NodeRef& t) {
@@ -415,11 +443,7 @@ NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, c
     NodeRef q = op_rope(split_heads(linear(n1, wq)), cos, sin);
     NodeRef k = op_rope(split_heads(linear(n1, wk)), cos, sin);
     NodeRef v = split_heads(linear(n1, wv));
-    NodeRef scores = make_matmul(q, view_transpose(k, 1, 2));                       // [B*heads, S, S]
-    NodeRef scaled = make_scalar(scores, WGF_OP_MUL_C, 1.0f / std::sqrt((float)D));
-    NodeRef masked = make_binary(scaled, view_broadcast_axis(mask, 0, B * n_heads), WGF_OP_ADD);
-    NodeRef probs = op_softmax_last_dim(masked);                                    // one fused row kernel
-    NodeRef ctx = make_matmul(probs, v);                                            // [B*heads, S, D]
+    NodeRef ctx = op_attention(q, k, v, mask, true, 1.0f / std::sqrt((float)D));  // [B*heads, S, D]
     NodeRef merged = op_reshape(view_transpose(op_reshape(ctx, {B, (int64_t)n_heads, S, D}), 1, 2), {B * S, Hd});
     NodeRef h = make_binary(x2, linear(merged, wo), WGF_OP_ADD);
     NodeRef n2 = op_layer_norm(h, norm2, eps);
@@ -883,6 +907,13 @@ TensorData resolve_node(Node* n) {
             out = run_matmul(dev, a, b);
             break;
         }
+        case NodeKind::Attention: {
+            TensorData q = resolve_node(n->inputs[0].get());
+            TensorData k = resolve_node(n->inputs[1].get());
+            TensorData v = resolve_node(n->inputs[2].get());
+            out = run_attention(dev, q, k, v, n->axis != 0, n->imm);
+            break;
+        }
         case NodeKind::Resize: {  // src/compute_graph/resolve.rs:210-226
             TensorData in = resolve_node(n->inputs[0].get());
             const bool reshape = n->new_shape == n->fill_shape;
@@ -1012,7 +1043,7 @@ void resolve_many(const std::vector<NodeRef>& nodes) {
 // ---------------------------------------------------------------------------------------
 std::string graphviz(const NodeRef& root) {
     static const char* kinds[] = {"tensor", "element_wise", "pair_wise", "reduce", "mat_mul",
-                                  "map_layout", "resize", "slice_assign", "all_reduce"};
+                                  "map_layout", "resize", "slice_assign", "all_reduce", "attention"};
     std::ostringstream s;
     s << "digraph compute_graph {\n";
     std::unordered_set<Node*> seen;

@@ -17,7 +17,8 @@ namespace wgf {
 struct Comm;
 
 enum class NodeKind : uint8_t {
-    Tensor, ElementWise, PairWise, Reduce, MatMul, MapLayout, Resize, SliceAssign, AllReduce
+    Tensor, ElementWise, PairWise, Reduce, MatMul, MapLayout, Resize, SliceAssign, AllReduce,
+    Attention   // fused causal softmax attention (no counterpart in the crate); imm = scale
 };
 
 struct ViewOp {
@@ -107,6 +108,11 @@ NodeRef op_layer_norm(const NodeRef& x, const NodeRef& weight, float eps);
 NodeRef op_softmax(const NodeRef& x);
 NodeRef op_softmax_last_dim(const NodeRef& x);
 NodeRef op_rope(const NodeRef& x, const NodeRef& cos, const NodeRef& sin);
+// softmax(scale * q k^T + mask) v over [batch*heads, seq, head_dim] tensors.  `mask` is an
+// additive [seq, seq] tensor or null; with a null mask `causal` masks the keys after each
+// query and, where the shapes allow (16-bit, head_dim 128, seq a multiple of 128), one fused
+// tensor-core kernel runs instead of matmul / softmax / matmul.
+NodeRef op_attention(const NodeRef& q, const NodeRef& k, const NodeRef& v, const NodeRef& mask, bool causal, float scale);
 NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, const NodeRef& wv, const NodeRef& wo,
                        const NodeRef& wg, const NodeRef& wu, const NodeRef& wd, const NodeRef& norm1,
                        const NodeRef& norm2, const NodeRef& cos, const NodeRef& sin, const NodeRef& mask,
