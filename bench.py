@@ -329,8 +329,11 @@ def run_gpu(args):
         # the reduction rides along)
         kernel_bytes = BYTES_CHAIN + (4 if fused else 0)
         achieved = kernel_bytes / (row_ms * 1e-3) / 1e9
-        # ncu capture of one launch of this kernel on this workload (summary under profiles/)
-        traffic = None if fused else 218_444_800
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
+        # the ncu captures summarised under profiles/ (134.26 MB read + 85.19 MB written with the
+        # reduction riding along; 134.25 + 84.19 without); the rest of the 134 MB output is still
+        # dirty in L2 when the kernel ends
+        traffic = 219_449_088 if fused else 218_444_800
         sum_exp = None
         if not fused:
             sum_exp = {"achieved": BYTES_SUM / (sum_ms * 1e-3) / 1e9, "launch_ms": sum_ms,

@@ -46,7 +46,8 @@ struct AtParams {
     int causal;
     int is_bf16;
     float scale_log2e;
-    long long o_rs, o_bs;    // output row / batch stride in elements
+    int heads;               // batch*heads index n = batch * heads + head
+    long long o_rs, o_hs, o_bs;   // output row / head / batch stride in elements
     unsigned* error;         // device word: 0 = ok, else code of the wait that gave up
 };
 
@@ -327,7 +328,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             o_phase ^= 1;
             tc_fence_after();
             const float inv = 1.0f / l;
-            T* orow = O + (long long)b * p.o_bs + ((long long)qt * 128 + r) * p.o_rs;
+            T* orow = O + (long long)(b / p.heads) * p.o_bs + (long long)(b % p.heads) * p.o_hs + ((long long)qt * 128 + r) * p.o_rs;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 unsigned v[32];
@@ -364,13 +365,15 @@ bool attention_supported(DType dt, int64_t seq_q, int64_t seq_k, int64_t head_di
 }
 
 TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& k_in, const TensorData& v_in, bool causal,
-                         float scale) {
+                         float scale, int merge_heads) {
     WGF_CHECK(q_in.layout.rank() == 3 && k_in.layout.shape == q_in.layout.shape && v_in.layout.shape == q_in.layout.shape,
               WGF_ERR_SHAPE, "attention takes q, k, v of one shape [batch*heads, seq, 128]");
     WGF_CHECK(q_in.dtype == k_in.dtype && q_in.dtype == v_in.dtype, WGF_ERR_DTYPE, "attention operands differ in element type");
     const int64_t BH = q_in.layout.shape[0], S = q_in.layout.shape[1], D = q_in.layout.shape[2];
     WGF_CHECK(attention_supported(q_in.dtype, S, S, D) && BH >= 1 && BH < (1ll << 31), WGF_ERR_UNSUPPORTED,
               "fused attention needs 16-bit elements, head dimension 128 and a sequence length that is a multiple of 128");
+    const int64_t heads = merge_heads > 0 ? merge_heads : 1;
+    WGF_CHECK(BH % heads == 0, WGF_ERR_SHAPE, "attention: batch*heads is not a multiple of the head count");
     dev.make_current();
     // rows must be contiguous and 16-byte aligned for TMA; anything else is gathered first
     auto usable = [](const TensorData& t) {
@@ -384,7 +387,8 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     for (const TensorData* t : {&q, &k, &v}) dev.wait_for(*t->buf);
     TensorData out;
     out.dtype = q.dtype;
-    out.layout = Layout::contiguous({BH, S, D});
+    // [n, seq, d], or with merged heads [batch, seq, heads * d] (head h of batch b at columns h*d ..)
+    out.layout = merge_heads > 0 ? Layout::contiguous({BH / heads, S, heads * D}) : Layout::contiguous({BH, S, D});
     out.buf = dev.alloc((size_t)(BH * S * D) * 2, false);
     if (dev.dry) {
         dev.begin_launch("attention_tc");
@@ -403,8 +407,10 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     p.causal = causal ? 1 : 0;
     p.is_bf16 = bf16 ? 1 : 0;
     p.scale_log2e = scale * 1.4426950408889634f;
-    p.o_rs = D;
-    p.o_bs = S * D;
+    p.heads = (int)heads;
+    p.o_rs = heads * D;
+    p.o_hs = D;
+    p.o_bs = S * heads * D;
     p.error = dev.error_word();
     const long long items = BH * (S / 128);
     const unsigned grid = (unsigned)std::min<long long>(items, dev.sm_count);

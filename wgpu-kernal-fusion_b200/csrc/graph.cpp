@@ -378,6 +378,8 @@ NodeRef op_rope(const NodeRef& x, const NodeRef& cos, const NodeRef& sin) {
     WGF_CHECK(cos->shape[1] * 2 == d && cos->shape[0] >= seq, WGF_ERR_SHAPE,
               "rope cos/sin must be [>= sequence, embed / 2]");
     WGF_CHECK(cos->dtype == x->dtype && sin->dtype == x->dtype, WGF_ERR_DTYPE, "rope element types differ");
+    // One kernel with the roundings of the composed form below (kept for odd embed sizes)
+    if (d % 2 == 0 && d >= 2) return new_node(NodeKind::Rope, x->dev, x->shape, x->dtype, {x, cos, sin});
     NodeRef c = view_broadcast_axis(op_narrow(op_cat({cos, cos}, 1), 0, 0, seq), 0, heads);
     NodeRef s = view_broadcast_axis(op_narrow(op_cat({sin, sin}, 1), 0, 0, seq), 0, heads);
     NodeRef x1 = op_narrow(x, 2, 0, d / 2), x2 = op_narrow(x, 2, d / 2, d - d / 2);
@@ -440,11 +442,32 @@ NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, c
     };
     NodeRef x2 = op_reshape(x, {B * S, Hd});
     NodeRef n1 = op_layer_norm(x2, norm1, eps);
-    NodeRef q = op_rope(split_heads(linear(n1, wq)), cos, sin);
-    NodeRef k = op_rope(split_heads(linear(n1, wk)), cos, sin);
+    WGF_CHECK(cos->rank() == 2 && sin->rank() == 2 && cos->shape == sin->shape && cos->shape[1] * 2 == D && cos->shape[0] >= S,
+              WGF_ERR_SHAPE, "rope cos/sin must be [>= sequence, head_dim / 2]");
+    WGF_CHECK(cos->dtype == x->dtype && sin->dtype == x->dtype, WGF_ERR_DTYPE, "rope element types differ");
+    // rotary embedding read straight from the projection's [B, S, heads, D] layout (a transposed
+    // view) and written as [B*heads, S, D]: splitting the heads costs no copy of its own
+    auto rope_heads = [&](const NodeRef& t) {
+        NodeRef t4 = view_transpose(op_reshape(t, {B, S, (int64_t)n_heads, D}), 1, 2);       // [B, heads, S, D]
+        NodeRef r = new_node(NodeKind::Rope, t->dev, {B, (int64_t)n_heads, S, D}, t->dtype, {t4, cos, sin});
+        return op_reshape(r, {B * n_heads, S, D});
+    };
+    NodeRef q = rope_heads(linear(n1, wq));
+    NodeRef k = rope_heads(linear(n1, wk));
     NodeRef v = split_heads(linear(n1, wv));
-    NodeRef ctx = op_attention(q, k, v, mask, true, 1.0f / std::sqrt((float)D));  // [B*heads, S, D]
-    NodeRef merged = op_reshape(view_transpose(op_reshape(ctx, {B, (int64_t)n_heads, S, D}), 1, 2), {B * S, Hd});
+    const float scale = 1.0f / std::sqrt((float)D);
+    NodeRef merged;
+    if (!mask && attention_supported(x->dtype, S, S, D)) {
+        // the fused kernel writes the heads side by side: [B, S, heads * D] without a merging copy
+        NodeRef att = new_node(NodeKind::Attention, x->dev, {B, S, Hd}, x->dtype, {q, k, v});
+        att->imm = scale;
+        att->axis = 1;
+        att->new_shape = {(int64_t)n_heads};
+        merged = op_reshape(att, {B * S, Hd});
+    } else {
+        NodeRef ctx = op_attention(q, k, v, mask, true, scale);  // [B*heads, S, D]
+        merged = op_reshape(view_transpose(op_reshape(ctx, {B, (int64_t)n_heads, S, D}), 1, 2), {B * S, Hd});
+    }
     NodeRef h = make_binary(x2, linear(merged, wo), WGF_OP_ADD);
     NodeRef n2 = op_layer_norm(h, norm2, eps);
     NodeRef act = make_binary(op_silu(linear(n2, wg)), linear(n2, wu), WGF_OP_MUL);  // one fused kernel
@@ -907,11 +930,18 @@ TensorData resolve_node(Node* n) {
             out = run_matmul(dev, a, b);
             break;
         }
+        case NodeKind::Rope: {
+            TensorData x = resolve_node(n->inputs[0].get());
+            TensorData c = resolve_node(n->inputs[1].get());
+            TensorData s = resolve_node(n->inputs[2].get());
+            out = run_rope(dev, x, c, s);
+            break;
+        }
         case NodeKind::Attention: {
             TensorData q = resolve_node(n->inputs[0].get());
             TensorData k = resolve_node(n->inputs[1].get());
             TensorData v = resolve_node(n->inputs[2].get());
-            out = run_attention(dev, q, k, v, n->axis != 0, n->imm);
+            out = run_attention(dev, q, k, v, n->axis != 0, n->imm, n->new_shape.empty() ? 0 : (int)n->new_shape[0]);
             break;
         }
         case NodeKind::Resize: {  // src/compute_graph/resolve.rs:210-226
@@ -1043,7 +1073,7 @@ void resolve_many(const std::vector<NodeRef>& nodes) {
 // ---------------------------------------------------------------------------------------
 std::string graphviz(const NodeRef& root) {
     static const char* kinds[] = {"tensor", "element_wise", "pair_wise", "reduce", "mat_mul",
-                                  "map_layout", "resize", "slice_assign", "all_reduce", "attention"};
+                                  "map_layout", "resize", "slice_assign", "all_reduce", "attention", "rope"};
     std::ostringstream s;
     s << "digraph compute_graph {\n";
     std::unordered_set<Node*> seen;

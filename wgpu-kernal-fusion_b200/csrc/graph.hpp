@@ -18,7 +18,8 @@ struct Comm;
 
 enum class NodeKind : uint8_t {
     Tensor, ElementWise, PairWise, Reduce, MatMul, MapLayout, Resize, SliceAssign, AllReduce,
-    Attention   // fused causal softmax attention (no counterpart in the crate); imm = scale
+    Attention,  // fused causal softmax attention (no counterpart in the crate); imm = scale
+    Rope        // rotary embedding as one kernel; inputs x, cos, sin
 };
 
 struct ViewOp {

@@ -33,5 +33,8 @@ void run_copy(Device& dev, const TensorData& dst, const TensorData& src);
 // A dense row-major copy of `src` (a new buffer).
 TensorData run_compact(Device& dev, const TensorData& src);
 TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b);
+// Rotary embedding of x [.., seq, embed] (rank 3 or 4, last axis contiguous or gathered first)
+// with cos / sin [>= seq, embed / 2]; bit-identical to the chain of separate ops (rope.cu).
+TensorData run_rope(Device& dev, const TensorData& x, const TensorData& cos, const TensorData& sin);
 
 }  // namespace wgf
