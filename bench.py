@@ -484,7 +484,7 @@ def run_configs(args):
             peak_tf = float(json.load(f).get("bf16_tflops", peak_tf))
     dev = wgf.Device(int(os.environ.get("LOCAL_RANK", "0")))
     sampler = ClockSampler(0)
-    rows = sweep.run(wgf, dev, peak_gbs, peak_tf, iters=args.steps, warmup=max(args.warmup, 3))
+    rows = sweep.run(wgf, dev, peak_gbs, peak_tf, iters=args.steps, warmup=max(args.warmup, 3), only=args.rows)
     print(json.dumps({"workload": "configs", "rows": len(rows), "peak_hbm_gbs": peak_gbs, "peak_bf16_tflops": peak_tf,
                       "peaks": which, "clocks": sampler.stop()}))
 
@@ -498,6 +498,7 @@ def main():
     ap.add_argument("--workload", default="fused_chain", choices=["fused_chain", "llama_block", "configs"])
     ap.add_argument("--seq", type=int, default=2048, help="sequence length of the llama_block workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--rows", default=None, help="configs workload: only the rows whose name contains this text")
     ap.add_argument("--separate-kernels", action="store_true",
                     help="fused_chain: request the two results one by one (row kernel, then streaming reduce); "
                          "llama_block: attention as matmul + masked softmax + matmul instead of the fused kernel")

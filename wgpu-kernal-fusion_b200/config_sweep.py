@@ -1,6 +1,7 @@
 """Times every benchmark configuration on one GPU and prints one JSON object per row.
 
-Run as  python bench.py --workload configs  (one GPU).  Each row builds its lazy graph afresh every
+Run as  python bench.py --workload configs [--rows TEXT]  (one GPU; --rows keeps the rows whose name
+contains TEXT, e.g. "C2", "attention", "matmul f16").  Each row builds its lazy graph afresh every
 iteration, materialises it with per-kernel timestamps on (the crate's own method: timestamp queries
 around each dispatch, benches/elementwise.rs:42-43) and reports, per iteration, the median over the
 iterations of the summed kernel times.  Inputs larger than the 126 MB L2 are reused as they are;
@@ -29,8 +30,8 @@ def normal(g, shape, mu=0.0, sigma=1.0):
 
 
 class Row:
-    def __init__(self, name, build, nbytes=None, flop=None, variants=1, note=""):
-        self.name, self.build, self.nbytes, self.flop, self.variants, self.note = name, build, nbytes, flop, variants, note
+    def __init__(self, name, build, nbytes=None, flop=None, variants=1):
+        self.name, self.build, self.nbytes, self.flop, self.variants = name, build, nbytes, flop, variants
 
 
 def time_row(dev, row, iters, warmup):
@@ -59,90 +60,144 @@ def time_row(dev, row, iters, warmup):
     return per_iter[len(per_iter) // 2] * 1e-3, per_iter[0] * 1e-3, labels
 
 
-def rows_for(wgf, dev, peak_gbs):
-    out = []
-    F16 = wgf.F16
+# Each group allocates its inputs only when one of its rows is wanted.
+def group_c1(wgf, dev):
+    """Fused element-wise chain y = cos(sin(x*2+1))*0.5 + exp(-x*x)."""
+    x1 = [dev.tensor(uniform(rng(1, k), (1024, 1024), -1, 1)) for k in range(64)]   # 256 MiB of inputs for the cold run
 
-    # C1: y = cos(sin(x*2+1))*0.5 + exp(-x*x) on [1024,1024] f32; 64 copies of x = 256 MiB for the cold run
-    x1 = [dev.tensor(uniform(rng(1, k), (1024, 1024), -1, 1)) for k in range(64)]
-
-    def c1(x):
+    def chain(x):
         return (x * 2.0 + 1.0).sin().cos() * 0.5 + (-(x * x)).exp()
-    out.append(Row("C1 chain f32 [1024,1024] cold", lambda k: c1(x1[k]), nbytes=8388608, variants=64))
-    out.append(Row("C1 chain f32 [1024,1024] warm", lambda k: c1(x1[0]), nbytes=8388608))
     xb = dev.tensor(uniform(rng(1, 100), (8192, 4096), -1, 1))
-    out.append(Row("C1' chain f32 [8192,4096]", lambda k: c1(xb), nbytes=2 * 134217728))
-    out.append(Row("x*2+1 f32 [8192,4096]", lambda k: xb * 2.0 + 1.0, nbytes=2 * 134217728))
+    return [Row("C1 chain f32 [1024,1024] cold", lambda k: chain(x1[k]), nbytes=8388608, variants=64),
+            Row("C1 chain f32 [1024,1024] warm", lambda k: chain(x1[0]), nbytes=8388608),
+            Row("C1' chain f32 [8192,4096]", lambda k: chain(xb), nbytes=2 * 134217728),
+            Row("C1 x*2+1 f32 [8192,4096]", lambda k: xb * 2.0 + 1.0, nbytes=2 * 134217728)]
 
-    # C2
+
+def group_c2(wgf, dev):
+    """Row-wise RmsNorm / softmax and reductions of f32 [8192,4096]."""
     x2 = dev.tensor(normal(rng(2, 0), (8192, 4096)))
     w2 = dev.tensor(normal(rng(2, 1), (4096,), 1.0, 0.1))
     normed = x2.layer_norm(w2, 1e-5)
     normed.materialize()
-    out.append(Row("C2a RmsNorm rows f32 [8192,4096]", lambda k: x2.layer_norm(w2, 1e-5), nbytes=268451840))
-    out.append(Row("C2b softmax rows f32 [8192,4096]", lambda k: normed.softmax_last_dim(), nbytes=268435456))
-    out.append(Row("C2ab RmsNorm->softmax f32 [8192,4096]", lambda k: x2.layer_norm(w2, 1e-5).softmax_last_dim(),
-                   nbytes=268451840))
-    out.append(Row("C2c sum(exp(x)) f32 [8192,4096]", lambda k: x2.exp().sum(0).sum(0), nbytes=134217728))
-    out.append(Row("sum(x) all f32 [8192,4096]", lambda k: x2.sum(0).sum(0), nbytes=134217728))
-    out.append(Row("sum(x, axis 1) f32 [8192,4096]", lambda k: x2.sum(1), nbytes=134217728 + 32768))
-    out.append(Row("max(x, axis 1) f32 [8192,4096]", lambda k: x2.max(1), nbytes=134217728 + 32768))
-    out.append(Row("sum(x, axis 0) f32 [8192,4096]", lambda k: x2.sum(0), nbytes=134217728 + 16384))
 
-    # C3
+    class Both:
+        """RmsNorm->softmax and sum(exp(x)) requested together: one kernel."""
+
+        def __init__(self):
+            self.y = x2.layer_norm(w2, 1e-5).softmax_last_dim()
+            self.s = x2.exp().sum(0).sum(0)
+
+        def materialize(self):
+            wgf.Tensor.materialize_all([self.y, self.s])
+
+        def all_timing_information(self):
+            return self.y.all_timing_information()
+
+        def timing_labels(self):
+            return self.y.timing_labels()
+
+        def release(self):
+            self.y.release()
+            self.s.release()
+
+    return [Row("C2a RmsNorm rows f32 [8192,4096]", lambda k: x2.layer_norm(w2, 1e-5), nbytes=268451840),
+            Row("C2b softmax rows f32 [8192,4096]", lambda k: normed.softmax_last_dim(), nbytes=268435456),
+            Row("C2ab RmsNorm->softmax f32 [8192,4096]", lambda k: x2.layer_norm(w2, 1e-5).softmax_last_dim(), nbytes=268451840),
+            Row("C2ab+c RmsNorm->softmax with sum(exp(x)) riding along", lambda k: Both(), nbytes=268451844),
+            Row("C2c sum(exp(x)) f32 [8192,4096]", lambda k: x2.exp().sum(0).sum(0), nbytes=134217728),
+            Row("C2 sum(x) all f32 [8192,4096]", lambda k: x2.sum(0).sum(0), nbytes=134217728),
+            Row("C2 sum(x, axis 1) f32 [8192,4096]", lambda k: x2.sum(1), nbytes=134217728 + 32768),
+            Row("C2 max(x, axis 1) f32 [8192,4096]", lambda k: x2.max(1), nbytes=134217728 + 32768),
+            Row("C2 sum(x, axis 0) f32 [8192,4096]", lambda k: x2.sum(0), nbytes=134217728 + 16384)]
+
+
+def group_c3(wgf, dev):
+    """Pair-wise with broadcast operands, transposed views, casts."""
     a = dev.tensor(normal(rng(3, 0), (64, 512, 1024)))
     b = dev.tensor(uniform(rng(3, 1), (512, 1024), -1, 1))
     c = dev.tensor(uniform(rng(3, 2), (64, 1024), 0, 1))
     bv = b.broadcast((64, 512, 1024))
     cv = c.broadcast_axis(1, 512)
-    out.append(Row("C3a silu(a*1.5)+b*c f32 [64,512,1024]", lambda k: (a * 1.5).silu() + bv * cv, nbytes=270794752))
     at, bt, ct = a.transpose(0, 1), bv.transpose(0, 1), cv.transpose(0, 1)
-    out.append(Row("C3b same, operands permuted (1,0,2)", lambda k: (at * 1.5).silu() + bt * ct, nbytes=270794752))
     a12, b12, c12 = a.transpose(1, 2), bv.transpose(1, 2), cv.transpose(1, 2)
-    out.append(Row("C3b' same, a.transpose(1,2): strided inner axis", lambda k: (a12 * 1.5).silu() + b12 * c12,
-                   nbytes=270794752))
-    out.append(Row("C3c cast f32->f16->f32 [64,512,1024]", lambda k: a.cast(F16).cast(wgf.F32), nbytes=268435456))
-    out.append(Row("cast f32->f16 [64,512,1024]", lambda k: a.cast(F16), nbytes=134217728 + 67108864))
-    out.append(Row("reshape of a.transpose(1,2) (gather) f32", lambda k: a12.reshape((64 * 1024, 512)), nbytes=268435456))
+    a2 = dev.tensor(normal(rng(3, 3), (64, 512, 1024)))
+    ah, a2h = a.cast(wgf.F16), a2.cast(wgf.F16)
+    ah.materialize(), a2h.materialize()
+    return [Row("C3a silu(a*1.5)+b*c f32 [64,512,1024]", lambda k: (a * 1.5).silu() + bv * cv, nbytes=270794752),
+            Row("C3b same, operands permuted (1,0,2)", lambda k: (at * 1.5).silu() + bt * ct, nbytes=270794752),
+            Row("C3b' same, a.transpose(1,2): strided inner axis", lambda k: (a12 * 1.5).silu() + b12 * c12, nbytes=270794752),
+            Row("C3c cast f32->f16->f32 [64,512,1024]", lambda k: a.cast(wgf.F16).cast(wgf.F32), nbytes=268435456),
+            Row("C3 cast f32->f16 [64,512,1024]", lambda k: a.cast(wgf.F16), nbytes=134217728 + 67108864),
+            Row("C3 reshape of a.transpose(1,2) (gather) f32", lambda k: a12.reshape((64 * 1024, 512)), nbytes=268435456),
+            Row("C3 a+b f32 [64,512,1024]", lambda k: a + a2, nbytes=3 * 134217728),
+            Row("C3 a+b f16 [64,512,1024]", lambda k: ah + a2h, nbytes=3 * 67108864),
+            Row("C3 silu(a)*b f16 [64,512,1024]", lambda k: ah.silu() * a2h, nbytes=3 * 67108864),
+            Row("C3 softmax rows f16 [64*512,1024]", lambda k: ah.softmax_last_dim(), nbytes=2 * 67108864)]
 
-    # C4
+
+def group_c4(wgf, dev):
+    """MatMul: square f32 / f16, batched f16, decode GEMV."""
     n = 4096
     af = dev.tensor(uniform(rng(4, 0), (n, n), -1, 1))
     bf = dev.tensor(uniform(rng(4, 1), (n, n), -1, 1))
-    ah, bh = af.cast(F16), bf.cast(F16)
+    ah, bh = af.cast(wgf.F16), bf.cast(wgf.F16)
     ah.materialize(), bh.materialize()
-    out.append(Row("C4a matmul f32 4096^3", lambda k: af.mat_mul(bf), flop=2 * n ** 3))
-    out.append(Row("C4b matmul f16 4096^3", lambda k: ah.mat_mul(bh), flop=2 * n ** 3))
-    out.append(Row("C4b matmul f16 4096^3, B transposed view", lambda k: ah.mat_mul(bh.transpose(0, 1)), flop=2 * n ** 3))
     a3 = dev.tensor(uniform(rng(4, 2), (32, 1024, 128), -1, 1).astype(np.float16))
     b3 = dev.tensor(uniform(rng(4, 3), (32, 128, 1024), -1, 1).astype(np.float16))
-    out.append(Row("C4c batched f16 [32,1024,128]x[32,128,1024]", lambda k: a3.mat_mul(b3), nbytes=83886080, flop=8589934592))
     xv = dev.tensor(uniform(rng(4, 4), (1, 4096), -1, 1).astype(np.float16))
     wv = dev.tensor(uniform(rng(4, 5), (4096, 11008), -1, 1).astype(np.float16))
     wt = dev.tensor(uniform(rng(4, 6), (11008, 4096), -1, 1).astype(np.float16))
-    out.append(Row("C4d GEMV f16 [1,4096]x[4096,11008]", lambda k: xv.mat_mul(wv), nbytes=90207744))
-    out.append(Row("C4d GEMV f16, weight stored [11008,4096]", lambda k: xv.mat_mul(wt.transpose(0, 1)), nbytes=90207744))
-    return out
+    return [Row("C4a matmul f32 4096^3", lambda k: af.mat_mul(bf), flop=2 * n ** 3),
+            Row("C4b matmul f16 4096^3", lambda k: ah.mat_mul(bh), flop=2 * n ** 3),
+            Row("C4b matmul f16 4096^3, B transposed view", lambda k: ah.mat_mul(bh.transpose(0, 1)), flop=2 * n ** 3),
+            Row("C4c batched f16 [32,1024,128]x[32,128,1024]", lambda k: a3.mat_mul(b3), nbytes=83886080, flop=8589934592),
+            Row("C4d GEMV f16 [1,4096]x[4096,11008]", lambda k: xv.mat_mul(wv), nbytes=90207744),
+            Row("C4d GEMV f16, weight stored [11008,4096]", lambda k: xv.mat_mul(wt.transpose(0, 1)), nbytes=90207744)]
 
 
-def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, emit=print):
+def group_c5(wgf, dev):
+    """Pieces of the Llama block at its full shape: fused causal attention, rope, SiLU gate."""
+    g = rng(5, 8)
+    bh, s, d = 256, 2048, 128
+    q, k, v = (dev.tensor(normal(g, (bh, s, d)).astype(np.float16)) for _ in range(3))
+    pos = np.arange(s, dtype=np.float32)[:, None]
+    inv = (1.0 / (10000.0 ** (np.arange(0, d, 2, dtype=np.float32) / d)))[None, :]
+    cos, sin = dev.tensor(np.cos(pos * inv).astype(np.float16)), dev.tensor(np.sin(pos * inv).astype(np.float16))
+    gate, up = (dev.tensor(normal(g, (16384, 11008)).astype(np.float16)) for _ in range(2))
+    causal_flop = 4 * bh * s * s * d // 2          # QK^T and PV, the masked half not counted
+    return [Row("C5 attention f16 causal [256,2048,128]", lambda i: q.attention(k, v, causal=True), flop=causal_flop),
+            Row("C5 attention f16 full [256,2048,128]", lambda i: q.attention(k, v), flop=2 * causal_flop),
+            Row("C5 rope f16 [256,2048,128]", lambda i: q.rope(cos, sin), nbytes=2 * bh * s * d * 2),
+            Row("C5 silu(gate)*up f16 [16384,11008]", lambda i: gate.silu() * up, nbytes=3 * 16384 * 11008 * 2)]
+
+
+GROUPS = [("C1", group_c1), ("C2", group_c2), ("C3", group_c3), ("C4", group_c4), ("C5", group_c5)]
+
+
+def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, only=None, emit=print):
     dev.set_timing(True)
     results = []
-    for row in rows_for(wgf, dev, peak_gbs):
-        med, best, labels = time_row(dev, row, iters, warmup)
-        med = max(med, 1e-9)          # the compile-only device records no time
-        r = {"row": row.name, "kernels": labels, "median_us": round(med, 2), "best_us": round(best, 2)}
-        if row.nbytes:
-            r["gbs"] = round(row.nbytes / med / 1e3, 1)
-            r["frac_hbm"] = round(row.nbytes / med / 1e3 / peak_gbs, 3)
-        if row.flop:
-            r["tflops"] = round(row.flop / med / 1e6, 1)
-            if not row.nbytes and "f32" in row.name:
-                # FFMA peak: 148 SMs x 128 lanes x 2 flop at the 1965 MHz maximum clock
-                r["frac_ffma_peak"] = round(row.flop / med / 1e6 / 74.5, 3)
-            elif not row.nbytes:
-                r["frac_bf16_peak"] = round(row.flop / med / 1e6 / peak_tflops, 3)
-        results.append(r)
-        emit(json.dumps(r))
+    for prefix, make in GROUPS:
+        if only and not (only.startswith(prefix) or not only.startswith("C")):
+            continue
+        rows = [r for r in make(wgf, dev) if not only or only in r.name]
+        for row in rows:
+            med, best, labels = time_row(dev, row, iters, warmup)
+            med = max(med, 1e-9)          # the compile-only device records no time
+            r = {"row": row.name, "kernels": labels, "median_us": round(med, 2), "best_us": round(best, 2)}
+            if row.nbytes:
+                r["gbs"] = round(row.nbytes / med / 1e3, 1)
+                r["frac_hbm"] = round(row.nbytes / med / 1e3 / peak_gbs, 3)
+            if row.flop:
+                r["tflops"] = round(row.flop / med / 1e6, 1)
+                if not row.nbytes and "f32" in row.name:
+                    # FFMA peak: 148 SMs x 128 lanes x 2 flop at the 1965 MHz maximum clock
+                    r["frac_ffma_peak"] = round(row.flop / med / 1e6 / 74.5, 3)
+                elif not row.nbytes:
+                    r["frac_bf16_peak"] = round(row.flop / med / 1e6 / peak_tflops, 3)
+            results.append(r)
+            emit(json.dumps(r))
+        del rows
     dev.set_timing(False)
     return results
