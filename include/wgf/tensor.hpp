@@ -322,6 +322,16 @@ class Tensor {
         check(wgf_tensor_rope(h_, cos.raw(), sin.raw(), &out));
         return Tensor(out);
     }
+    // ---- beyond the crate's API ---------------------------------------------------------------
+    // softmax(scale * this k^T [+ mask]) v for [batch*heads, seq, head_dim] tensors; mask may be null.
+    Tensor attention(const Tensor& k, const Tensor& v, const Tensor<2, D>* mask, bool causal, float scale) const {
+        static_assert(R == 3, "attention takes [batch*heads, sequence, head_dim]");
+        wgf_tensor* out = nullptr;
+        check(wgf_tensor_attention(h_, k.raw(), v.raw(), mask ? mask->raw() : nullptr, causal ? 1 : 0, scale, &out));
+        return Tensor(out);
+    }
+    // Queues the kernels of this tensor's graph without downloading (LazyTensorData::materialize).
+    void materialize() const { check(wgf_tensor_materialize(h_)); }
 
     explicit Tensor(wgf_tensor* raw) : h_(raw) {}
     wgf_tensor* raw() const { return h_; }
@@ -355,5 +365,13 @@ class Tensor {
     }
     wgf_tensor* h_ = nullptr;
 };
+
+// One request for several tensors of any rank and type (wgf_tensor_materialize_many): a
+// whole-tensor reduction among them is computed inside the row kernel of another one.
+template <typename... Ts>
+void materialize_all(const Ts&... tensors) {
+    wgf_tensor* raw[] = {tensors.raw()...};
+    check(wgf_tensor_materialize_many(raw, (uint32_t)sizeof...(Ts)));
+}
 
 }  // namespace wgf

@@ -47,6 +47,10 @@ int main(int argc, char** argv) {
     std::vector<float> ones(10 * 10 * 20, 1.f);
     Tensor<3, float> big(device, {10, 10, 20}, ones.data());
     auto total = big.sum(0).sum(0).sum(0);
+    // beyond the crate: two results as one request (the reduction rides along in the row kernel)
+    auto probs = data.softmax_last_dim();
+    auto sum_all = data.sum(0).sum(0);
+    wgf::materialize_all(probs, sum_all);
 
     EXPECT((joined.shape() == std::array<int64_t, 2>{3, 4}));
     EXPECT((bc.shape() == std::array<int64_t, 3>{2, 2, 3}));
@@ -84,6 +88,9 @@ int main(int argc, char** argv) {
     EXPECT((half.as_slice() == data.as_slice()));
     EXPECT((total.as_slice()[{}] == 2000.f));
     EXPECT(!total.all_timing_information().empty());
+    EXPECT((sum_all.as_slice()[{}] == 21.f));
+    auto pr = probs.as_slice();
+    EXPECT(std::fabs(pr[{1, 0}] + pr[{1, 1}] - 1.f) < 1e-6f);
 
     // tests/inplace_clone.rs:6-37: an in-place optimisation must not change a tensor that is still held
     for (int round = 0; round < 2; ++round) {
