@@ -16,6 +16,7 @@
 namespace wgf {
 
 bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d);
+bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d);
 
 namespace {
 
@@ -361,9 +362,11 @@ bool matmul_fast_path(Device& dev, const void* a, const void* b, void* c, DType 
             return false;
         case DType::F16:
             if (run_gemv<__half>(dev, a, b, c, d)) return true;
+            if (matmul_tc_pair_path(dev, a, b, c, dt, d)) return true;
             return matmul_tc_path(dev, a, b, c, dt, d);
         default:
             if (run_gemv<__nv_bfloat16>(dev, a, b, c, d)) return true;
+            if (matmul_tc_pair_path(dev, a, b, c, dt, d)) return true;
             return matmul_tc_path(dev, a, b, c, dt, d);
     }
 }

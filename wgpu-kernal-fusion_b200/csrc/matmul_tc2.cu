@@ -1,0 +1,389 @@
+// f16 / bf16 matmul on CTA PAIRS (tcgen05 cta_group::2): two CTAs of a cluster on neighbouring
+// SMs share one 256 x 256 output tile.  Each CTA stages its own 128 rows of A and its own 128
+// columns of B (the other half comes from the peer's shared memory inside the tensor cores)
+// and accumulates its 128 x 256 half of the tile in its own tensor memory.  Compared with one
+// CTA per 128 x 256 tile (matmul_tc.cu) every tcgen05.mma reads 8 KiB instead of 12 KiB of
+// operands per SM, so shared-memory bandwidth (128 bytes per clock) no longer caps the tensor
+// pipe at about 80 %.
+//
+// Roles per CTA: warp 0 = TMA producer (both CTAs load their halves; all loads of a stage
+// complete on the LEADER's "full" barrier), warp 1 = MMA issuer (leader only; its commits
+// arrive on both CTAs' barriers), warps 2-5 = epilogue (each CTA drains its own tensor memory
+// and tells the leader when an accumulator is free).  No TMA load uses multicast.  Every wait
+// is bounded and reports through the device error word.
+#include "matmul.hpp"
+#include "tc_common.cuh"
+
+namespace wgf {
+
+using namespace tc;
+
+namespace {
+
+constexpr int P_BM = 128;                 // rows of A per CTA (256 per pair)
+constexpr int P_BN = 256;                 // columns of the tile
+constexpr int P_BNH = 128;                // columns of B staged per CTA
+constexpr int P_BK = 64, P_STAGES = 6, P_UMMA_K = 16;
+constexpr int P_A_BYTES = P_BM * P_BK * 2;            // 16 KiB
+constexpr int P_B_BYTES = P_BNH * P_BK * 2;           // 16 KiB
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // per CTA; a stage of the pair is twice that
+constexpr int P_EPI_TILE_BYTES = 32 * 128;
+constexpr int P_EPI_BYTES = 4 * 2 * P_EPI_TILE_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int P_THREADS = 192;
+constexpr unsigned PEER_BIT_MASK = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared-memory address: the even CTA of the pair
+
+struct PairParams {
+    long long M, N, K, batch;
+    long long c_rs, c_bs;
+    int tiles_m, tiles_n;   // tiles of 256 x 256
+    int b_is_kn;
+    int is_bf16;
+    int use_tma_store;
+    unsigned* error;
+};
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(unsigned smem_dst, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[both CTAs' rows] * B[both CTAs' column halves]
+__device__ __forceinline__ void umma_pair_f16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                              unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, once every
+// tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit_pair(unsigned bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+// TMA load into this CTA's shared memory whose bytes are counted on `bar`, which may be the
+// peer's barrier (no multicast: one destination)
+__device__ __forceinline__ void tma_load_3d_pair(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// arrive on the barrier at the same offset in CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar, unsigned cta) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(bar), "r"(cta)
+        : "memory");
+}
+
+__host__ __device__ constexpr unsigned pair_instr_desc(bool b_mn_major) {
+    return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((unsigned)(P_BN >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+}
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_c, T* __restrict__ C, const __grid_constant__ PairParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* epi_smem = smem + P_STAGES * P_STAGE_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(epi_smem + P_EPI_BYTES);
+    // bars[0..5] full (used in the leader), [6..11] empty, [12..13] accumulator full, [14..15] accumulator empty (leader)
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * P_STAGES + 4);
+    const unsigned bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (P_STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * P_STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * P_STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_ctarank();           // 0: leader of the pair
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 8);             // one arrival per epilogue warp of either CTA
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    cluster_sync_all();                                 // both CTAs' barriers and tensor memory exist from here on
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+    const long long total_tiles = tiles_per_batch * p.batch;
+    const long long first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+    const int k_blocks = (int)((p.K + P_BK - 1) / P_BK);
+    const unsigned smem_base = smem_u32(smem);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 1;
+            bool ok = true;
+            for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+                const int b = (int)(tile / tiles_per_batch);
+                const int r = (int)(tile % tiles_per_batch);
+                const int m0 = (r % p.tiles_m) * 256 + (int)rank * P_BM;
+                const int n0 = (r / p.tiles_m) * P_BN + (int)rank * P_BNH;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase)) {
+                        atomicExch(p.error, 41u);
+                        ok = false;
+                        break;
+                    }
+                    const unsigned sa = smem_base + stage * P_STAGE_BYTES, sb = sa + P_A_BYTES;
+                    const unsigned fb = full_bar(stage) & PEER_BIT_MASK;        // the leader's barrier
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);   // both CTAs' bytes
+                    tma_load_3d_pair(sa, &map_a, fb, kb * P_BK, m0, b);
+                    if (p.b_is_kn) {
+#pragma unroll
+                        for (int j = 0; j < P_BNH / 64; ++j)
+                            tma_load_3d_pair(sb + j * (P_BK * 128), &map_b, fb, n0 + j * 64, kb * P_BK, b);
+                    } else {
+                        tma_load_3d_pair(sb, &map_b, fb, kb * P_BK, n0, b);
+                    }
+                    if (++stage == P_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            const unsigned idesc = pair_instr_desc(p.b_is_kn != 0) | ((unsigned)p.is_bf16 << 7) | ((unsigned)p.is_bf16 << 10);
+            int stage = 0;
+            unsigned phase = 0;
+            int acc = 0;
+            unsigned acc_phase = 1;
+            bool ok = true;
+            for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase)) {
+                    atomicExch(p.error, 42u);
+                    break;
+                }
+                tc_fence_after();
+                const unsigned tmem_d = tmem_base + (unsigned)acc * P_BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) {
+                        atomicExch(p.error, 43u);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const unsigned sa = smem_base + stage * P_STAGE_BYTES, sb = sa + P_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < P_BK / P_UMMA_K; ++k) {
+                        const unsigned long long adesc = smem_desc(sa + k * (P_UMMA_K * 2), 16, 1024);
+                        const unsigned long long bdesc = p.b_is_kn ? smem_desc(sb + k * (P_UMMA_K * 128), P_BK * 128, 1024)
+                                                                   : smem_desc(sb + k * (P_UMMA_K * 2), 16, 1024);
+                        umma_pair_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar(stage));      // frees the stage in both CTAs
+                    if (++stage == P_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                umma_commit_pair(acc_full_bar(acc));         // both halves of the accumulator are complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        const int quarter = warp & 3;
+        int acc = 0;
+        unsigned acc_phase = 0;
+        int epi_buf = 0;
+        const bool vec_ok = (p.c_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.c_bs % 8 == 0);
+        for (long long tile = first_tile; tile < total_tiles; tile += tile_step) {
+            const int b = (int)(tile / tiles_per_batch);
+            const int r = (int)(tile % tiles_per_batch);
+            const long long m0 = (long long)(r % p.tiles_m) * 256 + (long long)rank * P_BM, n0 = (long long)(r / p.tiles_m) * P_BN;
+            bool got = mbar_wait(acc_full_bar(acc), acc_phase);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+                if (lane == 0) atomicExch(p.error, 44u);
+                break;
+            }
+            tc_fence_after();
+            const long long m = m0 + quarter * 32 + lane;
+            T* crow = C + (long long)b * p.c_bs + m * p.c_rs;
+            if (p.use_tma_store) {
+#pragma unroll 1
+                for (int c = 0; c < P_BN; c += 64) {
+                    unsigned char* tile_smem = epi_smem + ((warp - 2) * 2 + epi_buf) * P_EPI_TILE_BYTES;
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        unsigned v[32];
+                        tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c + half * 32), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o;
+                            o.x = pack2<T>(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+                            o.y = pack2<T>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                            o.z = pack2<T>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                            o.w = pack2<T>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                            const int chunk = (half * 4 + q) ^ (lane & 7);
+                            *reinterpret_cast<uint4*>(tile_smem + lane * 128 + chunk * 16) = o;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    const long long mrow = m0 + quarter * 32, ncol = n0 + c;
+                    if (lane == 0 && mrow < p.M && ncol < p.N) {
+                        tma_store_3d(&map_c, smem_u32(tile_smem), (int)ncol, (int)mrow, b);
+                        bulk_commit();
+                    }
+                    epi_buf ^= 1;
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < P_BN; c += 32) {
+                    unsigned v[32];
+                    tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c), v);
+                    tmem_ld_wait();
+                    const long long n = n0 + c;
+                    if (m < p.M && n < p.N) {
+                        if (vec_ok && n + 31 < p.N) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint4 o;
+                                o.x = pack2<T>(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+                                o.y = pack2<T>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                                o.z = pack2<T>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                                o.w = pack2<T>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                                *reinterpret_cast<uint4*>(crow + n + 8 * q) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < p.N) {
+                                    unsigned pk = pack2<T>(__uint_as_float(v[j]), 0.f);
+                                    reinterpret_cast<unsigned short*>(crow)[n + j] = (unsigned short)(pk & 0xffff);
+                                }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_bar(acc), 0);    // the leader's barrier counts both CTAs' warps
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+        if (p.use_tma_store && lane == 0) bulk_wait_read<0>();
+    }
+    tc_fence_before();
+    cluster_sync_all();          // nobody signals into a CTA that has left, and both are done with tensor memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+// Takes the problem if it is big enough for 256 x 256 tiles; `false` hands it to the one-CTA kernel.
+bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d) {
+    if (getenv("WGF_MATMUL_NO_PAIR")) return false;
+    if (dt != DType::F16 && dt != DType::BF16) return false;
+    // a second half tile that is mostly padding wastes the peer CTA
+    const long long rem = d.M % 256;
+    if (d.M < 256 || d.N < 128 || d.K < 64 || (d.M < 2048 && rem != 0 && rem <= 128)) return false;
+    if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31) || d.batch >= (1ll << 31)) return false;
+    auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (d.a_cs != 1 || d.a_rs % 8 || !a16(a) || (d.batch > 1 && d.a_bs % 8)) return false;
+    const bool b_kn = d.b_cs == 1 && d.b_rs % 8 == 0;
+    const bool b_nk = d.b_rs == 1 && d.b_cs % 8 == 0;
+    if ((!b_kn && !b_nk) || !a16(b) || (d.batch > 1 && d.b_bs % 8)) return false;
+    if (dev.sm_count < 2) return false;
+    if (dev.dry) {
+        dev.begin_launch("matmul_tc2");
+        dev.end_launch();
+        return true;
+    }
+    const bool bf16 = dt == DType::BF16;
+    CUtensorMap map_a, map_b;
+    if (!encode_3d(&map_a, bf16, a, d.K, d.M, d.batch, d.a_rs, d.a_bs, P_BK, P_BM)) return false;
+    if (b_kn) {
+        if (!encode_3d(&map_b, bf16, b, d.N, d.K, d.batch, d.b_rs, d.b_bs, 64, P_BK)) return false;
+    } else {
+        if (!encode_3d(&map_b, bf16, b, d.K, d.N, d.batch, d.b_cs, d.b_bs, P_BK, P_BNH)) return false;
+    }
+    PairParams p{};
+    p.M = d.M;
+    p.N = d.N;
+    p.K = d.K;
+    p.batch = d.batch;
+    p.c_rs = d.c_rs;
+    p.c_bs = d.c_bs;
+    p.tiles_m = (int)((d.M + 255) / 256);
+    p.tiles_n = (int)((d.N + P_BN - 1) / P_BN);
+    p.b_is_kn = b_kn ? 1 : 0;
+    p.is_bf16 = bf16 ? 1 : 0;
+    CUtensorMap map_c = map_a;
+    p.use_tma_store = 0;
+    if (!getenv("WGF_TC_NO_TMA_STORE") && d.c_rs % 8 == 0 && (d.batch == 1 || d.c_bs % 8 == 0) && a16(c) &&
+        encode_3d(&map_c, bf16, c, d.N, d.M, d.batch, d.c_rs, d.c_bs, 64, 32))
+        p.use_tma_store = 1;
+    p.error = dev.error_word();
+    const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
+    const unsigned grid = 2u * (unsigned)std::min<long long>(total, dev.sm_count / 2);
+    static bool attr_set[2] = {false, false};
+    if (bf16) {
+        if (!attr_set[1]) {
+            WGF_CUDA(cudaFuncSetAttribute(matmul_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+            attr_set[1] = true;
+        }
+        dev.begin_launch("matmul_tc2");
+        matmul_tc2_kernel<__nv_bfloat16><<<grid, P_THREADS, P_SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__nv_bfloat16*)c, p);
+        dev.end_launch();
+    } else {
+        if (!attr_set[0]) {
+            WGF_CUDA(cudaFuncSetAttribute(matmul_tc2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+            attr_set[0] = true;
+        }
+        dev.begin_launch("matmul_tc2");
+        matmul_tc2_kernel<__half><<<grid, P_THREADS, P_SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__half*)c, p);
+        dev.end_launch();
+    }
+    return true;
+}
+
+}  // namespace wgf
