@@ -110,6 +110,28 @@ def test_skinny_gemv(m, kind, wgf, dev):
     assert normwise(result(ta.mat_mul(tbt.transpose(0, 1)), kind), ra @ rbt.T) <= TOL[kind]
 
 
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(1024, 1024, 4096), (1536, 1024, 2048), (512, 768, 8192), (2304, 256, 1600)])
+def test_matmul_tiles_split_along_k(shape, kind, wgf, dev, monkeypatch):
+    """Few 256 x 256 tiles and a long K: the CTA-pair kernel splits each tile's K range over
+    several clusters and the owner adds the fp32 partial tiles.  The smallest part allowed is
+    lowered from 32 to 8 k-blocks here so that 4-way and uneven 3-way splits occur."""
+    monkeypatch.setenv("WGF_MATMUL_KSPLIT_MIN", "8")
+    M, N, K = shape
+    g = seeded(4, 5)
+    a = g.random((M, K)) * 2 - 1
+    b = g.random((K, N)) * 2 - 1
+    ta, ra = make(dev, wgf, a, kind)
+    tb, rb = make(dev, wgf, b, kind)
+    ref = ra @ rb
+    assert normwise(result(ta.mat_mul(tb), kind), ref) <= TOL[kind]
+    bt = np.ascontiguousarray(b.T)
+    tbt, rbt = make(dev, wgf, bt, kind)
+    assert normwise(result(ta.mat_mul(tbt.transpose(0, 1)), kind), ref) <= TOL[kind]
+    # the same request twice: the flags of the first launch must not leak into the second
+    assert normwise(result(ta.mat_mul(tb), kind), ref) <= TOL[kind]
+
+
 def test_config4_full_sizes(wgf, dev):
     """Full benchmark sizes; checked on sampled rows against float64 (size-independent: any row is as good as another)."""
     g = seeded(4, 0)

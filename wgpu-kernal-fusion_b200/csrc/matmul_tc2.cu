@@ -40,8 +40,58 @@ struct PairParams {
     int b_is_kn;
     int is_bf16;
     int use_tma_store;
+    // Schedule: every cluster takes `full_waves` whole tiles (tile = wave * clusters + cluster);
+    // the `tail` tiles left over are split `split` ways along K (0 = not split) so that the last
+    // wave keeps all clusters busy.  Part 0 of a split tile owns the output: it adds the fp32
+    // partial tiles the other parts leave in `scratch` ([tail][split-1][256 columns][256 rows])
+    // once their per-warp flags ([tail][split-1][8]) are set.
+    int full_waves, tail, split;
+    float* scratch;
+    unsigned* flags;
     unsigned* error;
 };
+
+struct Unit {
+    long long tile;
+    int kb0, kb1;       // range of k-blocks
+    int part, parts;    // K-split: this is part `part` of `parts`
+    int tail_index;
+};
+
+// The `it`-th unit of work of cluster `cluster` (of `clusters`); false when there is none.
+__device__ __forceinline__ bool next_unit(const PairParams& p, long long cluster, long long clusters, int k_blocks, int it, Unit& u) {
+    u.kb0 = 0;
+    u.kb1 = k_blocks;
+    u.part = 0;
+    u.parts = 1;
+    u.tail_index = 0;
+    if (it < p.full_waves) {
+        u.tile = (long long)it * clusters + cluster;
+        return true;
+    }
+    if (it > p.full_waves) return false;
+    const long long base = (long long)p.full_waves * clusters;
+    if (p.split <= 1) {
+        if (cluster >= p.tail) return false;
+        u.tile = base + cluster;
+        return true;
+    }
+    if (cluster >= (long long)p.tail * p.split) return false;
+    u.tail_index = (int)(cluster / p.split);
+    u.part = (int)(cluster % p.split);
+    u.parts = p.split;
+    u.tile = base + u.tail_index;
+    const int per = (k_blocks + p.split - 1) / p.split;
+    u.kb0 = u.part * per;
+    u.kb1 = min(k_blocks, u.kb0 + per);
+    return true;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
     unsigned r;
@@ -135,8 +185,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const unsigned tmem_base = *tmem_slot;
 
     const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
-    const long long total_tiles = tiles_per_batch * p.batch;
-    const long long first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+    const long long cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
     const int k_blocks = (int)((p.K + P_BK - 1) / P_BK);
     const unsigned smem_base = smem_u32(smem);
 
@@ -146,12 +195,13 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int stage = 0;
             unsigned phase = 1;
             bool ok = true;
-            for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-                const int b = (int)(tile / tiles_per_batch);
-                const int r = (int)(tile % tiles_per_batch);
+            Unit u;
+            for (int it = 0; ok && next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
+                const int b = (int)(u.tile / tiles_per_batch);
+                const int r = (int)(u.tile % tiles_per_batch);
                 const int m0 = (r % p.tiles_m) * 256 + (int)rank * P_BM;
                 const int n0 = (r / p.tiles_m) * P_BN + (int)rank * P_BNH;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = u.kb0; kb < u.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase)) {
                         atomicExch(p.error, 41u);
                         ok = false;
@@ -184,14 +234,15 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int acc = 0;
             unsigned acc_phase = 1;
             bool ok = true;
-            for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+            Unit u;
+            for (int it = 0; ok && next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
                 if (!mbar_wait(acc_empty_bar(acc), acc_phase)) {
                     atomicExch(p.error, 42u);
                     break;
                 }
                 tc_fence_after();
                 const unsigned tmem_d = tmem_base + (unsigned)acc * P_BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = u.kb0; kb < u.kb1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase)) {
                         atomicExch(p.error, 43u);
                         ok = false;
@@ -204,7 +255,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         const unsigned long long adesc = smem_desc(sa + k * (P_UMMA_K * 2), 16, 1024);
                         const unsigned long long bdesc = p.b_is_kn ? smem_desc(sb + k * (P_UMMA_K * 128), P_BK * 128, 1024)
                                                                    : smem_desc(sb + k * (P_UMMA_K * 2), 16, 1024);
-                        umma_pair_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_pair_f16(tmem_d, adesc, bdesc, idesc, (kb != u.kb0 || k != 0) ? 1u : 0u);
                     }
                     umma_commit_pair(empty_bar(stage));      // frees the stage in both CTAs
                     if (++stage == P_STAGES) {
@@ -226,9 +277,10 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         unsigned acc_phase = 0;
         int epi_buf = 0;
         const bool vec_ok = (p.c_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.c_bs % 8 == 0);
-        for (long long tile = first_tile; tile < total_tiles; tile += tile_step) {
-            const int b = (int)(tile / tiles_per_batch);
-            const int r = (int)(tile % tiles_per_batch);
+        Unit u;
+        for (int it = 0; next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
+            const int b = (int)(u.tile / tiles_per_batch);
+            const int r = (int)(u.tile % tiles_per_batch);
             const long long m0 = (long long)(r % p.tiles_m) * 256 + (long long)rank * P_BM, n0 = (long long)(r / p.tiles_m) * P_BN;
             bool got = mbar_wait(acc_full_bar(acc), acc_phase);
             got = __all_sync(0xffffffffu, got);
@@ -239,6 +291,59 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const long long m = m0 + quarter * 32 + lane;
             T* crow = C + (long long)b * p.c_bs + m * p.c_rs;
+            // K-split tiles: row of this thread in the 256-row tile, slot of this warp among the 8 of the pair
+            const int trow = (int)rank * P_BM + quarter * 32 + lane;
+            const int wslot = (int)rank * 4 + quarter;
+            const size_t part_stride = 256 * 256;
+            const size_t first_part = (size_t)u.tail_index * (size_t)(u.parts - 1);
+            if (u.parts > 1 && u.part > 0) {
+                // not the owner of the tile: leave the fp32 partial sums in scratch, column-major so
+                // that the 32 lanes of a warp (32 rows) write 128 contiguous bytes, then raise the flag
+                float* part = p.scratch + (first_part + (size_t)(u.part - 1)) * part_stride;
+#pragma unroll 1
+                for (int c = 0; c < P_BN; c += 32) {
+                    unsigned v[32];
+                    tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) part[(size_t)(c + i) * 256 + trow] = __uint_as_float(v[i]);
+                }
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicExch(&p.flags[(first_part + (size_t)(u.part - 1)) * 8 + wslot], 1u);
+            } else {
+            if (u.parts > 1) {
+                // owner: the matching warp of every other part must have written its rows
+                bool all = true;
+                for (int pp = 1; pp < u.parts; ++pp) {
+                    const unsigned* f = &p.flags[(first_part + (size_t)(pp - 1)) * 8 + wslot];
+                    bool seen = false;
+                    unsigned long long start = 0;
+                    for (unsigned spin = 0; spin < SPIN_LIMIT && !seen; ++spin) {
+                        seen = ld_acquire_u32(f) != 0;
+                        if (!seen && (spin & 63) == 63) {
+                            const unsigned long long now = global_ns();
+                            if (start == 0) start = now;
+                            else if (now - start > 2000000000ull) break;
+                        }
+                    }
+                    all = all && seen;
+                }
+                all = __all_sync(0xffffffffu, all);
+                if (!all) {
+                    if (lane == 0) atomicExch(p.error, 45u);
+                    break;
+                }
+            }
+            // adds the other parts' partial sums to 32 accumulator columns starting at column c0
+            auto add_parts = [&](unsigned* v, int c0) {
+                for (int pp = 1; pp < u.parts; ++pp) {
+                    const float* part = p.scratch + (first_part + (size_t)(pp - 1)) * part_stride;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(part + (size_t)(c0 + i) * 256 + trow));
+                }
+            };
             if (p.use_tma_store) {
 #pragma unroll 1
                 for (int c = 0; c < P_BN; c += 64) {
@@ -250,6 +355,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         unsigned v[32];
                         tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c + half * 32), v);
                         tmem_ld_wait();
+                        if (u.parts > 1) add_parts(v, c + half * 32);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint4 o;
@@ -276,6 +382,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     unsigned v[32];
                     tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c), v);
                     tmem_ld_wait();
+                    if (u.parts > 1) add_parts(v, c);
                     const long long n = n0 + c;
                     if (m < p.M && n < p.N) {
                         if (vec_ok && n + 31 < p.N) {
@@ -299,6 +406,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                 }
             }
+            }   // owner or unsplit tile
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty_bar(acc), 0);    // the leader's barrier counts both CTAs' warps
@@ -364,7 +472,62 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
         p.use_tma_store = 1;
     p.error = dev.error_word();
     const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
-    const unsigned grid = 2u * (unsigned)std::min<long long>(total, dev.sm_count / 2);
+    // Schedule (see PairParams).  The leftover tiles of the last wave are split along K when
+    // that at least halves their time and every part keeps 32 or more k-blocks (K >= 2048 per
+    // part): the fix-up (a 256 KiB fp32 partial tile written, waited for and added per part)
+    // costs about as much as 8 k-blocks, and measured on 4096^3 (34 leftover tiles, split in
+    // two) the step is neutral: 105.0 us with, 105.4 us without.
+    // Parts of a split tile wait for one another, so every cluster of the grid has to be resident
+    // at once: the grid is capped by what the device reports for this kernel.
+    static int resident[2] = {-1, -1};
+    const int ti = bf16 ? 1 : 0;
+    if (resident[ti] < 0) {
+        const void* fn = bf16 ? (const void*)matmul_tc2_kernel<__nv_bfloat16> : (const void*)matmul_tc2_kernel<__half>;
+        WGF_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(dev.sm_count & ~1));
+        cfg.blockDim = dim3(P_THREADS);
+        cfg.dynamicSmemBytes = P_SMEM_BYTES;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2;
+        at.val.clusterDim.y = 1;
+        at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        resident[ti] = n;
+    }
+    if (resident[ti] < 1) return false;
+    long long clusters = std::min<long long>(dev.sm_count / 2, resident[ti]);
+    const int k_blocks = (int)((d.K + P_BK - 1) / P_BK);
+    p.full_waves = (int)(total / clusters);
+    p.tail = (int)(total % clusters);
+    p.split = 0;
+    if (p.tail > 0 && !getenv("WGF_MATMUL_NO_KSPLIT")) {
+        int s = (int)std::min<long long>(4, clusters / p.tail);
+        const int min_part = getenv("WGF_MATMUL_KSPLIT_MIN") ? std::max(1, atoi(getenv("WGF_MATMUL_KSPLIT_MIN"))) : 32;
+        while (s >= 2 && ((k_blocks + s - 1) / s < min_part || ((k_blocks + s - 1) / s) * (s - 1) >= k_blocks)) --s;
+        if (s >= 2) p.split = s;
+    }
+    if (p.full_waves == 0 && p.split == 0) clusters = p.tail;   // fewer tiles than clusters and no split: a smaller grid
+    BufferRef scratch, flags;
+    if (p.split >= 2) {
+        const size_t parts = (size_t)p.tail * (size_t)(p.split - 1);
+        scratch = dev.alloc(parts * 256 * 256 * sizeof(float), false);
+        flags = dev.alloc(parts * 8 * sizeof(unsigned), false);
+        WGF_CUDA(cudaMemsetAsync(flags->ptr, 0, parts * 8 * sizeof(unsigned), dev.stream));
+        p.scratch = (float*)scratch->ptr;
+        p.flags = (unsigned*)flags->ptr;
+    }
+    const unsigned grid = 2u * (unsigned)clusters;
+    if (getenv("WGF_MATMUL_VERBOSE"))
+        fprintf(stderr, "[wgf] matmul_tc2 %lldx%lldx%lld batch %lld: %lld tiles on %lld clusters (%d resident), %d full waves, tail %d split %d\n",
+                d.M, d.N, d.K, d.batch, total, clusters, resident[ti], p.full_waves, p.tail, p.split);
     static bool attr_set[2] = {false, false};
     if (bf16) {
         if (!attr_set[1]) {
