@@ -839,7 +839,7 @@ int32_t wgf_tensor_graph_size(wgf_tensor* t, uint64_t* nodes) {
     GRAPH_GUARD({
         REQUIRE(t);
         REQUIRE(nodes);
-        *nodes = graph_of(t->node)->nodes.size();
+        *nodes = graph_of(t->node)->live_nodes;
     })
 }
 

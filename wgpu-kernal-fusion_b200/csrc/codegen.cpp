@@ -478,8 +478,11 @@ std::string row_source(const Program& prog, const RowConfig& c) {
                 << "  for (u32 b_ = threadIdx.x; b_ < gridDim.x; b_ += THREADS) a_ = red_comb<" << op
                 << ">(a_, __ldcg(gpart + (u64)b_ * NGRAND + " << id << "));\n"
                 << "  __syncthreads();\n  a_ = group_reduce<" << op << ", THREADS>(a_, g_smem[" << id
-                << "], (int)threadIdx.x);\n  if (threadIdx.x == 0) store1<" << (int)gr.dtype << ">((void*)p.gout[" << id
-                << "], 0, a_); }\n";
+                << "], (int)threadIdx.x);\n  if (threadIdx.x == 0) {\n";
+        if (gr.all_reduce)   // the value of this GPU is rounded to the element type, then combined across GPUs
+            gfinish << "    a_ = peer_all_reduce<" << red_name(gr.ar_op) << ">(" << rounded(gr.dtype, "a_") << ", " << id
+                    << ", p);\n";
+        gfinish << "    store1<" << (int)gr.dtype << ">((void*)p.gout[" << id << "], 0, a_); } }\n";
     }
     // A group_reduce reuses its shared-memory slot in the next iteration: all reads of this
     // iteration must be done before the next row writes.
@@ -683,7 +686,7 @@ int64_t max_resident_row(bool) { return 32768; }
 
 TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
                     const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot,
-                    std::vector<TensorData>* grand_out) {
+                    std::vector<TensorData>* grand_out, const GrandComm* gc) {
     const int nin = prog.n_slots();
     WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
     WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
@@ -940,7 +943,14 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
                 g.dtype = gr.dtype;
                 w.put<uint64_t>((uint64_t)(uintptr_t)g.base_ptr());
                 grand_out->push_back(g);
+                WGF_CHECK(!gr.all_reduce || gc, WGF_ERR_INVALID_ARGUMENT, "in-kernel all-reduce without a communicator");
             }
+            w.put<uint64_t>(gc ? (uint64_t)(uintptr_t)gc->peer_table : 0);
+            w.put<uint64_t>((uint64_t)(uintptr_t)dev.error_word());
+            w.put<uint32_t>(gc ? gc->world : 1);
+            w.put<uint32_t>(gc ? gc->rank : 0);
+            w.put<uint32_t>(gc ? gc->seq : 0);
+            w.put<uint32_t>(0);
         }
         put_tail(w);
         dev.launch(k, dim3((unsigned)blocks), dim3(cfg.GROUP * cfg.RPC), 0, w.bytes.data(), "rows");

@@ -37,8 +37,8 @@ GraphInner::~GraphInner() {
 void merge_graphs(const NodeRef& a, const NodeRef& b) {
     auto ga = find_graph(a->graph), gb = find_graph(b->graph);
     if (ga == gb) return;
-    for (auto& kv : gb->nodes) ga->nodes.insert(kv);
-    gb->nodes.clear();
+    ga->live_nodes += gb->live_nodes;
+    gb->live_nodes = 0;
     ga->timings.insert(ga->timings.end(), gb->timings.begin(), gb->timings.end());
     gb->timings.clear();
     gb->forwarded = ga;
@@ -47,7 +47,7 @@ void merge_graphs(const NodeRef& a, const NodeRef& b) {
 
 Node::~Node() {
     drop_inputs();
-    if (graph) find_graph(graph)->nodes.erase(id);
+    if (graph) find_graph(graph)->live_nodes--;
 }
 
 void Node::drop_inputs() {
@@ -80,7 +80,7 @@ static NodeRef new_node(NodeKind kind, const DeviceRef& dev, std::vector<int64_t
         for (size_t i = 1; i < inputs.size(); ++i) merge_graphs(inputs[0], inputs[i]);
     }
     n->inputs = std::move(inputs);
-    find_graph(n->graph)->nodes[n->id] = n.get();
+    find_graph(n->graph)->live_nodes++;
     return n;
 }
 
@@ -482,11 +482,31 @@ namespace {
 
 bool is_ew(const Node* n) { return n->kind == NodeKind::ElementWise || n->kind == NodeKind::PairWise; }
 
+// A set of nodes (or a map node -> int) kept in the nodes' own scratch slots: membership means
+// "slot `kind` carries this set's epoch".  Sets of one kind used at the same time overwrite each
+// other's entries, so a caller that runs nested resolutions re-inserts what it still needs.
+static uint64_t g_mark_epoch = 0;
+struct MarkSet {
+    uint64_t epoch;
+    int kind;
+    explicit MarkSet(int k) : epoch(++g_mark_epoch), kind(k) {}
+    bool contains(const Node* n) const { return n->scratch[kind].epoch == epoch; }
+    bool insert(Node* n, int value = 0) {
+        if (contains(n)) return false;
+        n->scratch[kind].epoch = epoch;
+        n->scratch[kind].value = value;
+        return true;
+    }
+    int get(const Node* n) const { return n->scratch[kind].value; }
+    void erase(Node* n) const {
+        if (contains(n)) n->scratch[kind].epoch = 0;
+    }
+};
+
 // Will `x` be unreachable once `root` has been materialised and has let go of its inputs?
-bool dies_with(Node* x, Node* root, std::unordered_map<Node*, bool>& memo) {
+bool dies_with(Node* x, Node* root, MarkSet& memo) {
     if (x == root) return true;
-    auto it = memo.find(x);
-    if (it != memo.end()) return it->second;
+    if (memo.contains(x)) return memo.get(x) != 0;
     bool dead = x->handles == 0;
     if (dead)
         for (Node* c : x->consumers)
@@ -494,7 +514,7 @@ bool dies_with(Node* x, Node* root, std::unordered_map<Node*, bool>& memo) {
                 dead = false;
                 break;
             }
-    memo[x] = dead;
+    memo.insert(x, dead ? 1 : 0);
     return dead;
 }
 
@@ -511,14 +531,19 @@ struct Region {
     std::vector<int> axes;        // reduced axes of E (one, or a trailing block when folded)
     Node* fold_top = nullptr;     // outermost node of a folded reduce chain
     Node* fold_x = nullptr;       // its per-element input
-    std::unordered_map<Node*, char> has_reduce_memo;
-    std::vector<Node*> leaves;
-    std::unordered_set<Node*> leaf_set;
-    std::unordered_set<Node*> visited;
+    MarkSet has_reduce_memo{Node::S_HAS_REDUCE};
+    std::vector<Node*> leaves, fused_nodes;
+    MarkSet leaf_set{Node::S_LEAF};
+    MarkSet visited{Node::S_FUSED};
     int n_fused = 0;
 
     enum Dom { Elem, Row };
 
+    // Marks again what nested resolutions (of the leaves) may have overwritten.
+    void restamp() {
+        for (Node* n : fused_nodes) visited.insert(n);
+        for (Node* n : leaves) leaf_set.insert(n);
+    }
     bool reduce_matches(const Node* n) const {
         if (n == fold_top) return true;
         return n->kind == NodeKind::Reduce && !n->cached && axes.size() == 1 && n->axis == axes[0] &&
@@ -526,13 +551,12 @@ struct Region {
     }
     bool row_chain_has_reduce(Node* n) {
         if (n->cached || n->shape != Rw) return false;
-        auto it = has_reduce_memo.find(n);
-        if (it != has_reduce_memo.end()) return it->second;
+        if (has_reduce_memo.contains(n)) return has_reduce_memo.get(n) != 0;
         bool r = false;
         if (n->kind == NodeKind::Reduce) r = reduce_matches(n);
         else if (is_ew(n))
             for (auto& in : n->inputs) r = r || row_chain_has_reduce(in.get());
-        has_reduce_memo[n] = r;
+        has_reduce_memo.insert(n, r ? 1 : 0);
         return r;
     }
     bool bcast_of_row(const Node* n) const {
@@ -555,10 +579,11 @@ struct Region {
     }
     void collect(Node* n, Dom d) {
         if (!fused(n, d)) {
-            if (leaf_set.insert(n).second) leaves.push_back(n);
+            if (leaf_set.insert(n)) leaves.push_back(n);
             return;
         }
-        if (!visited.insert(n).second) return;
+        if (!visited.insert(n)) return;
+        fused_nodes.push_back(n);
         n_fused++;
         if (n == fold_top) {
             collect(fold_x, Elem);
@@ -574,8 +599,8 @@ struct Region {
 
 // Finds, below an element-shaped root, a broadcast-along-the-last-axis of a reduction over
 // that axis (RmsNorm, softmax, ...).
-bool find_row_pattern(Node* n, const std::vector<int64_t>& E, std::unordered_set<Node*>& seen, Region& probe) {
-    if (n->cached || n->shape != E || !seen.insert(n).second) return false;
+bool find_row_pattern(Node* n, const std::vector<int64_t>& E, MarkSet& seen, Region& probe) {
+    if (n->cached || n->shape != E || !seen.insert(n)) return false;
     if (n->kind == NodeKind::MapLayout) return probe.bcast_of_row(n) && probe.row_chain_has_reduce(n->inputs[0].get());
     if (!is_ew(n)) return false;
     for (auto& in : n->inputs)
@@ -584,8 +609,8 @@ bool find_row_pattern(Node* n, const std::vector<int64_t>& E, std::unordered_set
 }
 
 // Finds the first reduction below a row-shaped root, walking element-wise nodes of equal shape.
-Node* find_reduce_below(Node* n, const std::vector<int64_t>& shape, std::unordered_set<Node*>& seen) {
-    if (n->cached || n->shape != shape || !seen.insert(n).second) return nullptr;
+Node* find_reduce_below(Node* n, const std::vector<int64_t>& shape, MarkSet& seen) {
+    if (n->cached || n->shape != shape || !seen.insert(n)) return nullptr;
     if (n->kind == NodeKind::Reduce) return n;
     if (!is_ew(n)) return nullptr;
     for (auto& in : n->inputs)
@@ -634,7 +659,7 @@ struct Emitter {
     Program prog;
     std::vector<TensorData> slots;
     std::vector<Node*> slot_leaf;
-    std::unordered_map<Node*, int> value;
+    MarkSet value{Node::S_VALUE};
     bool ok = true;
 
     explicit Emitter(Region& r) : rg(r) {}
@@ -675,10 +700,9 @@ struct Emitter {
     }
 
     int emit(Node* n, Region::Dom d) {
-        auto it = value.find(n);
-        if (it != value.end()) return it->second;
+        if (value.contains(n)) return value.get(n);
         int v;
-        if (rg.leaf_set.count(n)) {
+        if (rg.leaf_set.contains(n)) {
             v = leaf(n, d);
         } else if (n == rg.fold_top) {
             v = prog.row_reduce(n->op, emit(rg.fold_x, Region::Elem));
@@ -696,7 +720,7 @@ struct Emitter {
             else if (n->op >= WGF_OP_ADD_C) v = prog.scalar(n->op, a, round_imm(n->imm, prog.ins[a].dtype));
             else v = prog.unary(n->op, a);
         }
-        value[n] = v;
+        value.insert(n, v);
         return v;
     }
 };
@@ -715,7 +739,7 @@ void plan_region(Region& rg, bool allow_fold) {
             probe.E = root->shape;
             probe.Rw.assign(root->shape.begin(), root->shape.end() - 1);
             probe.axes = {root->rank() - 1};
-            std::unordered_set<Node*> seen;
+            MarkSet seen(Node::S_SEEN);
             if (find_row_pattern(root, root->shape, seen, probe)) {
                 rg.row_mode = true;
                 rg.out_has_h = true;
@@ -726,7 +750,7 @@ void plan_region(Region& rg, bool allow_fold) {
             }
         }
         // (2) row-shaped result: element-wise epilogue on top of a reduction
-        std::unordered_set<Node*> seen;
+        MarkSet seen(Node::S_SEEN);
         if (Node* r = find_reduce_below(root, root->shape, seen)) {
             rg.row_mode = true;
             rg.out_has_h = false;
@@ -778,8 +802,13 @@ void plan_region(Region& rg, bool allow_fold) {
 
 // Nodes requested together with `g_companion_host` (resolve_many): whole-tensor reductions
 // that may ride along in the host's row kernel, which already has every element in registers.
+// Each candidate comes with the all-reduce node requested on top of it, if any.
+struct Candidate {
+    Node* reduce;
+    Node* all_reduce;
+};
 thread_local Node* g_companion_host = nullptr;
-thread_local std::vector<Node*>* g_companions = nullptr;
+thread_local std::vector<Candidate>* g_companions = nullptr;
 
 // The per-element expression under a reduction (or folded chain of reductions) of a whole
 // tensor of shape `E` to a scalar; nullptr if `c` is not of that form.
@@ -795,18 +824,19 @@ Node* companion_expr(Node* c, const std::vector<int64_t>& E) {
 // Adds the element-wise nodes under `n` to the host region `rg` (same index space); anything
 // else becomes an input of the kernel.
 void gather_companion(Node* n, Region& rg) {
-    if (rg.visited.count(n)) return;   // already computed by the host
+    if (rg.visited.contains(n)) return;   // already computed by the host
     if (!n->cached && is_ew(n) && n->shape == rg.E) {
         rg.visited.insert(n);
+        rg.fused_nodes.push_back(n);
         rg.n_fused++;
         for (auto& in : n->inputs) gather_companion(in.get(), rg);
-    } else if (rg.leaf_set.insert(n).second) {
+    } else if (rg.leaf_set.insert(n)) {
         rg.leaves.push_back(n);
     }
 }
 
 TensorData run_region(Node* root, bool allow_fold = true) {
-    std::vector<Node*> candidates;
+    std::vector<Candidate> candidates;
     if (g_companions && root == g_companion_host) {
         candidates = *g_companions;
         g_companions = nullptr;   // leaves resolved below must not pick them up again
@@ -816,27 +846,57 @@ TensorData run_region(Node* root, bool allow_fold = true) {
     plan_region(rg, allow_fold);
     rg.collect(root, rg.row_mode && !rg.out_has_h ? Region::Row : Region::Elem);
     for (Node* l : rg.leaves) resolve_node(l);   // a candidate the host depends on is computed here
-    std::vector<std::pair<Node*, Node*>> companions;   // (reduction node, its per-element expression)
+    rg.restamp();
+    struct Companion {
+        Node* reduce;       // the reduction node
+        Node* expr;         // its per-element expression
+        Node* all_reduce;   // the all-reduce node on top of it that the kernel performs too, or null
+    };
+    std::vector<Companion> companions;
+    Comm* kernel_comm = nullptr;   // one communicator per kernel
     if (rg.row_mode && rg.out_has_h && root->numel() > 0) {
-        for (Node* c : candidates) {
-            if (c->dev != root->dev || companions.size() >= 4) continue;
+        for (const Candidate& cand : candidates) {
+            Node* c = cand.reduce;
+            if (c->dev != root->dev || companions.size() >= (size_t)kMailboxValues) continue;
             Node* expr = companion_expr(c, rg.E);
             if (!expr) continue;
-            Region trial = rg;
-            gather_companion(expr, trial);
-            if (trial.leaves.size() > 12 || trial.n_fused > 200) continue;
-            rg = std::move(trial);
-            companions.emplace_back(c, expr);
+            const size_t nf = rg.fused_nodes.size(), nl = rg.leaves.size();
+            const int fused_before = rg.n_fused;
+            gather_companion(expr, rg);
+            if (rg.leaves.size() > 12 || rg.n_fused > 200) {   // too big: take its nodes out again
+                for (size_t i = nf; i < rg.fused_nodes.size(); ++i) rg.visited.erase(rg.fused_nodes[i]);
+                for (size_t i = nl; i < rg.leaves.size(); ++i) rg.leaf_set.erase(rg.leaves[i]);
+                rg.fused_nodes.resize(nf);
+                rg.leaves.resize(nl);
+                rg.n_fused = fused_before;
+                continue;
+            }
+            // The all-reduce on top of it is done by the same kernel over peer memory when the
+            // partial result of this GPU is not observable on its own.
+            Node* ar = cand.all_reduce;
+            const bool fuse_ar = ar && !ar->cached && ar->comm && ar->comm->peer_ok && c->handles == 0 &&
+                                 c->consumers.size() == 1 && c->consumers[0] == ar &&
+                                 (!kernel_comm || kernel_comm == ar->comm.get());
+            if (fuse_ar) kernel_comm = ar->comm.get();
+            companions.push_back(Companion{c, expr, fuse_ar ? ar : nullptr});
+        }
+        if (!companions.empty()) {
+            for (Node* l : rg.leaves) resolve_node(l);
+            rg.restamp();
         }
     }
-    for (Node* l : rg.leaves) resolve_node(l);
 
     Emitter em(rg);
     int res = em.emit(root, rg.row_mode && !rg.out_has_h ? Region::Row : Region::Elem);
     em.prog.result = res;
     for (auto& ce : companions) {
-        int v = em.emit(ce.second, Region::Elem);
-        em.prog.grands.push_back(Grand{ce.first->op, v, ce.first->dtype});
+        int v = em.emit(ce.expr, Region::Elem);
+        Grand g{ce.reduce->op, v, ce.reduce->dtype};
+        if (ce.all_reduce) {
+            g.all_reduce = true;
+            g.ar_op = ce.all_reduce->op;
+        }
+        em.prog.grands.push_back(g);
     }
     if (!em.ok) {
         WGF_CHECK(rg.fold_top != nullptr, WGF_ERR_UNSUPPORTED, "internal: unmergeable index space");
@@ -860,7 +920,7 @@ TensorData run_region(Node* root, bool allow_fold = true) {
     Node* donor = nullptr;
     TensorData saved;
     if (!rg.row_mode || rg.out_has_h) {
-        std::unordered_map<Node*, bool> memo;
+        MarkSet memo(Node::S_DIES);
         const DType odt = em.prog.out_dtype();
         for (int s = 0; s < (int)em.slots.size() && inplace < 0; ++s) {
             Node* l = em.slot_leaf[s];
@@ -886,7 +946,9 @@ TensorData run_region(Node* root, bool allow_fold = true) {
     std::vector<TensorData> grand_out;
     try {
         Device& dev = *root->dev;
-        if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace, &grand_out);
+        GrandComm gc{};
+        if (kernel_comm) gc = GrandComm{kernel_comm->peer_table, (uint32_t)kernel_comm->world, (uint32_t)kernel_comm->rank, ++kernel_comm->seq};
+        if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace, &grand_out, kernel_comm ? &gc : nullptr);
         else out = run_elementwise(dev, em.prog, em.slots, index_shape, inplace);
     } catch (...) {
         if (donor) {
@@ -896,7 +958,9 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         throw;
     }
     for (size_t i = 0; i < companions.size(); ++i) {
-        Node* c = companions[i].first;
+        // the value belongs to the all-reduce node when the kernel did that too (the reduction
+        // node below it is never materialised and goes away with the all-reduce's inputs)
+        Node* c = companions[i].all_reduce ? companions[i].all_reduce : companions[i].reduce;
         c->cached = grand_out[i];
         c->drop_inputs();
     }
@@ -974,7 +1038,7 @@ TensorData resolve_node(Node* n) {
             TensorData value = resolve_node(n->inputs[1].get());
             // The crate writes into the target's buffer.  That is kept only when nothing else
             // can still read the old contents; otherwise the target is copied first.
-            std::unordered_map<Node*, bool> memo;
+            MarkSet memo(Node::S_DIES);
             bool own = dies_with(tn, n, memo) && !target.layout.allocation_overlaps();
             if (own) {
                 tn->cached = TensorData();           // `target` now holds the only reference if unshared
@@ -998,7 +1062,7 @@ TensorData resolve_node(Node* n) {
             const bool dense_in = in.layout.is_dense() && !in.layout.allocation_overlaps();
             // The collective runs in place.  If nothing else can read the partial result any
             // more, its own buffer is used (no copy); otherwise a dense copy is reduced.
-            std::unordered_map<Node*, bool> memo;
+            MarkSet memo(Node::S_DIES);
             bool own = dense_in && dies_with(src, n, memo);
             if (own) {
                 src->cached = TensorData();
@@ -1043,13 +1107,19 @@ TensorData resolve(const NodeRef& n) {
 // and lists fusing sibling reductions as future work (README.md:19-22).
 void resolve_many(const std::vector<NodeRef>& nodes) {
     std::vector<NodeRef> keep;   // the candidates stay alive whatever the hosts resolve
+    std::vector<Candidate> comps;
     for (auto& n : nodes) {
         NodeRef c = n;
-        if (!c->cached && c->kind == NodeKind::AllReduce) c = c->inputs[0];
-        if (!c->cached && c->kind == NodeKind::Reduce && c->rank() == 0) keep.push_back(c);
+        Node* ar = nullptr;
+        if (!c->cached && c->kind == NodeKind::AllReduce) {
+            ar = c.get();
+            c = c->inputs[0];
+        }
+        if (!c->cached && c->kind == NodeKind::Reduce && c->rank() == 0) {
+            keep.push_back(c);
+            comps.push_back(Candidate{c.get(), ar});
+        }
     }
-    std::vector<Node*> comps;
-    for (auto& c : keep) comps.push_back(c.get());
     for (auto& n : nodes) {
         if (n->cached || !is_ew(n.get()) || comps.empty()) continue;
         g_companion_host = n.get();
@@ -1063,7 +1133,11 @@ void resolve_many(const std::vector<NodeRef>& nodes) {
         }
         g_companions = nullptr;
         g_companion_host = nullptr;
-        comps.erase(std::remove_if(comps.begin(), comps.end(), [](Node* c) { return (bool)c->cached; }), comps.end());
+        comps.erase(std::remove_if(comps.begin(), comps.end(),
+                                   [](const Candidate& c) {
+                                       return (bool)c.reduce->cached || (c.all_reduce && (bool)c.all_reduce->cached);
+                                   }),
+                    comps.end());
     }
     for (auto& n : nodes) resolve(n);
 }

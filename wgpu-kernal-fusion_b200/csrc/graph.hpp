@@ -51,6 +51,14 @@ struct Node {
     ViewOp view;
     std::vector<int64_t> new_shape, fill_shape, starts, ends;
     std::shared_ptr<Comm> comm;
+    // Scratch of the resolver, used instead of hash containers keyed by node: a "set" is an epoch
+    // number, and the node belongs to it while the slot of that kind carries the epoch.
+    struct Scratch {
+        uint64_t epoch = 0;
+        int value = 0;
+    };
+    enum { S_FUSED = 0, S_LEAF, S_HAS_REDUCE, S_SEEN, S_VALUE, S_DIES, S_COUNT };
+    Scratch scratch[S_COUNT];
     // state
     TensorData cached;
     int handles = 0;
@@ -70,7 +78,7 @@ using NodeRef = std::shared_ptr<Node>;
 
 struct GraphInner {
     std::shared_ptr<GraphInner> forwarded;          // set once this graph has been merged away
-    std::unordered_map<uint64_t, Node*> nodes;      // live nodes (the crate's node maps)
+    uint64_t live_nodes = 0;                        // nodes alive in this graph (the crate keeps node maps)
     std::vector<TimingRecord> timings;              // src/compute_graph/mod.rs:275
     DeviceRef dev;
     ~GraphInner();

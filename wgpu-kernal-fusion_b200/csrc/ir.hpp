@@ -26,10 +26,14 @@ struct Instr {
 
 // A companion output of a row kernel: Elem value `a` reduced with `op` over the WHOLE index
 // space (all rows, all columns) to one scalar, computed while the rows pass through registers.
+// With `all_reduce` the scalar is further combined (with `ar_op`) across the GPUs of a
+// communicator by the same kernel, over peer memory.
 struct Grand {
     uint16_t op;
     int a;
     DType dtype;
+    bool all_reduce = false;
+    uint16_t ar_op = 0;
 };
 
 struct Program {
@@ -133,15 +137,55 @@ struct Program {
 
     // Text form; immediates are kernel parameters, so their values are not part of it.
     std::string signature() const {
-        std::ostringstream s;
-        for (auto d : slot_dtype) s << "s" << (int)d;
-        s << "|";
-        for (auto& in : ins)
-            s << (int)in.kind << "." << in.op << "." << in.a << "." << in.b << "." << in.slot << "."
-              << (int)in.dtype << "." << (int)in.vk << ";";
-        s << "->" << result;
-        for (auto& g : grands) s << "|g" << g.op << "." << g.a << "." << (int)g.dtype;
-        return s.str();
+        std::string s;
+        s.reserve(16 + 24 * ins.size());
+        auto num = [&s](int v) {   // decimal, no stream machinery: this runs for every launch
+            char buf[12];
+            int n = 0;
+            unsigned u = v < 0 ? (unsigned)(-(long long)v) : (unsigned)v;
+            do {
+                buf[n++] = (char)('0' + u % 10);
+                u /= 10;
+            } while (u);
+            if (v < 0) s.push_back('-');
+            while (n) s.push_back(buf[--n]);
+        };
+        for (auto d : slot_dtype) {
+            s.push_back('s');
+            num((int)d);
+        }
+        s.push_back('|');
+        for (auto& in : ins) {
+            num((int)in.kind);
+            s.push_back('.');
+            num(in.op);
+            s.push_back('.');
+            num(in.a);
+            s.push_back('.');
+            num(in.b);
+            s.push_back('.');
+            num(in.slot);
+            s.push_back('.');
+            num((int)in.dtype);
+            s.push_back('.');
+            num((int)in.vk);
+            s.push_back(';');
+        }
+        s += "->";
+        num(result);
+        for (auto& g : grands) {
+            s += "|g";
+            num(g.op);
+            s.push_back('.');
+            num(g.a);
+            s.push_back('.');
+            num((int)g.dtype);
+            if (g.all_reduce) {
+                s.push_back('a');
+                num(g.ar_op);
+            }
+        }
+        return s;
     }
 };
 

@@ -17,9 +17,15 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
 // `out_has_h` says whether the result keeps the last axis (a Row-kind result is then written
 // to every column of its row).  A program with companion reductions (`prog.grands`) needs
 // `out_has_h` and a non-empty index space; their rank-0 results are returned in `grand_out`.
+// Companion reductions marked `all_reduce` exchange their values through the mailboxes of `gc`
+// (see Comm) with sequence number gc->seq.
+struct GrandComm {
+    const void* peer_table;   // device array of the ranks' mailbox addresses
+    uint32_t world, rank, seq;
+};
 TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
                     const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot,
-                    std::vector<TensorData>* grand_out = nullptr);
+                    std::vector<TensorData>* grand_out = nullptr, const GrandComm* gc = nullptr);
 
 // Longest row the register-resident row kernel accepts, for the given element width mix.
 int64_t max_resident_row(bool any_16bit);
