@@ -24,6 +24,7 @@ def test_all_reduce_inside_the_row_kernel(peer):
     if n < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"      # plain peer memory only: no multicast objects in a test
     env.pop("WGF_NO_PEER_ALLREDUCE", None)
     if not peer:
         env["WGF_NO_PEER_ALLREDUCE"] = "1"
