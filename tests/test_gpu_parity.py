@@ -412,3 +412,73 @@ def test_reduction_riding_along_f16_and_all_results_cached(wgf, dev, orc):
     d = orc.ulp_diff_f16(y.as_slice(), orc.Ref(x).softmax_last_dim().numpy())
     assert int(d.max()) <= 2
     assert dev.launch_count == before          # both were computed by the one request
+
+
+def bf16_bits(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def test_bf16_elementwise_reduce_and_cast(wgf, dev, orc):
+    """bf16 tensors (u16 bit patterns on both sides): + - * / exact, transcendental <= 1 ulp of bf16,
+    reductions and casts through the same kernels as f16."""
+    g = seeded(3, 5)
+    x, y = bf16_bits(g.standard_normal((37, 200)) * 3), bf16_bits(g.standard_normal((37, 200)) * 3 + 4)
+    tx, ty = dev.tensor(x, dtype=wgf.BF16), dev.tensor(y, dtype=wgf.BF16)
+    rx, ry = orc.Ref(x, bf16=True), orc.Ref(y, bf16=True)
+    for f in (lambda a, b: a + b, lambda a, b: a - b, lambda a, b: a * b, lambda a, b: a / b, lambda a, b: a * 1.5 + 0.25,
+              lambda a, b: (a + b) * (a - b) / (b + 3.0)):
+        np.testing.assert_array_equal(f(tx, ty).as_slice(), f(rx, ry).numpy())
+
+    def bf_ulps(got, ref):      # distance in bf16 steps: the patterns are sign-magnitude
+        a, b = got.astype(np.int32), ref.astype(np.int32)
+        a = np.where(a & 0x8000, -(a & 0x7FFF), a)
+        b = np.where(b & 0x8000, -(b & 0x7FFF), b)
+        return np.abs(a - b)
+    for name in ("exp", "tanh", "sqrt", "sin"):
+        arg = bf16_bits(np.abs(g.standard_normal(4099)) * 2) if name == "sqrt" else bf16_bits(g.standard_normal(4099) * 2)
+        got = getattr(dev.tensor(arg, dtype=wgf.BF16), name)().as_slice()
+        ref = getattr(orc.Ref(arg, bf16=True), name)().numpy()
+        assert int(bf_ulps(got, ref).max()) <= 1, name
+    got = tx.max(1).as_slice()
+    np.testing.assert_array_equal(got, rx.max(1).numpy())
+    s = (tx.cast(wgf.F32).sum(0)).as_slice()
+    assert_rel(s, rx.cast(orc.F32).sum(0).numpy(), 1e-5)
+    np.testing.assert_array_equal(tx.cast(wgf.F32).cast(wgf.BF16).as_slice(), x)      # round trip is the identity
+    f = g.standard_normal(10000).astype(np.float32)
+    np.testing.assert_array_equal(dev.tensor(f).cast(wgf.BF16).as_slice(), bf16_bits(f))  # round to nearest even
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 2, 2, 3, 4), (2, 1, 3, 2, 2, 1, 2, 5), (3, 2, 2, 2, 2, 2, 2, 2)])
+def test_rank_6_to_8(shape, dev, orc):
+    """Ranks up to 8 (the C ABI's limit; the crate instantiates ranks up to 6): element-wise on permuted views,
+    reductions over inner, middle and outer axes, broadcast along a middle axis."""
+    g = seeded(3, 6)
+    x = g.standard_normal(shape, dtype=np.float32)
+    y = g.standard_normal(shape, dtype=np.float32)
+    r = len(shape)
+    tx, ty, rx, ry = dev.tensor(x), dev.tensor(y), orc.Ref(x), orc.Ref(y)
+    got = (tx.transpose(0, r - 1).transpose(1, r - 2) * 2.0 + ty.transpose(0, r - 1).transpose(1, r - 2)).as_slice()
+    ref = (rx.transpose(0, r - 1).transpose(1, r - 2) * 2.0 + ry.transpose(0, r - 1).transpose(1, r - 2)).numpy()
+    np.testing.assert_array_equal(got, ref)
+    for axis in (0, r // 2, r - 1):
+        assert_rel(tx.sum(axis).as_slice(), rx.sum(axis).numpy(), 1e-5 * 10)      # sums of signed values: looser, relative to the result
+        np.testing.assert_array_equal(tx.max(axis).as_slice(), rx.max(axis).numpy())
+    mid = r // 2
+    red = tx.max(mid)
+    back = red.broadcast_axis(mid, shape[mid])
+    np.testing.assert_array_equal((tx - back).as_slice(), (rx - rx.max(mid).broadcast_axis(mid, shape[mid])).numpy())
+
+
+def test_joint_request_edge_cases(wgf, dev):
+    wgf.Tensor.materialize_all([])                                   # nothing to do
+    x = dev.tensor(np.arange(12, dtype=np.float32).reshape(3, 4))
+    s = x.sum(0).sum(0)
+    before = dev.launch_count
+    wgf.Tensor.materialize_all([s, s, x])                            # duplicates and an already materialised tensor
+    assert dev.launch_count - before == 1
+    assert float(s.as_slice()) == 66.0
+    e = dev.tensor(np.zeros((0, 8), np.float32))
+    y, t = e.softmax_last_dim(), e.sum(0).sum(0)
+    wgf.Tensor.materialize_all([y, t])                               # empty index space: the reduction is the identity
+    assert y.as_slice().shape == (0, 8) and float(t.as_slice()) == 0.0
