@@ -268,8 +268,10 @@ def run_gpu(args):
     barrier()
     clocks = sampler.stop() if sampler else None
     kernels_per_step = 1 if fused else 2
-    per_step = kernels_per_step + (1 if comm is not None else 0)
     recs = xs[0].all_timing_information()[n_timing_before:]
+    # one more record per step when the all-reduce is a launch of its own (NCCL) rather than part of
+    # the reduction kernel (peer memory)
+    per_step = max(kernels_per_step, len(recs) // max(args.steps, 1))
     row_ns = recs[0::per_step]
     row_ms = float(np.mean(row_ns)) / 1e6 if row_ns else float("nan")
     sum_ms = None
@@ -277,7 +279,7 @@ def run_gpu(args):
         sum_ns = recs[1::per_step]
         sum_ms = float(np.mean(sum_ns)) / 1e6 if sum_ns else float("nan")
     # what the all-reduce costs the device stream (the collective itself runs beside it)
-    ar_ms = float(np.mean(recs[kernels_per_step::per_step])) / 1e6 if comm is not None and len(recs) >= per_step else None
+    ar_ms = float(np.mean(recs[kernels_per_step::per_step])) / 1e6 if per_step > kernels_per_step else None
 
     # ---- end to end through the C ABI with host buffers ---------------------------------------
     # Every step uploads its own input from pinned host memory and downloads its results.  The
@@ -371,6 +373,8 @@ def run_gpu(args):
                     "steps": e2e_steps, "h2d_bytes_per_step": ROWS * H * 4, "d2h_bytes_per_step": ROWS * H * 4 + 4},
             "gpu_launches": launches,
             "host_queue_ms_per_step": host_ms,
+            "all_reduce": (None if comm is None else
+                           "inside the reduction kernel over peer memory" if per_step == kernels_per_step else "NCCL launch"),
             "all_reduce_on_device_stream_ms": ar_ms,
             "clocks": clocks,
         }))

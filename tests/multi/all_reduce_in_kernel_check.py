@@ -48,6 +48,16 @@ for step in range(40):
     eq = sum((a.astype(np.float64) ** 2).sum() for a in xs)
     gs, gm, gq = float(s.as_slice()), float(m.as_slice()), float(q.as_slice())
     rows = y.as_slice().sum(1)
+    # the same all-reduced sum requested on its own: a streaming reduction that does the exchange itself
+    before = dev.launch_count
+    alone = (x * 2.0).exp().sum(0).sum(0).all_reduce(comm)
+    alone.materialize()
+    alone_launches = dev.launch_count - before
+    ea = sum(np.exp(2.0 * a.astype(np.float64)).sum() for a in xs)
+    ga = float(alone.as_slice())
+    if abs(ga - ea) / ea > 1e-5 or alone_launches != (2 if os.environ.get("WGF_NO_PEER_ALLREDUCE") else 1):
+        print(f"rank {rank} step {step}: stand-alone all-reduce: {alone_launches} launches, got {ga}, expected {ea}", flush=True)
+        bad += 1
     ok = (abs(gs - es) / es < 1e-5 and gm == em and abs(gq - eq) / eq < 1e-5 and launches == expected_launches
           and np.abs(rows - 1).max() < 1e-5)
     if not ok:

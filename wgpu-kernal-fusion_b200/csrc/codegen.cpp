@@ -481,7 +481,7 @@ std::string row_source(const Program& prog, const RowConfig& c) {
                 << "], (int)threadIdx.x);\n  if (threadIdx.x == 0) {\n";
         if (gr.all_reduce)   // the value of this GPU is rounded to the element type, then combined across GPUs
             gfinish << "    a_ = peer_all_reduce<" << red_name(gr.ar_op) << ">(" << rounded(gr.dtype, "a_") << ", " << id
-                    << ", p);\n";
+                    << ", p.gpeers, p.gworld, p.grank, p.gseq, p.gerr);\n";
         gfinish << "    store1<" << (int)gr.dtype << ">((void*)p.gout[" << id << "], 0, a_); } }\n";
     }
     // A group_reduce reuses its shared-memory slot in the next iteration: all reads of this
@@ -590,8 +590,12 @@ std::string stream_source(const Program& prog, const StreamConfig& c) {
     s << "#define STREAM_COMBINE_PARTIAL(PP) " << comb.str() << "\n";
     s << "#define STREAM_BLOCK_REDUCE " << blk.str() << "\n";
     s << "#define STREAM_LOAD(COL, NV, X) " << load.str() << "\n";
-    s << "#define STREAM_POST " << post.str() << " if (t == 0) store1<" << (int)prog.out_dtype()
-      << ">((void*)p.ptr[NIN], roff[NIN], " << vn(prog.result) << ");\n";
+    s << "#define STREAM_AR " << (prog.result_all_reduce ? 1 : 0) << "\n";
+    s << "#define STREAM_POST " << post.str() << " if (t == 0) { float r_ = " << vn(prog.result) << "; ";
+    if (prog.result_all_reduce)   // the one result of the kernel is combined across the GPUs before it is stored
+        s << "r_ = peer_all_reduce<" << red_name(prog.result_ar_op) << ">(" << rounded(prog.out_dtype(), "r_")
+          << ", 0, p.gpeers, p.gworld, p.grank, p.gseq, p.gerr); ";
+    s << "store1<" << (int)prog.out_dtype() << ">((void*)p.ptr[NIN], roff[NIN], r_); }\n";
     s << JIT_STREAM_KERNEL;
     return s.str();
 }
@@ -858,6 +862,8 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
         WGF_CHECK(H <= max_resident_row(any16), WGF_ERR_UNSUPPORTED, "row too long for a row-fused kernel");
     }
 
+    WGF_CHECK(!prog.result_all_reduce || use_stream, WGF_ERR_UNSUPPORTED, "in-kernel all-reduce is part of the streaming reduction only");
+
     auto put_common = [&](ParamWriter& w) {
         w.put<uint64_t>((uint64_t)rows);
         for (int t = 0; t < nin; ++t) w.put<uint64_t>((uint64_t)(uintptr_t)in[t].base_ptr());
@@ -994,6 +1000,15 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
     w.put<uint64_t>((uint64_t)H);
     w.put<uint32_t>((uint32_t)split);
     w.put<uint32_t>(0);
+    if (prog.result_all_reduce) {
+        WGF_CHECK(gc && rows == 1, WGF_ERR_INVALID_ARGUMENT, "in-kernel all-reduce needs a communicator and a single result");
+        w.put<uint64_t>((uint64_t)(uintptr_t)gc->peer_table);
+        w.put<uint64_t>((uint64_t)(uintptr_t)dev.error_word());
+        w.put<uint32_t>(gc->world);
+        w.put<uint32_t>(gc->rank);
+        w.put<uint32_t>(gc->seq);
+        w.put<uint32_t>(0);
+    }
     put_tail(w);
     dev.launch(k, dim3((unsigned)(rows * split)), dim3(256), 0, w.bytes.data(), "stream_reduce");
     return out;

@@ -835,12 +835,23 @@ void gather_companion(Node* n, Region& rg) {
     }
 }
 
+// An all-reduce node asks the kernel that computes its (rank-0) input to do the exchange too.
+struct ArRequest {
+    Node* root;
+    Comm* comm;
+    uint16_t op;
+    bool done;
+};
+thread_local ArRequest* g_ar_request = nullptr;
+
 TensorData run_region(Node* root, bool allow_fold = true) {
     std::vector<Candidate> candidates;
     if (g_companions && root == g_companion_host) {
         candidates = *g_companions;
         g_companions = nullptr;   // leaves resolved below must not pick them up again
     }
+    ArRequest* arq = g_ar_request && g_ar_request->root == root ? g_ar_request : nullptr;
+    g_ar_request = nullptr;       // likewise
     Region rg;
     rg.root = root;
     plan_region(rg, allow_fold);
@@ -900,7 +911,20 @@ TensorData run_region(Node* root, bool allow_fold = true) {
     }
     if (!em.ok) {
         WGF_CHECK(rg.fold_top != nullptr, WGF_ERR_UNSUPPORTED, "internal: unmergeable index space");
+        g_ar_request = arq;
         return run_region(root, false);  // some input cannot be flattened: reduce axis by axis
+    }
+    // A streaming reduction to one scalar that feeds only an all-reduce does the exchange itself.
+    bool result_ar = false;
+    if (arq && rg.row_mode && !rg.out_has_h && root->rank() == 0 && !em.prog.multi_phase() && companions.empty()) {
+        int64_t elements = 1;
+        for (auto v : rg.E) elements *= v;
+        if (elements > 0) {
+            em.prog.result_all_reduce = true;
+            em.prog.result_ar_op = arq->op;
+            kernel_comm = arq->comm;
+            result_ar = true;
+        }
     }
 
     // index space
@@ -957,6 +981,7 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         }
         throw;
     }
+    if (result_ar) arq->done = true;
     for (size_t i = 0; i < companions.size(); ++i) {
         // the value belongs to the all-reduce node when the kernel did that too (the reduction
         // node below it is never materialised and goes away with the all-reduce's inputs)
@@ -1058,7 +1083,24 @@ TensorData resolve_node(Node* n) {
         }
         case NodeKind::AllReduce: {
             Node* src = n->inputs[0].get();
-            TensorData in = resolve_node(src);
+            // A scalar that only this all-reduce can see is exchanged by the kernel that computes
+            // it (over peer memory) where that kernel is a streaming reduction; see ArRequest.
+            ArRequest arq{src, n->comm.get(), n->op, false};
+            if (!src->cached && n->comm && n->comm->peer_ok && src->rank() == 0 && src->handles == 0 &&
+                src->consumers.size() == 1 && (src->kind == NodeKind::Reduce || is_ew(src)))
+                g_ar_request = &arq;
+            TensorData in;
+            try {
+                in = resolve_node(src);
+            } catch (...) {
+                g_ar_request = nullptr;
+                throw;
+            }
+            g_ar_request = nullptr;
+            if (arq.done) {
+                out = in;
+                break;
+            }
             const bool dense_in = in.layout.is_dense() && !in.layout.allocation_overlaps();
             // The collective runs in place.  If nothing else can read the partial result any
             // more, its own buffer is used (no copy); otherwise a dense copy is reduced.

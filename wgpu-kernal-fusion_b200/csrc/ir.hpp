@@ -42,6 +42,10 @@ struct Program {
     std::vector<float> imms;
     std::vector<Grand> grands;
     int result = -1;
+    // The single (rank-0) result of a streaming reduction is combined with `result_ar_op` across
+    // the GPUs of a communicator by the kernel itself.
+    bool result_all_reduce = false;
+    uint16_t result_ar_op = 0;
 
     int n_slots() const { return (int)slot_dtype.size(); }
     DType out_dtype() const { return ins[result].dtype; }
@@ -173,6 +177,10 @@ struct Program {
         }
         s += "->";
         num(result);
+        if (result_all_reduce) {
+            s.push_back('A');
+            num(result_ar_op);
+        }
         for (auto& g : grands) {
             s += "|g";
             num(g.op);

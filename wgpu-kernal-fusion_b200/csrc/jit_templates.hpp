@@ -181,6 +181,50 @@ template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t)
     }
     return v;
 }
+
+// All-reduce of one scalar across the GPUs of a communicator from inside the kernel (one
+// thread).  Mailboxes hold 64-bit words {sequence << 32 | value bits} at
+// [parity][source rank][value index]; a single 64-bit store / load is atomic, so a word with
+// the expected sequence number carries the value that belongs to it.  The value goes to every
+// peer by a store over NVLink, the peers' values are read from this GPU's own mailbox and
+// combined in rank order.  The wait is bounded (2 s): it then sets the error word.
+template <int OP> DEV float peer_all_reduce(float mine, int index, u64 peers, u32 world, u32 rank, u32 seq, u64 err) {
+    const u64* table = (const u64*)peers;
+    const u32 parity = seq & 1u;
+    const u64 word = ((u64)seq << 32) | (u64)__float_as_uint(mine);
+    for (u32 r = 0; r < world; ++r) {
+        if (r == rank) continue;
+        u64* slot = (u64*)table[r] + ((u64)(parity * world + rank) * 4 + index);
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(word) : "memory");
+    }
+    const u64* own = (const u64*)table[rank];
+    float acc = mine;
+    for (u32 r = 0; r < world; ++r) {
+        float v = mine;
+        if (r != rank) {
+            const u64* slot = own + ((u64)(parity * world + r) * 4 + index);
+            u64 w = 0, start = 0;
+            bool got = false;
+            for (u32 spin = 0; spin < (1u << 26) && !got; ++spin) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
+                got = (u32)(w >> 32) == seq;
+                if (!got && (spin & 255u) == 255u) {
+                    u64 now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (start == 0) start = now;
+                    else if (now - start > 2000000000ull) break;
+                }
+            }
+            if (!got) {
+                atomicExch((u32*)err, 51u);
+                return mine;
+            }
+            v = __uint_as_float((u32)w);
+        }
+        acc = r == 0 ? v : red_comb<OP>(acc, v);
+    }
+    return acc;
+}
 )CUDA";
 
 // ---------------------------------------------------------------------------------------
@@ -296,52 +340,6 @@ struct Params {
     float imm[NIMM > 0 ? NIMM : 1];
 };
 
-#if NGRAND > 0
-// All-reduce of one scalar across the GPUs of a communicator from inside the kernel (one
-// thread).  Mailboxes hold 64-bit words {sequence << 32 | value bits} at
-// [parity][source rank][value index]; a single 64-bit store / load is atomic, so a word with
-// the expected sequence number carries the value that belongs to it.  The value goes to every
-// peer by a store over NVLink, the peers' values are read from this GPU's own mailbox and
-// combined in rank order.  The wait is bounded (2 s): it then sets the error word.
-template <int OP> DEV float peer_all_reduce(float mine, int index, const Params& p) {
-    const u64* table = (const u64*)p.gpeers;
-    const u32 world = p.gworld, rank = p.grank, seq = p.gseq, parity = seq & 1u;
-    const u64 word = ((u64)seq << 32) | (u64)__float_as_uint(mine);
-    for (u32 r = 0; r < world; ++r) {
-        if (r == rank) continue;
-        u64* slot = (u64*)table[r] + ((u64)(parity * world + rank) * 4 + index);
-        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(word) : "memory");
-    }
-    const u64* own = (const u64*)table[rank];
-    float acc = mine;
-    for (u32 r = 0; r < world; ++r) {
-        float v = mine;
-        if (r != rank) {
-            const u64* slot = own + ((u64)(parity * world + r) * 4 + index);
-            u64 w = 0, start = 0;
-            bool got = false;
-            for (u32 spin = 0; spin < (1u << 26) && !got; ++spin) {
-                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
-                got = (u32)(w >> 32) == seq;
-                if (!got && (spin & 255u) == 255u) {
-                    u64 now;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                    if (start == 0) start = now;
-                    else if (now - start > 2000000000ull) break;
-                }
-            }
-            if (!got) {
-                atomicExch((u32*)p.gerr, 51u);
-                return mine;
-            }
-            v = __uint_as_float((u32)w);
-        }
-        acc = r == 0 ? v : red_comb<OP>(acc, v);
-    }
-    return acc;
-}
-#endif
-
 DEV void row_offsets(const Params& p, u64 row, bool rv, i64* roff) {
 #pragma unroll
     for (int s = 0; s <= NIN; ++s) roff[s] = 0;
@@ -437,6 +435,11 @@ struct Params {
     u64 H;
     u32 split;
     u32 pad_;
+#if STREAM_AR
+    u64 gpeers;         // all-reduce of the result inside this kernel: the ranks' mailbox addresses
+    u64 gerr;           // u32 device error word
+    u32 gworld, grank, gseq, gpad_;
+#endif
     u32 oshape[RO];
     u32 mm[RO];
     u32 ms[RO];
