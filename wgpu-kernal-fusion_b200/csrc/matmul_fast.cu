@@ -2,7 +2,8 @@
 // everything, src/matmul.rs:56-155):
 //   * sgemm_kernel       f32, 128x128x16 tiles, 8x8 register tile per thread, FFMA pipe;
 //   * gemv_kn_kernel     skinny M (decode GEMV) with B stored [K,N]: streams B once at HBM speed,
-//                        16-byte loads along N, split over K, fp32 partials + a small finish kernel;
+//                        16-byte loads along N, split over K, fp32 partials combined by the last CTA
+//                        of each column block (ticket);
 //   * gemv_nk_kernel     skinny M with B stored [N,K] (a transposed view): one warp per output column;
 //   * f16 / bf16 large:  tcgen05 kernel in matmul_tc.cu.
 // All accumulate in fp32 and round once.
@@ -163,13 +164,16 @@ template <typename T> __device__ __forceinline__ void unpack16(const uint4& raw,
 constexpr int GV_MAXM = 8;
 
 // B is [K,N] row-major.  Each lane owns VEC consecutive columns; the 8 warps of a CTA take
-// interleaved k rows of the CTA's k range; partial[ksplit][M][N] in fp32.
+// interleaved k rows of the CTA's k range; partial[ksplit][M][N] in fp32.  With `counters`
+// (one zeroed word per column block) the last CTA to arrive for a column block adds the
+// k-split partials in split order and stores C, so no finishing launch is needed.
 template <typename T, int MM>
 __global__ void __launch_bounds__(256)
-gemv_kn_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restrict__ partial,
-               const __grid_constant__ MatmulDims d, int k_per_cta) {
+gemv_kn_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restrict__ partial, T* __restrict__ C,
+               unsigned* __restrict__ counters, const __grid_constant__ MatmulDims d, int k_per_cta) {
     constexpr int VEC = Vec16<T>::N;
     __shared__ float red[8][32 * VEC + 1];
+    __shared__ unsigned is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long n = ((long long)blockIdx.x * 32 + lane) * VEC;
     const long long kbeg = (long long)blockIdx.y * k_per_cta;
@@ -180,11 +184,12 @@ gemv_kn_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restri
 #pragma unroll
         for (int j = 0; j < VEC; ++j) acc[m][j] = 0.f;
     if (n < d.N) {
-        for (long long k = kbeg + warp; k < kend; k += 8 * 4) {
-            uint4 raw[4];
-            float av[4][MM];
+        constexpr int UN = MM <= 2 ? 8 : 4;     // k rows in flight per lane (16-byte loads)
+        for (long long k = kbeg + warp; k < kend; k += 8 * UN) {
+            uint4 raw[UN];
+            float av[UN][MM];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < UN; ++u) {
                 const long long kk = k + u * 8;
                 if (kk < kend) {
                     raw[u] = *reinterpret_cast<const uint4*>(B + kk * d.b_rs + n);
@@ -197,7 +202,7 @@ gemv_kn_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restri
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < UN; ++u) {
                 float bv[VEC];
                 unpack16<T>(raw[u], bv);
 #pragma unroll
@@ -222,6 +227,28 @@ gemv_kn_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restri
         }
         __syncthreads();
     }
+    if (counters == nullptr) return;
+    // ticket: the last CTA of this column block combines the splits
+    __threadfence();            // every thread's partial sums are visible device-wide ...
+    __syncthreads();            // ... before thread 0 takes the ticket
+    if (threadIdx.x == 0) {
+        const unsigned ticket = atomicAdd(counters + blockIdx.x, 1u);
+        is_last = ticket == gridDim.y - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int c = threadIdx.x; c < 32 * VEC; c += 256) {
+        const long long col = (long long)blockIdx.x * 32 * VEC + c;
+        if (col >= d.N) continue;
+#pragma unroll
+        for (int m = 0; m < MM; ++m) {
+            float s = 0.f;
+            for (unsigned k = 0; k < gridDim.y; ++k) s += __ldcg(partial + ((long long)k * MM + m) * d.N + col);
+            C[(long long)m * d.c_rs + col] = st_from<T>(s);
+        }
+    }
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 
 template <typename T>
@@ -305,14 +332,16 @@ bool run_gemv(Device& dev, const void* a, const void* b, void* c, const MatmulDi
         const int k_per_cta = (int)((d.K + splits - 1) / splits);
         splits = (d.K + k_per_cta - 1) / k_per_cta;
         BufferRef scratch = dev.alloc((size_t)(splits * d.M * d.N) * sizeof(float), false);
+        const bool ticketed = nblocks <= Device::kCounters && !getenv("WGF_GEMV_FINISH_KERNEL");
         pick([&](auto mm) {
             constexpr int MM = decltype(mm)::value;
             dev.begin_launch("gemv_kn");
             if (!dev.dry)
                 gemv_kn_kernel<T, MM><<<dim3((unsigned)nblocks, (unsigned)splits), 256, 0, dev.stream>>>(
-                    (const T*)a, (const T*)b, (float*)scratch->ptr, d, k_per_cta);
+                    (const T*)a, (const T*)b, (float*)scratch->ptr, (T*)c, ticketed ? (unsigned*)dev.counters() : (unsigned*)nullptr, d, k_per_cta);
             dev.end_launch();
         });
+        if (ticketed) return true;
         dev.begin_launch("gemv_finish");
         if (!dev.dry)
             gemv_finish_kernel<T><<<(unsigned)((d.M * d.N + 255) / 256), 256, 0, dev.stream>>>(
