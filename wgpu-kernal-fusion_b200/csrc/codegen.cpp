@@ -603,6 +603,7 @@ std::string stream_source(const Program& prog, const StreamConfig& c) {
 // ---- column reduce: reduced axis is not the innermost one --------------------------------
 struct ColConfig {
     int C, U, out_mode;
+    int TX = 32;                // threads along the contiguous axis per CTA (256 / TX thread rows share K)
     std::vector<int> mode;      // per slot: 0 vector, 1 scalar, 2 one value for all columns
     std::vector<char> is_row;   // per slot: does not vary along the reduced axis
 };
@@ -669,7 +670,8 @@ std::string col_source(const Program& prog, const ColConfig& c) {
     std::ostringstream s;
     s << prelude();
     s << "#define NIN " << prog.n_slots() << "\n#define NINE " << nine << "\n#define NROWL " << nrowl << "\n#define NPRE "
-      << npre << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM "
+      << npre << "\n#define C " << c.C << "\n#define U " << c.U << "\n#define TX " << c.TX << "\n#define TY " << 256 / c.TX
+      << "\n#define NRED " << prog.n_reduces() << "\n#define NIMM "
       << prog.imms.size() << "\n#define OUT_DT " << (int)prog.out_dtype() << "\n#define OUT_MODE " << c.out_mode << "\n";
     s << "DEV void pre_phase(const float* rl, const float* imm, float* rv) {\n" << pre.str() << "}\n";
     s << "DEV void elem_phase(const float* xe, const float* rv, const float* imm, float* a) {\n" << elem.str() << "}\n";
@@ -814,15 +816,18 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             }
             int nine = 0;
             for (int t = 0; t < nin; ++t) nine += !slot_row[t];
-            cfg.U = std::max(1, std::min(4, 32 / (std::max(nine, 1) * cfg.C)));
+            cfg.U = std::max(1, std::min(tune("COL_U", 4), tune("COL_BUDGET", 32) / (std::max(nine, 1) * cfg.C)));
+            // measured on f32 [8192,4096].sum(0): 64 threads along the row and 4 thread rows
+            // 32.2 us; 32 x 8: 38.0; 128 x 2: 37.0; 256 x 1: 44.1
+            cfg.TX = tune("COL_TX", I >= 64ll * cfg.C ? 64 : 32);
             std::ostringstream key;
-            key << "col|" << cfg.C << "|" << cfg.U << "|" << cfg.out_mode << "|";
+            key << "col|" << cfg.C << "|" << cfg.U << "|" << cfg.TX << "|" << cfg.out_mode << "|";
             for (int m : cfg.mode) key << m;
             key << "|";
             for (int v : cfg.is_row) key << v;
             key << "|" << prog.signature();
             const JitKernel& k = dev.kernel(key.str(), "wgf_col_reduce", [&] { return col_source(prog, cfg); });
-            const int64_t tiles = (I + 32ll * cfg.C - 1) / (32ll * cfg.C);
+            const int64_t tiles = (I + (int64_t)cfg.TX * cfg.C - 1) / ((int64_t)cfg.TX * cfg.C);
             int64_t split = std::max<int64_t>(1, ((int64_t)dev.sm_count * 4 + tiles * O - 1) / (tiles * O));
             split = std::min<int64_t>(split, std::max<int64_t>(1, H / 64));
             if (tiles * O > Device::kCounters || tiles > 65535 * 32768ll) split = 1;
@@ -848,7 +853,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             for (float f : prog.imms) w.put<float>(f);
             if (prog.imms.empty()) w.put<float>(0.f);
             w.finish();
-            dev.launch(k, dim3((unsigned)tiles, (unsigned)split, (unsigned)O), dim3(32, 8), 0, w.bytes.data(), "col_reduce");
+            dev.launch(k, dim3((unsigned)tiles, (unsigned)split, (unsigned)O), dim3(cfg.TX, 256 / cfg.TX), 0, w.bytes.data(), "col_reduce");
             return out;
         }
     }

@@ -539,7 +539,9 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(co
 // in registers; partials of split CTAs go to scratch, the last CTA per column tile (ticket)
 // combines them in index order.  A reduction over axis 0 of a row-major matrix therefore
 // reads whole rows, where the crate walks one column per workgroup (src/reduce.rs:349-373).
-// Defines expected: NIN NINE NROWL NPRE C U NRED NIMM; macro COL_LOAD_ELEM(K, X),
+// TX threads run along I per CTA (a CTA reads TX * 16 contiguous bytes of every row it
+// visits) and TY = 256 / TX thread rows share K.
+// Defines expected: NIN NINE NROWL NPRE C U TX TY NRED NIMM; macro COL_LOAD_ELEM(K, X),
 // COL_LOAD_ROW(X); functions pre_phase, elem_phase, post_phase; per-reduction macros
 // COL_INIT(j) COL_COMB(j, PP, STRIDE) COL_SMEM_ADD(j, w).
 // ---------------------------------------------------------------------------------------
@@ -557,12 +559,12 @@ struct Params {
 };
 
 extern "C" __global__ void __launch_bounds__(256, 2) wgf_col_reduce(const __grid_constant__ Params p) {
-    __shared__ float red[NRED][8][32 * C + 1];
+    __shared__ float red[NRED][TY][TX * C + 1];
     __shared__ u32 is_last;
     const int tx = threadIdx.x, ty = threadIdx.y;
     const u64 o = blockIdx.z;
     const u32 sp = blockIdx.y;
-    const u64 col = ((u64)blockIdx.x * 32 + tx) * C;
+    const u64 col = ((u64)blockIdx.x * TX + tx) * C;
     const bool cv = col < p.I;
     const float* imm = p.imm;
     // values that do not depend on k: per-column operands and arithmetic on them
@@ -586,12 +588,12 @@ extern "C" __global__ void __launch_bounds__(256, 2) wgf_col_reduce(const __grid
     const u64 kbeg = (u64)sp * p.kper;
     const u64 kend = kbeg + p.kper < p.K ? kbeg + p.kper : p.K;
     if (cv) {
-        for (u64 k0 = kbeg + ty; k0 < kend; k0 += 8 * U) {
+        for (u64 k0 = kbeg + ty; k0 < kend; k0 += TY * U) {
             float x[U][NINE > 0 ? NINE : 1][C];
             bool kv[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const u64 k = k0 + (u64)u * 8;
+                const u64 k = k0 + (u64)u * TY;
                 kv[u] = k < kend;
                 if (kv[u]) { COL_LOAD_ELEM(k, x[u]) }
             }
@@ -625,7 +627,7 @@ extern "C" __global__ void __launch_bounds__(256, 2) wgf_col_reduce(const __grid
         for (int j = 0; j < C; ++j) {
             COL_INIT(j)
 #pragma unroll
-            for (int w = 0; w < 8; ++w) { COL_SMEM_ADD(j, w) }
+            for (int w = 0; w < TY; ++w) { COL_SMEM_ADD(j, w) }
         }
     }
     const u64 tiles = gridDim.x;
