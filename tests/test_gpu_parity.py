@@ -482,3 +482,36 @@ def test_joint_request_edge_cases(wgf, dev):
     y, t = e.softmax_last_dim(), e.sum(0).sum(0)
     wgf.Tensor.materialize_all([y, t])                               # empty index space: the reduction is the identity
     assert y.as_slice().shape == (0, 8) and float(t.as_slice()) == 0.0
+
+
+@pytest.mark.parametrize("case", ["2d", "3d_12", "3d_02", "ragged", "f16", "two_staged_and_broadcast"])
+def test_transposed_operands_staged_through_shared_memory(case, wgf, dev, orc):
+    """Operands that are contiguous along another axis than the output, large enough for the tiled
+    kernel (>= 65536 elements): one launch, bit-exact (only + - * here), ragged tile edges included."""
+    g = seeded(3, 7)
+    if case == "2d":
+        x, y = g.standard_normal((300, 700), dtype=np.float32), g.standard_normal((700, 300), dtype=np.float32)
+        build = lambda X, Y: X.transpose(0, 1) * 2.0 + Y
+    elif case == "3d_12":
+        x, y = g.standard_normal((64, 130, 257), dtype=np.float32), g.standard_normal((64, 257, 130), dtype=np.float32)
+        build = lambda X, Y: (X.transpose(1, 2) - Y) * X.transpose(1, 2)
+    elif case == "3d_02":
+        x, y = g.standard_normal((96, 20, 72), dtype=np.float32), g.standard_normal((72, 20, 96), dtype=np.float32)
+        build = lambda X, Y: X.transpose(0, 2) + Y * 0.5
+    elif case == "ragged":
+        x, y = g.standard_normal((1001, 77), dtype=np.float32), g.standard_normal((77, 1001), dtype=np.float32)
+        build = lambda X, Y: X.transpose(0, 1) * Y
+    elif case == "f16":
+        x = g.standard_normal((256, 300, 40), dtype=np.float32).astype(np.float16)
+        y = g.standard_normal((40, 300, 256), dtype=np.float32).astype(np.float16)
+        build = lambda X, Y: X.transpose(0, 2) * 2.0 + Y
+    else:
+        x, y = g.standard_normal((32, 256, 512), dtype=np.float32), g.standard_normal((256, 512), dtype=np.float32)
+        # a and the broadcast b are both read through their transposes; c stays a broadcast along the new inner axis
+        build = lambda X, Y: X.transpose(1, 2) * 1.5 + Y.broadcast((32, 256, 512)).transpose(1, 2)
+    tx, ty = dev.tensor(x), dev.tensor(y)
+    before = dev.launch_count
+    got = build(tx, ty).as_slice()
+    assert dev.launch_count - before == 1
+    ref = build(orc.Ref(x), orc.Ref(y)).numpy()
+    np.testing.assert_array_equal(got, ref)

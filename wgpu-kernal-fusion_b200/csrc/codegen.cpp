@@ -220,18 +220,35 @@ std::string debug_ew_source(const Program& prog, int rank, int chunk) {
     return ew_source(prog, c);
 }
 
+// With `try_tiled` only the shared-memory-staged variant is attempted: an empty result means
+// that it does not apply.
 static TensorData run_elementwise_impl(Device& dev, const Program& prog, const std::vector<TensorData>& in,
-                                       const std::vector<int64_t>& shape, int inplace_slot);
+                                       const std::vector<int64_t>& shape, int inplace_slot, bool try_tiled = false);
 
 // Operands whose innermost axis is strided (a transposed view) would be read with adjacent
-// threads far apart.  When such an operand is contiguous along another axis it is first
-// brought into the kernel's index order by the tiled-transpose copy (both passes coalesced);
-// the private copy may then serve as the output buffer.
+// threads far apart.  When such operands are contiguous along another axis, the kernel stages
+// their tiles through shared memory (JIT_EW_TILE_KERNEL); where that variant does not apply
+// (operands contiguous along different axes, too many of them) each is first brought into the
+// kernel's index order by the tiled-transpose copy, and the private copy may then serve as
+// the output buffer.
 TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<TensorData>& in,
                            const std::vector<int64_t>& shape, int inplace_slot) {
     int64_t n = 1;
     for (auto v : shape) n *= v;
     if (n < 65536 || shape.empty() || !tune("EW_PRETRANSPOSE", 1)) return run_elementwise_impl(dev, prog, in, shape, inplace_slot);
+    if (tune("EW_TILED", 1)) {
+        bool transposed = false;
+        for (size_t t = 0; t < in.size(); ++t) {
+            const Layout& l = in[t].layout;
+            const int r = l.rank();
+            if (r < 2 || l.shape != shape || l.shape[r - 1] <= 1 || l.strides[r - 1] == 0 || l.strides[r - 1] == 1) continue;
+            for (int d = 0; d < r - 1; ++d) transposed |= l.strides[d] == 1 && l.shape[d] >= 8;
+        }
+        if (transposed) {
+            TensorData out = run_elementwise_impl(dev, prog, in, shape, inplace_slot, true);
+            if (out.buf) return out;
+        }
+    }
     std::vector<TensorData> ins;
     for (size_t t = 0; t < in.size(); ++t) {
         const Layout& l = in[t].layout;
@@ -260,7 +277,7 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
 }
 
 static TensorData run_elementwise_impl(Device& dev, const Program& prog, const std::vector<TensorData>& in,
-                                       const std::vector<int64_t>& shape, int inplace_slot) {
+                                       const std::vector<int64_t>& shape, int inplace_slot, bool try_tiled) {
     const int nin = prog.n_slots();
     WGF_CHECK((int)in.size() == nin, WGF_ERR_INVALID_ARGUMENT, "input count does not match the program");
     WGF_CHECK(nin >= 1 && nin <= 16, WGF_ERR_UNSUPPORTED, "fused kernel takes 1..16 inputs");
@@ -313,6 +330,80 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
     cfg.mode.resize(nin);
     for (int t = 0; t < nin; ++t) cfg.mode[t] = classify(in[t], st[t]);
     cfg.out_mode = classify(out, st[nin]);
+
+    if (try_tiled) {
+        // Operands that are contiguous along another axis than the output (transposed views) are
+        // staged through shared memory tile by tile; see JIT_EW_TILE_KERNEL.  All of them must
+        // share that axis; shared memory holds two staged tiles of 4-element chunks or one of 8.
+        int pax = -1, nstaged = 0;
+        bool ok = R >= 2;
+        std::vector<int> sidx(nin, -1);
+        for (int t = 0; t < nin && ok; ++t) {
+            if (cfg.mode[t] != 3) continue;
+            int dc = -1;
+            for (int d = 0; d < R - 1; ++d)
+                if (st[t][d] == 1 && cshape[d] >= 8) dc = d;
+            if (dc < 0) continue;   // stays a strided operand
+            if (pax >= 0 && pax != dc) ok = false;
+            pax = dc;
+            sidx[t] = nstaged++;
+        }
+        ok = ok && nstaged >= 1 && nstaged <= (cfg.C >= 8 ? 1 : 2);
+        int64_t tiles = 0;
+        if (ok) {
+            const int64_t tiles_p = (cshape[pax] + 31) / 32, tiles_l = (cshape[R - 1] + 32ll * cfg.C - 1) / (32ll * cfg.C);
+            tiles = tiles_p * tiles_l;
+            for (int d = 0; d < R - 1; ++d) {
+                ok = ok && cshape[d] < (1ll << 31);
+                if (d != pax) tiles *= cshape[d];
+            }
+            ok = ok && cshape[R - 1] < (1ll << 31) && tiles < (1ll << 31);
+        }
+        if (!ok) return TensorData();   // the caller falls back to a transposing copy
+        std::ostringstream key;
+        key << "ewt|" << R << "|" << cfg.C << "|" << pax << "|" << cfg.out_mode << "|";
+        for (int t = 0; t < nin; ++t) key << (sidx[t] >= 0 ? 4 : cfg.mode[t]);
+        key << "|" << prog.signature();
+        const JitKernel& k = dev.kernel(key.str(), "wgf_elementwise_tiled", [&] {
+            std::ostringstream s;
+            s << prelude();
+            s << "#define R " << R << "\n#define NIN " << nin << "\n#define C " << cfg.C << "\n#define NIMM " << prog.imms.size()
+              << "\n#define OUT_DT " << (int)out_dt << "\n#define OUT_MODE " << cfg.out_mode << "\n#define PAX " << pax
+              << "\n#define NSTAGED " << nstaged << "\n";
+            s << ew_prog_text(prog);
+            s << "#define TILE_STAGE \\\n";
+            for (int t = 0; t < nin; ++t)
+                if (sidx[t] >= 0)
+                    s << "    for (int i = warp; i < TL; i += 8) { const u32 ll = l0 + i; if (pp < P && ll < L) stage[" << sidx[t]
+                      << "][lane][i] = load1<" << (int)prog.slot_dtype[t] << ">((const void*)p.ptr[" << t << "], base[" << t
+                      << "] + (i64)pp * p.stride[" << t << " * R + PAX] + (i64)ll * p.stride[" << t << " * R + R - 1]); } \\\n";
+            s << "\n#define TILE_INPUTS(X) \\\n";
+            for (int t = 0; t < nin; ++t) {
+                if (sidx[t] >= 0)
+                    s << "    for (int j = 0; j < C; ++j) X[" << t << "][j] = stage[" << sidx[t] << "][pi][tx * C + j]; \\\n";
+                else
+                    s << "    load_chunk<" << (int)prog.slot_dtype[t] << ", C, " << cfg.mode[t] << ">((const void*)p.ptr[" << t
+                      << "], base[" << t << "] + (i64)pp * p.stride[" << t << " * R + PAX] + (i64)l * p.stride[" << t
+                      << " * R + R - 1], p.stride[" << t << " * R + R - 1], nvalid, X[" << t << "]); \\\n";
+            }
+            s << "\n";
+            s << JIT_EW_TILE_KERNEL;
+            return s.str();
+        });
+        ParamWriter w;
+        for (int t = 0; t < nin; ++t) w.put<uint64_t>((uint64_t)(uintptr_t)in[t].base_ptr());
+        w.put<uint64_t>((uint64_t)(uintptr_t)out.base_ptr());
+        for (int t = 0; t <= nin; ++t)
+            for (int d = 0; d < R; ++d) w.put<int64_t>(st[t][d]);
+        for (int d = 0; d < R; ++d) w.put<uint32_t>((uint32_t)cshape[d]);
+        w.put<uint32_t>((uint32_t)((cshape[pax] + 31) / 32));
+        w.put<uint32_t>((uint32_t)((cshape[R - 1] + 32ll * cfg.C - 1) / (32ll * cfg.C)));
+        for (float f : prog.imms) w.put<float>(f);
+        if (prog.imms.empty()) w.put<float>(0.f);
+        w.finish();
+        dev.launch(k, dim3((unsigned)tiles), dim3(256), 0, w.bytes.data(), "elementwise_tiled");
+        return out;
+    }
     const int64_t nchunks = (n + cfg.C - 1) / cfg.C;
     // U chunks per thread are loaded before the first is used, at most EW_BUDGET input values
     // held as floats.  Measured on B200: 16 beats 32 and 64 on every chain with two or more

@@ -308,6 +308,74 @@ extern "C" __global__ void __launch_bounds__(256, MINB) wgf_elementwise(const __
 )CUDA";
 
 // ---------------------------------------------------------------------------------------
+// Element-wise template for operands that are contiguous along ANOTHER axis than the output
+// (transposed views).  A CTA works on a tile of TP x TL elements of the plane (PAX, last
+// axis): it first brings the tile of every such operand into shared memory with the threads
+// running along PAX, where that operand is contiguous (coalesced 128-byte reads), then
+// computes with the threads running along the last axis, where the output and the other
+// operands are contiguous, taking the staged operands from shared memory.  Nothing is read
+// with adjacent threads a row apart (the crate's strided kernel, src/visit_tiled.rs:100-144)
+// and no transposed copy goes through HBM first.
+// Defines expected: R NIN C NIMM OUT_DT OUT_MODE PAX NSTAGED; macros TILE_STAGE (loads of the
+// staged operands) and TILE_INPUTS(X) (fills X[NIN][C] for one chunk); function prog.
+// ---------------------------------------------------------------------------------------
+static const char* const JIT_EW_TILE_KERNEL = R"CUDA(
+#define TP 32
+#define TL (32 * C)
+struct Params {
+    u64 ptr[NIN + 1];
+    i64 stride[(NIN + 1) * R];
+    u32 shape[R];
+    u32 tiles_p, tiles_l;
+    float imm[NIMM > 0 ? NIMM : 1];
+};
+
+extern "C" __global__ void __launch_bounds__(256) wgf_elementwise_tiled(const __grid_constant__ Params p) {
+    __shared__ __align__(16) float stage[NSTAGED][TP][TL + 4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    u32 id = blockIdx.x;
+    const u32 tl = id % p.tiles_l;
+    id /= p.tiles_l;
+    const u32 tp = id % p.tiles_p;
+    id /= p.tiles_p;
+    i64 base[NIN + 1];
+#pragma unroll
+    for (int s = 0; s <= NIN; ++s) base[s] = 0;
+#pragma unroll
+    for (int d = R - 2; d >= 0; --d) {
+        if (d == PAX) continue;
+        const u32 c = id % p.shape[d];
+        id /= p.shape[d];
+#pragma unroll
+        for (int s = 0; s <= NIN; ++s) base[s] += (i64)c * p.stride[s * R + d];
+    }
+    const u32 P = p.shape[PAX], L = p.shape[R - 1];
+    const u32 p0 = tp * TP, l0 = tl * TL;
+    // stage: lane runs along PAX, a warp takes every 8th index of the last axis
+    {
+        const u32 pp = p0 + lane;
+        TILE_STAGE
+    }
+    __syncthreads();
+    const int tx = lane, ty = warp;             // 32 chunks along the last axis, 8 rows of PAX per pass
+    const u32 l = l0 + tx * C;
+#pragma unroll 1
+    for (int pass = 0; pass < TP / 8; ++pass) {
+        const int pi = ty + pass * 8;
+        const u32 pp = p0 + pi;
+        if (pp >= P || l >= L) continue;
+        const int nvalid = L - l < (u32)C ? (int)(L - l) : C;
+        float x[NIN][C];
+        TILE_INPUTS(x)
+        float y[C];
+#pragma unroll
+        for (int j = 0; j < C; ++j) y[j] = prog(x, j, p.imm);
+        store_chunk<OUT_DT, C, OUT_MODE>((void*)p.ptr[NIN], base[NIN] + (i64)pp * p.stride[NIN * R + PAX] + (i64)l, nvalid, y);
+    }
+}
+)CUDA";
+
+// ---------------------------------------------------------------------------------------
 // Row template: index space [outer..., H]; GROUP threads share a row, RPC rows per CTA;
 // each thread keeps EPT = NCH*C elements of the row in registers across all reductions.
 // CTAs are persistent: each walks rows blockIdx.x*RPC + g, + gridDim.x*RPC, ... and loads
