@@ -252,22 +252,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int qt = p.n_q_tiles - 1 - (int)(w / p.bh), b = (int)(w % p.bh);
             const int n_kv = p.causal ? qt + 1 : p.n_k_tiles;
             // ---- pass 1: row maximum of the raw scores
-            float m = -INFINITY;
+            // (four independent chains: one warp per scheduler has nothing else to hide the latency
+            // of a 128-long dependent chain)
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             for (int j = 0; j < n_kv && ok; ++j) {
                 if (!(ok = wait_all(S_FULL + sb, s_phase[sb], 31u))) break;
                 s_phase[sb] ^= 1;
                 tc_fence_after();
                 const bool diag = p.causal && j == qt;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    unsigned v[32];
+                for (int c = 0; c < 4; c += 2) {
+                    unsigned v[64];
                     tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)c * 32u, v);
+                    tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)(c + 1) * 32u, v + 32);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < 64; ++i) {
                         float s = __uint_as_float(v[i]);
                         if (diag && c * 32 + i > r) s = -INFINITY;
-                        m = fmaxf(m, s);
+                        m4[i & 3] = fmaxf(m4[i & 3], s);
                     }
                 }
                 tc_fence_before();
@@ -277,8 +280,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             if (!ok) break;
             // ---- pass 2: P = exp2((S - m) * scale * log2 e) -> shared memory, row sums
+            const float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             const float mc = m * p.scale_log2e;
-            float l = 0.f;
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < n_kv && ok; ++j) {
                 if (!(ok = wait_all(S_FULL + sb, s_phase[sb], 32u))) break;
                 s_phase[sb] ^= 1;
@@ -286,18 +290,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 pe_phase ^= 1;
                 tc_fence_after();
                 const bool diag = p.causal && j == qt;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    unsigned v[32];
-                    tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)c * 32u, v);
-                    tmem_ld_wait();
+                // 32 score columns at a time; the TMEM load of the next 32 is in flight while the
+                // exponentials of the current ones are computed
+                auto process = [&](const unsigned* v, int c) {
                     float e[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         float s = __uint_as_float(v[i]);
                         if (diag && c * 32 + i > r) s = -INFINITY;
                         e[i] = ex2_approx(fmaf(s, p.scale_log2e, -mc));
-                        l += e[i];
+                        l4[i & 3] += e[i];
                     }
                     // A-operand layout (K-major, 128-byte swizzle): row r of panel c/2 is 128 bytes
                     // at r * 128; its 16-byte chunk q sits at position q ^ (r % 8)
@@ -312,7 +314,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
                         *reinterpret_cast<uint4*>(row + chunk * 16) = o;
                     }
-                }
+                };
+                const unsigned s_addr = lane_base + (unsigned)sb * AT_S_COLS;
+                unsigned va[32], vb[32];
+                tmem_ld_32x32(s_addr, va);
+                tmem_ld_wait();
+                tmem_ld_32x32(s_addr + 32u, vb);
+                process(va, 0);
+                tmem_ld_wait();
+                tmem_ld_32x32(s_addr + 64u, va);
+                process(vb, 1);
+                tmem_ld_wait();
+                tmem_ld_32x32(s_addr + 96u, vb);
+                process(va, 2);
+                tmem_ld_wait();
+                process(vb, 3);
                 tc_fence_before();
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor cores
                 __syncwarp();
@@ -327,7 +343,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (!(ok = wait_all(O_FULL, o_phase, 34u))) break;
             o_phase ^= 1;
             tc_fence_after();
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / ((l4[0] + l4[1]) + (l4[2] + l4[3]));
             T* orow = O + (long long)(b / p.heads) * p.o_bs + (long long)(b % p.heads) * p.o_hs + ((long long)qt * 128 + r) * p.o_rs;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {

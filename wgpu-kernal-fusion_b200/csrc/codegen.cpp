@@ -334,9 +334,10 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
     if (try_tiled) {
         // Operands that are contiguous along another axis than the output (transposed views) are
         // staged through shared memory tile by tile; see JIT_EW_TILE_KERNEL.  All of them must
-        // share that axis; shared memory holds two staged tiles of 4-element chunks or one of 8.
+        // share that axis and allow 16-byte loads along it; 4-byte elements and chunks of 4 only;
+        // shared memory holds up to two staged 64 x 64 tiles.
         int pax = -1, nstaged = 0;
-        bool ok = R >= 2;
+        bool ok = R >= 2 && !any16 && cfg.C == 4;
         std::vector<int> sidx(nin, -1);
         for (int t = 0; t < nin && ok; ++t) {
             if (cfg.mode[t] != 3) continue;
@@ -347,11 +348,14 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
             if (pax >= 0 && pax != dc) ok = false;
             pax = dc;
             sidx[t] = nstaged++;
+            ok = ok && cshape[dc] % 4 == 0 && aligned_to(in[t], 16);
+            for (int d = 0; d < R && ok; ++d)
+                if (d != dc) ok = st[t][d] % 4 == 0;
         }
-        ok = ok && nstaged >= 1 && nstaged <= (cfg.C >= 8 ? 1 : 2);
+        ok = ok && nstaged >= 1 && nstaged <= 2;
         int64_t tiles = 0;
         if (ok) {
-            const int64_t tiles_p = (cshape[pax] + 31) / 32, tiles_l = (cshape[R - 1] + 32ll * cfg.C - 1) / (32ll * cfg.C);
+            const int64_t tiles_p = (cshape[pax] + 63) / 64, tiles_l = (cshape[R - 1] + 63) / 64;
             tiles = tiles_p * tiles_l;
             for (int d = 0; d < R - 1; ++d) {
                 ok = ok && cshape[d] < (1ll << 31);
@@ -374,9 +378,13 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
             s << "#define TILE_STAGE \\\n";
             for (int t = 0; t < nin; ++t)
                 if (sidx[t] >= 0)
-                    s << "    for (int i = warp; i < TL; i += 8) { const u32 ll = l0 + i; if (pp < P && ll < L) stage[" << sidx[t]
-                      << "][lane][i] = load1<" << (int)prog.slot_dtype[t] << ">((const void*)p.ptr[" << t << "], base[" << t
-                      << "] + (i64)pp * p.stride[" << t << " * R + PAX] + (i64)ll * p.stride[" << t << " * R + R - 1]); } \\\n";
+                    s << "    { float4 v_[4]; \\\n"
+                      << "      for (int i = 0; i < 4; ++i) { const u32 ll = l0 + r16 + 16 * i; \\\n"
+                      << "        v_[i] = (pp < P && ll < L) ? *(const float4*)((const float*)p.ptr[" << t << "] + base[" << t
+                      << "] + (i64)pp + (i64)ll * p.stride[" << t << " * R + R - 1]) : make_float4(0.f, 0.f, 0.f, 0.f); } \\\n"
+                      << "      for (int i = 0; i < 4; ++i) { const int li = r16 + 16 * i; \\\n"
+                      << "        stage[" << sidx[t] << "][4 * c16 + 0][li] = v_[i].x; stage[" << sidx[t] << "][4 * c16 + 1][li] = v_[i].y; \\\n"
+                      << "        stage[" << sidx[t] << "][4 * c16 + 2][li] = v_[i].z; stage[" << sidx[t] << "][4 * c16 + 3][li] = v_[i].w; } } \\\n";
             s << "\n#define TILE_INPUTS(X) \\\n";
             for (int t = 0; t < nin; ++t) {
                 if (sidx[t] >= 0)
@@ -396,8 +404,8 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
         for (int t = 0; t <= nin; ++t)
             for (int d = 0; d < R; ++d) w.put<int64_t>(st[t][d]);
         for (int d = 0; d < R; ++d) w.put<uint32_t>((uint32_t)cshape[d]);
-        w.put<uint32_t>((uint32_t)((cshape[pax] + 31) / 32));
-        w.put<uint32_t>((uint32_t)((cshape[R - 1] + 32ll * cfg.C - 1) / (32ll * cfg.C)));
+        w.put<uint32_t>((uint32_t)((cshape[pax] + 63) / 64));
+        w.put<uint32_t>((uint32_t)((cshape[R - 1] + 63) / 64));
         for (float f : prog.imms) w.put<float>(f);
         if (prog.imms.empty()) w.put<float>(0.f);
         w.finish();

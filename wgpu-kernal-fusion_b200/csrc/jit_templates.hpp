@@ -311,17 +311,20 @@ extern "C" __global__ void __launch_bounds__(256, MINB) wgf_elementwise(const __
 // Element-wise template for operands that are contiguous along ANOTHER axis than the output
 // (transposed views).  A CTA works on a tile of TP x TL elements of the plane (PAX, last
 // axis): it first brings the tile of every such operand into shared memory with the threads
-// running along PAX, where that operand is contiguous (coalesced 128-byte reads), then
-// computes with the threads running along the last axis, where the output and the other
-// operands are contiguous, taking the staged operands from shared memory.  Nothing is read
-// with adjacent threads a row apart (the crate's strided kernel, src/visit_tiled.rs:100-144)
-// and no transposed copy goes through HBM first.
-// Defines expected: R NIN C NIMM OUT_DT OUT_MODE PAX NSTAGED; macros TILE_STAGE (loads of the
-// staged operands) and TILE_INPUTS(X) (fills X[NIN][C] for one chunk); function prog.
+// running along PAX, where that operand is contiguous (16-byte loads, four in flight per
+// thread and operand), then computes with the threads running along the last axis, where the
+// output and the other operands are contiguous, taking the staged operands from shared
+// memory (rows padded by one word: two-way bank conflicts at most on either side).  Nothing is
+// read with adjacent threads a row apart (the crate's strided kernel,
+// src/visit_tiled.rs:100-144) and no transposed copy goes through HBM first.  4-byte elements,
+// chunks of 4; the staged operands' extents along PAX, their other strides and their base
+// addresses are multiples of 4 elements (the launcher checks).
+// Defines expected: R NIN C (= 4) NIMM OUT_DT OUT_MODE PAX NSTAGED; macros TILE_STAGE (loads of
+// the staged operands) and TILE_INPUTS(X) (fills X[NIN][C] for one chunk); function prog.
 // ---------------------------------------------------------------------------------------
 static const char* const JIT_EW_TILE_KERNEL = R"CUDA(
-#define TP 32
-#define TL (32 * C)
+#define TP 64
+#define TL 64
 struct Params {
     u64 ptr[NIN + 1];
     i64 stride[(NIN + 1) * R];
@@ -331,8 +334,9 @@ struct Params {
 };
 
 extern "C" __global__ void __launch_bounds__(256) wgf_elementwise_tiled(const __grid_constant__ Params p) {
-    __shared__ __align__(16) float stage[NSTAGED][TP][TL + 4];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float stage[NSTAGED][TP][TL + 1];
+    const int tid = threadIdx.x;
+    const int c16 = tid & 15, r16 = tid >> 4;   // 16 vectors / chunks along one tile axis, 16 rows along the other
     u32 id = blockIdx.x;
     const u32 tl = id % p.tiles_l;
     id /= p.tiles_l;
@@ -351,17 +355,17 @@ extern "C" __global__ void __launch_bounds__(256) wgf_elementwise_tiled(const __
     }
     const u32 P = p.shape[PAX], L = p.shape[R - 1];
     const u32 p0 = tp * TP, l0 = tl * TL;
-    // stage: lane runs along PAX, a warp takes every 8th index of the last axis
+    // stage: a thread loads 4 consecutive elements along PAX for 4 indices of the last axis
     {
-        const u32 pp = p0 + lane;
+        const u32 pp = p0 + 4 * c16;
         TILE_STAGE
     }
     __syncthreads();
-    const int tx = lane, ty = warp;             // 32 chunks along the last axis, 8 rows of PAX per pass
+    const int tx = c16, ty = r16;               // 16 chunks along the last axis, 16 rows of PAX per pass
     const u32 l = l0 + tx * C;
 #pragma unroll 1
-    for (int pass = 0; pass < TP / 8; ++pass) {
-        const int pi = ty + pass * 8;
+    for (int pass = 0; pass < TP / 16; ++pass) {
+        const int pi = ty + pass * 16;
         const u32 pp = p0 + pi;
         if (pp >= P || l >= L) continue;
         const int nvalid = L - l < (u32)C ? (int)(L - l) : C;
