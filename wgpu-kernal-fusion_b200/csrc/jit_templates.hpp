@@ -187,7 +187,8 @@ template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t)
 // [parity][source rank][value index]; a single 64-bit store / load is atomic, so a word with
 // the expected sequence number carries the value that belongs to it.  The value goes to every
 // peer by a store over NVLink, the peers' values are read from this GPU's own mailbox and
-// combined in rank order.  The wait is bounded (2 s): it then sets the error word.
+// combined in rank order.  The wait is bounded (5 s, enough for a peer that still compiles its
+// kernel on the first step): it then sets the error word.
 template <int OP> DEV float peer_all_reduce(float mine, int index, u64 peers, u32 world, u32 rank, u32 seq, u64 err) {
     const u64* table = (const u64*)peers;
     const u32 parity = seq & 1u;
@@ -212,7 +213,7 @@ template <int OP> DEV float peer_all_reduce(float mine, int index, u64 peers, u3
                     u64 now;
                     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                     if (start == 0) start = now;
-                    else if (now - start > 2000000000ull) break;
+                    else if (now - start > 5000000000ull) break;
                 }
             }
             if (!got) {
