@@ -124,7 +124,12 @@ int tune(const char* name, int dflt) {
 }
 
 // The helpers every generated kernel starts with.
-std::string prelude() { return JIT_PRELUDE; }
+std::string prelude() {
+    // warp-wide max / min through redux.sync (f32 form of sm_100a)
+    static const std::string text =
+        std::string("#define WGF_REDUX ") + (tune("REDUX", 1) ? "1\n" : "0\n") + JIT_PRELUDE;
+    return text;
+}
 
 int pow2_at_least(int64_t v) {
     int p = 1;

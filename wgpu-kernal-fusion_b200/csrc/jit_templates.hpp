@@ -168,16 +168,36 @@ template <int OP> DEV float red_comb(float a, float b) {
     return OP == RED_SUM ? a + b : OP == RED_PROD ? a * b : OP == RED_MAX ? fmaxf(a, b) : fminf(a, b);
 }
 // All-lanes reduction over the `GROUP` consecutive threads that share a row.  `slot` points
-// at GROUP/32 floats of shared memory private to this (reduction, row) pair.
+// at GROUP/32 floats of shared memory private to this (reduction, row) pair, 16-byte aligned
+// when GROUP >= 128.  The warps' values are combined in warp order whichever way they are read.
 template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t) {
+#if WGF_REDUX
+    // max / min of a warp in one instruction (redux.sync on f32, sm_100a); NaN operands are
+    // skipped exactly as fmaxf / fminf skip them
+    if (OP == RED_MAX) asm volatile("redux.sync.max.f32 %0, %0, 0xffffffff;" : "+f"(v));
+    else if (OP == RED_MIN) asm volatile("redux.sync.min.f32 %0, %0, 0xffffffff;" : "+f"(v));
+    else
+#endif
+    {
 #pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) v = red_comb<OP>(v, __shfl_xor_sync(0xffffffffu, v, m));
+        for (int m = 16; m >= 1; m >>= 1) v = red_comb<OP>(v, __shfl_xor_sync(0xffffffffu, v, m));
+    }
     if (GROUP > 32) {
         if ((t & 31) == 0) slot[t >> 5] = v;
         __syncthreads();
-        v = slot[0];
+        if (GROUP >= 128) {
+            const float4* s4 = (const float4*)slot;
 #pragma unroll
-        for (int w = 1; w < GROUP / 32; ++w) v = red_comb<OP>(v, slot[w]);
+            for (int w = 0; w < GROUP / 128; ++w) {
+                const float4 q = s4[w];
+                v = w == 0 ? q.x : red_comb<OP>(v, q.x);
+                v = red_comb<OP>(red_comb<OP>(red_comb<OP>(v, q.y), q.z), q.w);
+            }
+        } else {
+            v = slot[0];
+#pragma unroll
+            for (int w = 1; w < GROUP / 32; ++w) v = red_comb<OP>(v, slot[w]);
+        }
     }
     return v;
 }
@@ -433,7 +453,7 @@ DEV void row_offsets(const Params& p, u64 row, bool rv, i64* roff) {
 
 extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __grid_constant__ Params p) {
 #if GROUP > 32 && NRED > 0
-    __shared__ float red_smem[NRED][RPC][GROUP / 32];
+    __shared__ __align__(16) float red_smem[NRED][RPC][GROUP / 32];
 #endif
     const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
     const float* imm = p.imm;
@@ -468,7 +488,7 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __gri
 #if NGRAND > 0
     // Companion whole-tensor reductions: CTA partial -> scratch; the last CTA to arrive
     // (ticket) combines all partials in index order and stores the scalars.
-    __shared__ float g_smem[NGRAND][THREADS / 32];
+    __shared__ __align__(16) float g_smem[NGRAND][THREADS / 32];
     __shared__ u32 g_last;
     float* gpart = (float*)p.gpartials;
     ROW_GRAND_BLOCK
@@ -536,7 +556,7 @@ DEV void load_tile(const Params& p, const i64* roff, u64 base, u64 nch, int t, T
 }
 
 extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(const __grid_constant__ Params p) {
-    __shared__ float red_smem[NRED][THREADS / 32];
+    __shared__ __align__(16) float red_smem[NRED][THREADS / 32];
     __shared__ u32 is_last;
     const int t = threadIdx.x;
     const u32 sp = blockIdx.x % p.split;

@@ -136,6 +136,7 @@ std::vector<char> compile_to_cubin(const std::string& source, const std::string&
                           "-default-device", "--extra-device-vectorization", "--ptxas-options=-v"};
     r = n.CompileProgram(prog, verbose ? 6 : 5, opts);
     if (verbose && r == 0) {
+        if (getenv("WGF_DUMP_SOURCE")) fprintf(stderr, "---- %s ----\n%s\n", name.c_str(), source.c_str());
         size_t ls = 0;
         n.GetProgramLogSize(prog, &ls);
         std::string log(ls, '\0');
