@@ -300,6 +300,39 @@ int32_t wgf_comm_release(wgf_comm* comm);
 int32_t wgf_tensor_all_reduce(wgf_tensor* t, wgf_comm* comm, uint32_t opcode, wgf_tensor** out);
 
 /* ======================================================================================
+ * Recorded schedules: the kernels of a materialisation, captured once as a CUDA graph and
+ * replayed with one call.  The crate pays its whole host cost (graph walk, shader text,
+ * bind groups, one submit per kernel: src/compute_graph/resolve.rs:16-248,
+ * src/kernel.rs:244-389) on every materialisation; a replay pays one graph launch.
+ *
+ *   wgf_schedule_begin(dev);
+ *   ... build tensors, wgf_tensor_materialize / _materialize_many ...   (captured, not run)
+ *   wgf_schedule_end(dev, &s);     (instantiates and runs the schedule once)
+ *   loop: write new input data into the input tensors' buffers (wgf_tensor_desc_of +
+ *         wgf_buffer_upload), wgf_schedule_launch(s), read the results' buffers.
+ *
+ * Inputs are the tensors that existed before wgf_schedule_begin; the schedule reads their
+ * buffers at every launch and never overwrites them.  Tensors materialised while recording
+ * keep their buffers for the life of the schedule and hold the values of the latest launch.
+ * While recording, calls that wait for the device or copy between host and device (sync,
+ * uploads, downloads, tensor creation from host data) and all-reduces fail with
+ * WGF_ERR_UNSUPPORTED; constants of scalar ops are recorded by value.  One recording at a
+ * time per device.  Memory taken while recording returns to the device's pool when the
+ * schedule is destroyed.
+ * ==================================================================================== */
+typedef struct wgf_schedule wgf_schedule;
+int32_t wgf_schedule_begin(wgf_device* dev);
+/* Ends the recording started by wgf_schedule_begin.  On failure the recording is over as
+ * well and *out is NULL. */
+int32_t wgf_schedule_end(wgf_device* dev, wgf_schedule** out);
+/* Queues one replay on the device's stream; does not wait. */
+int32_t wgf_schedule_launch(wgf_schedule* s);
+/* Kernels (and copies) one launch runs. */
+int32_t wgf_schedule_kernel_count(wgf_schedule* s, uint64_t* out);
+/* Waits for replays in flight, then frees the graph and returns its memory to the pool. */
+int32_t wgf_schedule_destroy(wgf_schedule* s);
+
+/* ======================================================================================
  * Reduction for callers that must not allocate.  (No counterpart in the crate: this entry
  * point exists for hosts of THIS library that cannot let a compute call reach the device
  * allocator -- code running inside a CUDA stream capture, real-time loops that rule out calls

@@ -244,3 +244,71 @@ def test_generated_kernels_compile_for_every_layout_class(wgf, drydev):
     big = d.tensor(np.zeros((2, 20000), np.float32))
     big.softmax_last_dim().materialize()
     d.tensor(np.zeros((3, 100000), np.float32)).sum(1).materialize()
+
+
+def test_recorded_schedule_state_machine(wgf, drydev):
+    """wgf_schedule_*: what a recording refuses, what it counts, where its memory goes."""
+    d = drydev
+    x = d.tensor(np.zeros((64, 512), np.float32))
+    w = d.tensor(np.zeros((512,), np.float32))
+    d.memory()
+    with pytest.raises(wgf.WgfError):                      # nothing to end
+        h = C.c_void_p()
+        wgf.check(wgf.lib().wgf_schedule_end(d.h, C.byref(h)))
+    in_use_before = d.memory()[1]
+    before = d.launch_count
+    with d.record() as s:
+        with pytest.raises(wgf.WgfError):                  # one recording at a time
+            wgf.check(wgf.lib().wgf_schedule_begin(d.h))
+        y = x.layer_norm(w, 1e-5).softmax_last_dim()
+        t = x.exp().sum(0).sum(0)
+        wgf.Tensor.materialize_all([y, t])
+        z = (y * 2.0 + 1.0).materialize()
+        for refused in (z.as_slice, d.sync, lambda: d.tensor(np.zeros(4, np.float32)),
+                        lambda: x.write(np.zeros((64, 512), np.float32))):
+            with pytest.raises(wgf.WgfError) as e:
+                refused()
+            assert e.value.status == "UNSUPPORTED"
+    assert s.kernel_count == d.launch_count - before == 2
+    s.launch()
+    s.launch()
+    assert d.launch_count - before == 6
+    # the recording's memory stays with the schedule, also once its tensors are gone ...
+    y.release(), t.release(), z.release()
+    held = d.memory()[1]
+    assert held > in_use_before
+    other = (x + 1.0).materialize()                        # must not get one of the schedule's blocks
+    assert d.memory()[1] > held
+    other.release()
+    # ... and returns to the pool with the schedule
+    s.destroy()
+    assert d.memory()[1] == in_use_before
+
+
+def test_recording_never_overwrites_its_inputs(wgf, drydev):
+    """Outside a recording a dead input donates its buffer; inside, an input of the schedule is
+    read again by every replay, so the result gets its own buffer."""
+    d = drydev
+    data = np.zeros((64, 64), np.float32)
+
+    def result_ptr_equals_input_ptr(record):
+        x = d.tensor(data)
+        px = C.c_void_p()
+        dx = x.desc()
+        wgf.check(wgf.lib().wgf_buffer_device_ptr(C.c_void_p(dx.buf), C.byref(px), None))
+        wgf.lib().wgf_buffer_release(C.c_void_p(dx.buf))
+        y = x + 1.0
+        x.release()
+        if record:
+            with d.record() as s:
+                y.materialize()
+        else:
+            y.materialize()
+        py = C.c_void_p()
+        dy = y.desc()
+        wgf.check(wgf.lib().wgf_buffer_device_ptr(C.c_void_p(dy.buf), C.byref(py), None))
+        wgf.lib().wgf_buffer_release(C.c_void_p(dy.buf))
+        return px.value == py.value
+
+    assert result_ptr_equals_input_ptr(False)
+    assert not result_ptr_equals_input_ptr(True)

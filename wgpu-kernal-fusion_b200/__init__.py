@@ -126,6 +126,11 @@ class Device:
                                                 C.c_void_p(pinned.ptr.value), C.byref(out)))
         return Tensor(self, out)
 
+    def record(self):
+        """`with dev.record() as s:` captures every kernel queued inside the block as one schedule
+        (wgf_schedule_begin / _end); afterwards `s.launch()` replays them with one call."""
+        return Schedule(self)
+
     def arange(self, start, end, step=1.0, dtype=F32):
         out = C.c_void_p()
         check(lib().wgf_tensor_arange(self.h, C.c_uint32(dtype), C.c_float(start), C.c_float(end),
@@ -370,6 +375,24 @@ class Tensor:
         check(lib().wgf_tensor_download(self.h, out.ctypes.data_as(C.c_void_p), C.c_uint64(out.nbytes)))
         return out
 
+    def write(self, data):
+        """New contents for a materialised, contiguous tensor, written into the buffer it already
+        has (the way to feed the inputs of a recorded schedule)."""
+        dt, shape = self._info()
+        a = np.ascontiguousarray(data, dtype=_NP[dt])
+        if tuple(a.shape) != tuple(shape):
+            raise ValueError(f"shape {a.shape} does not match the tensor's {tuple(shape)}")
+        d = self.desc()
+        try:
+            want = [int(np.prod(shape[i + 1:], dtype=np.int64)) for i in range(len(shape))]
+            if any(shape[i] > 1 and d.stride[i] != want[i] for i in range(len(shape))):
+                raise ValueError("write needs a contiguous tensor")
+            check(lib().wgf_buffer_upload(C.c_void_p(d.buf), C.c_uint64(d.offset * a.itemsize),
+                                          a.ctypes.data_as(C.c_void_p), C.c_uint64(a.nbytes)))
+        finally:
+            lib().wgf_buffer_release(C.c_void_p(d.buf))
+        return self
+
     def download_into(self, out):
         check(lib().wgf_tensor_download(self.h, out.ctypes.data_as(C.c_void_p), C.c_uint64(out.nbytes)))
         return out
@@ -423,6 +446,49 @@ class PinnedArray:
             self.array = None
             _lib.wgf_host_free(self.ptr)
             self.ptr = None
+
+
+class Schedule:
+    """A recorded schedule (wgf_schedule_*): the kernels of the materialisations made inside the
+    `with` block, replayed by `launch()`.  Inputs are tensors created before the block; feed them
+    with `Tensor.write`.  Tensors materialised inside hold the values of the latest launch."""
+
+    def __init__(self, dev):
+        self.dev = dev
+        self.h = None
+
+    def __enter__(self):
+        check(lib().wgf_schedule_begin(self.dev.h))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        h = C.c_void_p()
+        status = lib().wgf_schedule_end(self.dev.h, C.byref(h))
+        if exc_type is None:
+            check(status)
+            self.h = h
+        elif status == 0:
+            lib().wgf_schedule_destroy(h)
+        return False
+
+    def launch(self):
+        check(lib().wgf_schedule_launch(self.h))
+
+    @property
+    def kernel_count(self):
+        v = C.c_uint64()
+        check(lib().wgf_schedule_kernel_count(self.h, C.byref(v)))
+        return v.value
+
+    def destroy(self):
+        if self.h:
+            check(lib().wgf_schedule_destroy(self.h))
+            self.h = None
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.wgf_schedule_destroy(self.h)
+            self.h = None
 
 
 def shard_range(n_units, world, rank):

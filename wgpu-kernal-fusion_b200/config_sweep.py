@@ -30,8 +30,9 @@ def normal(g, shape, mu=0.0, sigma=1.0):
 
 
 class Row:
-    def __init__(self, name, build, nbytes=None, flop=None, variants=1):
+    def __init__(self, name, build, nbytes=None, flop=None, variants=1, custom=None):
         self.name, self.build, self.nbytes, self.flop, self.variants = name, build, nbytes, flop, variants
+        self.custom = custom          # a row that measures itself: returns the fields of its JSON object
 
 
 def time_row(dev, row, iters, warmup):
@@ -68,7 +69,36 @@ def group_c1(wgf, dev):
     def chain(x):
         return (x * 2.0 + 1.0).sin().cos() * 0.5 + (-(x * x)).exp()
     xb = dev.tensor(uniform(rng(1, 100), (8192, 4096), -1, 1))
-    return [Row("C1 chain f32 [1024,1024] cold", lambda k: chain(x1[k]), nbytes=8388608, variants=64),
+
+    def host_cost(passes=200):
+        """Wall-clock per materialisation of the small chain (the kernel itself takes a few
+        microseconds): built and resolved every time, against one replay of a recorded schedule."""
+        import time
+        dev.set_timing(False)
+        chain(x1[0]).materialize()
+        dev.sync()
+        t0 = time.perf_counter()
+        for _ in range(passes):
+            chain(x1[0]).materialize()
+        dev.sync()
+        eager = (time.perf_counter() - t0) / passes
+        with dev.record() as s:
+            y = chain(x1[0]).materialize()
+        dev.sync()
+        t0 = time.perf_counter()
+        for _ in range(passes):
+            s.launch()
+        dev.sync()
+        replay = (time.perf_counter() - t0) / passes
+        y.release()
+        s.destroy()
+        dev.set_timing(True)
+        return {"eager_us_per_pass": round(eager * 1e6, 2), "replay_us_per_pass": round(replay * 1e6, 2),
+                "passes": passes, "bytes": 8388608, "replay_gbs": round(8388608 / replay / 1e9, 1)}
+
+    return [Row("C1 chain f32 [1024,1024] wall clock per pass, resolved each time vs recorded schedule", None,
+                custom=host_cost),
+            Row("C1 chain f32 [1024,1024] cold", lambda k: chain(x1[k]), nbytes=8388608, variants=64),
             Row("C1 chain f32 [1024,1024] warm", lambda k: chain(x1[0]), nbytes=8388608),
             Row("C1' chain f32 [8192,4096]", lambda k: chain(xb), nbytes=2 * 134217728),
             Row("C1 x*2+1 f32 [8192,4096]", lambda k: xb * 2.0 + 1.0, nbytes=2 * 134217728)]
@@ -183,6 +213,11 @@ def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, only=None, emit=pri
             continue
         rows = [r for r in make(wgf, dev) if not only or only in r.name]
         for row in rows:
+            if row.custom:
+                r = {"row": row.name, **row.custom()}
+                results.append(r)
+                emit(json.dumps(r))
+                continue
             med, best, labels = time_row(dev, row, iters, warmup)
             med = max(med, 1e-9)          # the compile-only device records no time
             r = {"row": row.name, "kernels": labels, "median_us": round(med, 2), "best_us": round(best, 2)}

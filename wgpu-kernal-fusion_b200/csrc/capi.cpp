@@ -874,6 +874,48 @@ int32_t wgf_comm_release(wgf_comm* comm) {
         delete comm;
     });
 }
+// ---- recorded schedules --------------------------------------------------------------------
+struct wgf_schedule {
+    DeviceRef dev;
+    Device::Recorded rec;
+};
+
+int32_t wgf_schedule_begin(wgf_device* dev) {
+    GRAPH_GUARD({
+        REQUIRE(dev);
+        dev->ref->begin_recording();
+    })
+}
+int32_t wgf_schedule_end(wgf_device* dev, wgf_schedule** out) {
+    GRAPH_GUARD({
+        REQUIRE(dev);
+        REQUIRE(out);
+        *out = nullptr;
+        Device::Recorded rec = dev->ref->end_recording();
+        *out = new wgf_schedule{dev->ref, rec};
+    })
+}
+int32_t wgf_schedule_launch(wgf_schedule* s) {
+    GRAPH_GUARD({
+        REQUIRE(s);
+        s->dev->replay(s->rec);
+    })
+}
+int32_t wgf_schedule_kernel_count(wgf_schedule* s, uint64_t* out) {
+    return guard([&] {
+        REQUIRE(s);
+        REQUIRE(out);
+        *out = s->rec.kernels;
+    });
+}
+int32_t wgf_schedule_destroy(wgf_schedule* s) {
+    GRAPH_GUARD({
+        REQUIRE(s);
+        s->dev->destroy_recorded(s->rec);
+        delete s;
+    })
+}
+
 int32_t wgf_tensor_all_reduce(wgf_tensor* t, wgf_comm* comm, uint32_t opcode, wgf_tensor** out) {
     GRAPH_GUARD({
         REQUIRE(t);

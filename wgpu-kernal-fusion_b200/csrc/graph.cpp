@@ -504,6 +504,13 @@ struct MarkSet {
 };
 
 // Will `x` be unreachable once `root` has been materialised and has let go of its inputs?
+// While a schedule is being recorded, a buffer may be overwritten in place only if it was
+// produced inside the recording: a replay runs its producer again.  Overwriting a buffer from
+// outside (an input of the schedule) would make the second run read what the first one wrote.
+bool replay_may_overwrite(const Device& dev, const TensorData& td) {
+    return !dev.recording() || (td.buf && td.buf->arena == dev.arena());
+}
+
 bool dies_with(Node* x, Node* root, MarkSet& memo) {
     if (x == root) return true;
     if (memo.contains(x)) return memo.get(x) != 0;
@@ -950,6 +957,7 @@ TensorData run_region(Node* root, bool allow_fold = true) {
             Node* l = em.slot_leaf[s];
             if (!l || !dies_with(l, root, memo)) continue;
             const TensorData& sd = em.slots[s];
+            if (!replay_may_overwrite(*root->dev, sd)) continue;
             if (dtype_size(sd.dtype) != dtype_size(odt) || !sd.layout.is_dense() || sd.layout.allocation_overlaps())
                 continue;
             long shared = 0;
@@ -971,6 +979,8 @@ TensorData run_region(Node* root, bool allow_fold = true) {
     try {
         Device& dev = *root->dev;
         GrandComm gc{};
+        // the exchange carries a sequence number that the host advances per launch
+        if (kernel_comm) dev.refuse_while_recording("an all-reduce");
         if (kernel_comm) gc = GrandComm{kernel_comm->peer_table, (uint32_t)kernel_comm->world, (uint32_t)kernel_comm->rank, ++kernel_comm->seq};
         if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace, &grand_out, kernel_comm ? &gc : nullptr);
         else out = run_elementwise(dev, em.prog, em.slots, index_shape, inplace);
@@ -1064,7 +1074,8 @@ TensorData resolve_node(Node* n) {
             // The crate writes into the target's buffer.  That is kept only when nothing else
             // can still read the old contents; otherwise the target is copied first.
             MarkSet memo(Node::S_DIES);
-            bool own = dies_with(tn, n, memo) && !target.layout.allocation_overlaps();
+            bool own = dies_with(tn, n, memo) && !target.layout.allocation_overlaps() &&
+                       replay_may_overwrite(dev, target);
             if (own) {
                 tn->cached = TensorData();           // `target` now holds the only reference if unshared
                 own = target.buf.use_count() == 1;
@@ -1082,6 +1093,7 @@ TensorData resolve_node(Node* n) {
             break;
         }
         case NodeKind::AllReduce: {
+            dev.refuse_while_recording("an all-reduce");
             Node* src = n->inputs[0].get();
             // A scalar that only this all-reduce can see is exchanged by the kernel that computes
             // it (over peer memory) where that kernel is a streaming reduction; see ArRequest.

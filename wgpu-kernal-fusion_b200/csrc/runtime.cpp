@@ -175,6 +175,15 @@ std::vector<char> compile_to_cubin(const std::string& source, const std::string&
 // ---------------------------------------------------------------------------------------
 Buffer::~Buffer() {
     if (ptr && dev) {
+        if (arena) {
+            // a block of a recorded schedule stays with the schedule while that one lives
+            std::lock_guard<std::mutex> g(arena->mu);
+            if (!arena->closed) {
+                if (pending) dev->recycle(pending);
+                arena->free.emplace(block, ptr);
+                return;
+            }
+        }
         // a collective may still touch the block: it goes back to the pool once that is over
         if (pending) dev->release_block_after(ptr, block, pending);
         else dev->release_block(ptr, block);
@@ -213,7 +222,9 @@ cudaStream_t Device::collective_stream() {
 void Device::wait_for(Buffer& b) {
     if (!b.pending) return;
     cudaSetDevice(ordinal);
-    cudaStreamWaitEvent(stream, b.pending, 0);
+    // an event recorded outside a capture cannot become a dependency inside it: wait on the host
+    if (recording()) cudaEventSynchronize(b.pending);
+    else cudaStreamWaitEvent(stream, b.pending, 0);
     recycle(b.pending);
     b.pending = nullptr;
 }
@@ -249,6 +260,14 @@ std::shared_ptr<Device> Device::create(int ordinal) {
 }
 
 Device::~Device() {
+    if (arena_ && !dry && stream) {
+        // destroyed in the middle of a recording: close the capture and drop what it holds
+        cudaSetDevice(ordinal);
+        cudaGraph_t g = nullptr;
+        cudaStreamEndCapture(stream, &g);
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+    }
     if (dry) {
         for (auto& kv : free_) free(kv.second);
         return;
@@ -281,6 +300,7 @@ void Device::make_current() const {
 }
 
 void Device::sync() {
+    refuse_while_recording("wgf_device_sync");
     if (dry) return;
     make_current();
     WGF_CUDA(cudaStreamSynchronize(stream));
@@ -330,7 +350,7 @@ void* Device::raw_alloc(size_t block) {
     }
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, block);
-    if (e == cudaErrorMemoryAllocation) {
+    if (e == cudaErrorMemoryAllocation && !recording()) {
         cudaGetLastError();
         // give cached blocks back to the driver and retry once
         WGF_CUDA(cudaStreamSynchronize(stream));
@@ -354,7 +374,17 @@ BufferRef Device::alloc(size_t bytes, bool zero) {
     make_current();
     size_t block = round_block(bytes);
     void* p = nullptr;
-    {
+    if (arena_) {
+        // blocks that this recording has already used and released come first
+        std::lock_guard<std::mutex> g(arena_->mu);
+        auto it = arena_->free.lower_bound(block);
+        if (it != arena_->free.end() && it->first <= block + block / 4 + 4096) {
+            p = it->second;
+            block = it->first;
+            arena_->free.erase(it);
+        }
+    }
+    if (!p) {
         std::lock_guard<std::mutex> g(mu_);
         if (!deferred_.empty()) drain_deferred_locked();
         auto it = free_.lower_bound(block);
@@ -370,6 +400,7 @@ BufferRef Device::alloc(size_t bytes, bool zero) {
     }
     auto b = std::make_shared<Buffer>();
     b->dev = shared_from_this();
+    b->arena = arena_;
     b->ptr = p;
     b->bytes = bytes;
     b->block = block;
@@ -386,6 +417,7 @@ void Device::release_block(void* p, size_t block) {
 }
 
 void Device::trim() {
+    refuse_while_recording("trimming the pool");
     if (dry) return;
     make_current();
     WGF_CUDA(cudaStreamSynchronize(stream));
@@ -399,6 +431,7 @@ void Device::trim() {
 
 void Device::upload(const Buffer& b, size_t off, const void* src, size_t n) {
     WGF_CHECK(off + n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "upload past the end of the buffer");
+    refuse_while_recording("an upload");
     if (!n || dry) return;
     make_current();
     WGF_CUDA(cudaMemcpyAsync((char*)b.ptr + off, src, n, cudaMemcpyHostToDevice, stream));
@@ -412,6 +445,7 @@ void Device::upload(const Buffer& b, size_t off, const void* src, size_t n) {
 // that earlier kernels still use; the buffer carries the completion event (Buffer::pending).
 void Device::upload_async(Buffer& b, const void* src, size_t n) {
     WGF_CHECK(n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "upload past the end of the buffer");
+    refuse_while_recording("an upload");
     if (!n || dry) return;
     make_current();
     cudaPointerAttributes attr;
@@ -433,6 +467,7 @@ void Device::upload_async(Buffer& b, const void* src, size_t n) {
 
 void Device::download(const Buffer& b, size_t off, void* dst, size_t n) {
     WGF_CHECK(off + n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "download past the end of the buffer");
+    refuse_while_recording("a download");
     WGF_CHECK(!dry, WGF_ERR_CUDA, "compile-only device: nothing was executed, there is nothing to download");
     make_current();
     wait_for(const_cast<Buffer&>(b));
@@ -505,7 +540,7 @@ int Device::max_blocks_per_sm(const JitKernel& k, int threads) {
 
 void Device::begin_launch(const char* what) {
     launches++;
-    if (timing && sink && !dry) {
+    if (timing && sink && !dry && !recording()) {
         pending_.start = event();
         pending_.stop = event();
         pending_.what = what;
@@ -540,6 +575,79 @@ void Device::launch(const JitKernel& k, dim3 grid, dim3 block, size_t smem, cons
                                                (unsigned)smem, (CUstream)stream, args, nullptr);
     cu_check(r, what);
     end_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// recorded schedules
+// ---------------------------------------------------------------------------------------
+void Device::refuse_while_recording(const char* what) const {
+    if (recording())
+        fail(WGF_ERR_UNSUPPORTED, std::string(what) + " is not possible while a schedule is being recorded "
+                                                       "(finish it with wgf_schedule_end first)");
+}
+
+void Device::begin_recording() {
+    WGF_CHECK(!recording(), WGF_ERR_INVALID_ARGUMENT, "a schedule is already being recorded on this device");
+    if (!dry) {
+        make_current();
+        // everything the capture must not contain happens now: the one-time set-up of the
+        // ticket counters and the error word, and the end of all work on the other streams
+        counters();
+        error_word();
+        sync();
+        WGF_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeRelaxed));
+    }
+    arena_ = std::make_shared<Arena>();
+    recording_from_ = launches.load();
+}
+
+Device::Recorded Device::end_recording() {
+    WGF_CHECK(recording(), WGF_ERR_INVALID_ARGUMENT, "no schedule is being recorded on this device");
+    Recorded r;
+    r.arena = arena_;
+    r.kernels = launches.load() - recording_from_;
+    arena_.reset();
+    if (dry) return r;
+    make_current();
+    cudaError_t e = cudaStreamEndCapture(stream, &r.graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&r.exec, r.graph, 0);
+    if (e == cudaSuccess) e = cudaGraphLaunch(r.exec, stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        destroy_recorded(r);
+        fail(WGF_ERR_CUDA, std::string("recording the schedule failed: ") + cudaGetErrorString(e));
+    }
+    return r;
+}
+
+void Device::replay(const Recorded& r) {
+    refuse_while_recording("replaying a schedule");
+    launches += r.kernels;
+    if (dry) return;
+    make_current();
+    WGF_CUDA(cudaGraphLaunch(r.exec, stream));
+}
+
+void Device::destroy_recorded(Recorded& r) {
+    if (!dry) {
+        cudaSetDevice(ordinal);
+        // a replay may still be running: its memory must not reach the pool before it ends
+        if (r.exec) cudaStreamSynchronize(stream);
+        if (r.exec) cudaGraphExecDestroy(r.exec);
+        if (r.graph) cudaGraphDestroy(r.graph);
+    }
+    r.exec = nullptr;
+    r.graph = nullptr;
+    if (r.arena) {
+        std::multimap<size_t, void*> blocks;
+        {
+            std::lock_guard<std::mutex> g(r.arena->mu);
+            r.arena->closed = true;
+            blocks.swap(r.arena->free);
+        }
+        for (auto& kv : blocks) release_block(kv.second, kv.first);
+        r.arena.reset();
+    }
 }
 
 }  // namespace wgf

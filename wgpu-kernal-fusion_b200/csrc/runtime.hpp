@@ -26,6 +26,16 @@ namespace wgf {
 
 struct Device;
 
+// Memory of a recorded schedule (Device::begin_recording).  Blocks handed out while recording
+// come back here instead of to the device pool for as long as the schedule lives, so that a
+// replay, which writes to the same addresses again, cannot touch memory that the pool has
+// given to someone else in the meantime.
+struct Arena {
+    std::mutex mu;
+    bool closed = false;                   // schedule destroyed: blocks go to the device pool again
+    std::multimap<size_t, void*> free;     // blocks of the schedule that no live buffer holds
+};
+
 struct Buffer {
     std::shared_ptr<Device> dev;
     void* ptr = nullptr;
@@ -35,6 +45,7 @@ struct Buffer {
     // buffer.  The device stream waits for it before the next use of the buffer and before
     // the block goes back to the pool (Device::wait_for, ~Buffer).
     cudaEvent_t pending = nullptr;
+    std::shared_ptr<Arena> arena;   // set for buffers allocated while a schedule was being recorded
     ~Buffer();
 };
 using BufferRef = std::shared_ptr<Buffer>;
@@ -113,6 +124,25 @@ struct Device : std::enable_shared_from_this<Device> {
     void begin_launch(const char* what);
     void end_launch();
 
+    // ---- recorded schedules (CUDA graph capture of everything queued on `stream`) ----
+    // While recording, kernels are captured instead of run; calls that wait for the device,
+    // copy between host and device, or involve another stream fail with WGF_ERR_UNSUPPORTED.
+    struct Recorded {
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        std::shared_ptr<Arena> arena;
+        uint64_t kernels = 0;
+    };
+    bool recording() const { return (bool)arena_; }
+    void begin_recording();
+    // Ends the capture, instantiates the graph and runs it once, so that every tensor
+    // materialised while recording holds its value as after an ordinary materialisation.
+    Recorded end_recording();
+    void replay(const Recorded& r);
+    void destroy_recorded(Recorded& r);
+    void refuse_while_recording(const char* what) const;
+    const std::shared_ptr<Arena>& arena() const { return arena_; }
+
     // Timing sink: while set, every launch appends an event pair to it.
     std::vector<TimingRecord>* sink = nullptr;
     cudaEvent_t event();
@@ -135,6 +165,8 @@ struct Device : std::enable_shared_from_this<Device> {
         cudaEvent_t ev;
     };
     std::vector<Deferred> deferred_;
+    std::shared_ptr<Arena> arena_;     // non-null while recording
+    uint64_t recording_from_ = 0;      // value of `launches` when recording began
     void drain_deferred_locked();
     void* raw_alloc(size_t block);
 };
