@@ -68,6 +68,39 @@ class Device {
     wgf_device* h_ = nullptr;
 };
 
+// A recorded schedule (wgf_schedule_*).  Everything materialised between construction and
+// finish() is captured instead of run; launch() replays it with one call.
+//     wgf::Schedule s(dev);  auto y = f(x);  y.materialize();  s.finish();
+//     for (...) { x.write(host_data);  s.launch();  y.as_slice(); }
+class Schedule {
+   public:
+    explicit Schedule(const Device& dev) : dev_(dev) { check(wgf_schedule_begin(dev_.raw())); }
+    Schedule(const Schedule&) = delete;
+    Schedule& operator=(const Schedule&) = delete;
+    ~Schedule() {
+        if (recording_) {
+            wgf_schedule* dropped = nullptr;
+            if (wgf_schedule_end(dev_.raw(), &dropped) == WGF_OK) wgf_schedule_destroy(dropped);
+        }
+        if (h_) wgf_schedule_destroy(h_);
+    }
+    void finish() {
+        recording_ = false;
+        check(wgf_schedule_end(dev_.raw(), &h_));
+    }
+    void launch() const { check(wgf_schedule_launch(h_)); }
+    uint64_t kernel_count() const {
+        uint64_t n = 0;
+        check(wgf_schedule_kernel_count(h_, &n));
+        return n;
+    }
+
+   private:
+    Device dev_;
+    wgf_schedule* h_ = nullptr;
+    bool recording_ = true;
+};
+
 // TensorSlice, src/tensor.rs:669-855: host copy of a materialised tensor with index access.
 template <int R, typename D>
 class TensorSlice {
@@ -173,6 +206,23 @@ class Tensor {
         std::vector<D> host(n);
         check(wgf_tensor_download(h_, host.data(), n * sizeof(D)));
         return TensorSlice<R, D>(s, std::move(host));
+    }
+    // New contents (row-major, numel values) for a materialised contiguous tensor, written into
+    // the buffer it already has: the way to feed the inputs of a recorded schedule.
+    void write(const D* values) const {
+        wgf_tensor_desc d;
+        check(wgf_tensor_desc_of(h_, &d));
+        size_t n = 1;
+        bool dense = true;
+        for (int i = R - 1; i >= 0; --i) {
+            dense = dense && (d.shape[i] <= 1 || d.stride[i] == (int64_t)n);
+            n *= (size_t)d.shape[i];
+        }
+        int32_t st = dense ? wgf_buffer_upload(d.buf, (uint64_t)d.offset * sizeof(D), values, n * sizeof(D))
+                           : (int32_t)WGF_ERR_UNSUPPORTED;
+        wgf_buffer_release(d.buf);
+        if (!dense) throw Error(WGF_ERR_UNSUPPORTED, "write needs a contiguous tensor");
+        check(st);
     }
     std::vector<uint64_t> all_timing_information() const {
         uint32_t n = 0;
