@@ -37,6 +37,7 @@ struct TcParams {
     long long M, N, K, batch;
     long long c_rs, c_bs;
     int tiles_m, tiles_n;
+    int band;          // tile rows per band of the tile order (tc::banded_tile)
     int b_is_kn;       // 1: B stored [K,N] (N-major), 0: B stored [N,K] (K-major)
     int is_bf16;
     int use_tma_store; // 1: epilogue stages through shared memory and stores by TMA (needs N % 8 == 0)
@@ -102,7 +103,9 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int b = (int)(tile / tiles_per_batch);
                 const int r = (int)(tile % tiles_per_batch);
-                const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
+                int mt, nt;
+                tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
+                const int m0 = mt * BM, n0 = nt * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase)) {
                         atomicExch(p.error, 1u);
@@ -185,7 +188,9 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = (int)(tile / tiles_per_batch);
             const int r = (int)(tile % tiles_per_batch);
-            const long long m0 = (long long)(r % p.tiles_m) * BM, n0 = (long long)(r / p.tiles_m) * BN;
+            int mt, nt;
+            tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
+            const long long m0 = (long long)mt * BM, n0 = (long long)nt * BN;
             if (!mbar_wait(acc_full_bar(acc), acc_phase)) {
                 if (lane == 0) atomicExch(p.error, 4u);
                 break;
@@ -323,6 +328,7 @@ bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt
     p.error = dev.error_word();
     const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
     const unsigned grid = (unsigned)std::min<long long>(total, dev.sm_count);
+    p.band = band_rows((int)grid, BM, BN, p.tiles_m);
     static bool attr_set[2] = {false, false};
     if (bf16) {
         if (!attr_set[1]) {

@@ -37,6 +37,7 @@ struct PairParams {
     long long M, N, K, batch;
     long long c_rs, c_bs;
     int tiles_m, tiles_n;   // tiles of 256 x 256
+    int band;               // tile rows per band of the tile order (tc::banded_tile)
     int b_is_kn;
     int is_bf16;
     int use_tma_store;
@@ -199,8 +200,10 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (int it = 0; ok && next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
                 const int b = (int)(u.tile / tiles_per_batch);
                 const int r = (int)(u.tile % tiles_per_batch);
-                const int m0 = (r % p.tiles_m) * 256 + (int)rank * P_BM;
-                const int n0 = (r / p.tiles_m) * P_BN + (int)rank * P_BNH;
+                int mt, nt;
+                tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
+                const int m0 = mt * 256 + (int)rank * P_BM;
+                const int n0 = nt * P_BN + (int)rank * P_BNH;
                 for (int kb = u.kb0; kb < u.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase)) {
                         atomicExch(p.error, 41u);
@@ -281,7 +284,9 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int it = 0; next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
             const int b = (int)(u.tile / tiles_per_batch);
             const int r = (int)(u.tile % tiles_per_batch);
-            const long long m0 = (long long)(r % p.tiles_m) * 256 + (long long)rank * P_BM, n0 = (long long)(r / p.tiles_m) * P_BN;
+            int mt, nt;
+            tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
+            const long long m0 = (long long)mt * 256 + (long long)rank * P_BM, n0 = (long long)nt * P_BN;
             bool got = mbar_wait(acc_full_bar(acc), acc_phase);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
@@ -505,6 +510,7 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
     if (resident[ti] < 1) return false;
     long long clusters = std::min<long long>(dev.sm_count / 2, resident[ti]);
     const int k_blocks = (int)((d.K + P_BK - 1) / P_BK);
+    p.band = band_rows((int)clusters, 256, P_BN, p.tiles_m);
     p.full_waves = (int)(total / clusters);
     p.tail = (int)(total % clusters);
     p.split = 0;

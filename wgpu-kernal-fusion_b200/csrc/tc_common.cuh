@@ -123,6 +123,29 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
     return d;
 }
 
+// Order of the output tiles of one batch.  Tile rows are grouped into bands of `band` rows;
+// inside a band the index runs down the rows first, then along the columns.  The CTAs of a
+// wave work on consecutive indices, so with band ~ sqrt(CTAs) a wave covers a near-square block
+// of tiles and reads about 2*sqrt(CTAs) operand panels, instead of one panel of B and every
+// panel of A (which for a tall A is more than L2 holds, wave after wave).
+__host__ __device__ __forceinline__ void banded_tile(int r, int tiles_m, int tiles_n, int band, int& mt, int& nt) {
+    const int per_band = band * tiles_n;
+    const int b = r / per_band;
+    const int first = b * band;
+    const int rows = tiles_m - first < band ? tiles_m - first : band;
+    const int within = r - b * per_band;
+    mt = first + within % rows;
+    nt = within / rows;
+}
+// Rows per band for `ctas` concurrent tiles whose A panel is `tile_m` rows and B panel `tile_n` columns tall.
+inline int band_rows(int ctas, int tile_m, int tile_n, int tiles_m) {
+    int best = 1;
+    // cost of a wave ~ band*tile_m + (ctas/band)*tile_n rows of K elements; smallest at band = sqrt(ctas*tile_n/tile_m)
+    while ((long long)(best + 1) * (best + 1) * tile_m <= (long long)ctas * tile_n) best++;
+    if (const char* e = getenv("WGF_MATMUL_BAND")) best = atoi(e) > 0 ? atoi(e) : best;
+    return best < tiles_m ? best : (tiles_m > 0 ? tiles_m : 1);
+}
+
 template <typename T> __device__ __forceinline__ unsigned pack2(float lo, float hi);
 template <> __device__ __forceinline__ unsigned pack2<__half>(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
