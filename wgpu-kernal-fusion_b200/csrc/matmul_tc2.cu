@@ -4,7 +4,9 @@
 // and accumulates its 128 x 256 half of the tile in its own tensor memory.  Compared with one
 // CTA per 128 x 256 tile (matmul_tc.cu) every tcgen05.mma reads 8 KiB instead of 12 KiB of
 // operands per SM, so shared-memory bandwidth (128 bytes per clock) no longer caps the tensor
-// pipe at about 80 %.
+// pipe at about 80 %.  Tiles are walked in bands (tc::banded_tile) so that a wave reuses its
+// operand panels through L2, and leftover tiles that would fill at most half of the last wave
+// are cut into two 256 x 128 units.
 //
 // Roles per CTA: warp 0 = TMA producer (both CTAs load their halves; all loads of a stage
 // complete on the LEADER's "full" barrier), warp 1 = MMA issuer (leader only; its commits
@@ -41,57 +43,34 @@ struct PairParams {
     int b_is_kn;
     int is_bf16;
     int use_tma_store;
-    // Schedule: every cluster takes `full_waves` whole tiles (tile = wave * clusters + cluster);
-    // the `tail` tiles left over are split `split` ways along K (0 = not split) so that the last
-    // wave keeps all clusters busy.  Part 0 of a split tile owns the output: it adds the fp32
-    // partial tiles the other parts leave in `scratch` ([tail][split-1][256 columns][256 rows])
-    // once their per-warp flags ([tail][split-1][8]) are set.
-    int full_waves, tail, split;
-    float* scratch;
-    unsigned* flags;
+    // Schedule: every cluster takes `full_waves` whole tiles (tile = wave * clusters + cluster).
+    // When the `tail` tiles left over would keep at most half of the clusters busy, each of them
+    // is cut along N into `nsplit` = 2 units of 256 x 128, so that the last wave takes half the
+    // time of a full one (the tcgen05.mma shape becomes M256 x N128, 64 columns of B per CTA).
+    int full_waves, tail, nsplit;
     unsigned* error;
 };
 
 struct Unit {
     long long tile;
-    int kb0, kb1;       // range of k-blocks
-    int part, parts;    // K-split: this is part `part` of `parts`
-    int tail_index;
+    int nw;      // width of the unit in columns: P_BN, or P_BN / nsplit for a tail tile
+    int noff;    // first column of the unit inside its tile
 };
 
 // The `it`-th unit of work of cluster `cluster` (of `clusters`); false when there is none.
-__device__ __forceinline__ bool next_unit(const PairParams& p, long long cluster, long long clusters, int k_blocks, int it, Unit& u) {
-    u.kb0 = 0;
-    u.kb1 = k_blocks;
-    u.part = 0;
-    u.parts = 1;
-    u.tail_index = 0;
+__device__ __forceinline__ bool next_unit(const PairParams& p, long long cluster, long long clusters, int it, Unit& u) {
+    u.nw = P_BN;
+    u.noff = 0;
     if (it < p.full_waves) {
         u.tile = (long long)it * clusters + cluster;
         return true;
     }
     if (it > p.full_waves) return false;
-    const long long base = (long long)p.full_waves * clusters;
-    if (p.split <= 1) {
-        if (cluster >= p.tail) return false;
-        u.tile = base + cluster;
-        return true;
-    }
-    if (cluster >= (long long)p.tail * p.split) return false;
-    u.tail_index = (int)(cluster / p.split);
-    u.part = (int)(cluster % p.split);
-    u.parts = p.split;
-    u.tile = base + u.tail_index;
-    const int per = (k_blocks + p.split - 1) / p.split;
-    u.kb0 = u.part * per;
-    u.kb1 = min(k_blocks, u.kb0 + per);
+    if (cluster >= (long long)p.tail * p.nsplit) return false;
+    u.tile = (long long)p.full_waves * clusters + cluster / p.nsplit;
+    u.nw = P_BN / p.nsplit;
+    u.noff = (int)(cluster % p.nsplit) * u.nw;
     return true;
-}
-
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
 }
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
@@ -146,8 +125,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(unsigned bar, unsigned cta) 
         : "memory");
 }
 
-__host__ __device__ constexpr unsigned pair_instr_desc(bool b_mn_major) {
-    return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((unsigned)(P_BN >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+__host__ __device__ constexpr unsigned pair_instr_desc(bool b_mn_major, int n) {
+    return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
 }
 
 template <typename T>
@@ -197,14 +176,16 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             unsigned phase = 1;
             bool ok = true;
             Unit u;
-            for (int it = 0; ok && next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
+            for (int it = 0; ok && next_unit(p, cluster, clusters, it, u); ++it) {
                 const int b = (int)(u.tile / tiles_per_batch);
                 const int r = (int)(u.tile % tiles_per_batch);
                 int mt, nt;
                 tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
                 const int m0 = mt * 256 + (int)rank * P_BM;
-                const int n0 = nt * P_BN + (int)rank * P_BNH;
-                for (int kb = u.kb0; kb < u.kb1; ++kb) {
+                const int nh = u.nw / 2;                                  // columns of B this CTA stages
+                const int n0 = nt * P_BN + u.noff + (int)rank * nh;
+                const unsigned stage_tx = 2u * (unsigned)(P_A_BYTES + nh * P_BK * 2);   // both CTAs' bytes
+                for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase)) {
                         atomicExch(p.error, 41u);
                         ok = false;
@@ -212,14 +193,12 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                     const unsigned sa = smem_base + stage * P_STAGE_BYTES, sb = sa + P_A_BYTES;
                     const unsigned fb = full_bar(stage) & PEER_BIT_MASK;        // the leader's barrier
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);   // both CTAs' bytes
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), stage_tx);
                     tma_load_3d_pair(sa, &map_a, fb, kb * P_BK, m0, b);
-                    if (p.b_is_kn) {
-#pragma unroll
-                        for (int j = 0; j < P_BNH / 64; ++j)
-                            tma_load_3d_pair(sb + j * (P_BK * 128), &map_b, fb, n0 + j * 64, kb * P_BK, b);
-                    } else {
-                        tma_load_3d_pair(sb, &map_b, fb, kb * P_BK, n0, b);
+                    // B in boxes of 64 columns (N-major: a [P_BK x 64] panel; K-major: 64 rows of P_BK)
+                    for (int j = 0; j < nh / 64; ++j) {
+                        if (p.b_is_kn) tma_load_3d_pair(sb + j * (P_BK * 128), &map_b, fb, n0 + j * 64, kb * P_BK, b);
+                        else tma_load_3d_pair(sb + j * (64 * P_BK * 2), &map_b, fb, kb * P_BK, n0 + j * 64, b);
                     }
                     if (++stage == P_STAGES) {
                         stage = 0;
@@ -231,21 +210,22 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
-            const unsigned idesc = pair_instr_desc(p.b_is_kn != 0) | ((unsigned)p.is_bf16 << 7) | ((unsigned)p.is_bf16 << 10);
+            const unsigned idesc0 = pair_instr_desc(p.b_is_kn != 0, 0) | ((unsigned)p.is_bf16 << 7) | ((unsigned)p.is_bf16 << 10);
             int stage = 0;
             unsigned phase = 0;
             int acc = 0;
             unsigned acc_phase = 1;
             bool ok = true;
             Unit u;
-            for (int it = 0; ok && next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
+            for (int it = 0; ok && next_unit(p, cluster, clusters, it, u); ++it) {
+                const unsigned idesc = idesc0 | ((unsigned)(u.nw >> 3) << 17);   // N of the instruction = width of the unit
                 if (!mbar_wait(acc_empty_bar(acc), acc_phase)) {
                     atomicExch(p.error, 42u);
                     break;
                 }
                 tc_fence_after();
                 const unsigned tmem_d = tmem_base + (unsigned)acc * P_BN;
-                for (int kb = u.kb0; kb < u.kb1; ++kb) {
+                for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase)) {
                         atomicExch(p.error, 43u);
                         ok = false;
@@ -258,7 +238,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         const unsigned long long adesc = smem_desc(sa + k * (P_UMMA_K * 2), 16, 1024);
                         const unsigned long long bdesc = p.b_is_kn ? smem_desc(sb + k * (P_UMMA_K * 128), P_BK * 128, 1024)
                                                                    : smem_desc(sb + k * (P_UMMA_K * 2), 16, 1024);
-                        umma_pair_f16(tmem_d, adesc, bdesc, idesc, (kb != u.kb0 || k != 0) ? 1u : 0u);
+                        umma_pair_f16(tmem_d, adesc, bdesc, idesc, (kb != 0 || k != 0) ? 1u : 0u);
                     }
                     umma_commit_pair(empty_bar(stage));      // frees the stage in both CTAs
                     if (++stage == P_STAGES) {
@@ -281,12 +261,12 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         int epi_buf = 0;
         const bool vec_ok = (p.c_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.c_bs % 8 == 0);
         Unit u;
-        for (int it = 0; next_unit(p, cluster, clusters, k_blocks, it, u); ++it) {
+        for (int it = 0; next_unit(p, cluster, clusters, it, u); ++it) {
             const int b = (int)(u.tile / tiles_per_batch);
             const int r = (int)(u.tile % tiles_per_batch);
             int mt, nt;
             tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
-            const long long m0 = (long long)mt * 256 + (long long)rank * P_BM, n0 = (long long)nt * P_BN;
+            const long long m0 = (long long)mt * 256 + (long long)rank * P_BM, n0 = (long long)nt * P_BN + u.noff;
             bool got = mbar_wait(acc_full_bar(acc), acc_phase);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
@@ -296,62 +276,9 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const long long m = m0 + quarter * 32 + lane;
             T* crow = C + (long long)b * p.c_bs + m * p.c_rs;
-            // K-split tiles: row of this thread in the 256-row tile, slot of this warp among the 8 of the pair
-            const int trow = (int)rank * P_BM + quarter * 32 + lane;
-            const int wslot = (int)rank * 4 + quarter;
-            const size_t part_stride = 256 * 256;
-            const size_t first_part = (size_t)u.tail_index * (size_t)(u.parts - 1);
-            if (u.parts > 1 && u.part > 0) {
-                // not the owner of the tile: leave the fp32 partial sums in scratch, column-major so
-                // that the 32 lanes of a warp (32 rows) write 128 contiguous bytes, then raise the flag
-                float* part = p.scratch + (first_part + (size_t)(u.part - 1)) * part_stride;
-#pragma unroll 1
-                for (int c = 0; c < P_BN; c += 32) {
-                    unsigned v[32];
-                    tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c), v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) part[(size_t)(c + i) * 256 + trow] = __uint_as_float(v[i]);
-                }
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicExch(&p.flags[(first_part + (size_t)(u.part - 1)) * 8 + wslot], 1u);
-            } else {
-            if (u.parts > 1) {
-                // owner: the matching warp of every other part must have written its rows
-                bool all = true;
-                for (int pp = 1; pp < u.parts; ++pp) {
-                    const unsigned* f = &p.flags[(first_part + (size_t)(pp - 1)) * 8 + wslot];
-                    bool seen = false;
-                    unsigned long long start = 0;
-                    for (unsigned spin = 0; spin < SPIN_LIMIT && !seen; ++spin) {
-                        seen = ld_acquire_u32(f) != 0;
-                        if (!seen && (spin & 63) == 63) {
-                            const unsigned long long now = global_ns();
-                            if (start == 0) start = now;
-                            else if (now - start > 2000000000ull) break;
-                        }
-                    }
-                    all = all && seen;
-                }
-                all = __all_sync(0xffffffffu, all);
-                if (!all) {
-                    if (lane == 0) atomicExch(p.error, 45u);
-                    break;
-                }
-            }
-            // adds the other parts' partial sums to 32 accumulator columns starting at column c0
-            auto add_parts = [&](unsigned* v, int c0) {
-                for (int pp = 1; pp < u.parts; ++pp) {
-                    const float* part = p.scratch + (first_part + (size_t)(pp - 1)) * part_stride;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(part + (size_t)(c0 + i) * 256 + trow));
-                }
-            };
             if (p.use_tma_store) {
 #pragma unroll 1
-                for (int c = 0; c < P_BN; c += 64) {
+                for (int c = 0; c < u.nw; c += 64) {
                     unsigned char* tile_smem = epi_smem + ((warp - 2) * 2 + epi_buf) * P_EPI_TILE_BYTES;
                     if (lane == 0) bulk_wait_read<1>();
                     __syncwarp();
@@ -360,7 +287,6 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         unsigned v[32];
                         tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c + half * 32), v);
                         tmem_ld_wait();
-                        if (u.parts > 1) add_parts(v, c + half * 32);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint4 o;
@@ -383,11 +309,10 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             } else {
 #pragma unroll 1
-                for (int c = 0; c < P_BN; c += 32) {
+                for (int c = 0; c < u.nw; c += 32) {
                     unsigned v[32];
                     tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c), v);
                     tmem_ld_wait();
-                    if (u.parts > 1) add_parts(v, c);
                     const long long n = n0 + c;
                     if (m < p.M && n < p.N) {
                         if (vec_ok && n + 31 < p.N) {
@@ -411,7 +336,6 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                 }
             }
-            }   // owner or unsplit tile
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty_bar(acc), 0);    // the leader's barrier counts both CTAs' warps
@@ -457,7 +381,7 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
     if (b_kn) {
         if (!encode_3d(&map_b, bf16, b, d.N, d.K, d.batch, d.b_rs, d.b_bs, 64, P_BK)) return false;
     } else {
-        if (!encode_3d(&map_b, bf16, b, d.K, d.N, d.batch, d.b_cs, d.b_bs, P_BK, P_BNH)) return false;
+        if (!encode_3d(&map_b, bf16, b, d.K, d.N, d.batch, d.b_cs, d.b_bs, P_BK, 64)) return false;
     }
     PairParams p{};
     p.M = d.M;
@@ -477,13 +401,9 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
         p.use_tma_store = 1;
     p.error = dev.error_word();
     const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
-    // Schedule (see PairParams).  The leftover tiles of the last wave are split along K when
-    // that at least halves their time and every part keeps 32 or more k-blocks (K >= 2048 per
-    // part): the fix-up (a 256 KiB fp32 partial tile written, waited for and added per part)
-    // costs about as much as 8 k-blocks, and measured on 4096^3 (34 leftover tiles, split in
-    // two) the step is neutral: 105.0 us with, 105.4 us without.
-    // Parts of a split tile wait for one another, so every cluster of the grid has to be resident
-    // at once: the grid is capped by what the device reports for this kernel.
+    // Schedule (see PairParams).  One cluster per SM pair that the device reports as resident
+    // for this kernel; leftover tiles that would keep at most half of the clusters busy are cut
+    // in two along N (measured on 4096^3, 34 leftover tiles of 256: 104 us as whole tiles).
     static int resident[2] = {-1, -1};
     const int ti = bf16 ? 1 : 0;
     if (resident[ti] < 0) {
@@ -509,31 +429,15 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
     }
     if (resident[ti] < 1) return false;
     long long clusters = std::min<long long>(dev.sm_count / 2, resident[ti]);
-    const int k_blocks = (int)((d.K + P_BK - 1) / P_BK);
     p.band = band_rows((int)clusters, 256, P_BN, p.tiles_m);
     p.full_waves = (int)(total / clusters);
     p.tail = (int)(total % clusters);
-    p.split = 0;
-    if (p.tail > 0 && !getenv("WGF_MATMUL_NO_KSPLIT")) {
-        int s = (int)std::min<long long>(4, clusters / p.tail);
-        const int min_part = getenv("WGF_MATMUL_KSPLIT_MIN") ? std::max(1, atoi(getenv("WGF_MATMUL_KSPLIT_MIN"))) : 32;
-        while (s >= 2 && ((k_blocks + s - 1) / s < min_part || ((k_blocks + s - 1) / s) * (s - 1) >= k_blocks)) --s;
-        if (s >= 2) p.split = s;
-    }
-    if (p.full_waves == 0 && p.split == 0) clusters = p.tail;   // fewer tiles than clusters and no split: a smaller grid
-    BufferRef scratch, flags;
-    if (p.split >= 2) {
-        const size_t parts = (size_t)p.tail * (size_t)(p.split - 1);
-        scratch = dev.alloc(parts * 256 * 256 * sizeof(float), false);
-        flags = dev.alloc(parts * 8 * sizeof(unsigned), false);
-        WGF_CUDA(cudaMemsetAsync(flags->ptr, 0, parts * 8 * sizeof(unsigned), dev.stream));
-        p.scratch = (float*)scratch->ptr;
-        p.flags = (unsigned*)flags->ptr;
-    }
+    p.nsplit = (p.tail > 0 && 2ll * p.tail <= clusters && !getenv("WGF_MATMUL_NO_NSPLIT")) ? 2 : 1;
+    if (p.full_waves == 0) clusters = (long long)p.tail * p.nsplit;   // fewer units than clusters: a smaller grid
     const unsigned grid = 2u * (unsigned)clusters;
     if (getenv("WGF_MATMUL_VERBOSE"))
-        fprintf(stderr, "[wgf] matmul_tc2 %lldx%lldx%lld batch %lld: %lld tiles on %lld clusters (%d resident), %d full waves, tail %d split %d\n",
-                d.M, d.N, d.K, d.batch, total, clusters, resident[ti], p.full_waves, p.tail, p.split);
+        fprintf(stderr, "[wgf] matmul_tc2 %lldx%lldx%lld batch %lld: %lld tiles on %lld clusters (%d resident), %d full waves, tail %d cut in %d\n",
+                d.M, d.N, d.K, d.batch, total, clusters, resident[ti], p.full_waves, p.tail, p.nsplit);
     static bool attr_set[2] = {false, false};
     if (bf16) {
         if (!attr_set[1]) {
