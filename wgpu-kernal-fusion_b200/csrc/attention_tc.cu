@@ -14,9 +14,10 @@
 //   end      O / l -> global memory
 // Recomputing S costs a third more tensor work than the single-pass online softmax, but O is
 // never rescaled, so nothing has to be read back from and written again to tensor memory per
-// tile.  Measured with cycle counters around every wait: the softmax warps wait for the tensor
-// cores about half of the time; the M128 x N128 products are bound by operand delivery from
-// shared memory (8 KiB per 65 cycles of math), which the P stores and the K / V writes share.
+// tile.  What bounds the kernel is the latency of the per-tile chain S -> softmax -> P -> P V
+// (measured: cheaper softmax code, twice the softmax warps and a single-pass variant with a
+// third less tensor work all failed to make it faster; the softmax warps and the MMA warp each
+// wait for the other about half of the time).
 // Warp roles:
 //   warp 0     TMA producer (one lane): Q tile, then K / V tiles through a 4-stage ring
 //   warp 1     MMA issuer   (one lane): S into one of two TMEM buffers (2 x 128 columns), O in a
