@@ -195,11 +195,21 @@ def group_c5(wgf, dev):
     inv = (1.0 / (10000.0 ** (np.arange(0, d, 2, dtype=np.float32) / d)))[None, :]
     cos, sin = dev.tensor(np.cos(pos * inv).astype(np.float16)), dev.tensor(np.sin(pos * inv).astype(np.float16))
     gate, up = (dev.tensor(normal(g, (16384, 11008)).astype(np.float16)) for _ in range(2))
+    xt = dev.tensor(normal(g, (16384, 4096)).astype(np.float16))
+    wq, wu, wd = (dev.tensor((normal(g, shape) * 0.02).astype(np.float16))
+                  for shape in ((4096, 4096), (11008, 4096), (4096, 11008)))
     causal_flop = 4 * bh * s * s * d // 2          # QK^T and PV, the masked half not counted
     return [Row("C5 attention f16 causal [256,2048,128]", lambda i: q.attention(k, v, causal=True), flop=causal_flop),
             Row("C5 attention f16 full [256,2048,128]", lambda i: q.attention(k, v), flop=2 * causal_flop),
             Row("C5 rope f16 [256,2048,128]", lambda i: q.rope(cos, sin), nbytes=2 * bh * s * d * 2),
-            Row("C5 silu(gate)*up f16 [16384,11008]", lambda i: gate.silu() * up, nbytes=3 * 16384 * 11008 * 2)]
+            Row("C5 silu(gate)*up f16 [16384,11008]", lambda i: gate.silu() * up, nbytes=3 * 16384 * 11008 * 2),
+            # the block's projections: 16384 tokens against weights stored [out, in]
+            Row("C5 projection f16 [16384,4096] x W^T [4096,4096]", lambda i: xt.mat_mul(wq.transpose(0, 1)),
+                flop=2 * 16384 * 4096 * 4096),
+            Row("C5 up projection f16 [16384,4096] x W^T [11008,4096]", lambda i: xt.mat_mul(wu.transpose(0, 1)),
+                flop=2 * 16384 * 4096 * 11008),
+            Row("C5 down projection f16 [16384,11008] x W^T [4096,11008]", lambda i: gate.mat_mul(wd.transpose(0, 1)),
+                flop=2 * 16384 * 4096 * 11008)]
 
 
 GROUPS = [("C1", group_c1), ("C2", group_c2), ("C3", group_c3), ("C4", group_c4), ("C5", group_c5)]
