@@ -395,6 +395,346 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Two query tiles per CTA.  The kernel above is bound by the latency of its per-tile chain
+// S -> softmax -> P -> P V.  Here a CTA works on two adjacent query tiles of one batch*head at
+// the same time: each tile has its own Q, S, P and O and its own four softmax warps, the two
+// share the K / V ring (every K / V tile is loaded once for both), and the MMA warp alternates
+// between them, so one tile's tensor work fills the time the other spends in its softmax.
+// Tensor memory: S of tile t in columns 128 t, O in 256 + 128 t.  Shared memory: 2 Q + 2 P tiles
+// and a 3-stage ring (224 KiB).  Causal: the first tile of the pair needs one key tile less.
+// ---------------------------------------------------------------------------------------
+constexpr int A2_STAGES = 3;
+constexpr int A2_THREADS = 320;            // TMA warp, MMA warp, 2 x 4 softmax warps
+constexpr int A2_SMEM = (4 + A2_STAGES) * AT_TILE + 1024 /*alignment slack*/ + 512 /*barriers*/;
+enum {
+    Q2_FULL = 0, Q2_EMPTY = 2, KV2_FULL = 4, KV2_EMPTY = KV2_FULL + A2_STAGES, S2_FULL = KV2_EMPTY + A2_STAGES, S2_EMPTY = S2_FULL + 2,
+    P2_FULL = S2_EMPTY + 2, P2_EMPTY = P2_FULL + 2, O2_FULL = P2_EMPTY + 2, O2_EMPTY = O2_FULL + 2, N2_BARS = O2_EMPTY + 2
+};
+
+// Work item w -> (batch*head b, pair of query tiles pt): same orders as decode_item.
+__device__ __forceinline__ void decode_pair(const AtParams& p, int n_pairs, long long w, int& b, int& pt) {
+    if (p.causal) {
+        pt = n_pairs - 1 - (int)(w / p.bh);
+        b = (int)(w % p.bh);
+    } else {
+        b = (int)(w / n_pairs);
+        pt = (int)(w % n_pairs);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(A2_THREADS, 1)
+attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, T* __restrict__ O, const __grid_constant__ AtParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // [Q0][Q1][P0][P1][ring ...]
+    const unsigned q_smem0 = smem_u32(smem), p_smem0 = q_smem0 + 2 * AT_TILE, ring = p_smem0 + 2 * AT_TILE;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (4 + A2_STAGES) * AT_TILE);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + N2_BARS);
+    const unsigned bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (unsigned)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < N2_BARS; ++i) {
+            // one arrival per softmax warp of the tile
+            const bool four = (i >= S2_EMPTY && i < S2_EMPTY + 2) || (i >= P2_FULL && i < P2_FULL + 2) || (i >= O2_EMPTY && i < O2_EMPTY + 2);
+            mbar_init(bar(i), four ? 4 : 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const int n_pairs = (p.n_q_tiles + 1) / 2;
+    const long long items = (long long)p.bh * n_pairs;
+    // key tiles of tile t of pair pt (0: the pair has no second tile)
+    auto tiles_of = [&](int pt, int t) -> int {
+        const int qt = 2 * pt + t;
+        if (qt >= p.n_q_tiles) return 0;
+        return p.causal ? qt + 1 : p.n_k_tiles;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 1, q_phase[2] = {1, 1};   // fresh "empty" barriers count as already released
+            bool ok = true;
+            auto push = [&](const CUtensorMap* map, int row0, int b) -> bool {
+                if (!mbar_wait(bar(KV2_EMPTY + stage), phase)) {
+                    atomicExch(p.error, 61u);
+                    return false;
+                }
+                const unsigned dst = ring + (unsigned)stage * AT_TILE;
+                mbar_expect_tx(bar(KV2_FULL + stage), AT_TILE);
+                tma_load_3d(dst, map, bar(KV2_FULL + stage), 0, row0, b);
+                tma_load_3d(dst + AT_PANEL, map, bar(KV2_FULL + stage), 64, row0, b);
+                if (++stage == A2_STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                return true;
+            };
+            for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                int b, pt;
+                decode_pair(p, n_pairs, w, b, pt);
+                const int n_max = max(tiles_of(pt, 0), tiles_of(pt, 1));
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (tiles_of(pt, t) == 0) continue;
+                    if (!mbar_wait(bar(Q2_EMPTY + t), q_phase[t])) {
+                        atomicExch(p.error, 60u);
+                        ok = false;
+                        break;
+                    }
+                    q_phase[t] ^= 1;
+                    const unsigned qs = q_smem0 + (unsigned)t * AT_TILE;
+                    mbar_expect_tx(bar(Q2_FULL + t), AT_TILE);
+                    tma_load_3d(qs, &map_q, bar(Q2_FULL + t), 0, (2 * pt + t) * 128, b);
+                    tma_load_3d(qs + AT_PANEL, &map_q, bar(Q2_FULL + t), 64, (2 * pt + t) * 128, b);
+                }
+                // the order below is the order in which the MMA warp consumes the ring
+                for (int j = 0; j < n_max && ok; ++j) ok = push(&map_k, j * 128, b);
+                for (int j = 0; j < n_max && ok; ++j) {
+                    ok = push(&map_k, j * 128, b);
+                    if (ok && j > 0) ok = push(&map_v, (j - 1) * 128, b);
+                }
+                if (ok) ok = push(&map_v, (n_max - 1) * 128, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const unsigned idesc_s = at_idesc((unsigned)p.is_bf16, 0u), idesc_pv = at_idesc((unsigned)p.is_bf16, 1u);
+            int stage = 0;
+            unsigned phase = 0;
+            unsigned q_phase[2] = {0, 0}, p_phase[2] = {0, 0}, o_phase[2] = {1, 1}, s_phase[2] = {1, 1};
+            bool ok = true;
+            int nk[2];
+            auto advance = [&]() {
+                if (++stage == A2_STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            };
+            auto wait_or = [&](int which, unsigned ph, unsigned code) -> bool {
+                if (mbar_wait(bar(which), ph)) return true;
+                atomicExch(p.error, code);
+                return false;
+            };
+            // S_t = Q_t K^T for both tiles that still need key tile j; K is at the head of the ring
+            auto issue_s = [&](int j, bool last_pass) -> bool {
+                if (!wait_or(KV2_FULL + stage, phase, 71u)) return false;
+                const unsigned kt = ring + (unsigned)stage * AT_TILE;
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= nk[t]) continue;
+                    if (!wait_or(S2_EMPTY + t, s_phase[t], 72u)) return false;
+                    s_phase[t] ^= 1;
+                    tc_fence_after();
+                    const unsigned qs = q_smem0 + (unsigned)t * AT_TILE;
+                    const unsigned d = tmem_base + (unsigned)t * AT_S_COLS;
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const unsigned off = (unsigned)(kk >> 2) * AT_PANEL + (unsigned)(kk & 3) * 32u;
+                        umma_f16(d, smem_desc(qs + off, 16, 1024), smem_desc(kt + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar(S2_FULL + t));
+                    if (last_pass && j == nk[t] - 1) umma_commit(bar(Q2_EMPTY + t));   // Q_t is free once these are done
+                }
+                umma_commit(bar(KV2_EMPTY + stage));
+                advance();
+                return true;
+            };
+            // O_t (+)= P_t V for both tiles that have key tile j; V is at the head of the ring
+            auto issue_pv = [&](int j) -> bool {
+                if (!wait_or(KV2_FULL + stage, phase, 75u)) return false;
+                const unsigned vt = ring + (unsigned)stage * AT_TILE;
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= nk[t]) continue;
+                    if (j == 0) {
+                        if (!wait_or(O2_EMPTY + t, o_phase[t], 73u)) return false;
+                        o_phase[t] ^= 1;
+                    }
+                    if (!wait_or(P2_FULL + t, p_phase[t], 74u)) return false;
+                    p_phase[t] ^= 1;
+                    tc_fence_after();
+                    const unsigned ps = p_smem0 + (unsigned)t * AT_TILE;
+                    const unsigned d = tmem_base + AT_O_COL0 + (unsigned)t * 128u;
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const unsigned long long adesc = smem_desc(ps + (unsigned)(kk >> 2) * AT_PANEL + (unsigned)(kk & 3) * 32u, 16, 1024);
+                        const unsigned long long bdesc = smem_desc(vt + (unsigned)kk * 2048u, AT_PANEL, 1024);
+                        umma_f16(d, adesc, bdesc, idesc_pv, (j == 0 && kk == 0) ? 0u : 1u);
+                    }
+                    umma_commit(bar(P2_EMPTY + t));
+                    if (j == nk[t] - 1) umma_commit(bar(O2_FULL + t));
+                }
+                umma_commit(bar(KV2_EMPTY + stage));
+                advance();
+                return true;
+            };
+            for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                int b, pt;
+                decode_pair(p, n_pairs, w, b, pt);
+                nk[0] = tiles_of(pt, 0);
+                nk[1] = tiles_of(pt, 1);
+                const int n_max = max(nk[0], nk[1]);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (nk[t] == 0) continue;
+                    ok = wait_or(Q2_FULL + t, q_phase[t], 70u);
+                    q_phase[t] ^= 1;
+                }
+                if (!ok) break;
+                tc_fence_after();
+                for (int j = 0; j < n_max && ok; ++j) ok = issue_s(j, false);   // pass 1
+                for (int j = 0; j < n_max && ok; ++j) {                          // pass 2
+                    ok = issue_s(j, true);
+                    if (ok && j > 0) ok = issue_pv(j - 1);
+                }
+                if (ok) ok = issue_pv(n_max - 1);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax (warps 2-5: tile 0, warps 6-9: tile 1)
+        const int t = (warp - 2) >> 2;
+        const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31 belong to this warp
+        const int r = quarter * 32 + lane;                  // row of the query tile
+        const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+        const unsigned s_addr = lane_base + (unsigned)t * AT_S_COLS, o_addr = lane_base + AT_O_COL0 + (unsigned)t * 128u;
+        unsigned char* p_tile = smem + (2 + t) * AT_TILE;
+        unsigned s_phase = 0, pe_phase = 1, o_phase = 0;
+        bool ok = true;
+        auto wait_all = [&](int which, unsigned parity, unsigned code) -> bool {
+            bool got = mbar_wait(bar(which), parity);
+            got = __all_sync(0xffffffffu, got);
+            if (!got && lane == 0) atomicExch(p.error, code);
+            return got;
+        };
+        for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+            int b, pt;
+            decode_pair(p, n_pairs, w, b, pt);
+            const int n_kv = tiles_of(pt, t);
+            if (n_kv == 0) continue;                         // an odd tile count: the last pair has one tile
+            const int qt = 2 * pt + t;
+            // ---- pass 1: row maximum of the raw scores (four independent chains)
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (!(ok = wait_all(S2_FULL + t, s_phase, 81u))) break;
+                s_phase ^= 1;
+                tc_fence_after();
+                const bool diag = p.causal && j == qt;
+#pragma unroll 1
+                for (int c = 0; c < 4; c += 2) {
+                    unsigned v[64];
+                    tmem_ld_32x32(s_addr + (unsigned)c * 32u, v);
+                    tmem_ld_32x32(s_addr + (unsigned)(c + 1) * 32u, v + 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        float sv = __uint_as_float(v[i]);
+                        if (diag && c * 32 + i > r) sv = -INFINITY;
+                        m4[i & 3] = fmaxf(m4[i & 3], sv);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(S2_EMPTY + t));
+            }
+            if (!ok) break;
+            // ---- pass 2: P = exp2((S - m) * scale * log2 e) -> shared memory, row sums
+            const float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            const float mc = m * p.scale_log2e;
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (!(ok = wait_all(S2_FULL + t, s_phase, 82u))) break;
+                s_phase ^= 1;
+                if (!(ok = wait_all(P2_EMPTY + t, pe_phase, 83u))) break;     // the previous P V has read the P tile
+                pe_phase ^= 1;
+                tc_fence_after();
+                const bool diag = p.causal && j == qt;
+                auto process = [&](const unsigned* v, int c) {
+                    float e[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float sv = __uint_as_float(v[i]);
+                        if (diag && c * 32 + i > r) sv = -INFINITY;
+                        e[i] = ex2_approx(fmaf(sv, p.scale_log2e, -mc));
+                        l4[i & 3] += e[i];
+                    }
+                    unsigned char* row = p_tile + (c >> 1) * AT_PANEL + r * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 o;
+                        o.x = pack2<T>(e[8 * q + 0], e[8 * q + 1]);
+                        o.y = pack2<T>(e[8 * q + 2], e[8 * q + 3]);
+                        o.z = pack2<T>(e[8 * q + 4], e[8 * q + 5]);
+                        o.w = pack2<T>(e[8 * q + 6], e[8 * q + 7]);
+                        const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(row + chunk * 16) = o;
+                    }
+                };
+                unsigned va[32], vb[32];
+                tmem_ld_32x32(s_addr, va);
+                tmem_ld_wait();
+                tmem_ld_32x32(s_addr + 32u, vb);
+                process(va, 0);
+                tmem_ld_wait();
+                tmem_ld_32x32(s_addr + 64u, va);
+                process(vb, 1);
+                tmem_ld_wait();
+                tmem_ld_32x32(s_addr + 96u, vb);
+                process(va, 2);
+                tmem_ld_wait();
+                process(vb, 3);
+                tc_fence_before();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor cores
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar(P2_FULL + t));
+                    mbar_arrive(bar(S2_EMPTY + t));
+                }
+            }
+            if (!ok) break;
+            // ---- O / l -> global memory
+            if (!(ok = wait_all(O2_FULL + t, o_phase, 84u))) break;
+            o_phase ^= 1;
+            tc_fence_after();
+            const float inv = 1.0f / ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+            T* orow = O + (long long)(b / p.heads) * p.o_bs + (long long)(b % p.heads) * p.o_hs + ((long long)qt * 128 + r) * p.o_rs;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned v[32];
+                tmem_ld_32x32(o_addr + (unsigned)c * 32u, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = pack2<T>(__uint_as_float(v[8 * q + 0]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
+                    o.y = pack2<T>(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
+                    o.z = pack2<T>(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
+                    o.w = pack2<T>(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O2_EMPTY + t));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 }  // namespace
 
 bool attention_supported(DType dt, int64_t seq_q, int64_t seq_k, int64_t head_dim) {
@@ -450,22 +790,25 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     p.o_hs = D;
     p.o_bs = S * heads * D;
     p.error = dev.error_word();
-    const long long items = BH * (S / 128);
+    // two query tiles per CTA (attention_tc2_kernel) unless switched off; one per CTA otherwise
+    const bool pairs = !getenv("WGF_ATT_SINGLE");
+    const long long items = pairs ? BH * ((S / 128 + 1) / 2) : BH * (S / 128);
     const unsigned grid = (unsigned)std::min<long long>(items, dev.sm_count);
-    static bool attr_set[2] = {false, false};
+    static bool attr_set[4] = {false, false, false, false};
+    auto launch = [&](auto kernel, int slot, int threads, int smem_bytes, auto* optr) {
+        if (!attr_set[slot]) {
+            WGF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+            attr_set[slot] = true;
+        }
+        kernel<<<grid, threads, smem_bytes, dev.stream>>>(mq, mk, mv, optr, p);
+    };
     dev.begin_launch("attention_tc");
-    if (bf16) {
-        if (!attr_set[1]) {
-            WGF_CUDA(cudaFuncSetAttribute(attention_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
-            attr_set[1] = true;
-        }
-        attention_tc_kernel<__nv_bfloat16><<<grid, AT_THREADS, AT_SMEM, dev.stream>>>(mq, mk, mv, (__nv_bfloat16*)out.base_ptr(), p);
+    if (pairs) {
+        if (bf16) launch(attention_tc2_kernel<__nv_bfloat16>, 3, A2_THREADS, A2_SMEM, (__nv_bfloat16*)out.base_ptr());
+        else launch(attention_tc2_kernel<__half>, 2, A2_THREADS, A2_SMEM, (__half*)out.base_ptr());
     } else {
-        if (!attr_set[0]) {
-            WGF_CUDA(cudaFuncSetAttribute(attention_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
-            attr_set[0] = true;
-        }
-        attention_tc_kernel<__half><<<grid, AT_THREADS, AT_SMEM, dev.stream>>>(mq, mk, mv, (__half*)out.base_ptr(), p);
+        if (bf16) launch(attention_tc_kernel<__nv_bfloat16>, 1, AT_THREADS, AT_SMEM, (__nv_bfloat16*)out.base_ptr());
+        else launch(attention_tc_kernel<__half>, 0, AT_THREADS, AT_SMEM, (__half*)out.base_ptr());
     }
     dev.end_launch();
     return out;
