@@ -59,6 +59,37 @@ def test_fused_attention_large_scores_and_scale(wgf, dev):
     assert normwise(out, reference(q, k, v, True, 0.25)) <= 1e-2
 
 
+def test_fused_attention_growing_maxima(wgf, dev):
+    """Keys whose norm grows along the sequence: the row maxima keep growing from key tile to key
+    tile, so the one-pass kernel has to rescale its accumulators again and again."""
+    g = seeded(5, 6)
+    n, seq = 3, 1024
+    q = g.standard_normal((n, seq, 128), dtype=np.float32)
+    k = g.standard_normal((n, seq, 128), dtype=np.float32) * (1 + 7 * np.arange(seq, dtype=np.float32) / seq)[None, :, None]
+    # every query looks a little along every key direction it will meet, so later keys score higher
+    q = (q + 0.5 * np.sign(k.mean(axis=1, keepdims=True))).astype(np.float16)
+    k = (k + 0.5 * np.sign(k.mean(axis=1, keepdims=True)) * (1 + 7 * np.arange(seq, dtype=np.float32) / seq)[None, :, None]).astype(np.float16)
+    v = g.standard_normal((n, seq, 128), dtype=np.float32).astype(np.float16)
+    for causal in (True, False):
+        out = dev.tensor(q).attention(dev.tensor(k), dev.tensor(v), causal=causal, scale=0.5).as_slice()
+        assert np.isfinite(out.astype(np.float32)).all()
+        assert normwise(out, reference(q, k, v, causal, 0.5)) <= 1e-2
+
+
+@pytest.mark.parametrize("variant", ["WGF_ATT_TWO_PASS", "WGF_ATT_SINGLE"])
+@pytest.mark.parametrize("n,seq", [(3, 256), (2, 640), (5, 1024)])
+def test_fused_attention_other_kernel_variants(n, seq, variant, wgf, dev, monkeypatch):
+    """The variants kept beside the default (two query tiles per CTA, one pass): the same pair
+    kernel with two passes (exact maxima first), and the kernel with one query tile per CTA."""
+    monkeypatch.setenv(variant, "1")
+    g = seeded(5, 7)
+    q, k, v = (g.standard_normal((n, seq, 128), dtype=np.float32) for _ in range(3))
+    q, k, v = (q * 3).astype(np.float16), (k * 3).astype(np.float16), v.astype(np.float16)
+    for causal in (True, False):
+        out = dev.tensor(q).attention(dev.tensor(k), dev.tensor(v), causal=causal).as_slice()
+        assert normwise(out, reference(q, k, v, causal, 1 / np.sqrt(128))) <= 1e-2
+
+
 def test_fused_attention_bf16_and_strided_views(wgf, dev):
     g = seeded(5, 5)
     n, seq = 6, 256

@@ -5,6 +5,12 @@
 // from its primitives the same result takes a batched matmul, a softmax kernel and a second
 // batched matmul with two round trips of the score matrix through memory.
 //
+// Two kernels.  The default, attention_tc2_kernel (further down), gives a CTA two adjacent query
+// tiles at a time and makes one pass over the keys (online softmax); attention_tc_kernel, the
+// first version, gives it one query tile and makes two passes.  Both are described where they
+// are defined; WGF_ATT_SINGLE=1 selects the first, WGF_ATT_TWO_PASS=1 the two-pass form of the
+// default.  What follows describes attention_tc_kernel.
+//
 // One persistent CTA per SM walks (batch*head, 128-row query tile) work items in the order of
 // decode_item (heaviest first when causal, K / V sharing through L2 otherwise).
 // Key/value tiles are 128 rows.  Two passes over the keys of an item:
@@ -43,6 +49,7 @@ constexpr int AT_TILE = 2 * AT_PANEL;      // a [128 x 128] 16-bit tile: 32 KiB
 constexpr int AT_SMEM = (2 + AT_STAGES) * AT_TILE + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int AT_THREADS = 192;
 constexpr unsigned AT_S_COLS = 128, AT_O_COL0 = 256;
+constexpr float AT_LAG = 8.f;              // how far (in powers of two) a row maximum may outgrow its reference
 
 struct AtParams {
     int n_q_tiles, n_k_tiles;
@@ -404,6 +411,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // between them, so one tile's tensor work fills the time the other spends in its softmax.
 // Tensor memory: S of tile t in columns 128 t, O in 256 + 128 t.  Shared memory: 2 Q + 2 P tiles
 // and a 3-stage ring (224 KiB).  Causal: the first tile of the pair needs one key tile less.
+// Measured, f16 causal [256, 2048, 128]: one query tile per CTA, two passes 640 us; two tiles, two
+// passes 594 us; two tiles, one pass 535 us (the one pass alone, with one tile per CTA, was slower
+// than two passes: 773 us - it lengthens the chain that the second tile is there to hide).
 // ---------------------------------------------------------------------------------------
 constexpr int A2_STAGES = 3;
 constexpr int A2_THREADS = 320;            // TMA warp, MMA warp, 2 x 4 softmax warps
@@ -424,7 +434,8 @@ __device__ __forceinline__ void decode_pair(const AtParams& p, int n_pairs, long
     }
 }
 
-template <typename T>
+// ONLINE: one pass over the keys with a lazily updated reference maximum (see below) instead of two.
+template <typename T, bool ONLINE>
 __global__ void __launch_bounds__(A2_THREADS, 1)
 attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, T* __restrict__ O, const __grid_constant__ AtParams p) {
@@ -500,7 +511,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     tma_load_3d(qs + AT_PANEL, &map_q, bar(Q2_FULL + t), 64, (2 * pt + t) * 128, b);
                 }
                 // the order below is the order in which the MMA warp consumes the ring
-                for (int j = 0; j < n_max && ok; ++j) ok = push(&map_k, j * 128, b);
+                if (!ONLINE)
+                    for (int j = 0; j < n_max && ok; ++j) ok = push(&map_k, j * 128, b);
                 for (int j = 0; j < n_max && ok; ++j) {
                     ok = push(&map_k, j * 128, b);
                     if (ok && j > 0) ok = push(&map_v, (j - 1) * 128, b);
@@ -592,8 +604,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 if (!ok) break;
                 tc_fence_after();
-                for (int j = 0; j < n_max && ok; ++j) ok = issue_s(j, false);   // pass 1
-                for (int j = 0; j < n_max && ok; ++j) {                          // pass 2
+                if (!ONLINE)
+                    for (int j = 0; j < n_max && ok; ++j) ok = issue_s(j, false);   // pass 1
+                for (int j = 0; j < n_max && ok; ++j) {                          // pass 2, or the only pass
                     ok = issue_s(j, true);
                     if (ok && j > 0) ok = issue_pv(j - 1);
                 }
@@ -622,6 +635,114 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const int n_kv = tiles_of(pt, t);
             if (n_kv == 0) continue;                         // an odd tile count: the last pair has one tile
             const int qt = 2 * pt + t;
+            float l_run = 0.f;
+            if constexpr (ONLINE) {
+            // Online softmax.  Every row keeps a reference maximum `ref` (scores times scale*log2 e);
+            // P = exp2(s*c - ref).  `ref` follows the running maximum only when that has grown by
+            // more than AT_LAG since `ref` was set; then O and l of the row are multiplied by
+            // exp2(ref_old - ref_new).  In between P simply exceeds 1 (by at most 2^AT_LAG, which
+            // 16-bit P and the fp32 accumulators hold easily), so after the first key tile a rescale
+            // of O, a round trip of its row through tensor memory, is rare.
+            float ref = 0.f;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (!(ok = wait_all(S2_FULL + t, s_phase, 82u))) break;
+                s_phase ^= 1;
+                tc_fence_after();
+                const bool diag = p.causal && j == qt;
+                // sweep 1: maximum of the row of this tile (four chains)
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+                for (int c = 0; c < 4; c += 2) {
+                    unsigned v[64];
+                    tmem_ld_32x32(s_addr + (unsigned)c * 32u, v);
+                    tmem_ld_32x32(s_addr + (unsigned)(c + 1) * 32u, v + 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        float sv = __uint_as_float(v[i]);
+                        if (diag && c * 32 + i > r) sv = -INFINITY;
+                        m4[i & 3] = fmaxf(m4[i & 3], sv);
+                    }
+                }
+                const float mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2e;
+                // (key 0 is visible to every query, so the first tile gives every row a finite maximum)
+                const bool grow = j > 0 && mt > ref + AT_LAG;
+                float alpha = 1.f;
+                if (j == 0) ref = mt;
+                if (grow) {
+                    alpha = ex2_approx(ref - mt);
+                    ref = mt;
+                }
+                const bool any_grow = __any_sync(0xffffffffu, grow);
+                // sweep 2: P, kept in registers until the previous P V has released the P tile
+                unsigned e[64];
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                auto process = [&](const unsigned* v, int c) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+                        if (diag && c * 32 + i > r) s0 = -INFINITY;
+                        if (diag && c * 32 + i + 1 > r) s1 = -INFINITY;
+                        const float e0 = ex2_approx(fmaf(s0, p.scale_log2e, -ref));
+                        const float e1 = ex2_approx(fmaf(s1, p.scale_log2e, -ref));
+                        l4[i & 2] += e0;
+                        l4[(i & 2) + 1] += e1;
+                        e[c * 16 + (i >> 1)] = pack2<T>(e0, e1);
+                    }
+                };
+                {
+                    unsigned va[32], vb[32];
+                    tmem_ld_32x32(s_addr, va);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 32u, vb);
+                    process(va, 0);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 64u, va);
+                    process(vb, 1);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 96u, vb);
+                    process(va, 2);
+                    tmem_ld_wait();
+                    process(vb, 3);
+                }
+                l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+                // the scores are in registers: S can take this tile's next key tile
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(S2_EMPTY + t));
+                if (!(ok = wait_all(P2_EMPTY + t, pe_phase, 83u))) break;     // the previous P V is done: O is at rest, P is free
+                pe_phase ^= 1;
+                if (any_grow) {
+                    // rescale this warp's 32 rows of O (lanes whose maximum did not grow multiply by 1)
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        unsigned o[32];
+                        tmem_ld_32x32(o_addr + (unsigned)c * 32u, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32(o_addr + (unsigned)c * 32u, o);
+                    }
+                    tmem_st_wait();
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    unsigned char* row = p_tile + (c >> 1) * AT_PANEL + r * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(row + chunk * 16) =
+                            make_uint4(e[c * 16 + 4 * q], e[c * 16 + 4 * q + 1], e[c * 16 + 4 * q + 2], e[c * 16 + 4 * q + 3]);
+                    }
+                }
+                tc_fence_before();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor cores
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(P2_FULL + t));
+            }
+            if (!ok) break;
+            } else {
             // ---- pass 1: row maximum of the raw scores (four independent chains)
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             for (int j = 0; j < n_kv && ok; ++j) {
@@ -701,11 +822,13 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
             }
             if (!ok) break;
+            l_run = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            }
             // ---- O / l -> global memory
             if (!(ok = wait_all(O2_FULL + t, o_phase, 84u))) break;
             o_phase ^= 1;
             tc_fence_after();
-            const float inv = 1.0f / ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+            const float inv = 1.0f / l_run;
             T* orow = O + (long long)(b / p.heads) * p.o_bs + (long long)(b % p.heads) * p.o_hs + ((long long)qt * 128 + r) * p.o_rs;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -794,7 +917,7 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     const bool pairs = !getenv("WGF_ATT_SINGLE");
     const long long items = pairs ? BH * ((S / 128 + 1) / 2) : BH * (S / 128);
     const unsigned grid = (unsigned)std::min<long long>(items, dev.sm_count);
-    static bool attr_set[4] = {false, false, false, false};
+    static bool attr_set[6] = {false, false, false, false, false, false};
     auto launch = [&](auto kernel, int slot, int threads, int smem_bytes, auto* optr) {
         if (!attr_set[slot]) {
             WGF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -804,8 +927,14 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     };
     dev.begin_launch("attention_tc");
     if (pairs) {
-        if (bf16) launch(attention_tc2_kernel<__nv_bfloat16>, 3, A2_THREADS, A2_SMEM, (__nv_bfloat16*)out.base_ptr());
-        else launch(attention_tc2_kernel<__half>, 2, A2_THREADS, A2_SMEM, (__half*)out.base_ptr());
+        const bool online = !getenv("WGF_ATT_TWO_PASS");   // one pass (online softmax) unless switched off
+        if (online) {
+            if (bf16) launch(attention_tc2_kernel<__nv_bfloat16, true>, 5, A2_THREADS, A2_SMEM, (__nv_bfloat16*)out.base_ptr());
+            else launch(attention_tc2_kernel<__half, true>, 4, A2_THREADS, A2_SMEM, (__half*)out.base_ptr());
+        } else {
+            if (bf16) launch(attention_tc2_kernel<__nv_bfloat16, false>, 3, A2_THREADS, A2_SMEM, (__nv_bfloat16*)out.base_ptr());
+            else launch(attention_tc2_kernel<__half, false>, 2, A2_THREADS, A2_SMEM, (__half*)out.base_ptr());
+        }
     } else {
         if (bf16) launch(attention_tc_kernel<__nv_bfloat16>, 1, AT_THREADS, AT_SMEM, (__nv_bfloat16*)out.base_ptr());
         else launch(attention_tc_kernel<__half>, 0, AT_THREADS, AT_SMEM, (__half*)out.base_ptr());
