@@ -33,6 +33,7 @@
 // error word instead of hanging.
 #include <algorithm>
 #include <cmath>
+#include <type_traits>
 
 #include "attention.hpp"
 #include "tc_common.cuh"
@@ -649,62 +650,70 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 s_phase ^= 1;
                 tc_fence_after();
                 const bool diag = p.causal && j == qt;
-                // sweep 1: maximum of the row of this tile (four chains)
-                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-                for (int c = 0; c < 4; c += 2) {
-                    unsigned v[64];
-                    tmem_ld_32x32(s_addr + (unsigned)c * 32u, v);
-                    tmem_ld_32x32(s_addr + (unsigned)(c + 1) * 32u, v + 32);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        float sv = __uint_as_float(v[i]);
-                        if (diag && c * 32 + i > r) sv = -INFINITY;
-                        m4[i & 3] = fmaxf(m4[i & 3], sv);
-                    }
-                }
-                const float mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2e;
-                // (key 0 is visible to every query, so the first tile gives every row a finite maximum)
-                const bool grow = j > 0 && mt > ref + AT_LAG;
+                // Both sweeps in two instantiations: only the key tile on the diagonal of a causal item
+                // carries the mask tests.
                 float alpha = 1.f;
-                if (j == 0) ref = mt;
-                if (grow) {
-                    alpha = ex2_approx(ref - mt);
-                    ref = mt;
-                }
-                const bool any_grow = __any_sync(0xffffffffu, grow);
-                // sweep 2: P, kept in registers until the previous P V has released the P tile
+                bool any_grow = false;
                 unsigned e[64];
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
-                auto process = [&](const unsigned* v, int c) {
+                auto sweeps = [&](auto is_diag) {
+                    constexpr bool DIAG = decltype(is_diag)::value;
+                    // sweep 1: maximum of the row of this tile (four chains)
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+                    for (int c = 0; c < 4; c += 2) {
+                        unsigned v[64];
+                        tmem_ld_32x32(s_addr + (unsigned)c * 32u, v);
+                        tmem_ld_32x32(s_addr + (unsigned)(c + 1) * 32u, v + 32);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-                        if (diag && c * 32 + i > r) s0 = -INFINITY;
-                        if (diag && c * 32 + i + 1 > r) s1 = -INFINITY;
-                        const float e0 = ex2_approx(fmaf(s0, p.scale_log2e, -ref));
-                        const float e1 = ex2_approx(fmaf(s1, p.scale_log2e, -ref));
-                        l4[i & 2] += e0;
-                        l4[(i & 2) + 1] += e1;
-                        e[c * 16 + (i >> 1)] = pack2<T>(e0, e1);
+                        for (int i = 0; i < 64; ++i) {
+                            float sv = __uint_as_float(v[i]);
+                            if (DIAG && c * 32 + i > r) sv = -INFINITY;
+                            m4[i & 3] = fmaxf(m4[i & 3], sv);
+                        }
+                    }
+                    const float mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2e;
+                    // (key 0 is visible to every query, so the first tile gives every row a finite maximum)
+                    const bool grow = j > 0 && mt > ref + AT_LAG;
+                    if (j == 0) ref = mt;
+                    if (grow) {
+                        alpha = ex2_approx(ref - mt);
+                        ref = mt;
+                    }
+                    any_grow = __any_sync(0xffffffffu, grow);
+                    // sweep 2: P, kept in registers until the previous P V has released the P tile
+                    auto process = [&](const unsigned* v, int c) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+                            if (DIAG && c * 32 + i > r) s0 = -INFINITY;
+                            if (DIAG && c * 32 + i + 1 > r) s1 = -INFINITY;
+                            const float e0 = ex2_approx(fmaf(s0, p.scale_log2e, -ref));
+                            const float e1 = ex2_approx(fmaf(s1, p.scale_log2e, -ref));
+                            l4[i & 2] += e0;
+                            l4[(i & 2) + 1] += e1;
+                            e[c * 16 + (i >> 1)] = pack2<T>(e0, e1);
+                        }
+                    };
+                    {
+                        unsigned va[32], vb[32];
+                        tmem_ld_32x32(s_addr, va);
+                        tmem_ld_wait();
+                        tmem_ld_32x32(s_addr + 32u, vb);
+                        process(va, 0);
+                        tmem_ld_wait();
+                        tmem_ld_32x32(s_addr + 64u, va);
+                        process(vb, 1);
+                        tmem_ld_wait();
+                        tmem_ld_32x32(s_addr + 96u, vb);
+                        process(va, 2);
+                        tmem_ld_wait();
+                        process(vb, 3);
                     }
                 };
-                {
-                    unsigned va[32], vb[32];
-                    tmem_ld_32x32(s_addr, va);
-                    tmem_ld_wait();
-                    tmem_ld_32x32(s_addr + 32u, vb);
-                    process(va, 0);
-                    tmem_ld_wait();
-                    tmem_ld_32x32(s_addr + 64u, va);
-                    process(vb, 1);
-                    tmem_ld_wait();
-                    tmem_ld_32x32(s_addr + 96u, vb);
-                    process(va, 2);
-                    tmem_ld_wait();
-                    process(vb, 3);
-                }
+                if (diag) sweeps(std::true_type{});
+                else sweeps(std::false_type{});
                 l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
                 // the scores are in registers: S can take this tile's next key tile
                 tc_fence_before();
