@@ -52,6 +52,10 @@ std::string instr_expr(const Instr& in, const std::string& a, const std::string&
             if (in.op == WGF_OP_SQR) return rounded(in.dtype, "(" + a + " * " + a + ")");
             if (in.op == WGF_OP_NEG) return "(-" + a + ")";
             if (in.op == WGF_OP_ABS) return "fabsf(" + a + ")";
+            // exp of a 16-bit tensor: its result is rounded to 11 (8) bits anyway, so the two-instruction
+            // form (error about 1e-6 relative) gives the same 16-bit value as expf except where the
+            // exact result lies within that distance of a rounding boundary
+            if (in.op == WGF_OP_EXP && in.dtype != DType::F32) return rounded(in.dtype, "op_exp16(" + a + ")");
             return rounded(in.dtype, std::string(unary_fn(in.op)) + "(" + a + ")");
         case IKind::Scalar: {
             std::string c = "imm[" + std::to_string(in.slot) + "]";
