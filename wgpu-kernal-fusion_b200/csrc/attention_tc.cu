@@ -59,6 +59,10 @@ struct AtParams {
     int is_bf16;
     float scale_log2e;
     int heads;               // batch*heads index n = batch * heads + head
+    // V read in place from a [batch, seq, heads * 128] projection (v_heads > 0): its tensor map is
+    // {128, batch * seq, heads}, so item b = batch * v_heads + head finds its rows at
+    // (b / v_heads) * v_rows + row and its head at b % v_heads.  v_heads == 0: V is [n, seq, 128].
+    int v_heads, v_rows;
     long long o_rs, o_hs, o_bs;   // output row / head / batch stride in elements
     unsigned* error;         // device word: 0 = ok, else code of the wait that gave up
 };
@@ -123,6 +127,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const unsigned tmem_base = *tmem_slot;
 
     const long long items = (long long)p.bh * p.n_q_tiles;
+    auto v_row = [&](int row0, int b) { return p.v_heads > 0 ? (b / p.v_heads) * p.v_rows + row0 : row0; };
+    auto v_slab = [&](int b) { return p.v_heads > 0 ? b % p.v_heads : b; };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -161,9 +167,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int j = 0; j < n_kv && ok; ++j) ok = push(&map_k, j * 128, b);
                 for (int j = 0; j < n_kv && ok; ++j) {
                     ok = push(&map_k, j * 128, b);
-                    if (ok && j > 0) ok = push(&map_v, (j - 1) * 128, b);
+                    if (ok && j > 0) ok = push(&map_v, v_row((j - 1) * 128, b), v_slab(b));
                 }
-                if (ok) ok = push(&map_v, (n_kv - 1) * 128, b);
+                if (ok) ok = push(&map_v, v_row((n_kv - 1) * 128, b), v_slab(b));
             }
         }
     } else if (warp == 1) {
@@ -466,6 +472,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     const int n_pairs = (p.n_q_tiles + 1) / 2;
     const long long items = (long long)p.bh * n_pairs;
+    auto v_row = [&](int row0, int b) { return p.v_heads > 0 ? (b / p.v_heads) * p.v_rows + row0 : row0; };
+    auto v_slab = [&](int b) { return p.v_heads > 0 ? b % p.v_heads : b; };
     // key tiles of tile t of pair pt (0: the pair has no second tile)
     auto tiles_of = [&](int pt, int t) -> int {
         const int qt = 2 * pt + t;
@@ -516,9 +524,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (int j = 0; j < n_max && ok; ++j) ok = push(&map_k, j * 128, b);
                 for (int j = 0; j < n_max && ok; ++j) {
                     ok = push(&map_k, j * 128, b);
-                    if (ok && j > 0) ok = push(&map_v, (j - 1) * 128, b);
+                    if (ok && j > 0) ok = push(&map_v, v_row((j - 1) * 128, b), v_slab(b));
                 }
-                if (ok) ok = push(&map_v, (n_max - 1) * 128, b);
+                if (ok) ok = push(&map_v, v_row((n_max - 1) * 128, b), v_slab(b));
             }
         }
     } else if (warp == 1) {
@@ -876,7 +884,12 @@ bool attention_supported(DType dt, int64_t seq_q, int64_t seq_k, int64_t head_di
 
 TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& k_in, const TensorData& v_in, bool causal,
                          float scale, int merge_heads) {
-    WGF_CHECK(q_in.layout.rank() == 3 && k_in.layout.shape == q_in.layout.shape && v_in.layout.shape == q_in.layout.shape,
+    // v may also come as the [batch, heads, seq, 128] view of a [batch, seq, heads * 128] projection
+    const bool v_view = v_in.layout.rank() == 4;
+    WGF_CHECK(q_in.layout.rank() == 3 && k_in.layout.shape == q_in.layout.shape &&
+                  (v_view ? v_in.layout.shape[0] * v_in.layout.shape[1] == q_in.layout.shape[0] &&
+                                v_in.layout.shape[2] == q_in.layout.shape[1] && v_in.layout.shape[3] == q_in.layout.shape[2]
+                          : v_in.layout.shape == q_in.layout.shape),
               WGF_ERR_SHAPE, "attention takes q, k, v of one shape [batch*heads, seq, 128]");
     WGF_CHECK(q_in.dtype == k_in.dtype && q_in.dtype == v_in.dtype, WGF_ERR_DTYPE, "attention operands differ in element type");
     const int64_t BH = q_in.layout.shape[0], S = q_in.layout.shape[1], D = q_in.layout.shape[2];
@@ -893,7 +906,24 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     };
     TensorData q = usable(q_in) ? q_in : run_compact(dev, q_in);
     TensorData k = usable(k_in) ? k_in : run_compact(dev, k_in);
-    TensorData v = usable(v_in) ? v_in : run_compact(dev, v_in);
+    TensorData v = v_in;
+    int v_heads = 0;
+    if (v_view) {
+        // readable in place if batch folds into the row axis: stride(batch) == seq * stride(row)
+        const Layout& l = v_in.layout;
+        const bool in_place = l.strides[3] == 1 && l.strides[2] % 8 == 0 && l.strides[1] % 8 == 0 && l.strides[2] >= l.shape[3] &&
+                              l.strides[0] == l.shape[2] * l.strides[2] && ((uintptr_t)v_in.base_ptr() & 15) == 0 &&
+                              l.shape[0] * l.shape[2] < (1ll << 31);
+        if (in_place) {
+            v_heads = (int)l.shape[1];
+        } else {
+            v = run_compact(dev, v_in);
+            v.layout = Layout::contiguous({BH, S, D});
+            v.layout.offset = 0;
+        }
+    } else if (!usable(v_in)) {
+        v = run_compact(dev, v_in);
+    }
     for (const TensorData* t : {&q, &k, &v}) dev.wait_for(*t->buf);
     TensorData out;
     out.dtype = q.dtype;
@@ -909,7 +939,9 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     CUtensorMap mq, mk, mv;
     const bool maps_ok = encode_3d(&mq, bf16, q.base_ptr(), D, S, BH, q.layout.strides[1], q.layout.strides[0], 64, 128) &&
                          encode_3d(&mk, bf16, k.base_ptr(), D, S, BH, k.layout.strides[1], k.layout.strides[0], 64, 128) &&
-                         encode_3d(&mv, bf16, v.base_ptr(), D, S, BH, v.layout.strides[1], v.layout.strides[0], 64, 128);
+                         (v_heads > 0 ? encode_3d(&mv, bf16, v.base_ptr(), D, v.layout.shape[0] * S, v_heads, v.layout.strides[2],
+                                                  v.layout.strides[1], 64, 128)
+                                      : encode_3d(&mv, bf16, v.base_ptr(), D, S, BH, v.layout.strides[1], v.layout.strides[0], 64, 128));
     WGF_CHECK(maps_ok, WGF_ERR_CUDA, "attention: tensor map creation failed");
     AtParams p{};
     p.n_q_tiles = p.n_k_tiles = (int)(S / 128);
@@ -918,6 +950,8 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     p.is_bf16 = bf16 ? 1 : 0;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.heads = (int)heads;
+    p.v_heads = v_heads;
+    p.v_rows = (int)S;
     p.o_rs = heads * D;
     p.o_hs = D;
     p.o_bs = S * heads * D;

@@ -454,18 +454,20 @@ NodeRef op_llama_block(const NodeRef& x, const NodeRef& wq, const NodeRef& wk, c
     };
     NodeRef q = rope_heads(linear(n1, wq));
     NodeRef k = rope_heads(linear(n1, wk));
-    NodeRef v = split_heads(linear(n1, wv));
+    NodeRef v_proj = linear(n1, wv);
     const float scale = 1.0f / std::sqrt((float)D);
     NodeRef merged;
     if (!mask && attention_supported(x->dtype, S, S, D)) {
-        // the fused kernel writes the heads side by side: [B, S, heads * D] without a merging copy
-        NodeRef att = new_node(NodeKind::Attention, x->dev, {B, S, Hd}, x->dtype, {q, k, v});
+        // The fused kernel reads V in place through the [B, heads, S, D] view of the projection (no
+        // head-splitting copy) and writes the heads side by side: [B, S, heads * D] (no merging copy).
+        NodeRef v4 = view_transpose(op_reshape(v_proj, {B, S, (int64_t)n_heads, D}), 1, 2);
+        NodeRef att = new_node(NodeKind::Attention, x->dev, {B, S, Hd}, x->dtype, {q, k, v4});
         att->imm = scale;
         att->axis = 1;
         att->new_shape = {(int64_t)n_heads};
         merged = op_reshape(att, {B * S, Hd});
     } else {
-        NodeRef ctx = op_attention(q, k, v, mask, true, scale);  // [B*heads, S, D]
+        NodeRef ctx = op_attention(q, k, split_heads(v_proj), mask, true, scale);  // [B*heads, S, D]
         merged = op_reshape(view_transpose(op_reshape(ctx, {B, (int64_t)n_heads, S, D}), 1, 2), {B * S, Hd});
     }
     NodeRef h = make_binary(x2, linear(merged, wo), WGF_OP_ADD);
