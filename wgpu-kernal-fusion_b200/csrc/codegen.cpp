@@ -55,7 +55,7 @@ std::string instr_expr(const Instr& in, const std::string& a, const std::string&
             // exp of a 16-bit tensor: its result is rounded to 11 (8) bits anyway, so the two-instruction
             // form (error about 1e-6 relative) gives the same 16-bit value as expf except where the
             // exact result lies within that distance of a rounding boundary
-            if (in.op == WGF_OP_EXP && in.dtype != DType::F32) return rounded(in.dtype, "op_exp16(" + a + ")");
+            if (in.op == WGF_OP_EXP && (in.dtype != DType::F32 || in.approx)) return rounded(in.dtype, "op_exp_sfu(" + a + ")");
             return rounded(in.dtype, std::string(unary_fn(in.op)) + "(" + a + ")");
         case IKind::Scalar: {
             std::string c = "imm[" + std::to_string(in.slot) + "]";
@@ -478,7 +478,9 @@ void replace_all(std::string& text, const std::string& marker, const std::string
     }
 }
 
-std::string row_source(const Program& prog, const RowConfig& c) {
+std::string row_source(const Program& prog_in, const RowConfig& c) {
+    Program prog = prog_in;
+    prog.mark_sum_only();   // exps that only feed sums
     std::ostringstream s;
     s << prelude();
     s << "#define RO " << c.RO << "\n#define NIN " << prog.n_slots() << "\n#define C " << c.C
@@ -614,7 +616,9 @@ struct StreamConfig {
     std::vector<int> mode;
 };
 
-std::string stream_source(const Program& prog, const StreamConfig& c) {
+std::string stream_source(const Program& prog_in, const StreamConfig& c) {
+    Program prog = prog_in;
+    prog.mark_sum_only();   // exps that only feed sums
     const int n = (int)prog.ins.size();
     std::vector<char> dep(n, 0);
     for (int i = 0; i < n; ++i) {
@@ -716,7 +720,9 @@ struct ColConfig {
     std::vector<char> is_row;   // per slot: does not vary along the reduced axis
 };
 
-std::string col_source(const Program& prog, const ColConfig& c) {
+std::string col_source(const Program& prog_in, const ColConfig& c) {
+    Program prog = prog_in;
+    prog.mark_sum_only();   // exps that only feed sums
     const int n = (int)prog.ins.size();
     std::vector<char> dep(n, 0);
     for (int i = 0; i < n; ++i) {

@@ -22,6 +22,10 @@ struct Instr {
     int slot = -1;     // Load: input slot; Scalar: index into imms
     DType dtype = DType::F32;
     VKind vk = VKind::Elem;
+    // Set by Program::mark_sum_only for an f32 exp whose value nothing can observe except through
+    // sums: it may be computed as 2^(x * log2 e) by the special-function unit (about 1e-6
+    // relative, |x| * 6e-8 more for large |x|), well inside the 1e-5 bound of a reduction.
+    bool approx = false;
 };
 
 // A companion output of a row kernel: Elem value `a` reduced with `op` over the WHOLE index
@@ -48,6 +52,28 @@ struct Program {
     uint16_t result_ar_op = 0;
 
     int n_slots() const { return (int)slot_dtype.size(); }
+    // Marks every f32 exp that is used only as the operand of sum reductions (Instr::approx).
+    // The marks follow from the instructions, so they need no place in the signature.
+    void mark_sum_only() {
+        for (int i = 0; i < (int)ins.size(); ++i) {
+            Instr& e = ins[i];
+            e.approx = false;
+            if (e.kind != IKind::Unary || e.op != WGF_OP_EXP || e.dtype != DType::F32 || i == result) continue;
+            int uses = 0;
+            bool only_sums = true;
+            for (const Instr& u : ins) {
+                if (u.kind == IKind::Load || (u.a != i && u.b != i)) continue;
+                uses++;
+                only_sums = only_sums && u.kind == IKind::RowReduce && u.op == WGF_OP_SUM;
+            }
+            for (const Grand& g : grands)
+                if (g.a == i) {
+                    uses++;
+                    only_sums = only_sums && g.op == WGF_OP_SUM;
+                }
+            e.approx = uses > 0 && only_sums;
+        }
+    }
     DType out_dtype() const { return ins[result].dtype; }
     VKind out_kind() const { return ins[result].vk; }
     int n_reduces() const {

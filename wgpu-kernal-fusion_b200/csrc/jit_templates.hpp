@@ -30,8 +30,9 @@ DEV float rb(float x) { return b2f(f2b(x)); }
 // Unary functions.  Single-precision CUDA functions documented at <= 2 ulp are used as they
 // are; the ones documented above that (tan, sinh, asinh, acosh, atanh, pow) go through double.
 DEV float op_exp(float x) { return expf(x); }
-// for results that are rounded to a 16-bit type: 2^(x * log2 e) by the special-function unit
-DEV float op_exp16(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f)); return y; }
+// 2^(x * log2 e) by the special-function unit (about 1e-6 relative): for results that are rounded to a
+// 16-bit type, and for f32 values that only feed sums
+DEV float op_exp_sfu(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f)); return y; }
 DEV float op_exp2(float x) { return exp2f(x); }
 DEV float op_log(float x) { return logf(x); }
 DEV float op_log2(float x) { return log2f(x); }
