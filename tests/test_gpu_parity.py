@@ -520,3 +520,24 @@ def test_transposed_operands_staged_through_shared_memory(case, wgf, dev, orc):
     assert dev.launch_count - before == expected
     ref = build(orc.Ref(x), orc.Ref(y)).numpy()
     np.testing.assert_array_equal(got, ref)
+
+
+@pytest.mark.parametrize("lo,hi", [(-3.0, 3.0), (45.0, 70.0), (-85.0, -60.0), (-20.0, 20.0)])   # the sums stay finite in f32
+def test_exp_that_only_feeds_a_sum_stays_inside_the_reduction_bound(lo, hi, wgf, dev):
+    """sum(exp(x)) computes its exponentials with the two-instruction form (nothing but the sum can
+    see them); the sums must hold the 1e-5 bound of reductions over the whole range of exp, alone,
+    per row, and riding along in a row kernel."""
+    x = (seeded(2, 9).random((512, 1024), dtype=np.float32) * (hi - lo) + lo).astype(np.float32)
+    e = np.exp(x.astype(np.float64))
+    t = dev.tensor(x)
+    assert_rel(t.exp().sum(0).sum(0).as_slice(), np.float64(e.sum()), 1e-5)
+    assert_rel(t.exp().sum(1).as_slice(), e.sum(1), 1e-5)
+    assert_rel(t.exp().sum(0).as_slice(), e.sum(0), 1e-5)
+    y, s = t.softmax_last_dim(), t.exp().sum(0).sum(0)
+    wgf.Tensor.materialize_all([y, s])
+    assert_rel(s.as_slice(), np.float64(e.sum()), 1e-5)
+    # an exp that is also an output keeps the 2-ulp function
+    both = t.exp()
+    tot = both.sum(1)
+    wgf.Tensor.materialize_all([both, tot])
+    assert np.array_equal(both.as_slice(), dev.tensor(x).exp().as_slice())
