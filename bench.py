@@ -5,14 +5,15 @@
 Workload (one step, per GPU): x = f32 [8192, 4096] N(0,1) resident in HBM, w = f32 [4096] N(1, 0.1);
   y = softmax_rows(rms_norm(x, w, eps 1e-5))      268 451 840 algorithmic bytes
   s = sum(exp(x)) over the whole tensor            134 217 728 algorithmic bytes
-      (+ an NCCL all-reduce of the per-GPU scalar when N > 1: rows are sharded, weak scaling)
+      (+ an all-reduce of the per-GPU scalar when N > 1, done by the same kernel over peer memory,
+       NCCL as the fallback: rows are sharded, weak scaling)
 Both results are requested together, so one fused row kernel computes y and, from the same registers,
 the partial sums of s: x is read from HBM once.  --separate-kernels requests them one by one (row
 kernel, then a streaming reduce), which is all the reference's one-tensor-per-call API can express.
 Inputs are synthetic (seeded PCG64).  Four input buffers are rotated so that every step reads x
 from HBM, not from L2.  `value` = algorithmic bytes of all ranks / device time (CUDA events on the
 library's stream, max over ranks).  `e2e` = the same metric through the public C ABI with HOST
-buffers: upload of x from pinned memory, both kernels, download of y and s, every step.
+buffers: upload of x from pinned memory, the kernel, download of y and s, every step.
 
 `--impl reference` times the CPU restatement of the reference's math (oracle/oracle.c, fast mode:
 float + libm, one memory pass per kernel the reference's resolver would launch, all host threads).
