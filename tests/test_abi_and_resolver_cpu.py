@@ -312,3 +312,33 @@ def test_recording_never_overwrites_its_inputs(wgf, drydev):
 
     assert result_ptr_equals_input_ptr(False)
     assert not result_ptr_equals_input_ptr(True)
+
+
+def test_exp_form_follows_who_can_see_the_value(tmp_path):
+    """Generated source: an f32 exp seen only by sums uses the two-instruction form, the exp of a
+    softmax (it also reaches the output) and a plain exp keep expf, a 16-bit exp uses the short form."""
+    import subprocess
+    import sys
+    script = tmp_path / "dump.py"
+    script.write_text(
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {os.path.join(ROOT, 'tests')!r})\n"
+        "from conftest import load_package\n"
+        "wgf = load_package(); d = wgf.Device(-1)\n"
+        "x = d.tensor(np.zeros((64, 512), np.float32)); h = d.tensor(np.zeros((64, 512), np.float16))\n"
+        "for name, t in (('SUMEXP', lambda: x.exp().sum(0).sum(0)), ('ROWSUMEXP', lambda: (x * 0.5).exp().sum(1)),\n"
+        "                ('SOFTMAX', lambda: x.softmax_last_dim()), ('PLAIN', lambda: x.exp() * 2.0),\n"
+        "                ('HALF', lambda: h.exp() * 2.0)):\n"
+        "    print('@@', name, file=sys.stderr, flush=True); t().materialize()\n")
+    env = dict(os.environ, WGF_KERNEL_CACHE=str(tmp_path / "cache"), WGF_JIT_VERBOSE="1", WGF_DUMP_SOURCE="1")
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    parts = {}
+    for chunk in r.stderr.split("@@ ")[1:]:
+        name, _, text = chunk.partition("\n")
+        body = text.split('extern "C" __global__')[-1] if 'extern "C" __global__' in text else text
+        calls = [c for c in ("op_exp_sfu(v", "op_exp(v", "op_exp_sfu(x", "op_exp(x") if c in text.replace("DEV float op_exp", "")]
+        assert calls, f"no kernel source was generated for {name.strip()}"
+        parts[name.strip()] = (body, calls)
+    uses = {k: ("sfu" if any("sfu" in c for c in v[1]) else "expf") for k, v in parts.items()}
+    assert uses == {"SUMEXP": "sfu", "ROWSUMEXP": "sfu", "SOFTMAX": "expf", "PLAIN": "expf", "HALF": "sfu"}, uses
