@@ -302,12 +302,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)c * 32u, v);
                     tmem_ld_32x32(lane_base + (unsigned)sb * AT_S_COLS + (unsigned)(c + 1) * 32u, v + 32);
                     tmem_ld_wait();
+                    if (diag) {   // only the key tile on the diagonal carries the mask tests
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        float s = __uint_as_float(v[i]);
-                        if (diag && c * 32 + i > r) s = -INFINITY;
-                        m4[i & 3] = fmaxf(m4[i & 3], s);
+                        for (int i = 0; i < 64; ++i)
+                            if (c * 32 + i > r) v[i] = 0xff800000u;   // -inf above the diagonal
                     }
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -328,13 +329,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const bool diag = p.causal && j == qt;
                 // 32 score columns at a time; the TMEM load of the next 32 is in flight while the
                 // exponentials of the current ones are computed
-                auto process = [&](const unsigned* v, int c) {
+                auto process = [&](unsigned* v, int c) {
+                    if (diag) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i > r) v[i] = 0xff800000u;   // -inf above the diagonal: P = 0
+                    }
                     float e[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        float s = __uint_as_float(v[i]);
-                        if (diag && c * 32 + i > r) s = -INFINITY;
-                        e[i] = ex2_approx(fmaf(s, p.scale_log2e, -mc));
+                        e[i] = ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2e, -mc));
                         l4[i & 3] += e[i];
                     }
                     // A-operand layout (K-major, 128-byte swizzle): row r of panel c/2 is 128 bytes
@@ -773,12 +777,13 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     tmem_ld_32x32(s_addr + (unsigned)c * 32u, v);
                     tmem_ld_32x32(s_addr + (unsigned)(c + 1) * 32u, v + 32);
                     tmem_ld_wait();
+                    if (diag) {   // only the key tile on the diagonal carries the mask tests
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        float sv = __uint_as_float(v[i]);
-                        if (diag && c * 32 + i > r) sv = -INFINITY;
-                        m4[i & 3] = fmaxf(m4[i & 3], sv);
+                        for (int i = 0; i < 64; ++i)
+                            if (c * 32 + i > r) v[i] = 0xff800000u;   // -inf above the diagonal
                     }
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -796,13 +801,16 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 pe_phase ^= 1;
                 tc_fence_after();
                 const bool diag = p.causal && j == qt;
-                auto process = [&](const unsigned* v, int c) {
+                auto process = [&](unsigned* v, int c) {
+                    if (diag) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i > r) v[i] = 0xff800000u;   // -inf above the diagonal: P = 0
+                    }
                     float e[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        float sv = __uint_as_float(v[i]);
-                        if (diag && c * 32 + i > r) sv = -INFINITY;
-                        e[i] = ex2_approx(fmaf(sv, p.scale_log2e, -mc));
+                        e[i] = ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2e, -mc));
                         l4[i & 3] += e[i];
                     }
                     unsigned char* row = p_tile + (c >> 1) * AT_PANEL + r * 128;
