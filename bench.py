@@ -11,12 +11,24 @@ Both results are requested together, so one fused row kernel computes y and, fro
 the partial sums of s: x is read from HBM once.  --separate-kernels requests them one by one (row
 kernel, then a streaming reduce), which is all the reference's one-tensor-per-call API can express.
 Inputs are synthetic (seeded PCG64).  Four input buffers are rotated so that every step reads x
-from HBM, not from L2.  `value` = algorithmic bytes of all ranks / device time (CUDA events on the
-library's stream, max over ranks).  `e2e` = the same metric through the public C ABI with HOST
-buffers: upload of x from pinned memory, the kernel, download of y and s, every step.
+from HBM, not from L2.  `value` = bytes the step has to move (x and w in, y and the scalar out:
+268 451 844 per GPU; with --separate-kernels x is read twice: 402 669 568) of all ranks / device time
+(CUDA events on the library's stream, max over ranks).  `e2e` = the same metric through the public
+C ABI with HOST buffers: upload of x from pinned memory, the kernel, download of y and s, every step.
+
+Beside the headline the line carries
+  check        the step's results against the CPU oracle, computed outside the timed regions at every
+               N: y on 32 sampled rows per rank, s against the float64 sum over all ranks' shards;
+               the process exits non-zero when it fails
+  long_run     the same step for at least 0.25 s, with its own clock samples
+  matmul       f16 4096^3 on the tensor cores (TFLOP/s, fraction of the measured bf16 burst)
+  llama_block  Llama-style decoder block forward, batch 8 x seq 2048 sharded by batch over the GPUs
+               of the line (strong scaling), tokens/s
+(--no-extras leaves the last three out).
 
 `--impl reference` times the CPU restatement of the reference's math (oracle/oracle.c, fast mode:
-float + libm, one memory pass per kernel the reference's resolver would launch, all host threads).
+float + libm, one memory pass per kernel the reference's resolver would launch) on every host core,
+whatever OMP_NUM_THREADS the launcher exported; at N > 1 a step covers N shards.
 """
 import argparse
 import ctypes
@@ -34,7 +46,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 ROWS, H = 8192, 4096
 BYTES_CHAIN = ROWS * H * 4 * 2 + H * 4          # read x, read w, write y
 BYTES_SUM = ROWS * H * 4                        # read x (+ 4 bytes out)
-BYTES_STEP = BYTES_CHAIN + BYTES_SUM
+BYTES_STEP_SEPARATE = BYTES_CHAIN + BYTES_SUM    # two kernels, x read by each
+BYTES_STEP_FUSED = BYTES_CHAIN + 4              # one kernel: x, w in; y and the scalar out
 NBUF = 4
 
 
@@ -124,7 +137,13 @@ class CpuWorkload:
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import oracle
         self.lib = oracle.lib()
-        self.cores = int(self.lib.orc_threads())
+        # every host core this process may run on, whatever OMP_NUM_THREADS says (torch.distributed.run
+        # exports OMP_NUM_THREADS=1 to its children)
+        try:
+            avail = len(os.sched_getaffinity(0))
+        except AttributeError:
+            avail = os.cpu_count() or 1
+        self.cores = int(self.lib.orc_set_threads(avail))
         self.rows = rows
         self.x = make_inputs(0, 0)[:rows].copy()
         self.w = make_weight()
@@ -133,7 +152,7 @@ class CpuWorkload:
         self.tmp, self.normed = np.empty((rows, H), f), np.empty((rows, H), f)
         self.t1, self.t2, self.out = np.empty((rows, H), f), np.empty((rows, H), f), np.empty((rows, H), f)
         self.col = np.empty(H, f)
-        self.bytes_step = rows * H * 4 * 3 + H * 4
+        self.bytes_step = rows * H * 4 * 2 + H * 4 + 4      # the same unit of work as the GPU arm's value
 
     def step(self):
         p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
@@ -144,14 +163,15 @@ class CpuWorkload:
                                 R, ctypes.c_int64(H))
         return float(L.orc_fast_sum_exp(p(self.x), p(self.col), R, ctypes.c_int64(H)))
 
-    def time(self, steps, warmup):
+    def time(self, steps, warmup, shards=1):
+        """One step = `shards` passes over the sample (the N shards of an N-GPU line, one after the other)."""
         for _ in range(warmup):
             self.step()
         t0 = time.perf_counter()
-        for _ in range(steps):
+        for _ in range(steps * shards):
             self.step()
         dt = time.perf_counter() - t0
-        return self.bytes_step * steps / dt / 1e9, dt / steps * 1e3
+        return self.bytes_step * shards * steps / dt / 1e9, dt / steps * 1e3
 
 
 def run_reference(args):
@@ -160,22 +180,180 @@ def run_reference(args):
         return
     # Each step is a bounded sample of the workload: as many leading rows as keep the whole
     # run near one minute (never fewer than 256 rows = 4 MiB per array, beyond the core caches).
+    shards = max(args.gpus, 1)
     probe = CpuWorkload(256)
     _, probe_ms = probe.time(2, 1)
-    budget_ms = 60e3 / max(args.steps + args.warmup, 1)
+    budget_ms = 60e3 / max((args.steps + args.warmup) * shards, 1)
     rows = int(min(ROWS, max(256, 256 * budget_ms / max(probe_ms, 1e-3))))
     rows -= rows % 256
     cpu = CpuWorkload(rows)
-    gbs, ms = cpu.time(args.steps, args.warmup)
-    sample = f"first {rows} of {ROWS} rows ({rows}x{H} f32) per step, {args.steps} steps after {args.warmup} warm-up"
+    gbs, ms = cpu.time(args.steps, args.warmup, shards)
+    sample = (f"first {rows} of {ROWS} rows ({rows}x{H} f32) of each of {shards} shard(s) per step, "
+              f"{args.steps} steps after {args.warmup} warm-up")
     print(json.dumps({
         "impl": "reference", "metric": "fused_chain_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "rmsnorm->softmax rows + sum(exp(x)), f32 [8192,4096]", "device": "host cpu"},
+        "config": {"workload": "rmsnorm->softmax rows + sum(exp(x)), f32 [8192,4096] per GPU", "device": "host cpu",
+                   "bytes_per_step_per_gpu": BYTES_STEP_FUSED, "shards_per_step": shards},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+# --------------------------------------------------------------------------------------------
+# Secondary workloads of the metric: f16 matmul on the tensor cores, Llama-style decoder block
+# --------------------------------------------------------------------------------------------
+def bf16_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f).get("bf16_tflops", 1590.0)), "measured"
+    return 1590.0, "fallback"
+
+
+def all_host_threads():
+    """Context manager: numpy's BLAS on every host core (launchers export OMP_NUM_THREADS=1)."""
+    try:
+        from threadpoolctl import threadpool_limits
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+        return threadpool_limits(limits=n)
+    except ImportError:
+        import contextlib
+        return contextlib.nullcontext()
+
+
+class LlamaBlock:
+    """Llama-style decoder block forward, f16, random init: hidden 4096, 32 heads x 128, MLP 11008,
+    global batch 8 x seq, sharded by batch over the ranks (strong scaling), causal attention."""
+    Hd, heads, inter, Bg = 4096, 32, 11008, 8
+
+    def __init__(self, wgf, dev, world, rank, seq, masked):
+        self.wgf, self.dev, self.seq = wgf, dev, seq
+        Hd, heads, inter = self.Hd, self.heads, self.inter
+        D = Hd // heads
+        self.b0, self.b1 = wgf.shard_range(self.Bg, world, rank)
+        g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 5))
+        h16 = lambda a: a.astype(np.float16)
+        shapes = [(Hd, Hd)] * 4 + [(inter, Hd), (inter, Hd), (Hd, inter)]
+        self.W_host = [h16(g.standard_normal(s, dtype=np.float32) * 0.02) for s in shapes]
+        self.W = [dev.tensor(w) for w in self.W_host]
+        self.n_host = np.ones(Hd, np.float16)
+        self.n1, self.n2 = dev.tensor(self.n_host), dev.tensor(self.n_host)
+        pos = np.arange(seq, dtype=np.float32)[:, None]
+        inv = (1.0 / (10000.0 ** (np.arange(0, D, 2, dtype=np.float32) / D)))[None, :]
+        self.cos_host, self.sin_host = h16(np.cos(pos * inv)), h16(np.sin(pos * inv))
+        self.cos, self.sin = dev.tensor(self.cos_host), dev.tensor(self.sin_host)
+        # causal attention: the fused tensor-core kernel (no mask tensor), or batched matmul + masked
+        # softmax + batched matmul through an additive mask
+        self.mask = None
+        if masked:
+            self.mask = dev.tensor(np.where(np.arange(seq)[None, :] <= np.arange(seq)[:, None], 0.0, -np.inf).astype(np.float16))
+        xg = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 5 + 1))
+        x_all = h16(xg.standard_normal((self.Bg, seq, Hd), dtype=np.float32))
+        self.x_host = x_all[self.b0:self.b1]
+        self.x = dev.tensor(self.x_host) if self.b1 > self.b0 else None
+
+    def request(self):
+        return self.x.llama_block(self.W, self.n1, self.n2, self.cos, self.sin, self.mask, self.heads, 1e-5)
+
+    def step(self):
+        if self.x is not None:
+            self.request().materialize()
+
+    def check(self):
+        """Output rows of sampled tokens of this rank's first batch element against float64
+        (oracle/llama_ref.py): norm-wise error, bound 2e-2 for the f16 block."""
+        if self.x is None:
+            return 0.0
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import llama_ref
+        tokens = np.array([0, 127, 128, self.seq // 2, self.seq - 1])
+        out = self.request().as_slice()
+        with all_host_threads():
+            ref = llama_ref.llama_block_tokens(self.x_host[0], self.W_host, self.n_host, self.n_host, self.cos_host,
+                                               self.sin_host, self.heads, 1e-5, tokens)
+        if not np.isfinite(out.astype(np.float32)).all():
+            return float("inf")
+        return float(np.max(np.abs(out[0, tokens].astype(np.float64) - ref)) / np.max(np.abs(ref)))
+
+    def flop(self):
+        tokens = self.Bg * self.seq      # attention counted in full (masked half included)
+        return tokens * (4 * 2 * self.Hd * self.Hd + 3 * 2 * self.Hd * self.inter + 4 * self.seq * self.Hd)
+
+
+def time_region(torch, stream, barrier, fn, steps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(steps):
+        fn(i)
+    e1.record(stream)
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def matmul_record(wgf, dev, torch, stream, barrier, launches=60):
+    """f16 [4096,4096] x [4096,4096] -> f16, fp32 accumulation in tensor memory: three operand pairs
+    rotated (192 MiB of operands, more than L2), `launches` timed launches after 5 warm-up ones.
+    Checked through a projection: C v against A (B v) in float64 for two random v (every tile of
+    the schedule takes part)."""
+    n = 4096
+    g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 4))
+    host = [((g.random((n, n), dtype=np.float32) * 2 - 1).astype(np.float16),
+             (g.random((n, n), dtype=np.float32) * 2 - 1).astype(np.float16)) for _ in range(3)]
+    ops = [(dev.tensor(a), dev.tensor(b)) for a, b in host]
+    fn = lambda i: ops[i % 3][0].mat_mul(ops[i % 3][1]).materialize()
+    for i in range(5):
+        fn(i)
+    sampler = ClockSampler(torch.cuda.current_device())
+    before = dev.launch_count
+    ms = time_region(torch, stream, barrier, fn, launches)
+    count = dev.launch_count - before
+    clocks = sampler.stop()
+    c = ops[0][0].mat_mul(ops[0][1]).as_slice().astype(np.float64)
+    v = g.standard_normal((n, 2))
+    with all_host_threads():
+        ref = host[0][0].astype(np.float64) @ (host[0][1].astype(np.float64) @ v)
+        err = float(np.max(np.abs(c @ v - ref)) / np.max(np.abs(ref)))
+    peak, kind = bf16_peak()
+    tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
+    return {"workload": "f16 4096^3 -> f16, fp32 accumulate", "tflops": tf, "kernel_ms": ms, "launches": launches,
+            "gpu_launches": count, "frac_bf16_burst": tf / peak, "peak_bf16_tflops": peak, "peak_kind": kind,
+            "frac_nominal_2250": tf / 2250.0, "l2": "three operand pairs rotated: 192 MiB of operands",
+            "check": {"projection_rel": err, "ok": bool(err <= 2e-4)}, "clocks": clocks}
+
+
+def llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=2048, masked=False, steps=10, warmup=3,
+                 check=True):
+    blk = LlamaBlock(wgf, dev, world, rank, seq, masked)
+    for _ in range(warmup):
+        blk.step()
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    before = dev.launch_count
+    ms = time_region(torch, stream, barrier, lambda i: blk.step(), steps)
+    launches = dev.launch_count - before
+    clocks = sampler.stop() if sampler else None
+    err = blk.check() if check else None
+    vals = torch.tensor([ms, float(launches), err if err is not None else 0.0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx, sm = vals.clone(), vals.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, launches, err = float(mx[0]), int(sm[1]), (float(mx[2]) if err is not None else None)
+    tokens = blk.Bg * seq
+    rec = {"workload": "llama-style decoder block forward, f16", "tokens_per_s": tokens / (ms * 1e-3), "ms_per_step": ms,
+           "steps": steps, "global_batch": blk.Bg, "seq_len": seq, "hidden": blk.Hd, "heads": blk.heads, "mlp": blk.inter,
+           "sharding": f"batch/{world}", "scaling": "strong", "gpu_launches": launches,
+           "kernels_per_step": launches // max(steps * min(world, blk.Bg), 1),
+           "tflops_nominal": blk.flop() / (ms * 1e-3) / 1e12,
+           "attention": "matmul + masked softmax + matmul" if masked else "fused tcgen05 kernel", "clocks": clocks}
+    if err is not None:
+        rec["check"] = {"sampled_tokens_rel": err, "ok": bool(err <= 2e-2)}
+    return rec
 
 
 # --------------------------------------------------------------------------------------------
@@ -315,19 +493,70 @@ def run_gpu(args):
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
 
+    # ---- correctness of the step, outside the timed regions, at every N -------------------------
+    # y on 32 sampled rows of this rank's shard against the CPU oracle (relative, the bound of the
+    # row-chain parity tests), s against the float64 sum of exp over ALL ranks' shards (1e-5).
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    x_host = make_inputs(rank, 0)
+    rows = np.unique(np.concatenate([[0, 1, ROWS // 2, ROWS - 2, ROWS - 1],
+                                     np.random.Generator(np.random.PCG64(7 + rank)).integers(0, ROWS, 27)]))
+    y = xs[0].layer_norm(w, 1e-5).softmax_last_dim()
+    s = xs[0].exp().sum(0).sum(0)
+    if comm is not None:
+        s = s.all_reduce(comm)
+    request(y, s)
+    y_rows = y.as_slice()[rows]
+    s_got = float(s.as_slice())
+    del y, s
+    y_ref = oracle.Ref(x_host[rows]).layer_norm(oracle.Ref(w_host), 1e-5).softmax_last_dim().numpy()
+    y_err = float(np.max(np.abs(y_rows.astype(np.float64) - y_ref) / np.maximum(np.abs(y_ref.astype(np.float64)), 1e-30)))
+    part = torch.tensor([np.exp(x_host.astype(np.float64)).sum()], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(part, op=dist.ReduceOp.SUM)
+    s_ref = float(part[0])
+    s_err = abs(s_got - s_ref) / s_ref
+    del x_host
+
+    # ---- the same step for at least 0.25 s, with its own clock samples -----------------------------
+    long_run = None
+    if not args.no_extras:
+        n_long = max(args.steps, int(0.25 / max(ms_total / args.steps * 1e-3, 1e-6)))
+        long_sampler = ClockSampler(local) if rank == 0 else None
+        long_ms = time_region(torch, stream, barrier, step, n_long)
+        long_run = {"steps": n_long, "ms_per_step": long_ms, "clocks": long_sampler.stop() if long_sampler else None}
+
     # ---- max over ranks ---------------------------------------------------------------------
-    vals = torch.tensor([ms_total, e2e_ms, float(launches)], dtype=torch.float64, device="cuda")
+    vals = torch.tensor([ms_total, e2e_ms, float(launches), y_err, s_err, long_run["ms_per_step"] if long_run else 0.0],
+                        dtype=torch.float64, device="cuda")
     if world > 1:
         mx = vals.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = vals.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         ms_total, e2e_ms, launches = float(mx[0]), float(mx[1]), int(sm[2])
+        y_err, s_err = float(mx[3]), float(mx[4])
+        if long_run:
+            long_run["ms_per_step"] = float(mx[5])
+    check = {"y_rows_max_rel": y_err, "y_rows_per_rank": int(len(rows)), "y_bound": 1e-4, "sum_rel": s_err,
+             "sum_bound": 1e-5, "sum": s_got, "sum_float64": s_ref, "ok": bool(y_err <= 1e-4 and s_err <= 1e-5)}
+
+    # ---- the other two parts of the metric: f16 matmul and the decoder block ------------------------
+    matmul = llama = None
+    if not args.no_extras:
+        xs.clear()
+        dev.set_timing(False)
+        if rank == 0:
+            matmul = matmul_record(wgf, dev, torch, stream, lambda: (dev.sync(), torch.cuda.synchronize()))
+        llama = llama_record(wgf, dev, torch, dist, stream, barrier, world, rank)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
         ms_step = ms_total / args.steps
-        value = BYTES_STEP * world / (ms_step * 1e-3) / 1e9
+        bytes_step = BYTES_STEP_FUSED if fused else BYTES_STEP_SEPARATE
+        value = bytes_step * world / (ms_step * 1e-3) / 1e9
+        if long_run:
+            long_run["value"] = bytes_step * world / (long_run["ms_per_step"] * 1e-3) / 1e9
         # bytes the dominant kernel has to move per launch: x, w in, y out (+ the 4-byte scalar when
         # the reduction rides along)
         kernel_bytes = BYTES_CHAIN + (4 if fused else 0)
@@ -358,36 +587,44 @@ def run_gpu(args):
             "config": {"workload": "rmsnorm->softmax rows + sum(exp(x)), f32 [8192,4096] per GPU",
                        "rows_per_gpu": ROWS, "row_len": H, "sharding": "rows" if world > 1 else "none",
                        "l2": f"{NBUF} input buffers of 128 MiB rotated: inputs larger than L2",
-                       "bytes_per_step_per_gpu": BYTES_STEP,
+                       "bytes_per_step_per_gpu": bytes_step,
+                       "algorithmic_bytes_if_separate": BYTES_STEP_SEPARATE,
                        "kernels_per_step": kernels_per_step,
-                       "note": ("value counts the algorithmic bytes of both results, x once for each "
-                                "(268 451 840 + 134 217 728); with both requested together one kernel reads x once "
-                                "and moves 268 451 844 bytes, which is what roofline.achieved counts"
-                                if fused else "two kernels per step: row kernel, then streaming reduce")},
+                       "note": ("one kernel per step reads x and w once and writes y and the scalar: value counts those "
+                                "bytes; the reference's resolver runs the step as 11 kernels"
+                                if fused else "two kernels per step: row kernel, then streaming reduce; each reads x")},
             "roofline": {"bound": "hbm",
                          "kernel": "fused rmsnorm->softmax row kernel" + (" with sum(exp(x)) riding along" if fused else ""),
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "launch_ms": row_ms,
                          "bytes_per_launch": kernel_bytes, "sum_exp_kernel": sum_exp},
             "cpu_baseline": cpu_baseline,
-            "e2e": {"value": BYTES_STEP * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+            "e2e": {"value": bytes_step * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "steps": e2e_steps, "h2d_bytes_per_step": ROWS * H * 4, "d2h_bytes_per_step": ROWS * H * 4 + 4},
             "gpu_launches": launches,
+            "check": check,
+            "long_run": long_run,
+            "matmul": matmul,
+            "llama_block": llama,
             "host_queue_ms_per_step": host_ms,
             "all_reduce": (None if comm is None else
                            "inside the reduction kernel over peer memory" if per_step == kernels_per_step else "NCCL launch"),
             "all_reduce_on_device_stream_ms": ar_ms,
             "clocks": clocks,
         }))
+        sys.stdout.flush()
+    ok = check["ok"] and (matmul is None or matmul["check"]["ok"]) and (llama is None or llama.get("check", {}).get("ok", True))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        print("bench: a correctness check failed (see the check keys of the line)", file=sys.stderr)
+        sys.exit(1)
 
 
 # --------------------------------------------------------------------------------------------
-# Secondary workload (--workload llama_block): Llama-style decoder block forward, f16, random init,
-# hidden 4096, 32 heads x 128, MLP 11008, batch 8 x seq 2048 sharded by batch over the GPUs (strong
-# scaling: the global batch stays 8).  Metric: tokens/s.  No collective: the shards are independent.
+# Secondary workload as the headline (--workload llama_block): tokens/s of the decoder block, batch 8
+# sharded by batch over the GPUs (strong scaling: the global batch stays 8).  No collective.
 # --------------------------------------------------------------------------------------------
 def run_llama(args):
     import torch
@@ -406,30 +643,7 @@ def run_llama(args):
     dev = wgf.Device(local)
     _, stream_ptr = dev.info()
     stream = torch.cuda.ExternalStream(stream_ptr, device=torch.device("cuda", local))
-    Hd, heads, inter, S, Bg = 4096, 32, 11008, args.seq, 8
-    D = Hd // heads
-    b0, b1 = wgf.shard_range(Bg, world, rank)
-    B = b1 - b0
-    g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 5))
-    h16 = lambda a: a.astype(np.float16)
-    shapes = [(Hd, Hd)] * 4 + [(inter, Hd), (inter, Hd), (Hd, inter)]
-    W = [dev.tensor(h16(g.standard_normal(s, dtype=np.float32) * 0.02)) for s in shapes]
-    n1, n2 = dev.tensor(np.ones(Hd, np.float16)), dev.tensor(np.ones(Hd, np.float16))
-    pos = np.arange(S, dtype=np.float32)[:, None]
-    inv = (1.0 / (10000.0 ** (np.arange(0, D, 2, dtype=np.float32) / D)))[None, :]
-    cos, sin = dev.tensor(h16(np.cos(pos * inv))), dev.tensor(h16(np.sin(pos * inv)))
-    # causal attention: the fused tensor-core kernel (no mask tensor), or, with --separate-kernels,
-    # batched matmul + masked softmax + batched matmul through an additive mask
-    mask = None
-    if args.separate_kernels:
-        mask = dev.tensor(np.where(np.arange(S)[None, :] <= np.arange(S)[:, None], 0.0, -np.inf).astype(np.float16))
-    x_all = h16(np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 5 + 1)).standard_normal((Bg, S, Hd), dtype=np.float32))
-    x = dev.tensor(x_all[b0:b1]) if B > 0 else None
     dev.set_timing(False)
-
-    def step():
-        if x is not None:
-            x.llama_block(W, n1, n2, cos, sin, mask, heads, 1e-5).materialize()
 
     def barrier():
         dev.sync()
@@ -437,39 +651,20 @@ def run_llama(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    launches_before = dev.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = dev.launch_count - launches_before
-    clocks = sampler.stop() if sampler else None
-    vals = torch.tensor([ms, float(launches)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        mx, sm = vals.clone(), vals.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        ms, launches = float(mx[0]), int(sm[1])
+    rec = llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=args.seq, masked=args.separate_kernels,
+                       steps=args.steps, warmup=max(args.warmup, 3), check=not args.no_cpu)
     if rank == 0:
-        tokens = Bg * S
-        flop = tokens * (4 * 2 * Hd * Hd + 3 * 2 * Hd * inter + 4 * S * Hd)   # attention counted in full (masked half included)
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
         print(json.dumps({
-            "metric": "llama_block_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "metric": "llama_block_tokens_per_s", "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "llama-style decoder block forward", "hidden": Hd, "heads": heads, "head_dim": D,
-                       "mlp": inter, "global_batch": Bg, "seq_len": S, "sharding": f"batch/{world}",
-                       "attention": "matmul + masked softmax + matmul" if args.separate_kernels else "fused tcgen05 kernel"},
-            "tflops_nominal": flop / (ms * 1e-3) / 1e12, "gpu_launches": launches, "clocks": clocks,
+            "config": {"workload": "llama-style decoder block forward", "hidden": rec["hidden"], "heads": rec["heads"],
+                       "head_dim": rec["hidden"] // rec["heads"], "mlp": rec["mlp"], "global_batch": rec["global_batch"],
+                       "seq_len": rec["seq_len"], "sharding": rec["sharding"], "attention": rec["attention"]},
+            "tflops_nominal": rec["tflops_nominal"], "gpu_launches": rec["gpu_launches"], "check": rec.get("check"),
+            "clocks": rec["clocks"],
         }))
     if world > 1:
         dist.barrier()
@@ -478,9 +673,9 @@ def run_llama(args):
 
 def run_configs(args):
     """--workload configs: every benchmark configuration on one GPU, one JSON object per row
-    (the sweep itself is wgpu-kernal-fusion_b200/config_sweep.py)."""
+    (the sweep itself is bench_configs.py)."""
     wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
-    sweep = load("wgf_b200_config_sweep", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "config_sweep.py"))
+    sweep = load("wgf_b200_bench_configs", os.path.join(ROOT, "bench_configs.py"))
     peak_gbs, which = measured_peak()
     peak_tf = 1590.0
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -502,7 +697,9 @@ def main():
     ap.add_argument("--impl", default="wgf", choices=["wgf", "reference"])
     ap.add_argument("--workload", default="fused_chain", choices=["fused_chain", "llama_block", "configs"])
     ap.add_argument("--seq", type=int, default=2048, help="sequence length of the llama_block workload")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (llama_block: the float64 check)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="fused_chain: leave out the long_run, matmul and llama_block records")
     ap.add_argument("--rows", default=None, help="configs workload: only the rows whose name contains this text")
     ap.add_argument("--separate-kernels", action="store_true",
                     help="fused_chain: request the two results one by one (row kernel, then streaming reduce); "

@@ -227,6 +227,22 @@ int orc_threads(void) {
 #endif
 }
 
+/* Sets the thread count of the timed functions, whatever OMP_NUM_THREADS says (process
+ * launchers export OMP_NUM_THREADS=1 for their children; the CPU baseline is meant to use
+ * every host core).  Returns the count now in effect. */
+int orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) {
+        omp_set_dynamic(0);
+        omp_set_num_threads(n);
+    }
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* layer_norm (src/composite/rms_norm.rs:8-15) resolves to 3 kernels: reduce(sum, pre sqr,
  * post /H +eps sqrt), pairwise div by the broadcast norm, pairwise mul by the broadcast weight. */
 void orc_fast_rms_norm(const float* x, const float* w, float eps, float* norm, float* tmp, float* out,
