@@ -266,15 +266,15 @@ class LlamaBlock:
 
     def check(self):
         """Output rows of sampled tokens of this rank's first batch element against float64
-        (oracle/llama_ref.py): norm-wise error, bound 2e-2 for the f16 block."""
+        (oracle/dense_ref.py): norm-wise error, bound 2e-2 for the f16 block."""
         if self.x is None:
             return 0.0
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
-        import llama_ref
+        import dense_ref
         tokens = np.array([0, 127, 128, self.seq // 2, self.seq - 1])
         out = self.request().as_slice()
         with all_host_threads():
-            ref = llama_ref.llama_block_tokens(self.x_host[0], self.W_host, self.n_host, self.n_host, self.cos_host,
+            ref = dense_ref.llama_block_tokens(self.x_host[0], self.W_host, self.n_host, self.n_host, self.cos_host,
                                                self.sin_host, self.heads, 1e-5, tokens)
         if not np.isfinite(out.astype(np.float32)).all():
             return float("inf")
@@ -299,8 +299,8 @@ def time_region(torch, stream, barrier, fn, steps):
 def matmul_record(wgf, dev, torch, stream, barrier, launches=60):
     """f16 [4096,4096] x [4096,4096] -> f16, fp32 accumulation in tensor memory: three operand pairs
     rotated (192 MiB of operands, more than L2), `launches` timed launches after 5 warm-up ones.
-    Checked through a projection: C v against A (B v) in float64 for two random v (every tile of
-    the schedule takes part)."""
+    Checked through projections: for every block of 256 columns C[:, blk] v against A (B[:, blk] v) in
+    float64 (every tile of the schedule takes part; oracle/dense_ref.py)."""
     n = 4096
     g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 4))
     host = [((g.random((n, n), dtype=np.float32) * 2 - 1).astype(np.float16),
@@ -315,16 +315,16 @@ def matmul_record(wgf, dev, torch, stream, barrier, launches=60):
     count = dev.launch_count - before
     clocks = sampler.stop()
     c = ops[0][0].mat_mul(ops[0][1]).as_slice().astype(np.float64)
-    v = g.standard_normal((n, 2))
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import dense_ref
     with all_host_threads():
-        ref = host[0][0].astype(np.float64) @ (host[0][1].astype(np.float64) @ v)
-        err = float(np.max(np.abs(c @ v - ref)) / np.max(np.abs(ref)))
+        err = dense_ref.matmul_projection_error(c, host[0][0], host[0][1], vectors=2)
     peak, kind = bf16_peak()
     tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
     return {"workload": "f16 4096^3 -> f16, fp32 accumulate", "tflops": tf, "kernel_ms": ms, "launches": launches,
             "gpu_launches": count, "frac_bf16_burst": tf / peak, "peak_bf16_tflops": peak, "peak_kind": kind,
             "frac_nominal_2250": tf / 2250.0, "l2": "three operand pairs rotated: 192 MiB of operands",
-            "check": {"projection_rel": err, "ok": bool(err <= 2e-4)}, "clocks": clocks}
+            "check": {"projection_rel": err, "bound": 1e-3, "ok": bool(err <= 1e-3)}, "clocks": clocks}
 
 
 def llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=2048, masked=False, steps=10, warmup=3,

@@ -1,5 +1,6 @@
-"""float64 numpy statement of the Llama-style decoder block and of causal attention, for sampled
-tokens of a large input.  TEST INFRASTRUCTURE ONLY (the checker of tests/ and of bench.py's
+"""float64 numpy statements of the tensor-core ops at full size: the Llama-style decoder block and
+causal attention for sampled tokens of a large input, and a matmul check that covers every tile
+through projections.  TEST INFRASTRUCTURE ONLY (the checker of tests/ and of bench.py's
 `check` keys); nothing in the product may import it.
 
 The crate has no model code (its composites stop at rms-norm, softmax, silu and rope:
@@ -66,3 +67,23 @@ def attention(q, k, v, causal, scale):
     s = s - s.max(-1, keepdims=True)
     p = np.exp(s)
     return (p / p.sum(-1, keepdims=True)) @ v
+
+
+def matmul_projection_error(c, a, b, block=256, vectors=3, seed=0):
+    """Largest error of C's column blocks projected on random vectors, relative to the largest
+    projection: for every block of `block` columns, C[:, blk] v against A (B[:, blk] v) in float64.
+    Every entry of C takes part at O(n^2) cost.  The rounding errors of the entries of a row are
+    independent, so they grow like sqrt(block) in a projection while the reference grows the same
+    way: the result is the typical relative error of an ENTRY (about 2^-12 for an f16 result), and a
+    tile whose entries are off by a relative e shows as about e."""
+    a64, b64, c64 = _f(a), _f(b), _f(c)
+    n = b64.shape[1]
+    g = np.random.Generator(np.random.PCG64(seed))
+    worst, scale = 0.0, 0.0
+    for j0 in range(0, n, block):
+        v = g.standard_normal((min(block, n - j0), vectors))
+        ref = a64 @ (b64[:, j0:j0 + block] @ v)
+        got = c64[:, j0:j0 + block] @ v
+        worst = max(worst, float(np.max(np.abs(got - ref))))
+        scale = max(scale, float(np.max(np.abs(ref))))
+    return worst / max(scale, 1e-300)
