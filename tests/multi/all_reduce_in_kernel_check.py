@@ -2,10 +2,11 @@
 
 Each rank owns a shard x_r of f32 [1024,512].  One request asks for the softmax rows of the shard and
 three all-reduced whole-tensor reductions of it (sum of exp, max, sum of squares): one kernel per rank
-computes all four and exchanges the three scalars with the other ranks over peer memory (no NCCL
-launch).  Checked against float64 numpy over all shards, for 40 steps (sequence numbers and both
-mailbox parities), and that every rank holds identical bits.  With WGF_NO_PEER_ALLREDUCE=1 the same
-script checks the NCCL path (four launches per step)."""
+computes all four and posts the three scalars to the other ranks over peer memory, one small kernel
+on the collective stream combines what the ranks posted (no NCCL launch).  Checked against float64
+numpy over all shards, for 40 steps (sequence numbers wrap the mailbox slots twice), and that every
+rank holds identical bits.  With WGF_NO_PEER_ALLREDUCE=1 the same script checks the NCCL path (four
+launches per step)."""
 import os
 import sys
 
@@ -25,7 +26,7 @@ dev = wgf.Device(local)
 ids = [wgf.Comm.unique_id() if rank == 0 else None]
 dist.broadcast_object_list(ids, src=0)
 comm = wgf.Comm(dev, world, rank, ids[0])
-expected_launches = 4 if os.environ.get("WGF_NO_PEER_ALLREDUCE") else 1
+expected_launches = 4 if os.environ.get("WGF_NO_PEER_ALLREDUCE") else 2
 
 
 def data(r, step):
@@ -55,7 +56,7 @@ for step in range(40):
     alone_launches = dev.launch_count - before
     ea = sum(np.exp(2.0 * a.astype(np.float64)).sum() for a in xs)
     ga = float(alone.as_slice())
-    if abs(ga - ea) / ea > 1e-5 or alone_launches != (2 if os.environ.get("WGF_NO_PEER_ALLREDUCE") else 1):
+    if abs(ga - ea) / ea > 1e-5 or alone_launches != 2:
         print(f"rank {rank} step {step}: stand-alone all-reduce: {alone_launches} launches, got {ga}, expected {ea}", flush=True)
         bad += 1
     ok = (abs(gs - es) / es < 1e-5 and gm == em and abs(gq - eq) / eq < 1e-5 and launches == expected_launches
@@ -68,6 +69,31 @@ for step in range(40):
     dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     if not torch.equal(t, t2):
         print(f"rank {rank} step {step}: the ranks hold different bits", flush=True)
+        bad += 1
+# Second phase: 100 exchanges queued without reading anything back, rank 1 starting late, so the
+# other ranks' device streams run ahead as far as the mailbox slots allow (the stream of a rank
+# waits for its own combine kernel of 8 exchanges earlier); then every result is read.
+import time  # noqa: E402
+
+x = dev.tensor(data(rank, 0))
+xs = [data(r, 0).astype(np.float64) for r in range(world)]
+dev.sync()
+dist.barrier()
+if rank == 1:
+    time.sleep(0.3)
+kept = []
+for k in range(100):
+    c = 0.5 + 0.01 * k
+    y = (x * c).softmax_last_dim()
+    s = (x * c).exp().sum(0).sum(0).all_reduce(comm)
+    wgf.Tensor.materialize_all([y, s])
+    kept.append((c, s))
+for c, s in kept:
+    c32 = float(np.float32(c))
+    expect = sum(np.exp((a.astype(np.float32) * np.float32(c32)).astype(np.float64)).sum() for a in xs)
+    got = float(s.as_slice())
+    if abs(got - expect) / expect > 1e-5:
+        print(f"rank {rank}: run-ahead exchange with factor {c}: got {got}, expected {expect}", flush=True)
         bad += 1
 print(f"rank {rank}: {'PASS' if bad == 0 else 'FAIL'}", flush=True)
 dist.barrier()

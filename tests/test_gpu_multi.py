@@ -34,3 +34,19 @@ def test_all_reduce_inside_the_row_kernel(peer):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("PASS") == n
+
+
+def test_a_peer_that_sits_an_exchange_out_gives_a_timeout_status():
+    """The combine kernel's wait has a limit (WGF_PEER_WAIT_MS): when a peer never posts, the kernel
+    returns, the next synchronisation reports WGF_ERR_TIMEOUT and the communicator can be released."""
+    if gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"
+    env["WGF_PEER_WAIT_MS"] = "50"
+    env.pop("WGF_NO_PEER_ALLREDUCE", None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29543", os.path.join(HERE, "multi", "peer_wait_runs_out.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("PASS") == 2

@@ -29,7 +29,7 @@ def _newer(src, dst, headers):
 def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     sources = sorted(f for f in os.listdir(CSRC) if f.endswith((".cpp", ".cu")))
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".hpp")]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".hpp", ".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "wgf.h"))
     jobs = []
     for f in sources:

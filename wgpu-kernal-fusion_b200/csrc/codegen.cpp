@@ -589,9 +589,9 @@ std::string row_source(const Program& prog_in, const RowConfig& c) {
                 << ">(a_, __ldcg(gpart + (u64)b_ * NGRAND + " << id << "));\n"
                 << "  __syncthreads();\n  a_ = group_reduce<" << op << ", THREADS>(a_, g_smem[" << id
                 << "], (int)threadIdx.x);\n  if (threadIdx.x == 0) {\n";
-        if (gr.all_reduce)   // the value of this GPU is rounded to the element type, then combined across GPUs
-            gfinish << "    a_ = peer_all_reduce<" << red_name(gr.ar_op) << ">(" << rounded(gr.dtype, "a_") << ", " << id
-                    << ", p.gpeers, p.gworld, p.grank, p.gseq, p.gerr);\n";
+        if (gr.all_reduce)   // the value of this GPU, rounded to the element type, goes to every rank's mailbox;
+                             // a kernel on the collective stream combines the ranks and overwrites gout
+            gfinish << "    peer_post(" << rounded(gr.dtype, "a_") << ", " << id << ", p.gpeers, p.gworld, p.grank, p.gseq);\n";
         gfinish << "    store1<" << (int)gr.dtype << ">((void*)p.gout[" << id << "], 0, a_); } }\n";
     }
     // A group_reduce reuses its shared-memory slot in the next iteration: all reads of this
@@ -704,9 +704,8 @@ std::string stream_source(const Program& prog_in, const StreamConfig& c) {
     s << "#define STREAM_LOAD(COL, NV, X) " << load.str() << "\n";
     s << "#define STREAM_AR " << (prog.result_all_reduce ? 1 : 0) << "\n";
     s << "#define STREAM_POST " << post.str() << " if (t == 0) { float r_ = " << vn(prog.result) << "; ";
-    if (prog.result_all_reduce)   // the one result of the kernel is combined across the GPUs before it is stored
-        s << "r_ = peer_all_reduce<" << red_name(prog.result_ar_op) << ">(" << rounded(prog.out_dtype(), "r_")
-          << ", 0, p.gpeers, p.gworld, p.grank, p.gseq, p.gerr); ";
+    if (prog.result_all_reduce)   // posted to every rank's mailbox; the combine kernel overwrites the result
+        s << "peer_post(" << rounded(prog.out_dtype(), "r_") << ", 0, p.gpeers, p.gworld, p.grank, p.gseq); ";
     s << "store1<" << (int)prog.out_dtype() << ">((void*)p.ptr[NIN], roff[NIN], r_); }\n";
     s << JIT_STREAM_KERNEL;
     return s.str();

@@ -53,33 +53,51 @@ Comm::~Comm() {
     if (dev) cudaSetDevice(dev->ordinal);
     for (int r = 0; r < (int)peer_mailbox.size(); ++r)
         if (r != rank && peer_mailbox[r]) cudaIpcCloseMemHandle(peer_mailbox[r]);
+    for (cudaEvent_t e : finished)
+        if (e) cudaEventDestroy(e);
     if (peer_table) cudaFree(peer_table);
     if (mailbox) cudaFree(mailbox);
     if (handle) Nccl::get().CommDestroy(handle);
 }
 
 namespace {
+// Device scratch that is freed on every way out of setup_mailboxes.
+struct DeviceScratch {
+    void* p = nullptr;
+    ~DeviceScratch() {
+        if (p) cudaFree(p);
+    }
+};
+
 // Maps every peer's mailbox (see Comm).  Anything that does not work leaves peer_ok false on
 // EVERY rank (the outcome is agreed through an all-reduce), and all-reduces go through NCCL.
+// Between the all-gather and the agreeing all-reduce a local CUDA failure only clears `ok`: a
+// rank that threw there would leave the others waiting inside the collective.
 void setup_mailboxes(Comm& c) {
+    // one warp of the combine kernel reads the ranks' words: 32 lanes x 2 rounds at most
     if (c.world < 2 || c.world > 64 || getenv("WGF_NO_PEER_ALLREDUCE")) return;
     Device& dev = *c.dev;
-    const size_t box_bytes = (size_t)2 * c.world * kMailboxValues * sizeof(uint64_t);
+    if (const char* ms = getenv("WGF_PEER_WAIT_MS")) {
+        const long long v = atoll(ms);
+        if (v > 0) c.wait_ns = (uint64_t)v * 1000000ull;
+    }
+    const size_t box_bytes = (size_t)kMailboxSlots * c.world * kMailboxValues * sizeof(uint64_t);
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    DeviceScratch gather, flag;   // gather: [world + 1] handles, slot `world` is the send buffer
+    WGF_CUDA(cudaMalloc(&gather.p, hb * (c.world + 1)));
+    WGF_CUDA(cudaMalloc(&flag.p, sizeof(int)));
     int ok = 1;
     cudaIpcMemHandle_t mine{};
-    char* gather = nullptr;     // [world + 1] handles: slot `world` is the send buffer
-    int* flag = nullptr;
     if (cudaMalloc(&c.mailbox, box_bytes) != cudaSuccess || cudaMemset(c.mailbox, 0, box_bytes) != cudaSuccess ||
         cudaIpcGetMemHandle(&mine, c.mailbox) != cudaSuccess)
         ok = 0;
-    const size_t hb = sizeof(cudaIpcMemHandle_t);
-    WGF_CUDA(cudaMalloc(&gather, hb * (c.world + 1)));
-    WGF_CUDA(cudaMalloc(&flag, sizeof(int)));
-    WGF_CUDA(cudaMemcpy(gather + hb * c.world, &mine, hb, cudaMemcpyHostToDevice));
-    nccl_check(Nccl::get().AllGather(gather + hb * c.world, gather, hb, /*ncclInt8*/ 0, c.handle, dev.stream), "ncclAllGather");
+    if (cudaMemcpy((char*)gather.p + hb * c.world, &mine, hb, cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
+    nccl_check(Nccl::get().AllGather((char*)gather.p + hb * c.world, gather.p, hb, /*ncclInt8*/ 0, c.handle, dev.stream),
+               "ncclAllGather");
     std::vector<cudaIpcMemHandle_t> all(c.world);
-    WGF_CUDA(cudaMemcpyAsync(all.data(), gather, hb * c.world, cudaMemcpyDeviceToHost, dev.stream));
-    WGF_CUDA(cudaStreamSynchronize(dev.stream));
+    if (cudaMemcpyAsync(all.data(), gather.p, hb * c.world, cudaMemcpyDeviceToHost, dev.stream) != cudaSuccess ||
+        cudaStreamSynchronize(dev.stream) != cudaSuccess)
+        ok = 0;
     c.peer_mailbox.assign(c.world, nullptr);
     for (int r = 0; r < c.world && ok; ++r) {
         if (r == c.rank) {
@@ -89,7 +107,6 @@ void setup_mailboxes(Comm& c) {
             ok = 0;
         }
     }
-    cudaGetLastError();   // a failed mapping is not an error of the library: NCCL takes over
     if (ok) {
         std::vector<uint64_t> table(c.world);
         for (int r = 0; r < c.world; ++r) table[r] = (uint64_t)(uintptr_t)c.peer_mailbox[r];
@@ -97,14 +114,23 @@ void setup_mailboxes(Comm& c) {
             cudaMemcpy(c.peer_table, table.data(), sizeof(uint64_t) * c.world, cudaMemcpyHostToDevice) != cudaSuccess)
             ok = 0;
     }
-    // every rank must take the same path: minimum of the outcomes
-    WGF_CUDA(cudaMemcpy(flag, &ok, sizeof(int), cudaMemcpyHostToDevice));
-    nccl_check(Nccl::get().AllReduce(flag, flag, 1, /*ncclInt32*/ 2, /*ncclMin*/ 3, c.handle, dev.stream), "ncclAllReduce");
-    WGF_CUDA(cudaMemcpyAsync(&ok, flag, sizeof(int), cudaMemcpyDeviceToHost, dev.stream));
+    if (ok) {
+        c.finished.assign(kMailboxSlots, nullptr);
+        for (auto& e : c.finished)
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
+                e = nullptr;
+                ok = 0;
+            }
+    }
+    if (cudaMemcpy(flag.p, &ok, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
+    cudaGetLastError();   // a failed mapping is not an error of the library: NCCL takes over
+    // every rank must take the same path: minimum of the outcomes (a rank whose copy above failed
+    // contributes whatever the word holds, and reads its own `ok` = 0 below)
+    nccl_check(Nccl::get().AllReduce(flag.p, flag.p, 1, /*ncclInt32*/ 2, /*ncclMin*/ 3, c.handle, dev.stream), "ncclAllReduce");
+    int agreed = 0;
+    WGF_CUDA(cudaMemcpyAsync(&agreed, flag.p, sizeof(int), cudaMemcpyDeviceToHost, dev.stream));
     WGF_CUDA(cudaStreamSynchronize(dev.stream));
-    cudaFree(gather);
-    cudaFree(flag);
-    c.peer_ok = ok != 0;
+    c.peer_ok = ok != 0 && agreed != 0;
 }
 }  // namespace
 
@@ -127,6 +153,7 @@ std::shared_ptr<Comm> comm_create(const DeviceRef& dev, int world, int rank, con
     std::memcpy(&nid, id, sizeof nid);
     nccl_check(Nccl::get().CommInitRank(&c->handle, world, nid, rank), "ncclCommInitRank");
     setup_mailboxes(*c);
+    dev->exchange_broken = false;   // fresh mailboxes and sequence numbers
     return c;
 }
 
@@ -151,6 +178,39 @@ void comm_all_reduce(Comm& c, Device& dev, Buffer& out, void* data, int64_t coun
     nccl_check(r, "ncclAllReduce");
     out.pending = dev.event();
     WGF_CUDA(cudaEventRecord(out.pending, cs));
+}
+
+uint32_t comm_peer_begin(Comm& c, Device& dev) {
+    const uint32_t seq = ++c.seq;
+    if (seq > (uint32_t)kMailboxLag) {
+        dev.make_current();
+        WGF_CUDA(cudaStreamWaitEvent(dev.stream, c.finished[(seq - kMailboxLag) % kMailboxSlots], 0));
+    }
+    return seq;
+}
+
+void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<PeerValue>& vals) {
+    WGF_CHECK(!vals.empty() && vals.size() <= (size_t)kMailboxValues, WGF_ERR_INVALID_ARGUMENT, "exchange of 1..4 values");
+    dev.make_current();
+    cudaStream_t cs = dev.collective_stream();
+    cudaEvent_t posted = dev.event();
+    WGF_CUDA(cudaEventRecord(posted, dev.stream));
+    WGF_CUDA(cudaStreamWaitEvent(cs, posted, 0));
+    dev.recycle(posted);
+    dev.launches++;
+    launch_peer_combine(cs, c.mailbox, dev.error_word(), c.wait_ns, (uint32_t)c.world, (uint32_t)c.rank, seq, vals);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fail(WGF_ERR_CUDA, std::string("peer_combine launch failed: ") + cudaGetErrorString(e));
+    }
+    WGF_CUDA(cudaEventRecord(c.finished[seq % kMailboxSlots], cs));
+    for (const PeerValue& v : vals) {
+        Buffer& b = *v.out.buf;
+        if (b.pending) dev.recycle(b.pending);   // written by the posting kernel on the device stream only
+        b.pending = dev.event();
+        WGF_CUDA(cudaEventRecord(b.pending, cs));
+    }
 }
 
 }  // namespace wgf

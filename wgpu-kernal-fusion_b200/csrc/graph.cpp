@@ -894,7 +894,7 @@ TensorData run_region(Node* root, bool allow_fold = true) {
             // The all-reduce on top of it is done by the same kernel over peer memory when the
             // partial result of this GPU is not observable on its own.
             Node* ar = cand.all_reduce;
-            const bool fuse_ar = ar && !ar->cached && ar->comm && ar->comm->peer_ok && c->handles == 0 &&
+            const bool fuse_ar = ar && !ar->cached && ar->comm && ar->comm->peer_ok && !root->dev->exchange_broken && c->handles == 0 &&
                                  c->consumers.size() == 1 && c->consumers[0] == ar &&
                                  (!kernel_comm || kernel_comm == ar->comm.get());
             if (fuse_ar) kernel_comm = ar->comm.get();
@@ -983,9 +983,21 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         GrandComm gc{};
         // the exchange carries a sequence number that the host advances per launch
         if (kernel_comm) dev.refuse_while_recording("an all-reduce");
-        if (kernel_comm) gc = GrandComm{kernel_comm->peer_table, (uint32_t)kernel_comm->world, (uint32_t)kernel_comm->rank, ++kernel_comm->seq};
+        if (kernel_comm)
+            gc = GrandComm{kernel_comm->peer_table, (uint32_t)kernel_comm->world, (uint32_t)kernel_comm->rank,
+                           comm_peer_begin(*kernel_comm, dev)};
         if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace, &grand_out, kernel_comm ? &gc : nullptr);
         else out = run_elementwise(dev, em.prog, em.slots, index_shape, inplace);
+        if (kernel_comm) {
+            // The kernel has posted this GPU's values to every rank's mailbox.  The other half of the
+            // exchange -- wait for the peers' values, combine in rank order, overwrite the results --
+            // runs on the collective stream beside whatever is queued next on the device stream.
+            std::vector<PeerValue> vals;
+            if (result_ar) vals.push_back(PeerValue{arq->op, 0u, out});
+            for (size_t i = 0; i < companions.size(); ++i)
+                if (companions[i].all_reduce) vals.push_back(PeerValue{companions[i].all_reduce->op, (uint32_t)i, grand_out[i]});
+            comm_peer_finish(*kernel_comm, dev, gc.seq, vals);
+        }
     } catch (...) {
         if (donor) {
             saved.buf = em.slots[inplace].buf;
@@ -1096,6 +1108,8 @@ TensorData resolve_node(Node* n) {
         }
         case NodeKind::AllReduce: {
             dev.refuse_while_recording("an all-reduce");
+            WGF_CHECK(!dev.exchange_broken, WGF_ERR_TIMEOUT,
+                      "an earlier all-reduce gave up waiting for a peer: the ranks are out of step; release the communicator");
             Node* src = n->inputs[0].get();
             // A scalar that only this all-reduce can see is exchanged by the kernel that computes
             // it (over peer memory) where that kernel is a streaming reduction; see ArRequest.

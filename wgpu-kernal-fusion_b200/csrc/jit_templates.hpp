@@ -205,49 +205,24 @@ template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t)
     return v;
 }
 
-// All-reduce of one scalar across the GPUs of a communicator from inside the kernel (one
-// thread).  Mailboxes hold 64-bit words {sequence << 32 | value bits} at
-// [parity][source rank][value index]; a single 64-bit store / load is atomic, so a word with
-// the expected sequence number carries the value that belongs to it.  The value goes to every
-// peer by a store over NVLink, the peers' values are read from this GPU's own mailbox and
-// combined in rank order.  The wait is bounded (5 s, enough for a peer that still compiles its
-// kernel on the first step): it then sets the error word.
-template <int OP> DEV float peer_all_reduce(float mine, int index, u64 peers, u32 world, u32 rank, u32 seq, u64 err) {
+// First half of an all-reduce of one scalar across the GPUs of a communicator, done from inside
+// the kernel that produces the value (one thread): the value is POSTED to every rank's mailbox,
+// this GPU's own included, by one 64-bit store each (over NVLink for the peers), and the kernel
+// goes on.  Mailboxes hold words {sequence << 32 | value bits} at
+// [sequence % PEER_SLOTS][source rank][value index]; a single 64-bit store is atomic, so a word
+// that carries the expected sequence number carries the value that belongs to it.  The second
+// half -- waiting for the peers' words and combining them in rank order -- is a one-CTA kernel on
+// the device's collective stream (peer_combine_kernel), off the path of the kernels queued behind
+// this one.  Nothing here waits.
+#define PEER_SLOTS 16u
+DEV void peer_post(float mine, int index, u64 peers, u32 world, u32 rank, u32 seq) {
     const u64* table = (const u64*)peers;
-    const u32 parity = seq & 1u;
     const u64 word = ((u64)seq << 32) | (u64)__float_as_uint(mine);
+    const u64 at = ((u64)((seq % PEER_SLOTS) * world + rank)) * 4 + (u64)index;
     for (u32 r = 0; r < world; ++r) {
-        if (r == rank) continue;
-        u64* slot = (u64*)table[r] + ((u64)(parity * world + rank) * 4 + index);
+        u64* slot = (u64*)table[r] + at;
         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(word) : "memory");
     }
-    const u64* own = (const u64*)table[rank];
-    float acc = mine;
-    for (u32 r = 0; r < world; ++r) {
-        float v = mine;
-        if (r != rank) {
-            const u64* slot = own + ((u64)(parity * world + r) * 4 + index);
-            u64 w = 0, start = 0;
-            bool got = false;
-            for (u32 spin = 0; spin < (1u << 26) && !got; ++spin) {
-                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
-                got = (u32)(w >> 32) == seq;
-                if (!got && (spin & 255u) == 255u) {
-                    u64 now;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                    if (start == 0) start = now;
-                    else if (now - start > 5000000000ull) break;
-                }
-            }
-            if (!got) {
-                atomicExch((u32*)err, 51u);
-                return mine;
-            }
-            v = __uint_as_float((u32)w);
-        }
-        acc = r == 0 ? v : red_comb<OP>(acc, v);
-    }
-    return acc;
 }
 )CUDA";
 

@@ -330,6 +330,7 @@ void Device::check_error_word() {
     WGF_CUDA(cudaMemcpy(&v, error_word_, sizeof v, cudaMemcpyDeviceToHost));
     if (v) {
         cudaMemset(error_word_, 0, sizeof v);
+        if (v == 51) exchange_broken = true;
         fail(WGF_ERR_TIMEOUT, "a kernel gave up on a bounded wait (code " + std::to_string(v) +
                                   "); its result is not valid");
     }

@@ -100,6 +100,10 @@ struct Device : std::enable_shared_from_this<Device> {
     // sync() and download() read it after the stream has drained and raise WGF_ERR_TIMEOUT.
     unsigned* error_word();
     void check_error_word();
+    // Set once a combine kernel of an all-reduce over peer memory gave up waiting for a peer (error
+    // code 51): the ranks are out of step from then on, and further all-reduces on this device are
+    // refused with WGF_ERR_TIMEOUT until its communicators have been released and made anew.
+    std::atomic<bool> exchange_broken{false};
     // Second stream for collectives, so that an all-reduce overlaps the kernels queued behind it.
     cudaStream_t collective_stream();
     // Orders the device stream behind any collective still using `b` (no-op otherwise).
