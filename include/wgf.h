@@ -73,6 +73,9 @@ typedef struct wgf_device wgf_device;
 typedef struct wgf_buffer wgf_buffer;
 typedef struct wgf_tensor wgf_tensor;
 typedef struct wgf_comm wgf_comm;
+/* Device time of what ONE call queued (PerformanceQueries / QueryResults, src/query.rs:10-126):
+ * created by the call, read later -- nothing waits until wgf_timing_elapsed_ns. */
+typedef struct wgf_timing wgf_timing;
 
 const char* wgf_last_error(void);
 /* Version of this ABI; bumped on any incompatible change. */
@@ -110,6 +113,12 @@ int32_t wgf_buffer_release(wgf_buffer* buf);
 int32_t wgf_buffer_use_count(wgf_buffer* buf, int64_t* out);
 int32_t wgf_buffer_upload(wgf_buffer* buf, uint64_t offset_bytes, const void* src, uint64_t bytes);
 int32_t wgf_buffer_download(wgf_buffer* buf, uint64_t offset_bytes, void* dst, uint64_t bytes);
+/* Stream-ordered upload from PAGE-LOCKED host memory (wgf_host_alloc) that does not wait: the copy
+ * runs on the upload stream behind everything queued on the device stream so far; later kernels
+ * that read the buffer are ordered behind it.  `done` (may be NULL) receives a handle on the copy:
+ * wgf_timing_wait returns once `src` may be reused, wgf_timing_elapsed_ns gives the copy time. */
+int32_t wgf_buffer_upload_async(wgf_buffer* buf, uint64_t offset_bytes, const void* src, uint64_t bytes,
+                                wgf_timing** done);
 int32_t wgf_buffer_device_ptr(wgf_buffer* buf, void** ptr, uint64_t* bytes);
 /* Page-locked host memory, so that uploads and downloads run at full PCIe speed (the crate
  * gets this from wgpu's mapped staging buffers, src/tensor.rs:345-381 and :533-549). */
@@ -117,7 +126,22 @@ int32_t wgf_host_alloc(uint64_t bytes, void** out);
 int32_t wgf_host_free(void* ptr);
 
 /* ======================================================================================
+ * Timing handles  (replace PerformanceQueries::wait_for_results / QueryResults::elapsed,
+ *                  src/query.rs:35-41 and :78-112)
+ * ==================================================================================== */
+/* Waits for the kernels the call queued and stores the sum of their device times. */
+int32_t wgf_timing_elapsed_ns(wgf_timing* t, uint64_t* out_ns);
+/* Waits for them without reading the time. */
+int32_t wgf_timing_wait(wgf_timing* t);
+/* Number of kernels (or copies) the call queued. */
+int32_t wgf_timing_kernel_count(wgf_timing* t, uint32_t* out);
+int32_t wgf_timing_release(wgf_timing* t);
+
+/* ======================================================================================
  * Kernel-level launches  (replace Untyped*Kernel::run_with_query)
+ * Each takes an optional `timing` out-parameter, the analogue of the crate's
+ * `Option<&PerformanceQueries>` argument: NULL = untimed; otherwise *timing receives a new
+ * handle (release it with wgf_timing_release).  The launch itself never waits.
  * ==================================================================================== */
 /* Layout {offset, shape, strides} + DataTypeEnum + buffer: src/layout.rs:33-38, src/tensor.rs:300-306 */
 typedef struct wgf_tensor_desc {
@@ -139,35 +163,37 @@ typedef struct wgf_ew_op {
 /* UntypedElementWiseKernel::run_with_query, src/element_wise.rs:89-164.
  * `inplace_ok` != 0 lets the result reuse `in`'s buffer when the dtype width is unchanged
  * (the crate decides this from the buffer's reference count, src/element_wise.rs:98-99).
- * `out->buf` is a new reference the caller must release.  `elapsed_ns` may be NULL; when
- * given, the call waits for the kernel and stores its device time. */
+ * `out->buf` is a new reference the caller must release. */
 int32_t wgf_launch_elementwise(wgf_device* dev, const wgf_tensor_desc* in, const wgf_ew_op* chain,
                                uint32_t n_ops, int32_t inplace_ok, wgf_tensor_desc* out,
-                               uint64_t* elapsed_ns);
+                               wgf_timing** timing);
 /* UntypedPairWiseKernel::run_with_query, src/pair_wise.rs:85-176: out = post(op(preA(a), preB(b))). */
 int32_t wgf_launch_pairwise(wgf_device* dev, const wgf_tensor_desc* a, const wgf_tensor_desc* b,
                             const wgf_ew_op* pre_a, uint32_t n_pre_a, const wgf_ew_op* pre_b,
                             uint32_t n_pre_b, uint32_t opcode, const wgf_ew_op* post, uint32_t n_post,
-                            wgf_tensor_desc* out, uint64_t* elapsed_ns);
+                            wgf_tensor_desc* out, wgf_timing** timing);
 /* UntypedReduceKernel::run_with_query, src/reduce.rs:283-386: out = post(reduce_axis(pre(in))). */
 int32_t wgf_launch_reduce(wgf_device* dev, const wgf_tensor_desc* in, uint32_t axis,
                           const wgf_ew_op* pre, uint32_t n_pre, uint32_t reduce_opcode,
                           const wgf_ew_op* post, uint32_t n_post, wgf_tensor_desc* out,
-                          uint64_t* elapsed_ns);
+                          wgf_timing** timing);
 /* UntypedMatMul::run_with_query, src/matmul.rs:157-214.  Rank 2, or rank 3 = batched.
- * Strides and offsets are honoured; accumulation is fp32 for every dtype. */
+ * Strides and offsets are honoured.  `acc_dtype` names the accumulator type: WGF_F32 is the
+ * one this backend has for every element type (fp32 accumulators in tensor memory for 16-bit
+ * operands, FFMA for f32); anything else is WGF_ERR_UNSUPPORTED.  (The crate accumulates in
+ * the element type, src/matmul.rs:87-149.) */
 int32_t wgf_launch_matmul(wgf_device* dev, const wgf_tensor_desc* a, const wgf_tensor_desc* b,
-                          wgf_tensor_desc* out, uint64_t* elapsed_ns);
+                          uint32_t acc_dtype, wgf_tensor_desc* out, wgf_timing** timing);
 /* UntypedResizeKernel::run_with_query, src/resize.rs:90-118: copy `in` into the leading
  * `fill_shape` box of a zero-filled tensor of `new_shape`. */
 int32_t wgf_launch_resize(wgf_device* dev, const wgf_tensor_desc* in, uint32_t new_rank,
                           const int64_t* new_shape, const int64_t* fill_shape, wgf_tensor_desc* out,
-                          uint64_t* elapsed_ns);
+                          wgf_timing** timing);
 /* UntypedSliceAssignKernel::run_with_query, src/slice_assign.rs:39-74: writes `value` into
  * target[starts..ends) IN PLACE on the target's buffer. */
 int32_t wgf_launch_slice_assign(wgf_device* dev, const wgf_tensor_desc* target, const int64_t* starts,
                                 const int64_t* ends, const wgf_tensor_desc* value,
-                                uint64_t* elapsed_ns);
+                                wgf_timing** timing);
 
 /* ======================================================================================
  * Graph-level API: the crate's `Tensor<R, D>` (src/tensor.rs:418-644).  A wgf_tensor is a

@@ -60,10 +60,15 @@ def test_launch_elementwise_chain_and_inplace(wgf, dev, orc):
     x = seeded(0, 10).standard_normal((33, 70)).astype(np.float32)
     b = Buf(wgf, dev, x)
     ops, n = chain(wgf, [(wgf.OP_MUL_C, 2.0, 0), (wgf.OP_ADD_C, 1.0, 0), (wgf.OP_SIN, 0, 0)])
-    out, ns = wgf.TensorDesc(), C.c_uint64()
+    out, timing = wgf.TensorDesc(), C.c_void_p()
     d = b.desc()
-    wgf.check(wgf.lib().wgf_launch_elementwise(dev.h, C.byref(d), ops, C.c_uint32(n), C.c_int32(0), C.byref(out), C.byref(ns)))
-    assert out.buf != d.buf and ns.value > 0
+    wgf.check(wgf.lib().wgf_launch_elementwise(dev.h, C.byref(d), ops, C.c_uint32(n), C.c_int32(0), C.byref(out), C.byref(timing)))
+    # the timing handle is read later (PerformanceQueries, src/query.rs:78-112): the launch did not wait
+    ns, count = C.c_uint64(), C.c_uint32()
+    wgf.check(wgf.lib().wgf_timing_kernel_count(timing, C.byref(count)))
+    wgf.check(wgf.lib().wgf_timing_elapsed_ns(timing, C.byref(ns)))
+    wgf.check(wgf.lib().wgf_timing_release(timing))
+    assert out.buf != d.buf and ns.value > 0 and count.value == 1
     ref = (orc.Ref(x) * 2.0 + 1.0).sin().numpy()
     got = fetch(wgf, out, np.float32)
     assert orc.ulp_diff_f32(got, ref).max() <= 2
@@ -117,7 +122,7 @@ def test_launch_matmul_resize_slice_assign(wgf, dev, orc):
     a, bm = g.standard_normal((37, 50)).astype(np.float32), g.standard_normal((50, 21)).astype(np.float32)
     ba, bb = Buf(wgf, dev, a), Buf(wgf, dev, bm)
     da, db, out = ba.desc(), bb.desc(), wgf.TensorDesc()
-    wgf.check(wgf.lib().wgf_launch_matmul(dev.h, C.byref(da), C.byref(db), C.byref(out), None))
+    wgf.check(wgf.lib().wgf_launch_matmul(dev.h, C.byref(da), C.byref(db), C.c_uint32(wgf.F32), C.byref(out), None))
     got = fetch(wgf, out, np.float32)
     ref = a.astype(np.float64) @ bm.astype(np.float64)
     assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-4
@@ -125,7 +130,7 @@ def test_launch_matmul_resize_slice_assign(wgf, dev, orc):
     dat = ba.desc(shape=(50, 37), strides=(1, 50))
     bc = Buf(wgf, dev, g.standard_normal((37, 8)).astype(np.float32))
     dc = bc.desc()
-    wgf.check(wgf.lib().wgf_launch_matmul(dev.h, C.byref(dat), C.byref(dc), C.byref(out), None))
+    wgf.check(wgf.lib().wgf_launch_matmul(dev.h, C.byref(dat), C.byref(dc), C.c_uint32(wgf.F32), C.byref(out), None))
     got = fetch(wgf, out, np.float32)
     # resize: zero-filled larger tensor with the input in its leading box (src/resize.rs:121-130)
     ns = (C.c_int64 * 2)(40, 64)
@@ -174,3 +179,45 @@ def test_buffer_use_count_and_bad_descriptors(wgf, dev):
     assert wgf.STATUS[rc] == "INVALID_ARGUMENT"
     assert wgf.STATUS[wgf.lib().wgf_buffer_release(None)] == "INVALID_HANDLE"
     b.release()
+
+
+def test_matmul_accumulator_type_and_async_upload(wgf, dev):
+    """The accumulator of wgf_launch_matmul is f32 for every element type: asking for another one is
+    refused, not ignored.  wgf_buffer_upload_async copies from page-locked memory without waiting and
+    hands back a handle that can be waited for and gives the copy time."""
+    g = seeded(4, 11)
+    a, bm = g.standard_normal((64, 64)).astype(np.float16), g.standard_normal((64, 64)).astype(np.float16)
+    ba, bb = Buf(wgf, dev, a), Buf(wgf, dev, bm)
+    da, db, out = ba.desc(), bb.desc(), wgf.TensorDesc()
+    rc = wgf.lib().wgf_launch_matmul(dev.h, C.byref(da), C.byref(db), C.c_uint32(wgf.F16), C.byref(out), None)
+    assert wgf.STATUS[rc] == "UNSUPPORTED"
+    rc = wgf.lib().wgf_launch_matmul(dev.h, C.byref(da), C.byref(db), C.c_uint32(77), C.byref(out), None)
+    assert wgf.STATUS[rc] == "DTYPE"
+    timing = C.c_void_p()
+    wgf.check(wgf.lib().wgf_launch_matmul(dev.h, C.byref(da), C.byref(db), C.c_uint32(wgf.F32), C.byref(out), C.byref(timing)))
+    ns = C.c_uint64()
+    wgf.check(wgf.lib().wgf_timing_elapsed_ns(timing, C.byref(ns)))
+    wgf.check(wgf.lib().wgf_timing_release(timing))
+    got = fetch(wgf, out, np.float16).astype(np.float64)
+    ref = a.astype(np.float64) @ bm.astype(np.float64)
+    assert ns.value > 0 and np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-2
+    # asynchronous upload into the middle of a buffer
+    n = 1 << 20
+    pin = wgf.PinnedArray((n,), np.float32)
+    pin.array[...] = g.standard_normal(n, dtype=np.float32)
+    buf = C.c_void_p()
+    wgf.check(wgf.lib().wgf_buffer_alloc(dev.h, C.c_uint64(8 * n), C.c_int32(1), C.byref(buf)))
+    done = C.c_void_p()
+    wgf.check(wgf.lib().wgf_buffer_upload_async(buf, C.c_uint64(4 * n), C.c_void_p(pin.ptr.value), C.c_uint64(4 * n), C.byref(done)))
+    wgf.check(wgf.lib().wgf_timing_wait(done))
+    wgf.check(wgf.lib().wgf_timing_elapsed_ns(done, C.byref(ns)))
+    wgf.check(wgf.lib().wgf_timing_release(done))
+    back = np.empty(2 * n, np.float32)
+    wgf.check(wgf.lib().wgf_buffer_download(buf, C.c_uint64(0), back.ctypes.data_as(C.c_void_p), C.c_uint64(8 * n)))
+    wgf.check(wgf.lib().wgf_buffer_release(buf))
+    assert ns.value > 0 and not back[:n].any() and np.array_equal(back[n:], pin.array)
+    pageable = np.zeros(16, np.float32)
+    wgf.check(wgf.lib().wgf_buffer_alloc(dev.h, C.c_uint64(64), C.c_int32(0), C.byref(buf)))
+    rc = wgf.lib().wgf_buffer_upload_async(buf, C.c_uint64(0), pageable.ctypes.data_as(C.c_void_p), C.c_uint64(64), None)
+    wgf.check(wgf.lib().wgf_buffer_release(buf))
+    assert wgf.STATUS[rc] == "INVALID_ARGUMENT"

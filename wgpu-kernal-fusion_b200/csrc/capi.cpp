@@ -22,6 +22,11 @@ struct wgf_tensor {
 struct wgf_comm {
     std::shared_ptr<Comm> ref;
 };
+// Event pairs of the kernels (or the copy) one call queued; read with wgf_timing_elapsed_ns.
+struct wgf_timing {
+    DeviceRef dev;
+    std::vector<TimingRecord> recs;
+};
 
 namespace {
 
@@ -114,34 +119,35 @@ int apply_chain(Program& p, int v, const wgf_ew_op* chain, uint32_t n) {
     return v;
 }
 
-// Runs `f` with a private timing sink and, if asked, waits and reports the device time.
+// Runs `f` with a private timing sink.  With `timing` given, the event pairs of the kernels `f`
+// queued go into a new handle; nothing waits (PerformanceQueries of the crate are read later too,
+// src/query.rs:78-112).
 template <typename F>
-void timed(Device& dev, uint64_t* elapsed_ns, F&& f) {
-    std::vector<TimingRecord> recs;
+void timed(const DeviceRef& devref, wgf_timing** timing, F&& f) {
+    Device& dev = *devref;
+    std::unique_ptr<wgf_timing> t;
+    if (timing) {
+        *timing = nullptr;
+        t.reset(new wgf_timing{devref, {}});
+    }
     bool was = dev.timing;
-    dev.timing = elapsed_ns != nullptr;
-    dev.sink = elapsed_ns ? &recs : nullptr;
+    dev.timing = timing != nullptr;
+    dev.sink = timing ? &t->recs : nullptr;
     try {
         f();
     } catch (...) {
         dev.sink = nullptr;
         dev.timing = was;
+        if (t)
+            for (auto& r : t->recs) {
+                dev.recycle(r.start);
+                dev.recycle(r.stop);
+            }
         throw;
     }
     dev.sink = nullptr;
     dev.timing = was;
-    if (elapsed_ns) {
-        double total = 0;
-        for (auto& r : recs) {
-            float ms = 0;
-            WGF_CUDA(cudaEventSynchronize(r.stop));
-            WGF_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
-            total += ms;
-            dev.recycle(r.start);
-            dev.recycle(r.stop);
-        }
-        *elapsed_ns = (uint64_t)(total * 1e6);
-    }
+    if (timing) *timing = t.release();
 }
 
 }  // namespace
@@ -153,7 +159,7 @@ void set_last_error(const std::string& msg) { g_last_error = msg; }
 extern "C" {
 
 const char* wgf_last_error(void) { return g_last_error.c_str(); }
-int32_t wgf_abi_version(void) { return 1; }
+int32_t wgf_abi_version(void) { return 2; }
 
 // ---------------------------------------------------------------- device
 int32_t wgf_device_create(int32_t ordinal, wgf_device** out) {
@@ -259,6 +265,23 @@ int32_t wgf_buffer_download(wgf_buffer* buf, uint64_t offset_bytes, void* dst, u
         buf->ref->dev->download(*buf->ref, offset_bytes, dst, bytes);
     });
 }
+int32_t wgf_buffer_upload_async(wgf_buffer* buf, uint64_t offset_bytes, const void* src, uint64_t bytes,
+                                wgf_timing** done) {
+    return guard([&] {
+        REQUIRE(buf);
+        WGF_CHECK(src || !bytes, WGF_ERR_INVALID_ARGUMENT, "null source");
+        if (done) *done = nullptr;
+        Device& dev = *buf->ref->dev;
+        TimingRecord rec;
+        const bool copies = bytes && !dev.dry;
+        dev.upload_async(*buf->ref, offset_bytes, src, bytes, done && copies ? &rec : nullptr);
+        if (done) {
+            std::unique_ptr<wgf_timing> t(new wgf_timing{buf->ref->dev, {}});
+            if (copies) t->recs.push_back(rec);
+            *done = t.release();
+        }
+    });
+}
 int32_t wgf_buffer_device_ptr(wgf_buffer* buf, void** ptr, uint64_t* bytes) {
     return guard([&] {
         REQUIRE(buf);
@@ -279,10 +302,53 @@ int32_t wgf_host_free(void* ptr) {
     });
 }
 
+// ---------------------------------------------------------------- timing handles
+int32_t wgf_timing_elapsed_ns(wgf_timing* t, uint64_t* out_ns) {
+    return guard([&] {
+        REQUIRE(t);
+        REQUIRE(out_ns);
+        t->dev->make_current();
+        double total = 0;
+        for (auto& r : t->recs) {
+            float ms = 0;
+            WGF_CUDA(cudaEventSynchronize(r.stop));
+            WGF_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
+            total += ms;
+        }
+        *out_ns = (uint64_t)(total * 1e6);
+    });
+}
+int32_t wgf_timing_wait(wgf_timing* t) {
+    return guard([&] {
+        REQUIRE(t);
+        t->dev->make_current();
+        for (auto& r : t->recs) WGF_CUDA(cudaEventSynchronize(r.stop));
+    });
+}
+int32_t wgf_timing_kernel_count(wgf_timing* t, uint32_t* out) {
+    return guard([&] {
+        REQUIRE(t);
+        REQUIRE(out);
+        *out = (uint32_t)t->recs.size();
+    });
+}
+int32_t wgf_timing_release(wgf_timing* t) {
+    return guard([&] {
+        REQUIRE(t);
+        for (auto& r : t->recs) {
+            // an event still in flight may be re-recorded by its next user: wait for it first
+            cudaEventSynchronize(r.stop);
+            t->dev->recycle(r.start);
+            t->dev->recycle(r.stop);
+        }
+        delete t;
+    });
+}
+
 // ---------------------------------------------------------------- kernel-level launches
 int32_t wgf_launch_elementwise(wgf_device* dev, const wgf_tensor_desc* in, const wgf_ew_op* chain,
                                uint32_t n_ops, int32_t inplace_ok, wgf_tensor_desc* out,
-                               uint64_t* elapsed_ns) {
+                               wgf_timing** timing) {
     return guard([&] {
         REQUIRE(dev);
         REQUIRE(out);
@@ -292,7 +358,7 @@ int32_t wgf_launch_elementwise(wgf_device* dev, const wgf_tensor_desc* in, const
         int v = p.load(p.new_slot(x.dtype), x.dtype, VKind::Elem);
         p.result = apply_chain(p, v, chain, n_ops);
         TensorData y;
-        timed(*dev->ref, elapsed_ns,
+        timed(dev->ref, timing,
               [&] { y = run_elementwise(*dev->ref, p, {x}, x.layout.shape, inplace_ok ? 0 : -1); });
         bool aliased = y.buf.get() == in->buf->ref.get();
         to_desc(y, aliased ? in->buf : nullptr, out);
@@ -302,7 +368,7 @@ int32_t wgf_launch_elementwise(wgf_device* dev, const wgf_tensor_desc* in, const
 int32_t wgf_launch_pairwise(wgf_device* dev, const wgf_tensor_desc* a, const wgf_tensor_desc* b,
                             const wgf_ew_op* pre_a, uint32_t n_pre_a, const wgf_ew_op* pre_b,
                             uint32_t n_pre_b, uint32_t opcode, const wgf_ew_op* post, uint32_t n_post,
-                            wgf_tensor_desc* out, uint64_t* elapsed_ns) {
+                            wgf_tensor_desc* out, wgf_timing** timing) {
     return guard([&] {
         REQUIRE(dev);
         REQUIRE(out);
@@ -315,7 +381,7 @@ int32_t wgf_launch_pairwise(wgf_device* dev, const wgf_tensor_desc* a, const wgf
         WGF_CHECK(p.ins[va].dtype == p.ins[vb].dtype, WGF_ERR_DTYPE, "pairwise operands must have equal element types");
         p.result = apply_chain(p, p.binary((uint16_t)opcode, va, vb), post, n_post);
         TensorData z;
-        timed(*dev->ref, elapsed_ns, [&] { z = run_elementwise(*dev->ref, p, {x, y}, x.layout.shape, -1); });
+        timed(dev->ref, timing, [&] { z = run_elementwise(*dev->ref, p, {x, y}, x.layout.shape, -1); });
         to_desc(z, nullptr, out);
     });
 }
@@ -323,7 +389,7 @@ int32_t wgf_launch_pairwise(wgf_device* dev, const wgf_tensor_desc* a, const wgf
 int32_t wgf_launch_reduce(wgf_device* dev, const wgf_tensor_desc* in, uint32_t axis,
                           const wgf_ew_op* pre, uint32_t n_pre, uint32_t reduce_opcode,
                           const wgf_ew_op* post, uint32_t n_post, wgf_tensor_desc* out,
-                          uint64_t* elapsed_ns) {
+                          wgf_timing** timing) {
     return guard([&] {
         REQUIRE(dev);
         REQUIRE(out);
@@ -342,25 +408,28 @@ int32_t wgf_launch_reduce(wgf_device* dev, const wgf_tensor_desc* in, uint32_t a
         int v = apply_chain(p, p.load(p.new_slot(x.dtype), x.dtype, VKind::Elem), pre, n_pre);
         p.result = apply_chain(p, p.row_reduce((uint16_t)reduce_opcode, v), post, n_post);
         TensorData y;
-        timed(*dev->ref, elapsed_ns, [&] { y = run_rows(*dev->ref, p, {x}, l.shape, false, -1); });
+        timed(dev->ref, timing, [&] { y = run_rows(*dev->ref, p, {x}, l.shape, false, -1); });
         to_desc(y, nullptr, out);
     });
 }
 
 int32_t wgf_launch_matmul(wgf_device* dev, const wgf_tensor_desc* a, const wgf_tensor_desc* b,
-                          wgf_tensor_desc* out, uint64_t* elapsed_ns) {
+                          uint32_t acc_dtype, wgf_tensor_desc* out, wgf_timing** timing) {
     return guard([&] {
         REQUIRE(dev);
         REQUIRE(out);
+        WGF_CHECK(valid_dtype(acc_dtype), WGF_ERR_DTYPE, "unknown accumulator type");
+        WGF_CHECK(acc_dtype == WGF_F32, WGF_ERR_UNSUPPORTED,
+                  "matmul accumulates in f32 for every element type (tensor memory / FFMA): pass WGF_F32");
         TensorData x = from_desc(a, true), y = from_desc(b, true), z;
-        timed(*dev->ref, elapsed_ns, [&] { z = run_matmul(*dev->ref, x, y); });
+        timed(dev->ref, timing, [&] { z = run_matmul(*dev->ref, x, y); });
         to_desc(z, nullptr, out);
     });
 }
 
 int32_t wgf_launch_resize(wgf_device* dev, const wgf_tensor_desc* in, uint32_t new_rank,
                           const int64_t* new_shape, const int64_t* fill_shape, wgf_tensor_desc* out,
-                          uint64_t* elapsed_ns) {
+                          wgf_timing** timing) {
     return guard([&] {
         REQUIRE(dev);
         REQUIRE(out);
@@ -377,7 +446,7 @@ int32_t wgf_launch_resize(wgf_device* dev, const wgf_tensor_desc* in, uint32_t n
         WGF_CHECK(nfill == x.layout.numel(), WGF_ERR_SHAPE, "fill box and input differ in element count");
         Device& d = *dev->ref;
         TensorData y;
-        timed(d, elapsed_ns, [&] {
+        timed(dev->ref, timing, [&] {
             y.dtype = x.dtype;
             y.layout = Layout::contiguous(ns);
             y.buf = d.alloc((size_t)std::max<int64_t>(y.layout.numel(), 1) * dtype_size(x.dtype), true);
@@ -397,7 +466,7 @@ int32_t wgf_launch_resize(wgf_device* dev, const wgf_tensor_desc* in, uint32_t n
 }
 
 int32_t wgf_launch_slice_assign(wgf_device* dev, const wgf_tensor_desc* target, const int64_t* starts,
-                                const int64_t* ends, const wgf_tensor_desc* value, uint64_t* elapsed_ns) {
+                                const int64_t* ends, const wgf_tensor_desc* value, wgf_timing** timing) {
     return guard([&] {
         REQUIRE(dev);
         REQUIRE(starts);
@@ -413,7 +482,7 @@ int32_t wgf_launch_slice_assign(wgf_device* dev, const wgf_tensor_desc* target, 
                       "slice_assign range outside the target");
         TensorData window = t;
         window.layout = op.apply(t.layout);
-        timed(*dev->ref, elapsed_ns, [&] { run_copy(*dev->ref, window, v); });
+        timed(dev->ref, timing, [&] { run_copy(*dev->ref, window, v); });
     });
 }
 
@@ -459,7 +528,7 @@ int32_t wgf_tensor_from_host_pinned(wgf_device* dev, uint32_t dtype, uint32_t ra
         size_t bytes = (size_t)td.layout.numel() * dtype_size(td.dtype);
         WGF_CHECK(data || !bytes, WGF_ERR_INVALID_ARGUMENT, "null data");
         td.buf = dev->ref->alloc(std::max<size_t>(bytes, 1), false);
-        if (bytes) dev->ref->upload_async(*td.buf, data, bytes);
+        if (bytes) dev->ref->upload_async(*td.buf, 0, data, bytes);
         *out = wrap(make_tensor(dev->ref, td));
     })
 }

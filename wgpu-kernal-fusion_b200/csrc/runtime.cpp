@@ -444,8 +444,8 @@ void Device::upload(const Buffer& b, size_t off, const void* src, size_t n) {
 // device stream is doing (kernels, a download in the other PCIe direction).  The copy is ordered
 // behind everything queued on the device stream so far, because the pool may have handed out a block
 // that earlier kernels still use; the buffer carries the completion event (Buffer::pending).
-void Device::upload_async(Buffer& b, const void* src, size_t n) {
-    WGF_CHECK(n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "upload past the end of the buffer");
+void Device::upload_async(Buffer& b, size_t off, const void* src, size_t n, TimingRecord* rec) {
+    WGF_CHECK(off + n <= b.bytes, WGF_ERR_INVALID_ARGUMENT, "upload past the end of the buffer");
     refuse_while_recording("an upload");
     if (!n || dry) return;
     make_current();
@@ -461,7 +461,14 @@ void Device::upload_async(Buffer& b, const void* src, size_t n) {
     WGF_CUDA(cudaEventRecord(before, stream));
     WGF_CUDA(cudaStreamWaitEvent(upload_stream_, before, 0));
     recycle(before);
-    WGF_CUDA(cudaMemcpyAsync(b.ptr, src, n, cudaMemcpyHostToDevice, upload_stream_));
+    if (rec) {
+        rec->start = event();
+        rec->stop = event();
+        rec->what = "upload";
+        WGF_CUDA(cudaEventRecord(rec->start, upload_stream_));
+    }
+    WGF_CUDA(cudaMemcpyAsync((char*)b.ptr + off, src, n, cudaMemcpyHostToDevice, upload_stream_));
+    if (rec) WGF_CUDA(cudaEventRecord(rec->stop, upload_stream_));
     b.pending = event();
     WGF_CUDA(cudaEventRecord(b.pending, upload_stream_));
 }

@@ -90,7 +90,8 @@ struct Device : std::enable_shared_from_this<Device> {
     // ---- memory ----
     BufferRef alloc(size_t bytes, bool zero);
     void upload(const Buffer& b, size_t off, const void* src, size_t n);
-    void upload_async(Buffer& b, const void* src, size_t n);   // src must be page-locked
+    // src must be page-locked; with `rec`, an event pair around the copy (on the upload stream) is stored there
+    void upload_async(Buffer& b, size_t off, const void* src, size_t n, TimingRecord* rec = nullptr);
     void download(const Buffer& b, size_t off, void* dst, size_t n);
     // 65536 zero-initialised u32 tickets for kernels that elect a last-arriving CTA; every
     // such kernel leaves them zero again.
