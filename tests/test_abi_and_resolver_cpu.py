@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol(wgf):
     assert len(names) >= 60
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, f"declared in wgf.h but not exported: {missing}"
-    assert lib.wgf_abi_version() == 1
+    assert lib.wgf_abi_version() == 2
 
 
 def test_no_gpu_means_error_not_fallback(wgf):
