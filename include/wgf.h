@@ -361,8 +361,8 @@ int32_t wgf_schedule_destroy(wgf_schedule* s);
 /* ======================================================================================
  * Reduction for callers that must not allocate.  (No counterpart in the crate: this entry
  * point exists for hosts of THIS library that cannot let a compute call reach the device
- * allocator -- code running inside a CUDA stream capture, real-time loops that rule out calls
- * of unbounded latency, embedders with a device-memory budget fixed up front.)
+ * allocator -- real-time loops that rule out calls of unbounded latency, embedders with a
+ * device-memory budget fixed up front, in which a hidden cudaMalloc would break the budget.)
  *
  * out[0] = reduce(pre(x[0..n))): x, out are DEVICE pointers owned by the caller, n <=
  * 2^31 f32 elements (more is rejected with WGF_ERR_UNSUPPORTED); `pre_opcode` is WGF_OP_EXP,

@@ -1,8 +1,9 @@
-"""wgf_full_reduce_f32_noalloc: the full-tensor reduction for callers that cannot allocate
-(work issued inside a CUDA stream capture, real-time loops, embedders with a fixed device-memory
-budget).  Its scratch is a fixed array inside the library, so it is checked here against the
-regular entry point, which takes its scratch from the device pool: same inputs, two calls in a
-row (the array keeps what the first call left behind), reduction tolerance 1e-5 relative.
+"""wgf_full_reduce_f32_noalloc: the full-tensor reduction for callers of this library that cannot
+let a compute call reach the device allocator (real-time loops that rule out calls of unbounded
+latency, embedders whose device-memory budget is fixed up front).  Its scratch is a fixed array
+inside the library image, so it is checked here against the regular entry point, which takes its
+scratch from the device pool -- same inputs, two calls in a row (the array keeps what the first call
+left behind) -- and against float64 numpy; reduction tolerance 1e-5 relative.
 
 Collected last on purpose: a failure here cannot hide the result of any other test."""
 import ctypes as C
@@ -13,6 +14,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 NONE = 0xFFFFFFFF
+F32_MAX = np.float32(3.40282e38)
 
 
 def _noalloc(wgf, dev, x_desc, n, pre, red, out_desc, offset_elems=0):
@@ -26,37 +28,81 @@ def _noalloc(wgf, dev, x_desc, n, pre, red, out_desc, offset_elems=0):
                                            C.c_uint32(red), op, C.c_void_p(stream))
 
 
-def test_matches_pooled_reduce_twice_in_a_row(wgf, dev):
+def free_device_memory(ordinal):
+    """cudaMemGetInfo of the device: what ANY allocation on it, pooled or not, would lower."""
+    import torch
+    return torch.cuda.mem_get_info(ordinal)[0]
+
+
+def numpy_reduce(x, pre, red, wgf):
+    v = x.astype(np.float64)
+    v = {wgf.OP_EXP: np.exp, wgf.OP_SQR: np.square, wgf.OP_ABS: np.abs}.get(pre, lambda a: a)(v)
+    if v.size == 0:   # the reduction's identity
+        return {wgf.OP_SUM: 0.0, wgf.OP_PRODUCT: 1.0, wgf.OP_MAX: -float(F32_MAX), wgf.OP_MIN: float(F32_MAX)}[red]
+    return float({wgf.OP_SUM: np.sum, wgf.OP_PRODUCT: np.prod, wgf.OP_MAX: np.max, wgf.OP_MIN: np.min}[red](v))
+
+
+def close(got, want, red, wgf):
+    if red in (wgf.OP_MAX, wgf.OP_MIN):
+        return np.float32(got) == np.float32(want)
+    return abs(got - want) <= 1e-5 * abs(want)
+
+
+def test_matches_pooled_reduce_and_float64_twice_in_a_row(wgf, dev):
     g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 2 + 7))
     a = g.standard_normal((1500, 1031)).astype(np.float32)          # ragged length: 1 546 500 elements
     b = (g.standard_normal(4099) * 0.5).astype(np.float32)
+    p = (1 + 1e-3 * g.standard_normal(3000)).astype(np.float32)     # a product that stays near 1
     cases = [(a, wgf.OP_EXP, wgf.OP_SUM, lambda t: t.exp()), (b, NONE, wgf.OP_MAX, lambda t: t),
-             (a, wgf.OP_SQR, wgf.OP_SUM, lambda t: t.sqr()), (b, wgf.OP_ABS, wgf.OP_MIN, lambda t: t.abs())]
+             (a, wgf.OP_SQR, wgf.OP_SUM, lambda t: t.sqr()), (b, wgf.OP_ABS, wgf.OP_MIN, lambda t: t.abs()),
+             (p, NONE, wgf.OP_PRODUCT, lambda t: t), (b[:3], NONE, wgf.OP_SUM, lambda t: t)]
     out_t = dev.tensor(np.zeros(1, np.float32))
     out_desc = out_t.desc()
-    mem_before = dev.memory()
+    free_device_memory(dev.ordinal)                                 # sets up the measuring side's own context first
     for x, pre, red, chain in cases:
         t = dev.tensor(x.reshape(-1))
         d = t.desc()
-        # the existing entry point (scratch from the pool)
-        want = float(chain(t).reduce(red, 0).as_slice())
-        for _ in range(2):  # two calls in a row share the fixed scratch
-            reserved = dev.memory()[0]
+        want = float(chain(t).reduce(red, 0).as_slice())            # the existing entry point (scratch from the pool)
+        exact = numpy_reduce(x, pre, red, wgf)
+        for _ in range(2):                                          # two calls in a row share the fixed scratch
+            dev.sync()
+            free_before = free_device_memory(dev.ordinal)
             wgf.check(_noalloc(wgf, dev, d, x.size, pre, red, out_desc))
+            dev.sync()
+            assert free_device_memory(dev.ordinal) >= free_before   # nothing was taken from the device
             got = float(out_t_download(wgf, dev, out_desc))
-            assert dev.memory()[0] == reserved            # the pool did not grow: nothing was allocated
-            if red in (wgf.OP_MAX, wgf.OP_MIN):
-                assert got == want
-            else:
-                assert abs(got - want) <= 1e-5 * abs(want)
-        # unaligned start (pointer 4 bytes past a 16-byte boundary) and short input
-        wgf.check(_noalloc(wgf, dev, d, x.size - 3, pre, red, out_desc, offset_elems=1))
-        got = float(out_t_download(wgf, dev, out_desc))
-        want2 = float(chain(dev.tensor(x.reshape(-1)[1:x.size - 2])).reduce(red, 0).as_slice())
-        assert got == want2 if red in (wgf.OP_MAX, wgf.OP_MIN) else abs(got - want2) <= 1e-5 * abs(want2)
+            assert close(got, want, red, wgf), (got, want)
+            assert close(got, exact, red, wgf), (got, exact)
+        if x.size > 8:
+            # unaligned start (pointer 4 bytes past a 16-byte boundary) and short input
+            wgf.check(_noalloc(wgf, dev, d, x.size - 3, pre, red, out_desc, offset_elems=1))
+            got = float(out_t_download(wgf, dev, out_desc))
+            assert close(got, numpy_reduce(x.reshape(-1)[1:x.size - 2], pre, red, wgf), red, wgf)
+        # nothing to reduce: the identity of the reduction
+        wgf.check(_noalloc(wgf, dev, d, 0, pre, red, out_desc))
+        assert close(float(out_t_download(wgf, dev, out_desc)), numpy_reduce(x[:0], pre, red, wgf), red, wgf)
         lib_release(wgf, d)
     lib_release(wgf, out_desc)
-    assert mem_before[0] >= 0
+
+
+def test_second_gpu_has_its_own_scratch_address(wgf, dev):
+    """The array's device address is looked up once per GPU, with that GPU current: a call whose
+    input lives on GPU 1 after one on GPU 0 must use GPU 1's copy of the array."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    g = np.random.Generator(np.random.PCG64(0xB2000000 + 16 * 2 + 8))
+    x = g.standard_normal(1 << 20).astype(np.float32)
+    devices = [dev, wgf.Device(1)]
+    for _ in range(2):
+        for d in devices:
+            t, o = d.tensor(x), d.tensor(np.zeros(1, np.float32))
+            td, od = t.desc(), o.desc()
+            wgf.check(_noalloc(wgf, d, td, x.size, wgf.OP_SQR, wgf.OP_SUM, od))
+            got = float(out_t_download(wgf, d, od))
+            assert abs(got - numpy_reduce(x, wgf.OP_SQR, wgf.OP_SUM, wgf)) <= 1e-5 * got
+            lib_release(wgf, td)
+            lib_release(wgf, od)
 
 
 def test_rejects_what_it_cannot_do(wgf, dev):

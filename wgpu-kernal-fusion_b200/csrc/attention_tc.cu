@@ -33,6 +33,7 @@
 // error word instead of hanging.
 #include <algorithm>
 #include <cmath>
+#include <mutex>
 #include <type_traits>
 
 #include "attention.hpp"
@@ -883,6 +884,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
 }
 
+#include "attention_ts.cuh"
+
 }  // namespace
 
 bool attention_supported(DType dt, int64_t seq_q, int64_t seq_k, int64_t head_dim) {
@@ -964,20 +967,44 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     p.o_hs = D;
     p.o_bs = S * heads * D;
     p.error = dev.error_word();
-    // two query tiles per CTA (attention_tc2_kernel) unless switched off; one per CTA otherwise
-    const bool pairs = !getenv("WGF_ATT_SINGLE");
+    // Kernel forms, newest first: P through tensor memory (attention_ts_kernel, the default); P through
+    // shared memory with two query tiles per CTA (WGF_ATT_SMEM_P=1: attention_tc2_kernel, one pass, or
+    // two with WGF_ATT_TWO_PASS=1); one query tile per CTA (WGF_ATT_SINGLE=1).
+    const bool single = getenv("WGF_ATT_SINGLE") != nullptr;
+    const bool two_pass = getenv("WGF_ATT_TWO_PASS") != nullptr;
+    const bool smem_p = single || two_pass || getenv("WGF_ATT_SMEM_P") != nullptr;
+    const bool pairs = !single;
     const long long items = pairs ? BH * ((S / 128 + 1) / 2) : BH * (S / 128);
     const unsigned grid = (unsigned)std::min<long long>(items, dev.sm_count);
-    static bool attr_set[6] = {false, false, false, false, false, false};
+    // the opt-in to more than 48 KiB of dynamic shared memory is a per-device attribute of the kernel
+    static std::mutex attr_mu;
+    static bool attr_set[64][12] = {};
     auto launch = [&](auto kernel, int slot, int threads, int smem_bytes, auto* optr) {
-        if (!attr_set[slot]) {
-            WGF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-            attr_set[slot] = true;
+        {
+            std::lock_guard<std::mutex> lk(attr_mu);
+            const int ord = dev.ordinal >= 0 && dev.ordinal < 64 ? dev.ordinal : 0;
+            if (!attr_set[ord][slot] || dev.ordinal >= 64) {
+                WGF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+                attr_set[ord][slot] = true;
+            }
         }
         kernel<<<grid, threads, smem_bytes, dev.stream>>>(mq, mk, mv, optr, p);
     };
     dev.begin_launch("attention_tc");
-    if (pairs) {
+    if (!smem_p) {
+        // share of the exponentials computed on the FMA pipe instead of the special-function unit
+        const char* pe = getenv("WGF_ATT_POLY");
+        const int poly = pe ? atoi(pe) : 0;
+        if (bf16) {
+            if (poly == 2) launch(attention_ts_kernel<__nv_bfloat16, 2>, 9, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
+            else if (poly == 4) launch(attention_ts_kernel<__nv_bfloat16, 4>, 10, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
+            else launch(attention_ts_kernel<__nv_bfloat16, 0>, 8, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
+        } else {
+            if (poly == 2) launch(attention_ts_kernel<__half, 2>, 7, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
+            else if (poly == 4) launch(attention_ts_kernel<__half, 4>, 11, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
+            else launch(attention_ts_kernel<__half, 0>, 6, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
+        }
+    } else if (pairs) {
         const bool online = !getenv("WGF_ATT_TWO_PASS");   // one pass (online softmax) unless switched off
         if (online) {
             if (bf16) launch(attention_tc2_kernel<__nv_bfloat16, true>, 5, A2_THREADS, A2_SMEM, (__nv_bfloat16*)out.base_ptr());

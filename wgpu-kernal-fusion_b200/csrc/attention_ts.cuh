@@ -1,0 +1,384 @@
+// attention_ts_kernel: fused softmax attention whose probabilities never leave tensor memory.
+// Included by attention_tc.cu (shares AtParams, at_idesc, decode_pair and the tile constants).
+//
+// What changes against attention_tc2_kernel.  There the softmax warps write P as a 16-bit tile
+// into shared memory, from where the P V product reads it back as its A operand: per key tile and
+// query tile 32 KiB written and 32 KiB read through the same shared memory that feeds the tensor
+// cores their other operands (an M128 x N128 x K16 tcgen05.mma with both operands in shared memory
+// reads 8 KiB per 64 cycles of math, all the SM delivers), plus a proxy fence and a hand-over per
+// tile.  Here P goes back into TENSOR memory, packed two 16-bit values per 32-bit column over the
+// first 64 of the 128 columns that held S (tcgen05.st), and P V takes its A operand from there
+// (tcgen05.mma with the A operand in tensor memory): the P V products read only V from shared
+// memory, nothing is stored to it by the softmax warps, and the four tiles of shared memory that
+// held Q0, Q1, P0, P1 shrink to two, which makes room for a 5-stage K / V ring.
+//
+// Work and roles (320 threads, one persistent CTA per SM, two adjacent query tiles per item):
+//   warp 0     TMA producer (one lane): Q0, Q1, then K(0), V(0), K(1), V(1), ... through the ring
+//   warp 1     MMA issuer (one lane), per key tile j and tile t:  P V_t(j), then S_t(j+1) = Q_t K(j+1)^T.
+//              The tensor pipe executes one thread's MMAs in issue order, so S_t(j+1) overwrites the
+//              columns of P_t(j) only after P V_t(j) has read them, and no barrier guards that.
+//   warps 2-5  softmax of tile 0, warps 6-9 of tile 1: thread r owns row r (tensor-memory lane r).
+//              One sweep: the 128 scores of the row are loaded into registers once; maximum,
+//              exponentials, row sum and the packed P come from the registers.
+// Online softmax with a lazily updated reference maximum as in attention_tc2_kernel: P =
+// exp2(s * c - ref); ref follows the running maximum only when that has outgrown it by more than
+// 2^AT_LAG, and only then O and l of the row are rescaled (O through tcgen05.ld / tcgen05.st).
+// When S_t(j) is complete every MMA issued before it is complete too (a commit covers all earlier
+// MMAs of the thread), P V_t(j-1) among them: O_t is at rest while the softmax warps of tile t work.
+// Tensor memory: S_t / P_t in columns 128 t, O_t in 256 + 128 t.  Every wait is bounded.
+
+constexpr int TS_STAGES = 5;
+constexpr int TS_THREADS = 320;
+constexpr int TS_SMEM = (2 + TS_STAGES) * AT_TILE + 1024 /*alignment slack*/ + 512 /*barriers*/;
+enum {
+    TQ_FULL = 0, TQ_EMPTY = 2, TKV_FULL = 4, TKV_EMPTY = TKV_FULL + TS_STAGES, TS_FULL = TKV_EMPTY + TS_STAGES,
+    TP_FULL = TS_FULL + 2, TO_FULL = TP_FULL + 2, TO_EMPTY = TO_FULL + 2, TS_BARS = TO_EMPTY + 2
+};
+
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (128 rows x 16 K-elements, two per 32-bit
+// column) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                            unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 16 registers of every lane -> 16 columns of the warp's 32 tensor-memory lanes.
+__device__ __forceinline__ void tmem_st_32x16(unsigned taddr, const unsigned* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+        : "memory");
+}
+
+// 2^x for x <= ~2^7 on the FMA and ALU pipes instead of the special-function unit (which gives 16
+// results per clock and SM: 1024 clocks for a 128 x 128 tile, as long as the tile's two MMAs):
+// x = n + f with n the nearest integer (magic-number rounding) and f in [-0.5, 0.5]; 2^f from a
+// cubic (relative error 1.0e-4, below the 4.9e-4 / 3.9e-3 rounding of the 16-bit P it feeds); n
+// goes into the exponent field by an integer add.  Arguments below -126 give 2^-126 * [0.7, 1.5):
+// nothing against a row maximum near 1.
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -126.f);
+    const float magic = 12582912.f;                 // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+    const float xr = x + magic;
+    const float f = x - (xr - magic);
+    float pf = fmaf(0.05500893f, f, 0.24221096f);       // minimax cubic for 2^f on [-0.5, 0.5] with p(0) = 1
+    pf = fmaf(pf, f, 0.69328293f);
+    pf = fmaf(pf, f, 1.0f);
+    return __int_as_float(__float_as_int(pf) + (__float_as_int(xr) << 23));
+}
+
+// POLY: every POLY-th pair of exponentials... 0 = all on the special-function unit; k > 0 = one pair in
+// k goes through ex2_poly (2 = half of them, 4 = a quarter).
+template <typename T, int POLY>
+__global__ void __launch_bounds__(TS_THREADS, 1)
+attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, T* __restrict__ O, const __grid_constant__ AtParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // [Q0][Q1][ring ...]
+    const unsigned q_smem0 = smem_u32(smem), ring = q_smem0 + 2 * AT_TILE;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (2 + TS_STAGES) * AT_TILE);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + TS_BARS);
+    const unsigned bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (unsigned)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TS_BARS; ++i) {
+            // one arrival per softmax warp of the tile
+            const bool four = (i >= TP_FULL && i < TP_FULL + 2) || (i >= TO_EMPTY && i < TO_EMPTY + 2);
+            mbar_init(bar(i), four ? 4 : 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const int n_pairs = (p.n_q_tiles + 1) / 2;
+    const long long items = (long long)p.bh * n_pairs;
+    auto v_row = [&](int row0, int b) { return p.v_heads > 0 ? (b / p.v_heads) * p.v_rows + row0 : row0; };
+    auto v_slab = [&](int b) { return p.v_heads > 0 ? b % p.v_heads : b; };
+    // key tiles of tile t of pair pt (0: the pair has no second tile)
+    auto tiles_of = [&](int pt, int t) -> int {
+        const int qt = 2 * pt + t;
+        if (qt >= p.n_q_tiles) return 0;
+        return p.causal ? qt + 1 : p.n_k_tiles;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            unsigned pos = 0;                          // tiles pushed so far: stage = pos % TS_STAGES
+            unsigned q_phase[2] = {1, 1};              // fresh "empty" barriers count as already released
+            bool ok = true;
+            auto push = [&](const CUtensorMap* map, int row0, int b) -> bool {
+                const unsigned stage = pos % TS_STAGES, phase = ((pos / TS_STAGES) & 1u) ^ 1u;
+                if (!mbar_wait(bar(TKV_EMPTY + stage), phase)) {
+                    atomicExch(p.error, 91u);
+                    return false;
+                }
+                const unsigned dst = ring + stage * AT_TILE;
+                mbar_expect_tx(bar(TKV_FULL + stage), AT_TILE);
+                tma_load_3d(dst, map, bar(TKV_FULL + stage), 0, row0, b);
+                tma_load_3d(dst + AT_PANEL, map, bar(TKV_FULL + stage), 64, row0, b);
+                ++pos;
+                return true;
+            };
+            for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                int b, pt;
+                decode_pair(p, n_pairs, w, b, pt);
+                const int n_max = max(tiles_of(pt, 0), tiles_of(pt, 1));
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (tiles_of(pt, t) == 0) continue;
+                    if (!mbar_wait(bar(TQ_EMPTY + t), q_phase[t])) {
+                        atomicExch(p.error, 90u);
+                        ok = false;
+                        break;
+                    }
+                    q_phase[t] ^= 1;
+                    const unsigned qs = q_smem0 + (unsigned)t * AT_TILE;
+                    mbar_expect_tx(bar(TQ_FULL + t), AT_TILE);
+                    tma_load_3d(qs, &map_q, bar(TQ_FULL + t), 0, (2 * pt + t) * 128, b);
+                    tma_load_3d(qs + AT_PANEL, &map_q, bar(TQ_FULL + t), 64, (2 * pt + t) * 128, b);
+                }
+                // the order in which the MMA warp takes them from the ring
+                for (int j = 0; j < n_max && ok; ++j) {
+                    ok = push(&map_k, j * 128, b);
+                    if (ok) ok = push(&map_v, v_row(j * 128, b), v_slab(b));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const unsigned idesc_s = at_idesc((unsigned)p.is_bf16, 0u), idesc_pv = at_idesc((unsigned)p.is_bf16, 1u);
+            unsigned pos = 0;                          // ring position of K(0) of the current item
+            unsigned q_phase[2] = {0, 0}, p_phase[2] = {0, 0}, o_phase[2] = {1, 1};
+            bool ok = true;
+            int nk[2];
+            auto wait_or = [&](int which, unsigned ph, unsigned code) -> bool {
+                if (mbar_wait(bar(which), ph)) return true;
+                atomicExch(p.error, code);
+                return false;
+            };
+            auto wait_ring = [&](unsigned at, unsigned code) -> bool {
+                return wait_or(TKV_FULL + (int)(at % TS_STAGES), (at / TS_STAGES) & 1u, code);
+            };
+            // S_t = Q_t K^T with K in ring position `at`
+            auto issue_s = [&](int t, unsigned at, bool last) {
+                const unsigned kt = ring + (at % TS_STAGES) * AT_TILE;
+                const unsigned qs = q_smem0 + (unsigned)t * AT_TILE;
+                const unsigned d = tmem_base + (unsigned)t * AT_S_COLS;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    // both K-major: rows of 128 bytes, 8-row groups 1024 bytes apart, 32 bytes per K
+                    // step inside a 64-column panel, the second panel 16 KiB further
+                    const unsigned off = (unsigned)(kk >> 2) * AT_PANEL + (unsigned)(kk & 3) * 32u;
+                    umma_f16(d, smem_desc(qs + off, 16, 1024), smem_desc(kt + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                }
+                umma_commit(bar(TS_FULL + t));
+                if (last) umma_commit(bar(TQ_EMPTY + t));   // Q_t is free once these are done
+            };
+            // O_t (+)= P_t V with V in ring position `at`; P_t in the first 64 columns of S_t
+            auto issue_pv = [&](int t, unsigned at, bool first, bool last) {
+                const unsigned vt = ring + (at % TS_STAGES) * AT_TILE;
+                const unsigned a = tmem_base + (unsigned)t * AT_S_COLS;
+                const unsigned d = tmem_base + AT_O_COL0 + (unsigned)t * 128u;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    // A = P from tensor memory: 16 keys = 8 columns per K step.  B = V, N-major: 64-column
+                    // panels 16 KiB apart (leading), 8-key groups 1024 bytes apart (stride), 16 keys =
+                    // 2048 bytes per K step
+                    const unsigned long long bdesc = smem_desc(vt + (unsigned)kk * 2048u, AT_PANEL, 1024);
+                    umma_f16_ts(d, a + (unsigned)kk * 8u, bdesc, idesc_pv, (first && kk == 0) ? 0u : 1u);
+                }
+                if (last) umma_commit(bar(TO_FULL + t));
+            };
+            for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                int b, pt;
+                decode_pair(p, n_pairs, w, b, pt);
+                nk[0] = tiles_of(pt, 0);
+                nk[1] = tiles_of(pt, 1);
+                const int n_max = max(nk[0], nk[1]);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (nk[t] == 0) continue;
+                    ok = wait_or(TQ_FULL + t, q_phase[t], 100u);
+                    q_phase[t] ^= 1;
+                }
+                if (!ok) break;
+                // S_t(0) for both tiles
+                if (!(ok = wait_ring(pos, 101u))) break;
+                tc_fence_after();
+                for (int t = 0; t < 2; ++t)
+                    if (nk[t] > 0) issue_s(t, pos, nk[t] == 1);
+                umma_commit(bar(TKV_EMPTY + (int)(pos % TS_STAGES)));
+                for (int j = 0; j < n_max && ok; ++j) {
+                    const unsigned at_v = pos + 2u * (unsigned)j + 1u, at_k = at_v + 1u;   // V(j), K(j+1)
+                    bool have_v = false, have_k = false;
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (j >= nk[t]) continue;
+                        if (j == 0) {                       // the previous item's O_t has been read out
+                            if (!(ok = wait_or(TO_EMPTY + t, o_phase[t], 102u))) break;
+                            o_phase[t] ^= 1;
+                        }
+                        if (!(ok = wait_or(TP_FULL + t, p_phase[t], 103u))) break;
+                        p_phase[t] ^= 1;
+                        if (!have_v) {
+                            if (!(ok = wait_ring(at_v, 104u))) break;
+                            have_v = true;
+                        }
+                        tc_fence_after();
+                        issue_pv(t, at_v, j == 0, j == nk[t] - 1);
+                        if (j + 1 < nk[t]) {
+                            if (!have_k) {
+                                if (!(ok = wait_ring(at_k, 105u))) break;
+                                have_k = true;
+                                tc_fence_after();
+                            }
+                            issue_s(t, at_k, j + 1 == nk[t] - 1);
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(bar(TKV_EMPTY + (int)(at_v % TS_STAGES)));
+                    if (j + 1 < n_max) umma_commit(bar(TKV_EMPTY + (int)(at_k % TS_STAGES)));
+                }
+                pos += 2u * (unsigned)n_max;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax (warps 2-5: tile 0, warps 6-9: tile 1)
+        const int t = (warp - 2) >> 2;
+        const int quarter = warp & 3;                       // tensor-memory lanes 32*quarter .. +31 belong to this warp
+        const int r = quarter * 32 + lane;                  // row of the query tile
+        const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+        const unsigned s_addr = lane_base + (unsigned)t * AT_S_COLS, o_addr = lane_base + AT_O_COL0 + (unsigned)t * 128u;
+        unsigned s_phase = 0, o_phase = 0;
+        bool ok = true;
+        auto wait_all = [&](int which, unsigned parity, unsigned code) -> bool {
+            bool got = mbar_wait(bar(which), parity);
+            got = __all_sync(0xffffffffu, got);
+            if (!got && lane == 0) atomicExch(p.error, code);
+            return got;
+        };
+        for (long long w = blockIdx.x; w < items && ok; w += gridDim.x) {
+            int b, pt;
+            decode_pair(p, n_pairs, w, b, pt);
+            const int n_kv = tiles_of(pt, t);
+            if (n_kv == 0) continue;                         // an odd tile count: the last pair has one tile
+            const int qt = 2 * pt + t;
+            float l_run = 0.f, ref = 0.f;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (!(ok = wait_all(TS_FULL + t, s_phase, 110u))) break;
+                s_phase ^= 1;
+                tc_fence_after();
+                float alpha = 1.f;
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                // the whole row of scores, once
+                unsigned v[128];
+                tmem_ld_32x32(s_addr, v);
+                tmem_ld_32x32(s_addr + 32u, v + 32);
+                tmem_ld_32x32(s_addr + 64u, v + 64);
+                tmem_ld_32x32(s_addr + 96u, v + 96);
+                tmem_ld_wait();
+                if (p.causal && j == qt) {   // only the key tile on the diagonal carries the mask
+#pragma unroll
+                    for (int i = 0; i < 128; ++i)
+                        if (i > r) v[i] = 0xff800000u;   // -inf above the diagonal
+                }
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < 128; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                const float mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2e;
+                // (key 0 is visible to every query, so the first tile gives every row a finite maximum)
+                const bool grow = j > 0 && mt > ref + AT_LAG;
+                if (j == 0) ref = mt;
+                if (grow) {
+                    alpha = ex2_approx(ref - mt);
+                    ref = mt;
+                }
+                if (__any_sync(0xffffffffu, grow)) {
+                    // S_t(j) is complete, so P V_t(j-1) is too: O_t is at rest.  Rescale this warp's 32
+                    // rows (lanes whose maximum did not grow multiply by 1).
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        unsigned o[32];
+                        tmem_ld_32x32(o_addr + (unsigned)c * 32u, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32(o_addr + (unsigned)c * 32u, o);
+                    }
+                }
+                // P = exp2(s * c - ref), packed two per column over the columns the scores came from
+                const float nref = -ref;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    unsigned pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float x0 = fmaf(__uint_as_float(v[c * 32 + i]), p.scale_log2e, nref);
+                        const float x1 = fmaf(__uint_as_float(v[c * 32 + i + 1]), p.scale_log2e, nref);
+                        float e0, e1;
+                        if (POLY > 0 && ((i >> 1) % (POLY > 0 ? POLY : 1)) == 0) {
+                            e0 = ex2_poly(x0);
+                            e1 = ex2_poly(x1);
+                        } else {
+                            e0 = ex2_approx(x0);
+                            e1 = ex2_approx(x1);
+                        }
+                        l4[i & 2] += e0;
+                        l4[(i & 2) + 1] += e1;
+                        pk[i >> 1] = pack2<T>(e0, e1);
+                    }
+                    tmem_st_32x16(s_addr + (unsigned)c * 16u, pk);
+                }
+                l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(TP_FULL + t));
+            }
+            if (!ok) break;
+            // ---- O / l -> global memory
+            if (!(ok = wait_all(TO_FULL + t, o_phase, 111u))) break;
+            o_phase ^= 1;
+            tc_fence_after();
+            const float inv = 1.0f / l_run;
+            T* orow = O + (long long)(b / p.heads) * p.o_bs + (long long)(b % p.heads) * p.o_hs + ((long long)qt * 128 + r) * p.o_rs;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned o[32];
+                tmem_ld_32x32(o_addr + (unsigned)c * 32u, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 u;
+                    u.x = pack2<T>(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+                    u.y = pack2<T>(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+                    u.z = pack2<T>(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+                    u.w = pack2<T>(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = u;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(TO_EMPTY + t));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}

@@ -71,6 +71,7 @@ TensorData from_desc(const wgf_tensor_desc* d, bool owning) {
     // A non-owning alias keeps the use count out of the in-place decision: at this level the
     // caller states whether the input may be overwritten.
     td.buf = owning ? d->buf->ref : BufferRef(BufferRef(), d->buf->ref.get());
+    d->buf->ref->dev->note_recorded_buffer(d->buf->ref);   // a recording keeps the buffers its kernels touch
     td.dtype = (DType)d->dtype;
     td.layout.offset = d->offset;
     td.layout.shape = vec(d->shape, d->rank);
@@ -101,6 +102,7 @@ void to_desc(const TensorData& td, wgf_buffer* reuse, wgf_tensor_desc* out) {
 }
 
 int apply_chain(Program& p, int v, const wgf_ew_op* chain, uint32_t n) {
+    WGF_CHECK(chain || !n, WGF_ERR_INVALID_ARGUMENT, "null chain with a non-zero length");
     for (uint32_t i = 0; i < n; ++i) {
         const wgf_ew_op& op = chain[i];
         if (op.opcode == WGF_OP_CAST) {

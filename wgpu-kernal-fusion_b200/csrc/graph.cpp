@@ -509,8 +509,17 @@ struct MarkSet {
 // While a schedule is being recorded, a buffer may be overwritten in place only if it was
 // produced inside the recording: a replay runs its producer again.  Overwriting a buffer from
 // outside (an input of the schedule) would make the second run read what the first one wrote.
+// After the recording the same holds the other way round: a buffer that belongs to a schedule
+// that still exists is written by every replay, so nothing outside may move into it in place
+// (a tensor computed in place from a recorded result would change under its holder at the next
+// replay).
 bool replay_may_overwrite(const Device& dev, const TensorData& td) {
-    return !dev.recording() || (td.buf && td.buf->arena == dev.arena());
+    if (dev.recording()) return td.buf && td.buf->arena == dev.arena();
+    if (td.buf && td.buf->arena) {
+        std::lock_guard<std::mutex> g(td.buf->arena->mu);
+        return td.buf->arena->closed;
+    }
+    return true;
 }
 
 bool dies_with(Node* x, Node* root, MarkSet& memo) {
@@ -1019,7 +1028,11 @@ TensorData run_region(Node* root, bool allow_fold = true) {
 }
 
 TensorData resolve_node(Node* n) {
-    if (n->cached) return n->cached;
+    if (n->cached) {
+        // every read of already materialised data passes here: a recording keeps what it reads
+        n->dev->note_recorded_buffer(n->cached.buf);
+        return n->cached;
+    }
     Device& dev = *n->dev;
     TensorData out;
     switch (n->kind) {

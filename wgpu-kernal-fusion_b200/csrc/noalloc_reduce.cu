@@ -1,8 +1,7 @@
 // Full-tensor reduction for callers that must not allocate.
 //
-// Some hosts of this library cannot tolerate an allocation inside a compute call: code that
-// runs between the begin and end of a CUDA stream capture (an allocation there either fails
-// or is baked into the graph), real-time loops that forbid anything with unbounded latency,
+// Some hosts of this library cannot tolerate an allocation inside a compute call: real-time
+// loops that forbid anything with unbounded latency (cudaMalloc may synchronise the device),
 // and embedders whose memory budget is fixed up front so that every byte on the device is
 // accounted for by them.  wgf_full_reduce_f32_noalloc gives those callers the streaming
 // reduction (the kernel behind `t.exp().sum(0).sum(0)` and friends) without the pool: its

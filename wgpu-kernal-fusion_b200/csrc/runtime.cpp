@@ -606,7 +606,15 @@ void Device::begin_recording() {
         WGF_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeRelaxed));
     }
     arena_ = std::make_shared<Arena>();
+    recorded_inputs_.clear();
     recording_from_ = launches.load();
+}
+
+void Device::note_recorded_buffer(const BufferRef& b) {
+    if (!recording() || !b || b->arena == arena_) return;
+    for (const BufferRef& have : recorded_inputs_)
+        if (have.get() == b.get()) return;
+    recorded_inputs_.push_back(b);
 }
 
 Device::Recorded Device::end_recording() {
@@ -614,6 +622,7 @@ Device::Recorded Device::end_recording() {
     Recorded r;
     r.arena = arena_;
     r.kernels = launches.load() - recording_from_;
+    r.inputs.swap(recorded_inputs_);
     arena_.reset();
     if (dry) return r;
     make_current();
@@ -646,6 +655,7 @@ void Device::destroy_recorded(Recorded& r) {
     }
     r.exec = nullptr;
     r.graph = nullptr;
+    r.inputs.clear();   // no replay can read them any more
     if (r.arena) {
         std::multimap<size_t, void*> blocks;
         {

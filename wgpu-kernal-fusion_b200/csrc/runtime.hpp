@@ -137,6 +137,10 @@ struct Device : std::enable_shared_from_this<Device> {
         cudaGraphExec_t exec = nullptr;
         std::shared_ptr<Arena> arena;
         uint64_t kernels = 0;
+        // Buffers from BEFORE the recording that its kernels read (inputs, weights): every replay
+        // reads their addresses again, so the schedule holds them until it is destroyed -- a
+        // caller that drops its handle does not send the block back to the pool under the graph.
+        std::vector<BufferRef> inputs;
     };
     bool recording() const { return (bool)arena_; }
     void begin_recording();
@@ -146,6 +150,9 @@ struct Device : std::enable_shared_from_this<Device> {
     void replay(const Recorded& r);
     void destroy_recorded(Recorded& r);
     void refuse_while_recording(const char* what) const;
+    // Called for every buffer a kernel of the recording is about to read or write; keeps the ones
+    // that do not belong to the recording's own arena (see Recorded::inputs).  No-op otherwise.
+    void note_recorded_buffer(const BufferRef& b);
     const std::shared_ptr<Arena>& arena() const { return arena_; }
 
     // Timing sink: while set, every launch appends an event pair to it.
@@ -171,6 +178,7 @@ struct Device : std::enable_shared_from_this<Device> {
     };
     std::vector<Deferred> deferred_;
     std::shared_ptr<Arena> arena_;     // non-null while recording
+    std::vector<BufferRef> recorded_inputs_;
     uint64_t recording_from_ = 0;      // value of `launches` when recording began
     void drain_deferred_locked();
     void* raw_alloc(size_t block);
