@@ -342,3 +342,45 @@ def test_exp_form_follows_who_can_see_the_value(tmp_path):
         parts[name.strip()] = (body, calls)
     uses = {k: ("sfu" if any("sfu" in c for c in v[1]) else "expf") for k, v in parts.items()}
     assert uses == {"SUMEXP": "sfu", "ROWSUMEXP": "sfu", "SOFTMAX": "expf", "PLAIN": "expf", "HALF": "sfu"}, uses
+
+
+def test_llama_block_kernel_count_with_and_without_matmul_epilogues(wgf, drydev, monkeypatch):
+    """On the compile-only device: the decoder block resolves to 11 kernels -- RmsNorm, three
+    projections, two rope kernels, fused attention, the output projection with the residual add in
+    its epilogue, RmsNorm, one GEMM for silu(gate) * up, the down projection with the second residual
+    add -- and to 14 when the epilogues are switched off."""
+    B, S, Hd, heads, inter = 1, 256, 512, 4, 1024
+    D = Hd // heads
+    z = lambda *shape: np.zeros(shape, np.float16)
+
+    def launches():
+        x = drydev.tensor(z(B, S, Hd))
+        W = [drydev.tensor(z(*s)) for s in [(Hd, Hd)] * 4 + [(inter, Hd), (inter, Hd), (Hd, inter)]]
+        n1, n2 = drydev.tensor(z(Hd)), drydev.tensor(z(Hd))
+        cos, sin = drydev.tensor(z(S, D // 2)), drydev.tensor(z(S, D // 2))
+        before = drydev.launch_count
+        x.llama_block(W, n1, n2, cos, sin, None, heads, 1e-5).materialize()
+        return drydev.launch_count - before
+
+    monkeypatch.delenv("WGF_NO_MATMUL_EPILOGUE", raising=False)
+    assert launches() == 11
+    monkeypatch.setenv("WGF_NO_MATMUL_EPILOGUE", "1")
+    assert launches() == 14
+
+
+def test_null_chain_with_a_length_is_an_error_not_a_crash(wgf, drydev):
+    """Kernel-level launches take their op chains as (pointer, count): a NULL pointer with a non-zero
+    count is refused with a status code by every one of them."""
+    import ctypes as C
+    x = drydev.tensor(np.zeros((4, 8), np.float32))
+    d, out = x.desc(), wgf.TensorDesc()
+    lib = wgf.lib()
+    rc = lib.wgf_launch_elementwise(drydev.h, C.byref(d), None, C.c_uint32(2), C.c_int32(0), C.byref(out), None)
+    assert wgf.STATUS[rc] == "INVALID_ARGUMENT"
+    rc = lib.wgf_launch_pairwise(drydev.h, C.byref(d), C.byref(d), None, C.c_uint32(1), None, C.c_uint32(0), C.c_uint32(wgf.OP_ADD),
+                                 None, C.c_uint32(0), C.byref(out), None)
+    assert wgf.STATUS[rc] == "INVALID_ARGUMENT"
+    rc = lib.wgf_launch_reduce(drydev.h, C.byref(d), C.c_uint32(1), None, C.c_uint32(0), C.c_uint32(wgf.OP_SUM), None, C.c_uint32(3),
+                               C.byref(out), None)
+    assert wgf.STATUS[rc] == "INVALID_ARGUMENT"
+    lib.wgf_buffer_release(C.c_void_p(d.buf))

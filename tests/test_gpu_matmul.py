@@ -160,3 +160,71 @@ def test_config4_full_sizes(wgf, dev):
     tx, rx = make(dev, wgf, x, "f16")
     tw, rw = make(dev, wgf, w, "f16")
     assert normwise(result(tx.mat_mul(tw), "f16"), rx @ rw) <= 1e-2
+
+
+def silu64(g):
+    return g / (1 + np.exp(-g))
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(256, 128, 64), (512, 384, 256), (1024, 1000, 192), (2304, 640, 128), (300, 256, 128)])
+def test_matmul_epilogues_give_the_bits_of_the_separate_kernels(shape, kind, wgf, dev, monkeypatch):
+    """`product + t`, `t + product` and `silu(a bg) * (a bu)` run inside the tensor-core kernel's
+    epilogue (one launch each); with WGF_NO_MATMUL_EPILOGUE=1 the same graphs run as separate kernels.
+    Both must give the same bits, and both must be within the 16-bit matmul bound of float64."""
+    M, N, K = shape
+    g = seeded(4, 6)
+    a, w, w2 = g.random((M, K)) * 2 - 1, g.random((N, K)) * 2 - 1, g.random((N, K)) * 2 - 1
+    r = g.standard_normal((M, N))
+    ta, ra = make(dev, wgf, a, kind)
+    tw, rw = make(dev, wgf, w, kind)
+    tw2, rw2 = make(dev, wgf, w2, kind)
+    tr, rr = make(dev, wgf, r, kind)
+    graphs = {
+        "residual": (lambda: tr + ta.mat_mul(tw.transpose(0, 1)), rr + ra @ rw.T),
+        "residual, product first": (lambda: ta.mat_mul(tw.transpose(0, 1)) + tr, rr + ra @ rw.T),
+        "silu_mul": (lambda: ta.mat_mul(tw.transpose(0, 1)).silu() * ta.mat_mul(tw2.transpose(0, 1)), silu64(ra @ rw.T) * (ra @ rw2.T)),
+        "silu_mul, up first": (lambda: ta.mat_mul(tw2.transpose(0, 1)) * ta.mat_mul(tw.transpose(0, 1)).silu(), silu64(ra @ rw.T) * (ra @ rw2.T)),
+    }
+    for name, (build, ref) in graphs.items():
+        monkeypatch.delenv("WGF_NO_MATMUL_EPILOGUE", raising=False)
+        before = dev.launch_count
+        fused = build().materialize()
+        n_fused = dev.launch_count - before
+        monkeypatch.setenv("WGF_NO_MATMUL_EPILOGUE", "1")
+        before = dev.launch_count
+        apart = build().materialize()
+        n_apart = dev.launch_count - before
+        monkeypatch.delenv("WGF_NO_MATMUL_EPILOGUE")
+        got, want = fused.as_slice(), apart.as_slice()
+        assert n_fused == 1 and n_apart >= 2, (name, n_fused, n_apart)
+        np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16), err_msg=name)
+        assert normwise(result(fused, kind), ref) <= (2e-2 if kind == "bf16" else 1e-2), name
+
+
+def test_matmul_epilogues_batched_row_major_and_views(wgf, dev, monkeypatch):
+    """The same with a batch axis, with B given row-major [K, N], and with a residual that is a
+    strided view; a product that something else also reads is not fused away."""
+    g = seeded(4, 7)
+    B, M, N, K = 3, 256, 256, 128
+    a, b, r = g.random((B, M, K)) * 2 - 1, g.random((B, K, N)) * 2 - 1, g.standard_normal((B, M, 2 * N))
+    ta, ra = make(dev, wgf, a, "f16")
+    tb, rb = make(dev, wgf, b, "f16")
+    tr, rr = make(dev, wgf, r, "f16")
+    view = tr.slice([(0, B), (0, M), (N // 2, N // 2 + N)])
+    before = dev.launch_count
+    fused = (ta.mat_mul(tb) + view).materialize()
+    assert dev.launch_count - before == 1
+    monkeypatch.setenv("WGF_NO_MATMUL_EPILOGUE", "1")
+    apart = (ta.mat_mul(tb) + view).as_slice()
+    monkeypatch.delenv("WGF_NO_MATMUL_EPILOGUE")
+    np.testing.assert_array_equal(fused.as_slice().view(np.uint16), apart.view(np.uint16))
+    assert normwise(fused.as_slice(), ra @ rb + rr[:, :, N // 2:N // 2 + N]) <= 1e-2
+    # the product is held by a handle: it has to exist on its own, so nothing is folded into its kernel
+    prod = ta.mat_mul(tb)
+    both = prod + view
+    before = dev.launch_count
+    both.materialize()
+    assert dev.launch_count - before == 2
+    np.testing.assert_array_equal(both.as_slice().view(np.uint16), apart.view(np.uint16))
+    assert normwise(prod.as_slice(), ra @ rb) <= 1e-2

@@ -60,11 +60,14 @@ def build(force=False, verbose=False):
         raise RuntimeError("libwgf.so: compilation failed")
     objs = [os.path.join(OBJ, f + ".o") for f in sources]
     if jobs or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ARCH + ["-cudart", "static", "-ldl", "-lpthread", "-Xlinker",
+        # linked under another name and moved into place, so that the library is never seen half written
+        tmp = LIB + ".tmp"
+        cmd = [NVCC, "-shared", "-o", tmp] + objs + ARCH + ["-cudart", "static", "-ldl", "-lpthread", "-Xlinker",
                                                              "--version-script=" + os.path.join(CSRC, "exports.map")]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("libwgf.so: link failed\n" + r.stdout + r.stderr)
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -9,6 +9,7 @@
 #include "attention.hpp"
 #include "comm.hpp"
 #include "half.hpp"
+#include "matmul.hpp"
 
 namespace wgf {
 
@@ -538,6 +539,83 @@ bool dies_with(Node* x, Node* root, MarkSet& memo) {
 
 TensorData resolve_node(Node* n);
 
+// ---- element-wise steps that move into the epilogue of the matmul that feeds them ----------------
+// The crate never fuses anything around a MatMul (src/compute_graph/resolve.rs:138-154).  Two
+// patterns are handed to the tensor-core kernel's epilogue here, when the product is a 16-bit
+// tensor that nothing else can read: `product + t` (either order) for a tensor t of the same shape,
+// and `silu(a . bg) * (a . bu)` with silu as the composite spells it, x / (1 + exp(-x)).  The
+// kernel rounds where the separate kernels would, so the result has the same bits either way; when
+// it does not take the problem (small or unaligned shapes, f32), the ordinary path runs.
+bool is16(DType d) { return d == DType::F16 || d == DType::BF16; }
+
+// true if `x` is an unmaterialised node without handles whose consumers are exactly `users`
+bool private_to(const Node* x, std::initializer_list<const Node*> users) {
+    if (x->cached || x->handles != 0 || x->consumers.size() != users.size()) return false;
+    for (const Node* u : users)
+        if (std::find(x->consumers.begin(), x->consumers.end(), u) == x->consumers.end()) return false;
+    return true;
+}
+
+// big enough for the CTA-pair kernel (its own test is on the materialised operands; this one keeps
+// small products out of the way of the ordinary fusion)
+bool pair_kernel_shape(const Node* m) {
+    const int r = m->rank();
+    if (r != 2 && r != 3) return false;
+    const int64_t M = m->shape[r - 2], N = m->shape[r - 1], K = m->inputs[0]->shape[r - 1];
+    return M >= 256 && N >= 128 && K >= 64;
+}
+
+struct EpilogueMatch {
+    int kind = MatmulEpilogue::NONE;
+    Node* m1 = nullptr;   // the product (RESIDUAL), or the gate product (SILU_MUL)
+    Node* m2 = nullptr;   // the up product (SILU_MUL)
+    Node* resid = nullptr;
+};
+
+// Does `n` together with the matmul(s) below it form one of the two patterns?  Looks at the graph only.
+EpilogueMatch match_matmul_epilogue(const Node* n) {
+    EpilogueMatch none;
+    if (n->cached || n->kind != NodeKind::PairWise || !is16(n->dtype) || n->numel() == 0) return none;
+    if (n->op == WGF_OP_ADD) {
+        for (int side = 0; side < 2; ++side) {
+            Node* m = n->inputs[side].get();
+            Node* r = n->inputs[1 - side].get();
+            if (m == r || m->kind != NodeKind::MatMul || !private_to(m, {n}) || !pair_kernel_shape(m)) continue;
+            EpilogueMatch e;
+            e.kind = MatmulEpilogue::RESIDUAL;
+            e.m1 = m;
+            e.resid = r;
+            return e;
+        }
+        return none;
+    }
+    if (n->op != WGF_OP_MUL) return none;
+    for (int side = 0; side < 2; ++side) {
+        Node* s = n->inputs[side].get();        // silu(m1) = m1 / (1 + exp(-m1))
+        Node* m2 = n->inputs[1 - side].get();
+        if (s == m2 || m2->kind != NodeKind::MatMul || !private_to(m2, {n}) || !pair_kernel_shape(m2)) continue;
+        if (s->kind != NodeKind::PairWise || s->op != WGF_OP_DIV || !private_to(s, {n})) continue;
+        Node* m1 = s->inputs[0].get();
+        Node* d1 = s->inputs[1].get();          // 1 + exp(-m1)
+        if (m1->kind != NodeKind::MatMul || d1->kind != NodeKind::ElementWise || d1->op != WGF_OP_ADD_C || d1->imm != 1.0f ||
+            !private_to(d1, {s}))
+            continue;
+        Node* e1 = d1->inputs[0].get();
+        if (e1->kind != NodeKind::ElementWise || e1->op != WGF_OP_EXP || !private_to(e1, {d1})) continue;
+        Node* n1 = e1->inputs[0].get();
+        if (n1->kind != NodeKind::ElementWise || n1->op != WGF_OP_NEG || !private_to(n1, {e1}) || n1->inputs[0].get() != m1) continue;
+        if (!private_to(m1, {s, n1}) || m1 == m2 || m1->inputs[0].get() != m2->inputs[0].get()) continue;
+        EpilogueMatch e;
+        e.kind = MatmulEpilogue::SILU_MUL;
+        e.m1 = m1;
+        e.m2 = m2;
+        return e;
+    }
+    return none;
+}
+
+bool epilogue_fusion_on() { return getenv("WGF_NO_MATMUL_EPILOGUE") == nullptr; }   // read per call: tests compare both ways in one process
+
 // One fused kernel: a region of element-wise / pair-wise nodes, optionally with reductions
 // over one axis and their broadcasts back ("row mode").
 struct Region {
@@ -586,6 +664,10 @@ struct Region {
         if (n != root && (n_fused >= 200 || leaves.size() >= 12)) return false;
         if (d == Elem) {
             if (n->shape != E) return false;
+            // a step that the matmul below it can do in its epilogue is left to that kernel
+            if (n != root && n->kind == NodeKind::PairWise && epilogue_fusion_on() &&
+                match_matmul_epilogue(n).kind != MatmulEpilogue::NONE)
+                return false;
             if (is_ew(n)) return true;
             if (row_mode && bcast_of_row(n)) return row_chain_has_reduce(n->inputs[0].get());
             return false;
@@ -1027,6 +1109,22 @@ TensorData run_region(Node* root, bool allow_fold = true) {
     return out;
 }
 
+bool try_matmul_epilogue(Node* n, TensorData& out) {
+    const EpilogueMatch e = match_matmul_epilogue(n);
+    if (e.kind == MatmulEpilogue::NONE || !epilogue_fusion_on()) return false;
+    Device& dev = *n->dev;
+    if (e.kind == MatmulEpilogue::RESIDUAL) {
+        TensorData a = resolve_node(e.m1->inputs[0].get());
+        TensorData b = resolve_node(e.m1->inputs[1].get());
+        TensorData res = resolve_node(e.resid);
+        return run_matmul_residual(dev, a, b, res, out);
+    }
+    TensorData a = resolve_node(e.m1->inputs[0].get());
+    TensorData bg = resolve_node(e.m1->inputs[1].get());
+    TensorData bu = resolve_node(e.m2->inputs[1].get());
+    return run_matmul_silu_mul(dev, a, bg, bu, out);
+}
+
 TensorData resolve_node(Node* n) {
     if (n->cached) {
         // every read of already materialised data passes here: a recording keeps what it reads
@@ -1048,7 +1146,7 @@ TensorData resolve_node(Node* n) {
         case NodeKind::ElementWise:
         case NodeKind::PairWise:
         case NodeKind::Reduce:
-            out = run_region(n);
+            if (!try_matmul_epilogue(n, out)) out = run_region(n);
             break;
         case NodeKind::MatMul: {  // src/compute_graph/resolve.rs:138-154
             TensorData a = resolve_node(n->inputs[0].get());

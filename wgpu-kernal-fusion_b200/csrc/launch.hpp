@@ -39,6 +39,11 @@ void run_copy(Device& dev, const TensorData& dst, const TensorData& src);
 // A dense row-major copy of `src` (a new buffer).
 TensorData run_compact(Device& dev, const TensorData& src);
 TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b);
+// The product with an element-wise step done in the kernel's epilogue (tcgen05 CTA-pair kernel, 16-bit
+// types): `out = round(a b) + resid`, and `out = silu(a bg) * (a bu)`.  Bit-identical to the separate
+// kernels.  Return false, having launched nothing, when that kernel does not take the problem.
+bool run_matmul_residual(Device& dev, const TensorData& a, const TensorData& b, const TensorData& resid, TensorData& out);
+bool run_matmul_silu_mul(Device& dev, const TensorData& a, const TensorData& bg, const TensorData& bu, TensorData& out);
 // Rotary embedding of x [.., seq, embed] (rank 3 or 4, last axis contiguous or gathered first)
 // with cos / sin [>= seq, embed / 2]; bit-identical to the chain of separate ops (rope.cu).
 TensorData run_rope(Device& dev, const TensorData& x, const TensorData& cos, const TensorData& sin);

@@ -85,7 +85,9 @@ void launch_strided(Device& dev, const void* a, const void* b, void* c, const Ma
 
 }  // namespace
 
-TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b) {
+namespace {
+// Shapes and strides of C = A B in elements; checks what the crate's front-end asserts.
+MatmulDims dims_of(const TensorData& a, const TensorData& b) {
     const int r = a.layout.rank();
     WGF_CHECK(r == b.layout.rank() && (r == 2 || r == 3), WGF_ERR_RANK, "matmul takes rank 2, or rank 3 (batched)");
     WGF_CHECK(a.dtype == b.dtype, WGF_ERR_DTYPE, "matmul operands must have equal element types");
@@ -104,6 +106,16 @@ TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b) {
     d.b_cs = b.layout.strides[r - 1];
     d.c_rs = d.N;
     d.c_bs = d.M * d.N;
+    return d;
+}
+}  // namespace
+
+bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d,
+                         const MatmulEpilogue* epi);
+
+TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b) {
+    const int r = a.layout.rank();
+    const MatmulDims d = dims_of(a, b);
     std::vector<int64_t> oshape = a.layout.shape;
     oshape[r - 1] = d.N;
     TensorData out;
@@ -125,6 +137,60 @@ TensorData run_matmul(Device& dev, const TensorData& a, const TensorData& b) {
         default: launch_strided<__nv_bfloat16>(dev, a.base_ptr(), b.base_ptr(), out.base_ptr(), d); break;
     }
     return out;
+}
+
+// C = round(A B) + R in one kernel, or false (nothing launched) when the tensor-core CTA-pair kernel
+// does not take this problem; the caller then runs the product and the addition as separate kernels.
+bool run_matmul_residual(Device& dev, const TensorData& a, const TensorData& b, const TensorData& resid, TensorData& out) {
+    const int r = a.layout.rank();
+    if (a.dtype == DType::F32 || resid.dtype != a.dtype) return false;
+    const MatmulDims d = dims_of(a, b);
+    std::vector<int64_t> oshape = a.layout.shape;
+    oshape[r - 1] = d.N;
+    if (resid.layout.shape != oshape || resid.layout.strides[r - 1] != 1 || d.K == 0) return false;
+    if (Layout::contiguous(oshape).numel() == 0) return false;
+    MatmulEpilogue epi;
+    epi.kind = MatmulEpilogue::RESIDUAL;
+    epi.resid = resid.base_ptr();
+    epi.r_rs = resid.layout.strides[r - 2];
+    epi.r_bs = r == 3 ? resid.layout.strides[0] : 0;
+    TensorData c;
+    c.dtype = a.dtype;
+    c.layout = Layout::contiguous(oshape);
+    c.buf = dev.alloc((size_t)c.layout.numel() * dtype_size(a.dtype), false);
+    dev.make_current();
+    dev.wait_for(*a.buf);
+    dev.wait_for(*b.buf);
+    dev.wait_for(*resid.buf);
+    if (!matmul_tc_pair_path(dev, a.base_ptr(), b.base_ptr(), c.base_ptr(), a.dtype, d, &epi)) return false;
+    out = c;
+    return true;
+}
+
+// C = silu(A Bg) * (A Bu) in one kernel (Bg and Bu of one shape and one set of strides), or false.
+bool run_matmul_silu_mul(Device& dev, const TensorData& a, const TensorData& bg, const TensorData& bu, TensorData& out) {
+    const int r = a.layout.rank();
+    if (a.dtype == DType::F32 || bg.dtype != a.dtype || bu.dtype != a.dtype) return false;
+    if (bg.layout.shape != bu.layout.shape || bg.layout.strides != bu.layout.strides) return false;
+    const MatmulDims d = dims_of(a, bg);
+    if (d.K == 0) return false;
+    std::vector<int64_t> oshape = a.layout.shape;
+    oshape[r - 1] = d.N;
+    if (Layout::contiguous(oshape).numel() == 0) return false;
+    MatmulEpilogue epi;
+    epi.kind = MatmulEpilogue::SILU_MUL;
+    epi.b2 = bu.base_ptr();
+    TensorData c;
+    c.dtype = a.dtype;
+    c.layout = Layout::contiguous(oshape);
+    c.buf = dev.alloc((size_t)c.layout.numel() * dtype_size(a.dtype), false);
+    dev.make_current();
+    dev.wait_for(*a.buf);
+    dev.wait_for(*bg.buf);
+    dev.wait_for(*bu.buf);
+    if (!matmul_tc_pair_path(dev, a.base_ptr(), bg.base_ptr(), c.base_ptr(), a.dtype, d, &epi)) return false;
+    out = c;
+    return true;
 }
 
 }  // namespace wgf

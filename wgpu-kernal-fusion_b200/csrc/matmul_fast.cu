@@ -17,7 +17,8 @@
 namespace wgf {
 
 bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d);
-bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d);
+bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d,
+                         const MatmulEpilogue* epi = nullptr);
 
 namespace {
 
@@ -332,7 +333,8 @@ bool run_gemv(Device& dev, const void* a, const void* b, void* c, const MatmulDi
         const int k_per_cta = (int)((d.K + splits - 1) / splits);
         splits = (d.K + k_per_cta - 1) / k_per_cta;
         BufferRef scratch = dev.alloc((size_t)(splits * d.M * d.N) * sizeof(float), false);
-        const bool ticketed = nblocks <= Device::kCounters && !getenv("WGF_GEMV_FINISH_KERNEL");
+        static const bool finish_kernel = getenv("WGF_GEMV_FINISH_KERNEL") != nullptr;   // diagnostic switch, read once
+        const bool ticketed = nblocks <= Device::kCounters && !finish_kernel;
         pick([&](auto mm) {
             constexpr int MM = decltype(mm)::value;
             dev.begin_launch("gemv_kn");
@@ -383,7 +385,8 @@ bool run_sgemm(Device& dev, const void* a, const void* b, void* c, const MatmulD
 }  // namespace
 
 bool matmul_fast_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d) {
-    if (getenv("WGF_MATMUL_FALLBACK")) return false;
+    static const bool fallback_only = getenv("WGF_MATMUL_FALLBACK") != nullptr;   // diagnostic switch, read once
+    if (fallback_only) return false;
     switch (dt) {
         case DType::F32:
             if (run_gemv<float>(dev, a, b, c, d)) return true;

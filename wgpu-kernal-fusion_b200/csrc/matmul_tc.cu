@@ -15,6 +15,8 @@
 // Layouts: A is [M,K] row-major (K-major).  B is either [N,K] row-major (a transposed view:
 // K-major) or [K,N] row-major (N-major); both go straight from global memory through TMA.
 // M, N, K need not divide the tile: TMA zero-fills out-of-range reads, stores are guarded.
+#include <mutex>
+
 #include "matmul.hpp"
 #include "tc_common.cuh"
 
@@ -283,7 +285,9 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }  // namespace
 
 bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d) {
-    if (getenv("WGF_MATMUL_NO_TC")) return false;
+    static const bool no_tc = getenv("WGF_MATMUL_NO_TC") != nullptr;            // diagnostic switches, read once
+    static const bool no_tma_store = getenv("WGF_TC_NO_TMA_STORE") != nullptr;
+    if (no_tc) return false;
     if (dt != DType::F16 && dt != DType::BF16) return false;
     // worth it only when a tile is reasonably full
     if (d.M < 64 || d.N < 64 || d.K < 32) return false;
@@ -322,31 +326,29 @@ bool matmul_tc_path(Device& dev, const void* a, const void* b, void* c, DType dt
     // C through TMA when its rows are 16-byte aligned; otherwise guarded stores from registers
     CUtensorMap map_c = map_a;
     p.use_tma_store = 0;
-    if (!getenv("WGF_TC_NO_TMA_STORE") && d.c_rs % 8 == 0 && (d.batch == 1 || d.c_bs % 8 == 0) && a16(c) &&
+    if (!no_tma_store && d.c_rs % 8 == 0 && (d.batch == 1 || d.c_bs % 8 == 0) && a16(c) &&
         encode_3d(&map_c, bf16, c, d.N, d.M, d.batch, d.c_rs, d.c_bs, 64, 32))
         p.use_tma_store = 1;
     p.error = dev.error_word();
     const long long total = (long long)p.tiles_m * p.tiles_n * d.batch;
     const unsigned grid = (unsigned)std::min<long long>(total, dev.sm_count);
     p.band = band_rows((int)grid, BM, BN, p.tiles_m);
-    static bool attr_set[2] = {false, false};
-    if (bf16) {
-        if (!attr_set[1]) {
-            WGF_CUDA(cudaFuncSetAttribute(matmul_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-            attr_set[1] = true;
+    // the opt-in to the kernel's dynamic shared memory is a per-device attribute
+    static std::mutex attr_mu;
+    static bool attr_set[64][2];
+    const void* fn = bf16 ? (const void*)matmul_tc_kernel<__nv_bfloat16> : (const void*)matmul_tc_kernel<__half>;
+    {
+        std::lock_guard<std::mutex> lk(attr_mu);
+        const int ord = dev.ordinal >= 0 && dev.ordinal < 64 ? dev.ordinal : -1;
+        if (ord < 0 || !attr_set[ord][bf16 ? 1 : 0]) {
+            WGF_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            if (ord >= 0) attr_set[ord][bf16 ? 1 : 0] = true;
         }
-        dev.begin_launch("matmul_tc");
-        matmul_tc_kernel<__nv_bfloat16><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__nv_bfloat16*)c, p);
-        dev.end_launch();
-    } else {
-        if (!attr_set[0]) {
-            WGF_CUDA(cudaFuncSetAttribute(matmul_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-            attr_set[0] = true;
-        }
-        dev.begin_launch("matmul_tc");
-        matmul_tc_kernel<__half><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__half*)c, p);
-        dev.end_launch();
     }
+    dev.begin_launch("matmul_tc");
+    if (bf16) matmul_tc_kernel<__nv_bfloat16><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__nv_bfloat16*)c, p);
+    else matmul_tc_kernel<__half><<<grid, TC_THREADS, SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__half*)c, p);
+    dev.end_launch();
     return true;
 }
 

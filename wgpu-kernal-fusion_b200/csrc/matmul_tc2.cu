@@ -13,6 +13,19 @@
 // arrive on both CTAs' barriers), warps 2-5 = epilogue (each CTA drains its own tensor memory
 // and tells the leader when an accumulator is free).  No TMA load uses multicast.  Every wait
 // is bounded and reports through the device error word.
+//
+// Epilogues (MatmulEpilogue, matmul.hpp).  The crate never fuses anything around a MatMul
+// (src/compute_graph/resolve.rs:138-154); here the resolver hands two patterns to this kernel:
+//   RESIDUAL   C = round(A B) + R for a same-shape R (the residual adds of a decoder block): the
+//              epilogue warps read R's rows with 16-byte loads while the accumulator is in registers
+//   SILU_MUL   C = silu(A Bg) * (A Bu): the two products share A, so one 256-column tile holds 128
+//              columns of the gate product and the same 128 columns of the up product (the leader CTA
+//              stages Bg, its peer Bu -- the MMA is unchanged), and the epilogue combines column c
+//              with column c + 128 and writes 128 columns.  The gate / up matrices never reach memory.
+// Both round exactly where the separate kernels round (the product to the 16-bit type first, then
+// every element-wise op on its own), so the results are bit-identical to the unfused graph.
+#include <mutex>
+
 #include "matmul.hpp"
 #include "tc_common.cuh"
 
@@ -49,7 +62,42 @@ struct PairParams {
     // time of a full one (the tcgen05.mma shape becomes M256 x N128, 64 columns of B per CTA).
     int full_waves, tail, nsplit;
     unsigned* error;
+    // epilogue: 0 none, 1 residual add, 2 silu(gate) * up (see the head of this file)
+    int epi;
+    const void* resid;       // [batch, M, N] like C, element type of C
+    long long r_rs, r_bs;
 };
+
+// x rounded to T and back: what a value looks like after it has been stored as T
+template <typename T> __device__ __forceinline__ float round16(float x);
+template <> __device__ __forceinline__ float round16<__half>(float x) { return __half2float(__float2half_rn(x)); }
+template <> __device__ __forceinline__ float round16<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+template <typename T> __device__ __forceinline__ float load16(const T* p);
+template <> __device__ __forceinline__ float load16<__half>(const __half* p) { return __half2float(*p); }
+template <> __device__ __forceinline__ float load16<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void unpack2(unsigned u, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<__half>(unsigned u, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+    lo = f.x;
+    hi = f.y;
+}
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(unsigned u, float& lo, float& hi) {
+    lo = __uint_as_float(u << 16);
+    hi = __uint_as_float(u & 0xffff0000u);
+}
+
+// silu(g) * u on values of a 16-bit tensor, op by op as the generated element-wise kernel does it
+// (src/composite/silu.rs:4-7: x / (1 + exp(-x)); each op computed in f32 and rounded to the element
+// type; exp through ex2.approx of x * log2 e, the form that kernel uses for 16-bit tensors).  The
+// result still has to be rounded to T (the store does that).
+template <typename T> __device__ __forceinline__ float silu_mul16(float gate_acc, float up_acc) {
+    const float g = round16<T>(gate_acc), u = round16<T>(up_acc);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(-g, 1.4426950408889634f)));
+    const float d = round16<T>(__fadd_rn(round16<T>(e), 1.0f));
+    const float q = round16<T>(__fdiv_rn(g, d));
+    return __fmul_rn(q, u);
+}
 
 struct Unit {
     long long tile;
@@ -132,7 +180,8 @@ __host__ __device__ constexpr unsigned pair_instr_desc(bool b_mn_major, int n) {
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                  const __grid_constant__ CUtensorMap map_c, T* __restrict__ C, const __grid_constant__ PairParams p) {
+                  const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c, T* __restrict__ C,
+                  const __grid_constant__ PairParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* epi_smem = smem + P_STAGES * P_STAGE_BYTES;
@@ -183,7 +232,11 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
                 const int m0 = mt * 256 + (int)rank * P_BM;
                 const int nh = u.nw / 2;                                  // columns of B this CTA stages
-                const int n0 = nt * P_BN + u.noff + (int)rank * nh;
+                // two B operands: both CTAs stage the same columns, the leader from the first (gate)
+                // operand and its peer from the second (up)
+                const bool dual = p.epi == 2;
+                const CUtensorMap* mb = dual && rank == 1 ? &map_b2 : &map_b;
+                const int n0 = dual ? nt * (P_BN / 2) + u.noff / 2 : nt * P_BN + u.noff + (int)rank * nh;
                 const unsigned stage_tx = 2u * (unsigned)(P_A_BYTES + nh * P_BK * 2);   // both CTAs' bytes
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase)) {
@@ -197,8 +250,8 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     tma_load_3d_pair(sa, &map_a, fb, kb * P_BK, m0, b);
                     // B in boxes of 64 columns (N-major: a [P_BK x 64] panel; K-major: 64 rows of P_BK)
                     for (int j = 0; j < nh / 64; ++j) {
-                        if (p.b_is_kn) tma_load_3d_pair(sb + j * (P_BK * 128), &map_b, fb, n0 + j * 64, kb * P_BK, b);
-                        else tma_load_3d_pair(sb + j * (64 * P_BK * 2), &map_b, fb, kb * P_BK, n0 + j * 64, b);
+                        if (p.b_is_kn) tma_load_3d_pair(sb + j * (P_BK * 128), mb, fb, n0 + j * 64, kb * P_BK, b);
+                        else tma_load_3d_pair(sb + j * (64 * P_BK * 2), mb, fb, kb * P_BK, n0 + j * 64, b);
                     }
                     if (++stage == P_STAGES) {
                         stage = 0;
@@ -266,7 +319,12 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int r = (int)(u.tile % tiles_per_batch);
             int mt, nt;
             tc::banded_tile(r, p.tiles_m, p.tiles_n, p.band, mt, nt);
-            const long long m0 = (long long)mt * 256 + (long long)rank * P_BM, n0 = (long long)nt * P_BN + u.noff;
+            // output columns of the unit: all of it, or (two B operands) half of it -- gate in the
+            // first half of the accumulator's columns, up in the second
+            const bool dual = p.epi == 2;
+            const int out_w = dual ? u.nw / 2 : u.nw;
+            const long long m0 = (long long)mt * 256 + (long long)rank * P_BM;
+            const long long n0 = dual ? (long long)nt * (P_BN / 2) + u.noff / 2 : (long long)nt * P_BN + u.noff;
             bool got = mbar_wait(acc_full_bar(acc), acc_phase);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
@@ -276,17 +334,56 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
             const long long m = m0 + quarter * 32 + lane;
             T* crow = C + (long long)b * p.c_bs + m * p.c_rs;
+            const T* rrow = p.epi == 1 ? reinterpret_cast<const T*>(p.resid) + (long long)b * p.r_bs + m * p.r_rs : nullptr;
+            const bool r_vec = p.epi == 1 && (p.r_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.resid) & 15) == 0) && (p.r_bs % 8 == 0);
+            const unsigned acc_addr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN);
+            // 32 finished values of this thread's row, output columns n .. n + 31 (as f32 bit patterns;
+            // the store rounds them to T)
+            auto finished = [&](int c, unsigned* v) {
+                tmem_ld_32x32(acc_addr + (unsigned)c, v);
+                if (dual) {
+                    unsigned w[32];
+                    tmem_ld_32x32(acc_addr + (unsigned)(out_w + c), w);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul16<T>(__uint_as_float(v[j]), __uint_as_float(w[j])));
+                    return;
+                }
+                tmem_ld_wait();
+                if (p.epi == 1) {
+                    const long long n = n0 + c;
+                    if (m < p.M && n < p.N) {
+                        if (r_vec && n + 31 < p.N) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + n + 8 * q);
+                                const unsigned rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                                for (int h = 0; h < 4; ++h) {
+                                    float lo, hi;
+                                    unpack2<T>(rw[h], lo, hi);
+                                    v[8 * q + 2 * h] = __float_as_uint(__fadd_rn(lo, round16<T>(__uint_as_float(v[8 * q + 2 * h]))));
+                                    v[8 * q + 2 * h + 1] = __float_as_uint(__fadd_rn(hi, round16<T>(__uint_as_float(v[8 * q + 2 * h + 1]))));
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < p.N) v[j] = __float_as_uint(__fadd_rn(load16<T>(rrow + n + j), round16<T>(__uint_as_float(v[j]))));
+                        }
+                    }
+                }
+            };
             if (p.use_tma_store) {
 #pragma unroll 1
-                for (int c = 0; c < u.nw; c += 64) {
+                for (int c = 0; c < out_w; c += 64) {
                     unsigned char* tile_smem = epi_smem + ((warp - 2) * 2 + epi_buf) * P_EPI_TILE_BYTES;
                     if (lane == 0) bulk_wait_read<1>();
                     __syncwarp();
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         unsigned v[32];
-                        tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c + half * 32), v);
-                        tmem_ld_wait();
+                        finished(c + half * 32, v);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint4 o;
@@ -309,10 +406,9 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
             } else {
 #pragma unroll 1
-                for (int c = 0; c < u.nw; c += 32) {
+                for (int c = 0; c < out_w; c += 32) {
                     unsigned v[32];
-                    tmem_ld_32x32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * P_BN + c), v);
-                    tmem_ld_wait();
+                    finished(c, v);
                     const long long n = n0 + c;
                     if (m < p.M && n < p.N) {
                         if (vec_ok && n + 31 < p.N) {
@@ -356,10 +452,17 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
 }  // namespace
 
-// Takes the problem if it is big enough for 256 x 256 tiles; `false` hands it to the one-CTA kernel.
-bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d) {
-    if (getenv("WGF_MATMUL_NO_PAIR")) return false;
+// Takes the problem if it is big enough for 256 x 256 tiles; `false` hands it to the one-CTA kernel
+// (which has no epilogues: a caller that asked for one then runs the separate kernels).
+bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DType dt, const MatmulDims& d,
+                         const MatmulEpilogue* epi) {
+    static const bool no_pair = getenv("WGF_MATMUL_NO_PAIR") != nullptr;
+    static const bool no_tma_store = getenv("WGF_TC_NO_TMA_STORE") != nullptr;
+    static const bool no_nsplit = getenv("WGF_MATMUL_NO_NSPLIT") != nullptr;
+    static const bool verbose = getenv("WGF_MATMUL_VERBOSE") != nullptr;
+    if (no_pair) return false;
     if (dt != DType::F16 && dt != DType::BF16) return false;
+    const int kind = epi ? epi->kind : MatmulEpilogue::NONE;
     // a second half tile that is mostly padding wastes the peer CTA
     const long long rem = d.M % 256;
     if (d.M < 256 || d.N < 128 || d.K < 64 || (d.M < 2048 && rem != 0 && rem <= 128)) return false;
@@ -369,20 +472,25 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
     const bool b_kn = d.b_cs == 1 && d.b_rs % 8 == 0;
     const bool b_nk = d.b_rs == 1 && d.b_cs % 8 == 0;
     if ((!b_kn && !b_nk) || !a16(b) || (d.batch > 1 && d.b_bs % 8)) return false;
+    if (kind == MatmulEpilogue::SILU_MUL && (!epi->b2 || !a16(epi->b2))) return false;
+    if (kind == MatmulEpilogue::RESIDUAL && !epi->resid) return false;
     if (dev.sm_count < 2) return false;
+    const char* label = kind == MatmulEpilogue::SILU_MUL ? "matmul_tc2_silu_mul" : kind == MatmulEpilogue::RESIDUAL ? "matmul_tc2_residual" : "matmul_tc2";
     if (dev.dry) {
-        dev.begin_launch("matmul_tc2");
+        dev.begin_launch(label);
         dev.end_launch();
         return true;
     }
     const bool bf16 = dt == DType::BF16;
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_b2;
     if (!encode_3d(&map_a, bf16, a, d.K, d.M, d.batch, d.a_rs, d.a_bs, P_BK, P_BM)) return false;
-    if (b_kn) {
-        if (!encode_3d(&map_b, bf16, b, d.N, d.K, d.batch, d.b_rs, d.b_bs, 64, P_BK)) return false;
-    } else {
-        if (!encode_3d(&map_b, bf16, b, d.K, d.N, d.batch, d.b_cs, d.b_bs, P_BK, 64)) return false;
-    }
+    auto encode_b = [&](CUtensorMap* m, const void* ptr) {
+        return b_kn ? encode_3d(m, bf16, ptr, d.N, d.K, d.batch, d.b_rs, d.b_bs, 64, P_BK)
+                    : encode_3d(m, bf16, ptr, d.K, d.N, d.batch, d.b_cs, d.b_bs, P_BK, 64);
+    };
+    if (!encode_b(&map_b, b)) return false;
+    map_b2 = map_b;
+    if (kind == MatmulEpilogue::SILU_MUL && !encode_b(&map_b2, epi->b2)) return false;   // same shape and strides as b
     PairParams p{};
     p.M = d.M;
     p.N = d.N;
@@ -391,12 +499,20 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
     p.c_rs = d.c_rs;
     p.c_bs = d.c_bs;
     p.tiles_m = (int)((d.M + 255) / 256);
-    p.tiles_n = (int)((d.N + P_BN - 1) / P_BN);
+    // with two B operands a 256-column tile of the accumulator covers 128 output columns
+    const int out_tile_n = kind == MatmulEpilogue::SILU_MUL ? P_BN / 2 : P_BN;
+    p.tiles_n = (int)((d.N + out_tile_n - 1) / out_tile_n);
     p.b_is_kn = b_kn ? 1 : 0;
     p.is_bf16 = bf16 ? 1 : 0;
+    p.epi = kind;
+    if (kind == MatmulEpilogue::RESIDUAL) {
+        p.resid = epi->resid;
+        p.r_rs = epi->r_rs;
+        p.r_bs = epi->r_bs;
+    }
     CUtensorMap map_c = map_a;
     p.use_tma_store = 0;
-    if (!getenv("WGF_TC_NO_TMA_STORE") && d.c_rs % 8 == 0 && (d.batch == 1 || d.c_bs % 8 == 0) && a16(c) &&
+    if (!no_tma_store && d.c_rs % 8 == 0 && (d.batch == 1 || d.c_bs % 8 == 0) && a16(c) &&
         encode_3d(&map_c, bf16, c, d.N, d.M, d.batch, d.c_rs, d.c_bs, 64, 32))
         p.use_tma_store = 1;
     p.error = dev.error_word();
@@ -404,58 +520,59 @@ bool matmul_tc_pair_path(Device& dev, const void* a, const void* b, void* c, DTy
     // Schedule (see PairParams).  One cluster per SM pair that the device reports as resident
     // for this kernel; leftover tiles that would keep at most half of the clusters busy are cut
     // in two along N (measured on 4096^3, 34 leftover tiles of 256: 104 us as whole tiles).
-    static int resident[2] = {-1, -1};
+    // The opt-in to the kernel's dynamic shared memory and the residency it gives are properties of
+    // (device, kernel): looked up once per device.
+    static std::mutex state_mu;
+    static int resident[64][2];
+    static bool known[64][2];
     const int ti = bf16 ? 1 : 0;
-    if (resident[ti] < 0) {
-        const void* fn = bf16 ? (const void*)matmul_tc2_kernel<__nv_bfloat16> : (const void*)matmul_tc2_kernel<__half>;
-        WGF_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(dev.sm_count & ~1));
-        cfg.blockDim = dim3(P_THREADS);
-        cfg.dynamicSmemBytes = P_SMEM_BYTES;
-        cudaLaunchAttribute at;
-        at.id = cudaLaunchAttributeClusterDimension;
-        at.val.clusterDim.x = 2;
-        at.val.clusterDim.y = 1;
-        at.val.clusterDim.z = 1;
-        cfg.attrs = &at;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
-            cudaGetLastError();
-            n = 0;
+    const void* fn = bf16 ? (const void*)matmul_tc2_kernel<__nv_bfloat16> : (const void*)matmul_tc2_kernel<__half>;
+    int n_resident = 0;
+    {
+        std::lock_guard<std::mutex> lk(state_mu);
+        const int ord = dev.ordinal >= 0 && dev.ordinal < 64 ? dev.ordinal : -1;
+        if (ord < 0 || !known[ord][ti]) {
+            WGF_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(dev.sm_count & ~1));
+            cfg.blockDim = dim3(P_THREADS);
+            cfg.dynamicSmemBytes = P_SMEM_BYTES;
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = 2;
+            at.val.clusterDim.y = 1;
+            at.val.clusterDim.z = 1;
+            cfg.attrs = &at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
+                cudaGetLastError();
+                n = 0;
+            }
+            n_resident = n;
+            if (ord >= 0) {
+                resident[ord][ti] = n;
+                known[ord][ti] = true;
+            }
+        } else {
+            n_resident = resident[ord][ti];
         }
-        resident[ti] = n;
     }
-    if (resident[ti] < 1) return false;
-    long long clusters = std::min<long long>(dev.sm_count / 2, resident[ti]);
-    p.band = band_rows((int)clusters, 256, P_BN, p.tiles_m);
+    if (n_resident < 1) return false;
+    long long clusters = std::min<long long>(dev.sm_count / 2, n_resident);
+    p.band = band_rows((int)clusters, 256, out_tile_n, p.tiles_m);
     p.full_waves = (int)(total / clusters);
     p.tail = (int)(total % clusters);
-    p.nsplit = (p.tail > 0 && 2ll * p.tail <= clusters && !getenv("WGF_MATMUL_NO_NSPLIT")) ? 2 : 1;
+    p.nsplit = (p.tail > 0 && 2ll * p.tail <= clusters && !no_nsplit) ? 2 : 1;
     if (p.full_waves == 0) clusters = (long long)p.tail * p.nsplit;   // fewer units than clusters: a smaller grid
     const unsigned grid = 2u * (unsigned)clusters;
-    if (getenv("WGF_MATMUL_VERBOSE"))
-        fprintf(stderr, "[wgf] matmul_tc2 %lldx%lldx%lld batch %lld: %lld tiles on %lld clusters (%d resident), %d full waves, tail %d cut in %d\n",
-                d.M, d.N, d.K, d.batch, total, clusters, resident[ti], p.full_waves, p.tail, p.nsplit);
-    static bool attr_set[2] = {false, false};
-    if (bf16) {
-        if (!attr_set[1]) {
-            WGF_CUDA(cudaFuncSetAttribute(matmul_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
-            attr_set[1] = true;
-        }
-        dev.begin_launch("matmul_tc2");
-        matmul_tc2_kernel<__nv_bfloat16><<<grid, P_THREADS, P_SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__nv_bfloat16*)c, p);
-        dev.end_launch();
-    } else {
-        if (!attr_set[0]) {
-            WGF_CUDA(cudaFuncSetAttribute(matmul_tc2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
-            attr_set[0] = true;
-        }
-        dev.begin_launch("matmul_tc2");
-        matmul_tc2_kernel<__half><<<grid, P_THREADS, P_SMEM_BYTES, dev.stream>>>(map_a, map_b, map_c, (__half*)c, p);
-        dev.end_launch();
-    }
+    if (verbose)
+        fprintf(stderr, "[wgf] matmul_tc2 %lldx%lldx%lld batch %lld epilogue %d: %lld tiles on %lld clusters (%d resident), %d full waves, tail %d cut in %d\n",
+                d.M, d.N, d.K, d.batch, kind, total, clusters, n_resident, p.full_waves, p.tail, p.nsplit);
+    dev.begin_launch(label);
+    if (bf16) matmul_tc2_kernel<__nv_bfloat16><<<grid, P_THREADS, P_SMEM_BYTES, dev.stream>>>(map_a, map_b, map_b2, map_c, (__nv_bfloat16*)c, p);
+    else matmul_tc2_kernel<__half><<<grid, P_THREADS, P_SMEM_BYTES, dev.stream>>>(map_a, map_b, map_b2, map_c, (__half*)c, p);
+    dev.end_launch();
     return true;
 }
 

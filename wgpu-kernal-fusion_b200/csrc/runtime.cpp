@@ -547,6 +547,8 @@ int Device::max_blocks_per_sm(const JitKernel& k, int threads) {
 }
 
 void Device::begin_launch(const char* what) {
+    static const bool trace = getenv("WGF_TRACE_LAUNCHES") != nullptr;   // diagnostic: one line per kernel queued
+    if (trace) fprintf(stderr, "[wgf] launch %s\n", what);
     launches++;
     if (timing && sink && !dry && !recording()) {
         pending_.start = event();

@@ -155,7 +155,11 @@ inline int band_rows(int ctas, int tile_m, int tile_n, int tiles_m) {
     int best = 1;
     // cost of a wave ~ band*tile_m + (ctas/band)*tile_n rows of K elements; smallest at band = sqrt(ctas*tile_n/tile_m)
     while ((long long)(best + 1) * (best + 1) * tile_m <= (long long)ctas * tile_n) best++;
-    if (const char* e = getenv("WGF_MATMUL_BAND")) best = atoi(e) > 0 ? atoi(e) : best;
+    static const int forced = [] {   // tuning override, read once
+        const char* e = getenv("WGF_MATMUL_BAND");
+        return e ? atoi(e) : 0;
+    }();
+    if (forced > 0) best = forced;
     return best < tiles_m ? best : (tiles_m > 0 ? tiles_m : 1);
 }
 
