@@ -65,7 +65,7 @@ std::string instr_expr(const Instr& in, const std::string& a, const std::string&
                 case WGF_OP_RSUB_C: return rounded(in.dtype, "(" + c + " - " + a + ")");
                 case WGF_OP_MUL_C: return rounded(in.dtype, "(" + a + " * " + c + ")");
                 case WGF_OP_DIV_C: return rounded(in.dtype, "(" + a + " / " + c + ")");
-                default: return rounded(in.dtype, "(" + c + " / " + a + ")");
+                default: return rounded(in.dtype, in.fast_div ? "op_div_full(" + c + ", " + a + ")" : "(" + c + " / " + a + ")");
             }
         }
         case IKind::Cast: return rounded(in.dtype, a);
@@ -74,7 +74,7 @@ std::string instr_expr(const Instr& in, const std::string& a, const std::string&
                 case WGF_OP_ADD: return rounded(in.dtype, "(" + a + " + " + b + ")");
                 case WGF_OP_SUB: return rounded(in.dtype, "(" + a + " - " + b + ")");
                 case WGF_OP_MUL: return rounded(in.dtype, "(" + a + " * " + b + ")");
-                case WGF_OP_DIV: return rounded(in.dtype, "(" + a + " / " + b + ")");
+                case WGF_OP_DIV: return rounded(in.dtype, in.fast_div ? "op_div_full(" + a + ", " + b + ")" : "(" + a + " / " + b + ")");
                 default: return rounded(in.dtype, "op_pow(" + a + ", " + b + ")");
             }
         default: return "";

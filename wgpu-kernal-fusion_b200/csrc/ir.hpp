@@ -26,7 +26,18 @@ struct Instr {
     // sums: it may be computed as 2^(x * log2 e) by the special-function unit (about 1e-6
     // relative, |x| * 6e-8 more for large |x|), well inside the 1e-5 bound of a reduction.
     bool approx = false;
+    // `inexact`: the value carries the error of an approximated function (a transcendental, pow, a
+    // reduction whose order is free) -- the oracle's value for it is only known to 2 ulp anyway.
+    // `fast_div`: a division whose DIVISOR is inexact (silu's x / (1 + exp(-x)), a softmax written
+    // out by hand): computed with div.full.f32 (<= 2 ulp over the full range, a third of the
+    // instructions of the IEEE sequence) -- an exactly rounded quotient of an approximate divisor
+    // buys nothing.  Quotients of exact values (t / 3.0, a / b) stay IEEE and bit-exact.  Both flags
+    // follow from the instructions, so they need no place in the signature.
+    bool inexact = false;
+    bool fast_div = false;
 };
+
+inline bool op_is_exact_unary(uint16_t op) { return op == WGF_OP_SQR || op == WGF_OP_SQRT || op == WGF_OP_ABS || op == WGF_OP_NEG; }
 
 // A companion output of a row kernel: Elem value `a` reduced with `op` over the WHOLE index
 // space (all rows, all columns) to one scalar, computed while the rows pass through registers.
@@ -102,6 +113,7 @@ struct Program {
         in.a = a;
         in.dtype = ins[a].dtype;
         in.vk = ins[a].vk;
+        in.inexact = ins[a].inexact || !op_is_exact_unary(op);
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
@@ -113,6 +125,8 @@ struct Program {
         imms.push_back(c);
         in.dtype = ins[a].dtype;
         in.vk = ins[a].vk;
+        in.inexact = ins[a].inexact;
+        in.fast_div = op == WGF_OP_RDIV_C && ins[a].inexact;
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
@@ -122,6 +136,7 @@ struct Program {
         in.a = a;
         in.dtype = to;
         in.vk = ins[a].vk;
+        in.inexact = ins[a].inexact;
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
@@ -132,6 +147,8 @@ struct Program {
         in.b = b;
         in.dtype = ins[a].dtype;
         in.vk = (ins[a].vk == VKind::Row && ins[b].vk == VKind::Row) ? VKind::Row : VKind::Elem;
+        in.inexact = ins[a].inexact || ins[b].inexact || op == WGF_OP_POW;
+        in.fast_div = op == WGF_OP_DIV && ins[b].inexact;
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
@@ -141,6 +158,7 @@ struct Program {
         in.a = a;
         in.dtype = ins[a].dtype;
         in.vk = VKind::Row;
+        in.inexact = ins[a].inexact || op == WGF_OP_SUM || op == WGF_OP_PRODUCT;   // max / min of exact values are exact
         ins.push_back(in);
         return (int)ins.size() - 1;
     }

@@ -33,6 +33,9 @@ DEV float op_exp(float x) { return expf(x); }
 // 2^(x * log2 e) by the special-function unit (about 1e-6 relative): for results that are rounded to a
 // 16-bit type, and for f32 values that only feed sums
 DEV float op_exp_sfu(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f)); return y; }
+// a / b to 2 ulp over the full range (div.full.f32): for quotients whose divisor is itself the result
+// of an approximated function (Instr::fast_div); exact quotients use the IEEE `/`
+DEV float op_div_full(float a, float b) { float q; asm("div.full.f32 %0, %1, %2;" : "=f"(q) : "f"(a), "f"(b)); return q; }
 DEV float op_exp2(float x) { return exp2f(x); }
 DEV float op_log(float x) { return logf(x); }
 DEV float op_log2(float x) { return log2f(x); }

@@ -95,7 +95,9 @@ template <typename T> __device__ __forceinline__ float silu_mul16(float gate_acc
     float e;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(-g, 1.4426950408889634f)));
     const float d = round16<T>(__fadd_rn(round16<T>(e), 1.0f));
-    const float q = round16<T>(__fdiv_rn(g, d));
+    float q;   // the divisor comes from an exp: that kernel divides with div.full.f32 (Instr::fast_div)
+    asm("div.full.f32 %0, %1, %2;" : "=f"(q) : "f"(g), "f"(d));
+    q = round16<T>(q);
     return __fmul_rn(q, u);
 }
 
