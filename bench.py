@@ -32,6 +32,7 @@ whatever OMP_NUM_THREADS the launcher exported; at N > 1 a step covers N shards.
 """
 import argparse
 import ctypes
+import datetime
 import importlib.util
 import json
 import os
@@ -378,7 +379,8 @@ def run_gpu(args):
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     if world > 1:
-        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+        # a rank that fails must not leave the others waiting for the default 10 minutes
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
 
     wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
     dev = wgf.Device(local)
@@ -537,7 +539,11 @@ def run_gpu(args):
     # ---- the same step for at least 0.25 s, with its own clock samples -----------------------------
     long_run = None
     if not args.no_extras:
-        n_long = max(args.steps, int(0.25 / max(ms_total / args.steps * 1e-3, 1e-6)))
+        # every rank must run the same number of steps (each step is an all-reduce): agree on the slowest rank's time
+        agreed = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+        n_long = max(args.steps, int(0.25 / max(float(agreed[0]) / args.steps * 1e-3, 1e-6)))
         long_sampler = ClockSampler(local) if rank == 0 else None
         long_ms = time_region(torch, stream, barrier, step, n_long, close_region)
         long_run = {"steps": n_long, "ms_per_step": long_ms, "clocks": long_sampler.stop() if long_sampler else None}
@@ -655,7 +661,7 @@ def run_llama(args):
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     if world > 1:
-        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
     dev = wgf.Device(local)
     _, stream_ptr = dev.info()
@@ -728,14 +734,27 @@ def main():
         args.steps = 10 if llama else 30 if configs else 2000
     if args.warmup is None:
         args.warmup = 3 if llama else 5 if configs else 200
-    if args.impl == "reference":
-        run_reference(args)
-    elif configs:
-        run_configs(args)
-    elif llama:
-        run_llama(args)
-    else:
-        run_gpu(args)
+    try:
+        if args.impl == "reference":
+            run_reference(args)
+        elif configs:
+            run_configs(args)
+        elif llama:
+            run_llama(args)
+        else:
+            run_gpu(args)
+    except SystemExit:
+        raise
+    except BaseException:
+        # Under a multi-process launcher a rank that dies in a Python exception can sit in the teardown
+        # of its libraries while the other ranks wait for it: report and leave at once, so that the
+        # launcher ends the job.
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            os._exit(1)
+        raise
 
 
 if __name__ == "__main__":

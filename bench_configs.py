@@ -196,8 +196,8 @@ def group_c5(wgf, dev):
     cos, sin = dev.tensor(np.cos(pos * inv).astype(np.float16)), dev.tensor(np.sin(pos * inv).astype(np.float16))
     gate, up = (dev.tensor(normal(g, (16384, 11008)).astype(np.float16)) for _ in range(2))
     xt = dev.tensor(normal(g, (16384, 4096)).astype(np.float16))
-    wq, wu, wd = (dev.tensor((normal(g, shape) * 0.02).astype(np.float16))
-                  for shape in ((4096, 4096), (11008, 4096), (4096, 11008)))
+    wq, wu, wd, wg = (dev.tensor((normal(g, shape) * 0.02).astype(np.float16))
+                      for shape in ((4096, 4096), (11008, 4096), (4096, 11008), (11008, 4096)))
     causal_flop = 4 * bh * s * s * d // 2          # QK^T and PV, the masked half not counted
     return [Row("C5 attention f16 causal [256,2048,128]", lambda i: q.attention(k, v, causal=True), flop=causal_flop),
             Row("C5 attention f16 full [256,2048,128]", lambda i: q.attention(k, v), flop=2 * causal_flop),
@@ -209,6 +209,11 @@ def group_c5(wgf, dev):
             Row("C5 up projection f16 [16384,4096] x W^T [11008,4096]", lambda i: xt.mat_mul(wu.transpose(0, 1)),
                 flop=2 * 16384 * 4096 * 11008),
             Row("C5 down projection f16 [16384,11008] x W^T [4096,11008]", lambda i: gate.mat_mul(wd.transpose(0, 1)),
+                flop=2 * 16384 * 4096 * 11008),
+            # the same products with the element-wise step that follows them done in the GEMM's epilogue
+            Row("C5 gate and up in one GEMM: silu(x Wg^T) * (x Wu^T) f16", lambda i: xt.mat_mul(wg.transpose(0, 1)).silu() * xt.mat_mul(wu.transpose(0, 1)),
+                flop=4 * 16384 * 4096 * 11008),
+            Row("C5 down projection with the residual add in its epilogue f16", lambda i: xt + gate.mat_mul(wd.transpose(0, 1)),
                 flop=2 * 16384 * 4096 * 11008)]
 
 

@@ -7,6 +7,7 @@ on the collective stream combines what the ranks posted (no NCCL launch).  Check
 numpy over all shards, for 40 steps (sequence numbers wrap the mailbox slots twice), and that every
 rank holds identical bits.  With WGF_NO_PEER_ALLREDUCE=1 the same script checks the NCCL path (four
 launches per step)."""
+import datetime
 import os
 import sys
 
@@ -20,7 +21,7 @@ from conftest import load_package  # noqa: E402
 
 rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
 torch.cuda.set_device(local)
-dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=90))
 wgf = load_package()
 dev = wgf.Device(local)
 ids = [wgf.Comm.unique_id() if rank == 0 else None]

@@ -6,6 +6,7 @@ steps, with nothing in flight).  Rank 0's combine kernel must give up after its 
 return, rank 0's next synchronisation must raise WGF_ERR_TIMEOUT, further all-reduces on that device
 must be refused, and both ranks must be able to release the communicator and leave cleanly.  No GPU
 is faulted: the wait is a bounded poll of a word that nobody writes."""
+import datetime
 import os
 import sys
 import time
@@ -21,7 +22,7 @@ from conftest import load_package  # noqa: E402
 rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
 assert world == 2
 torch.cuda.set_device(local)
-dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=60))
 wgf = load_package()
 dev = wgf.Device(local)
 ids = [wgf.Comm.unique_id() if rank == 0 else None]
@@ -62,6 +63,9 @@ if rank == 0:
     except wgf.WgfError as e:
         ok = ok and e.status == "TIMEOUT"
 dist.barrier()
+# ncclCommDestroy is a collective among the ranks of a node: every rank has to let go of its
+# communicator, and a tensor of an all-reduce node holds a reference to it
+s2 = None
 del s, comm
 dev.sync()
 print(f"rank {rank}: {'PASS' if ok else 'FAIL'}", flush=True)

@@ -31,7 +31,7 @@ def test_all_reduce_inside_the_row_kernel(peer):
     port = 29540 + (0 if peer else 1)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(HERE, "multi", "all_reduce_in_kernel_check.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("PASS") == n
 
@@ -47,6 +47,6 @@ def test_a_peer_that_sits_an_exchange_out_gives_a_timeout_status():
     env.pop("WGF_NO_PEER_ALLREDUCE", None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29543", os.path.join(HERE, "multi", "peer_wait_runs_out.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("PASS") == 2
