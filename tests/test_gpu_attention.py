@@ -76,12 +76,15 @@ def test_fused_attention_growing_maxima(wgf, dev):
         assert normwise(out, reference(q, k, v, causal, 0.5)) <= 1e-2
 
 
-@pytest.mark.parametrize("variant", ["WGF_ATT_TWO_PASS", "WGF_ATT_SINGLE"])
+@pytest.mark.parametrize("variant", ["WGF_ATT_TWO_PASS=1", "WGF_ATT_SINGLE=1", "WGF_ATT_SMEM_P=1", "WGF_ATT_MODE=0", "WGF_ATT_MODE=1",
+                                     "WGF_ATT_MODE=2"])
 @pytest.mark.parametrize("n,seq", [(3, 256), (2, 640), (5, 1024)])
 def test_fused_attention_other_kernel_variants(n, seq, variant, wgf, dev, monkeypatch):
-    """The variants kept beside the default (two query tiles per CTA, one pass): the same pair
-    kernel with two passes (exact maxima first), and the kernel with one query tile per CTA."""
-    monkeypatch.setenv(variant, "1")
+    """The kernel forms kept beside the default: P through shared memory (two query tiles per CTA, one
+    pass or two; one query tile per CTA), and the ways the softmax warps of the default kernel can go
+    over the scores (one sweep from registers, two sweeps over tensor memory, packed exponentials)."""
+    name, value = variant.split("=")
+    monkeypatch.setenv(name, value)
     g = seeded(5, 7)
     q, k, v = (g.standard_normal((n, seq, 128), dtype=np.float32) for _ in range(3))
     q, k, v = (q * 3).astype(np.float16), (k * 3).astype(np.float16), v.astype(np.float16)

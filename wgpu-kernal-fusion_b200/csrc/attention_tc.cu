@@ -992,16 +992,16 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     };
     dev.begin_launch("attention_tc");
     if (!smem_p) {
-        // share of the exponentials computed on the FMA pipe instead of the special-function unit
-        const char* pe = getenv("WGF_ATT_POLY");
-        const int poly = pe ? atoi(pe) : 0;
+        // how the softmax warps go over the scores (see attention_ts.cuh); WGF_ATT_MODE picks another form
+        const char* me = getenv("WGF_ATT_MODE");
+        const int mode = me ? atoi(me) : 0;
         if (bf16) {
-            if (poly == 2) launch(attention_ts_kernel<__nv_bfloat16, 2>, 9, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
-            else if (poly == 4) launch(attention_ts_kernel<__nv_bfloat16, 4>, 10, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
+            if (mode == 1) launch(attention_ts_kernel<__nv_bfloat16, 1>, 9, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
+            else if (mode == 2) launch(attention_ts_kernel<__nv_bfloat16, 2>, 10, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
             else launch(attention_ts_kernel<__nv_bfloat16, 0>, 8, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
         } else {
-            if (poly == 2) launch(attention_ts_kernel<__half, 2>, 7, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
-            else if (poly == 4) launch(attention_ts_kernel<__half, 4>, 11, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
+            if (mode == 1) launch(attention_ts_kernel<__half, 1>, 7, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
+            else if (mode == 2) launch(attention_ts_kernel<__half, 2>, 11, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
             else launch(attention_ts_kernel<__half, 0>, 6, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
         }
     } else if (pairs) {

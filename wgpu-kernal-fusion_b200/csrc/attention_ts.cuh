@@ -57,26 +57,59 @@ __device__ __forceinline__ void tmem_st_32x16(unsigned taddr, const unsigned* r)
         : "memory");
 }
 
-// 2^x for x <= ~2^7 on the FMA and ALU pipes instead of the special-function unit (which gives 16
-// results per clock and SM: 1024 clocks for a 128 x 128 tile, as long as the tile's two MMAs):
-// x = n + f with n the nearest integer (magic-number rounding) and f in [-0.5, 0.5]; 2^f from a
-// cubic (relative error 1.0e-4, below the 4.9e-4 / 3.9e-3 rounding of the 16-bit P it feeds); n
-// goes into the exponent field by an integer add.  Arguments below -126 give 2^-126 * [0.7, 1.5):
-// nothing against a row maximum near 1.
-__device__ __forceinline__ float ex2_poly(float x) {
-    x = fmaxf(x, -126.f);
-    const float magic = 12582912.f;                 // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-    const float xr = x + magic;
-    const float f = x - (xr - magic);
-    float pf = fmaf(0.05500893f, f, 0.24221096f);       // minimax cubic for 2^f on [-0.5, 0.5] with p(0) = 1
-    pf = fmaf(pf, f, 0.69328293f);
-    pf = fmaf(pf, f, 1.0f);
-    return __int_as_float(__float_as_int(pf) + (__float_as_int(xr) << 23));
+// Two exponentials with one special-function instruction: x0, x1 are rounded to the 16-bit type,
+// ex2.approx works on the packed pair and its result IS the packed pair of probabilities that
+// goes into tensor memory (no conversion afterwards).  The special-function unit gives 16 results
+// per clock and SM -- 1024 clocks for the 128 x 128 exponentials of a tile, as long as the tile's two
+// MMAs take -- and half that in packed form.  Cost: the argument is rounded to 11 (8) bits before
+// the exponential, a relative error of |x| * 2^-11 * ln 2 in P (3e-4 at x = -1, 3e-3 at x = -8, where
+// P is already below 2^-8 of the row maximum).
+template <typename T> __device__ __forceinline__ unsigned ex2_pair(float x0, float x1);
+template <> __device__ __forceinline__ unsigned ex2_pair<__half>(float x0, float x1) {
+    unsigned h, e;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(e) : "r"(h));
+    return e;
+}
+template <> __device__ __forceinline__ unsigned ex2_pair<__nv_bfloat16>(float x0, float x1) {
+    unsigned h, e;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(h));
+    return e;
+}
+__device__ __forceinline__ unsigned hadd2(unsigned a, unsigned b) {
+    unsigned r;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// Sum of the 32 probabilities in 16 packed registers, in f32.  f16: a tree of packed f16 adds (depth 4:
+// relative error below 4 * 2^-11 of a partial sum, values <= 2^8 each so nothing overflows), then one
+// conversion; bf16 (8 bits: too coarse to add in) unpacks every pair with a shift and a mask.
+template <typename T> __device__ __forceinline__ float sum_packed32(const unsigned* pk);
+template <> __device__ __forceinline__ float sum_packed32<__half>(const unsigned* pk) {
+    unsigned t8[8], t4[4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t8[i] = hadd2(pk[2 * i], pk[2 * i + 1]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t4[i] = hadd2(t8[2 * i], t8[2 * i + 1]);
+    const unsigned t = hadd2(hadd2(t4[0], t4[1]), hadd2(t4[2], t4[3]));
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&t));
+    return f.x + f.y;
+}
+template <> __device__ __forceinline__ float sum_packed32<__nv_bfloat16>(const unsigned* pk) {
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        s0 += __uint_as_float(pk[i] << 16);
+        s1 += __uint_as_float(pk[i] & 0xffff0000u);
+    }
+    return s0 + s1;
 }
 
-// POLY: every POLY-th pair of exponentials... 0 = all on the special-function unit; k > 0 = one pair in
-// k goes through ex2_poly (2 = half of them, 4 = a quarter).
-template <typename T, int POLY>
+// MODE 0: the 128 scores of a row are loaded into registers once (maximum, exponentials and P all come
+//         from them); 1: two sweeps over tensor memory, 32 scores at a time (a quarter of the
+//         registers); 2: two sweeps and packed exponentials (ex2_pair).
+template <typename T, int MODE>
 __global__ void __launch_bounds__(TS_THREADS, 1)
 attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, T* __restrict__ O, const __grid_constant__ AtParams p) {
@@ -283,21 +316,46 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tc_fence_after();
                 float alpha = 1.f;
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
-                // the whole row of scores, once
-                unsigned v[128];
-                tmem_ld_32x32(s_addr, v);
-                tmem_ld_32x32(s_addr + 32u, v + 32);
-                tmem_ld_32x32(s_addr + 64u, v + 64);
-                tmem_ld_32x32(s_addr + 96u, v + 96);
-                tmem_ld_wait();
-                if (p.causal && j == qt) {   // only the key tile on the diagonal carries the mask
-#pragma unroll
-                    for (int i = 0; i < 128; ++i)
-                        if (i > r) v[i] = 0xff800000u;   // -inf above the diagonal
-                }
+                const bool diag = p.causal && j == qt;   // only the key tile on the diagonal carries the mask
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                unsigned v[MODE == 0 ? 128 : 1];
+                auto maxes = [&](const unsigned* x, int c) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                    for (int i = 0; i < 32; ++i) {
+                        float sv = __uint_as_float(x[i]);
+                        if (diag && c * 32 + i > r) sv = -INFINITY;
+                        m4[i & 3] = fmaxf(m4[i & 3], sv);
+                    }
+                };
+                if constexpr (MODE == 0) {
+                    tmem_ld_32x32(s_addr, v);
+                    tmem_ld_32x32(s_addr + 32u, v + 32);
+                    tmem_ld_32x32(s_addr + 64u, v + 64);
+                    tmem_ld_32x32(s_addr + 96u, v + 96);
+                    tmem_ld_wait();
+                    if (diag) {
+#pragma unroll
+                        for (int i = 0; i < 128; ++i)
+                            if (i > r) v[i] = 0xff800000u;   // -inf above the diagonal
+                    }
+#pragma unroll
+                    for (int i = 0; i < 128; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                } else {
+                    // first sweep: the maximum, 32 scores at a time, the next load in flight meanwhile
+                    unsigned va[32], vb[32];
+                    tmem_ld_32x32(s_addr, va);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 32u, vb);
+                    maxes(va, 0);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 64u, va);
+                    maxes(vb, 1);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 96u, vb);
+                    maxes(va, 2);
+                    tmem_ld_wait();
+                    maxes(vb, 3);
+                }
                 const float mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2e;
                 // (key 0 is visible to every query, so the first tile gives every row a finite maximum)
                 const bool grow = j > 0 && mt > ref + AT_LAG;
@@ -320,27 +378,45 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     }
                 }
                 // P = exp2(s * c - ref), packed two per column over the columns the scores came from
+                // (chunk c of 32 scores becomes columns 16 c .. 16 c + 15: always behind the loads)
                 const float nref = -ref;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                auto probabilities = [&](const unsigned* x, int c) {
                     unsigned pk[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float x0 = fmaf(__uint_as_float(v[c * 32 + i]), p.scale_log2e, nref);
-                        const float x1 = fmaf(__uint_as_float(v[c * 32 + i + 1]), p.scale_log2e, nref);
-                        float e0, e1;
-                        if (POLY > 0 && ((i >> 1) % (POLY > 0 ? POLY : 1)) == 0) {
-                            e0 = ex2_poly(x0);
-                            e1 = ex2_poly(x1);
+                        float s0 = __uint_as_float(x[i]), s1 = __uint_as_float(x[i + 1]);
+                        if (MODE != 0 && diag && c * 32 + i > r) s0 = -INFINITY;
+                        if (MODE != 0 && diag && c * 32 + i + 1 > r) s1 = -INFINITY;
+                        const float x0 = fmaf(s0, p.scale_log2e, nref), x1 = fmaf(s1, p.scale_log2e, nref);
+                        if constexpr (MODE == 2) {
+                            pk[i >> 1] = ex2_pair<T>(x0, x1);
                         } else {
-                            e0 = ex2_approx(x0);
-                            e1 = ex2_approx(x1);
+                            const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                            l4[i & 2] += e0;
+                            l4[(i & 2) + 1] += e1;
+                            pk[i >> 1] = pack2<T>(e0, e1);
                         }
-                        l4[i & 2] += e0;
-                        l4[(i & 2) + 1] += e1;
-                        pk[i >> 1] = pack2<T>(e0, e1);
                     }
+                    if constexpr (MODE == 2) l4[c] += sum_packed32<T>(pk);
                     tmem_st_32x16(s_addr + (unsigned)c * 16u, pk);
+                };
+                if constexpr (MODE == 0) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) probabilities(v + c * 32, c);
+                } else {
+                    unsigned va[32], vb[32];
+                    tmem_ld_32x32(s_addr, va);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 32u, vb);
+                    probabilities(va, 0);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 64u, va);
+                    probabilities(vb, 1);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(s_addr + 96u, vb);
+                    probabilities(va, 2);
+                    tmem_ld_wait();
+                    probabilities(vb, 3);
                 }
                 l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
                 tmem_st_wait();

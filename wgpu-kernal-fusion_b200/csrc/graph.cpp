@@ -562,7 +562,8 @@ bool pair_kernel_shape(const Node* m) {
     const int r = m->rank();
     if (r != 2 && r != 3) return false;
     const int64_t M = m->shape[r - 2], N = m->shape[r - 1], K = m->inputs[0]->shape[r - 1];
-    return M >= 256 && N >= 128 && K >= 64;
+    const int64_t rem = M % 256;
+    return M >= 256 && N >= 128 && K >= 64 && !(M < 2048 && rem != 0 && rem <= 128);   // as matmul_tc_pair_path decides
 }
 
 struct EpilogueMatch {
