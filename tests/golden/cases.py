@@ -111,7 +111,7 @@ def _():
     return (lambda g: {"x": _n(g, (117,))}, lambda t, ns: t["x"].softmax())
 
 
-@case("silu_24x40", ("ulp", 4))
+@case("silu_24x40", ("ulp", 6))
 def _():
     return (lambda g: {"x": _n(g, (24, 40), 2)}, lambda t, ns: t["x"].silu())
 

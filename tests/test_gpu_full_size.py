@@ -82,10 +82,10 @@ def test_config3_pairwise_broadcast_at_64x512x1024(wgf, dev, orc):
     silu_ref = (orc.Ref(a[ii, jj]) * 1.5).silu()
     bc_ref = orc.Ref(b[jj]) * orc.Ref(c[ii])
     ref = (silu_ref + bc_ref).numpy()
-    # every op within 2 ulp on its own inputs; the final add can cancel: 2 ulp of the result plus
-    # 2 ulp of the larger addend
+    # every op within 2 ulp on its own inputs: the silu chain (mul, neg, exp, add, div.full) within 6 ulp
+    # of its value, b*c exactly rounded; the final add can cancel, so the bound is on the addends
     eps = np.float64(2.0 ** -23)
-    bound = 2 * eps * (np.abs(ref.astype(np.float64)) + np.maximum(np.abs(silu_ref.numpy()), np.abs(bc_ref.numpy())))
+    bound = eps * (np.abs(ref.astype(np.float64)) + 6 * np.abs(silu_ref.numpy().astype(np.float64)) + np.abs(bc_ref.numpy().astype(np.float64)))
 
     before = dev.launch_count
     got = ((ta * 1.5).silu() + tb.broadcast((A, B, H)) * tc.broadcast((A, B, H))).as_slice()
@@ -96,11 +96,11 @@ def test_config3_pairwise_broadcast_at_64x512x1024(wgf, dev, orc):
     assert dev.launch_count - before == 1
     assert got_t.shape == (B, A, H)
     np.testing.assert_array_equal(got_t, np.ascontiguousarray(got.transpose(1, 0, 2)))     # all elements
-    # a read through transpose(1,2): [64,1024,512]; silu alone (five ops deep: 4 ulp)
+    # a read through transpose(1,2): [64,1024,512]; silu alone (five ops deep, two of them to 2 ulp: 6 ulp)
     got_i = (ta.transpose(1, 2) * 1.5).silu().as_slice()
     assert got_i.shape == (A, H, B)
     ref_i = (orc.Ref(a[ii, jj]) * 1.5).silu().numpy()
-    assert int(orc.ulp_diff_f32(np.ascontiguousarray(got_i[ii, :, jj]), ref_i).max()) <= 4
+    assert int(orc.ulp_diff_f32(np.ascontiguousarray(got_i[ii, :, jj]), ref_i).max()) <= 6
     # the inner-transposed pairwise form: a^T(1,2) with b^T, c broadcast along the new inner axis
     got_p = ((ta.transpose(1, 2) * 1.5).silu() + tb.transpose(0, 1).broadcast_axis(0, A)
              * tc.broadcast_axis(2, B)).as_slice()

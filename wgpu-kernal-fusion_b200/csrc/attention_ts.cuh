@@ -77,6 +77,12 @@ template <> __device__ __forceinline__ unsigned ex2_pair<__nv_bfloat16>(float x0
     asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(h));
     return e;
 }
+// max(a, b, c) in one instruction
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ unsigned hadd2(unsigned a, unsigned b) {
     unsigned r;
     asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -339,7 +345,12 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                             if (i > r) v[i] = 0xff800000u;   // -inf above the diagonal
                     }
 #pragma unroll
-                    for (int i = 0; i < 128; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                    for (int i = 0; i < 128; i += 8) {   // four chains, two scores per instruction
+                        m4[0] = fmax3(m4[0], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                        m4[1] = fmax3(m4[1], __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                        m4[2] = fmax3(m4[2], __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                        m4[3] = fmax3(m4[3], __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                    }
                 } else {
                     // first sweep: the maximum, 32 scores at a time, the next load in flight meanwhile
                     unsigned va[32], vb[32];

@@ -34,12 +34,16 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
     unsigned long long start = 0;
     for (unsigned spin = 0; spin < SPIN_LIMIT; ++spin) {
         unsigned ok;
+        // the last operand is the time (ns) the hardware may keep the thread suspended before the test
+        // returns false; the thread wakes at once when the phase completes.  Without it a waiting warp
+        // re-issues the test (and this loop's bookkeeping) so often that, in the attention kernel, half
+        // of all executed instructions were waits taking issue slots from the warps that had work.
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(20000u)
             : "memory");
         if (ok) return true;
         // besides the iteration limit, never wait longer than two seconds of wall time
