@@ -325,8 +325,8 @@ def matmul_record(wgf, dev, torch, stream, barrier, launches=60):
     count = dev.launch_count - before
     clocks = sampler.stop()
     per_launch_ns = []
-    for o, n in zip(ops, seen):
-        per_launch_ns += o[0].all_timing_information()[n:]
+    for o, already in zip(ops, seen):
+        per_launch_ns += o[0].all_timing_information()[already:]
     dev.set_timing(False)
     ms = float(np.mean(per_launch_ns)) / 1e6
     c = ops[0][0].mat_mul(ops[0][1]).as_slice().astype(np.float64)
