@@ -66,6 +66,7 @@ struct AtParams {
     int v_heads, v_rows;
     long long o_rs, o_hs, o_bs;   // output row / head / batch stride in elements
     unsigned* error;         // device word: 0 = ok, else code of the wait that gave up
+    unsigned long long* prof;   // null, or 26 cycle totals written by CTA 0 of attention_ts_kernel (WGF_ATT_PROFILE=1)
 };
 
 // kind::f16 instruction descriptor for M = 128, N = 128 (fields as in matmul_tc.cu)
@@ -969,10 +970,16 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
     p.error = dev.error_word();
     // Kernel forms, newest first: P through tensor memory (attention_ts_kernel, the default); P through
     // shared memory with two query tiles per CTA (WGF_ATT_SMEM_P=1: attention_tc2_kernel, one pass, or
-    // two with WGF_ATT_TWO_PASS=1); one query tile per CTA (WGF_ATT_SINGLE=1).
+    // two with WGF_ATT_TWO_PASS=1); one query tile per CTA (WGF_ATT_SINGLE=1).  These switches are read
+    // at every call: the tests go through all the forms in one process.
     const bool single = getenv("WGF_ATT_SINGLE") != nullptr;
     const bool two_pass = getenv("WGF_ATT_TWO_PASS") != nullptr;
     const bool smem_p = single || two_pass || getenv("WGF_ATT_SMEM_P") != nullptr;
+    BufferRef prof_buf;
+    if (getenv("WGF_ATT_PROFILE") && !smem_p) {
+        prof_buf = dev.alloc(26 * sizeof(unsigned long long), true);
+        p.prof = (unsigned long long*)prof_buf->ptr;
+    }
     const bool pairs = !single;
     const long long items = pairs ? BH * ((S / 128 + 1) / 2) : BH * (S / 128);
     const unsigned grid = (unsigned)std::min<long long>(items, dev.sm_count);
@@ -995,13 +1002,14 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
         // how the softmax warps go over the scores (see attention_ts.cuh); WGF_ATT_MODE picks another form
         const char* me = getenv("WGF_ATT_MODE");
         const int mode = me ? atoi(me) : 0;
-        if (bf16) {
+        if (prof_buf) {
+            if (bf16) launch(attention_ts_kernel<__nv_bfloat16, 0, true>, 10, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
+            else launch(attention_ts_kernel<__half, 0, true>, 11, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
+        } else if (bf16) {
             if (mode == 1) launch(attention_ts_kernel<__nv_bfloat16, 1>, 9, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
-            else if (mode == 2) launch(attention_ts_kernel<__nv_bfloat16, 2>, 10, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
             else launch(attention_ts_kernel<__nv_bfloat16, 0>, 8, TS_THREADS, TS_SMEM, (__nv_bfloat16*)out.base_ptr());
         } else {
             if (mode == 1) launch(attention_ts_kernel<__half, 1>, 7, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
-            else if (mode == 2) launch(attention_ts_kernel<__half, 2>, 11, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
             else launch(attention_ts_kernel<__half, 0>, 6, TS_THREADS, TS_SMEM, (__half*)out.base_ptr());
         }
     } else if (pairs) {
@@ -1018,6 +1026,21 @@ TensorData run_attention(Device& dev, const TensorData& q_in, const TensorData& 
         else launch(attention_tc_kernel<__half>, 0, AT_THREADS, AT_SMEM, (__half*)out.base_ptr());
     }
     dev.end_launch();
+    if (prof_buf) {
+        // measurement aid: waits for the kernel and prints where CTA 0's warps spent their cycles
+        unsigned long long prof[26];
+        WGF_CUDA(cudaStreamSynchronize(dev.stream));
+        WGF_CUDA(cudaMemcpy(prof, prof_buf->ptr, sizeof prof, cudaMemcpyDeviceToHost));
+        const char* mma[10] = {"other", "wait Q", "wait K0", "wait O empty", "wait P0", "wait P1", "wait V", "wait K", "issue PV", "issue S"};
+        const char* sm[8] = {"other", "wait S", "load+max", "rescale", "exp+store", "hand-over", "wait O", "write-out"};
+        fprintf(stderr, "[wgf] attention_ts, CTA 0, cycles by role\n  MMA warp:");
+        for (int i = 0; i < 10; ++i) fprintf(stderr, " %s %llu,", mma[i], prof[i]);
+        for (int t = 0; t < 2; ++t) {
+            fprintf(stderr, "\n  softmax warps of tile %d:", t);
+            for (int i = 0; i < 8; ++i) fprintf(stderr, " %s %llu,", sm[i], prof[10 + 8 * t + i]);
+        }
+        fprintf(stderr, "\n");
+    }
     return out;
 }
 

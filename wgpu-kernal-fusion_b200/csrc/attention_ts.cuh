@@ -27,6 +27,13 @@
 // MMAs of the thread), P V_t(j-1) among them: O_t is at rest while the softmax warps of tile t work.
 // Tensor memory: S_t / P_t in columns 128 t, O_t in 256 + 128 t.  Every wait is bounded.
 
+// Cycle counters around the waits and phases of each role, CTA 0 only, in the PROF instantiation of
+// the kernel (WGF_ATT_PROFILE=1 selects it): 26 totals that run_attention prints after the launch.
+// The ordinary instantiation carries none of it.
+#define PROF_DECL(n) unsigned long long prof_acc[PROF ? n : 1] = {}; const bool prof_on = PROF && p.prof != nullptr && blockIdx.x == 0; unsigned long long prof_t = prof_on ? clock64() : 0; (void)prof_acc; (void)prof_t
+#define PROF_LAP(slot) do { if constexpr (PROF) { if (prof_on) { const unsigned long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; } } } while (0)
+#define PROF_FLUSH(base, n) do { if constexpr (PROF) { if (prof_on) for (int i_ = 0; i_ < (n); ++i_) p.prof[(base) + i_] = prof_acc[i_]; } } while (0)
+
 constexpr int TS_STAGES = 5;
 constexpr int TS_THREADS = 320;
 constexpr int TS_SMEM = (2 + TS_STAGES) * AT_TILE + 1024 /*alignment slack*/ + 512 /*barriers*/;
@@ -57,65 +64,23 @@ __device__ __forceinline__ void tmem_st_32x16(unsigned taddr, const unsigned* r)
         : "memory");
 }
 
-// Two exponentials with one special-function instruction: x0, x1 are rounded to the 16-bit type,
-// ex2.approx works on the packed pair and its result IS the packed pair of probabilities that
-// goes into tensor memory (no conversion afterwards).  The special-function unit gives 16 results
-// per clock and SM -- 1024 clocks for the 128 x 128 exponentials of a tile, as long as the tile's two
-// MMAs take -- and half that in packed form.  Cost: the argument is rounded to 11 (8) bits before
-// the exponential, a relative error of |x| * 2^-11 * ln 2 in P (3e-4 at x = -1, 3e-3 at x = -8, where
-// P is already below 2^-8 of the row maximum).
-template <typename T> __device__ __forceinline__ unsigned ex2_pair(float x0, float x1);
-template <> __device__ __forceinline__ unsigned ex2_pair<__half>(float x0, float x1) {
-    unsigned h, e;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(e) : "r"(h));
-    return e;
-}
-template <> __device__ __forceinline__ unsigned ex2_pair<__nv_bfloat16>(float x0, float x1) {
-    unsigned h, e;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
-    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(h));
-    return e;
-}
 // max(a, b, c) in one instruction
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-__device__ __forceinline__ unsigned hadd2(unsigned a, unsigned b) {
-    unsigned r;
-    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-// Sum of the 32 probabilities in 16 packed registers, in f32.  f16: a tree of packed f16 adds (depth 4:
-// relative error below 4 * 2^-11 of a partial sum, values <= 2^8 each so nothing overflows), then one
-// conversion; bf16 (8 bits: too coarse to add in) unpacks every pair with a shift and a mask.
-template <typename T> __device__ __forceinline__ float sum_packed32(const unsigned* pk);
-template <> __device__ __forceinline__ float sum_packed32<__half>(const unsigned* pk) {
-    unsigned t8[8], t4[4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) t8[i] = hadd2(pk[2 * i], pk[2 * i + 1]);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) t4[i] = hadd2(t8[2 * i], t8[2 * i + 1]);
-    const unsigned t = hadd2(hadd2(t4[0], t4[1]), hadd2(t4[2], t4[3]));
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&t));
-    return f.x + f.y;
-}
-template <> __device__ __forceinline__ float sum_packed32<__nv_bfloat16>(const unsigned* pk) {
-    float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        s0 += __uint_as_float(pk[i] << 16);
-        s1 += __uint_as_float(pk[i] & 0xffff0000u);
-    }
-    return s0 + s1;
-}
-
 // MODE 0: the 128 scores of a row are loaded into registers once (maximum, exponentials and P all come
 //         from them); 1: two sweeps over tensor memory, 32 scores at a time (a quarter of the
-//         registers); 2: two sweeps and packed exponentials (ex2_pair).
-template <typename T, int MODE>
+//         registers, no spills; measured slower: 429 / 732 us against 382 / 592 us causal / full on
+//         [256, 2048, 128]).  Also measured and dropped: packed exponentials (ex2.approx.f16x2 keeps the
+//         special-function unit as long as two scalar ones: 459 / 801 us), a cubic 2^x on the FMA pipe
+//         for half or a quarter of the elements (441 / 721 and 407 / 653 us) and P handed to the MMA
+//         warp in two halves (405 / 642 us): per key tile a softmax warp group computes for about 2100
+//         cycles and waits for S about as long, the MMA warp waits for P a quarter of its time -- the
+//         tiles' softmax phases overlap each other instead of the other tile's MMAs (cycle counters:
+//         WGF_ATT_PROFILE=1).
+template <typename T, int MODE, bool PROF = false>
 __global__ void __launch_bounds__(TS_THREADS, 1)
 attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, T* __restrict__ O, const __grid_constant__ AtParams p) {
@@ -205,6 +170,7 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             unsigned q_phase[2] = {0, 0}, p_phase[2] = {0, 0}, o_phase[2] = {1, 1};
             bool ok = true;
             int nk[2];
+            PROF_DECL(10);   // 0 bookkeeping, 1 Q, 2 K(0), 3 O empty, 4 P of tile 0, 5 P of tile 1, 6 V, 7 K(j+1), 8 issue of P V, 9 issue of S
             auto wait_or = [&](int which, unsigned ph, unsigned code) -> bool {
                 if (mbar_wait(bar(which), ph)) return true;
                 atomicExch(p.error, code);
@@ -249,14 +215,17 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 nk[0] = tiles_of(pt, 0);
                 nk[1] = tiles_of(pt, 1);
                 const int n_max = max(nk[0], nk[1]);
+                PROF_LAP(0);
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (nk[t] == 0) continue;
                     ok = wait_or(TQ_FULL + t, q_phase[t], 100u);
                     q_phase[t] ^= 1;
                 }
                 if (!ok) break;
+                PROF_LAP(1);
                 // S_t(0) for both tiles
                 if (!(ok = wait_ring(pos, 101u))) break;
+                PROF_LAP(2);
                 tc_fence_after();
                 for (int t = 0; t < 2; ++t)
                     if (nk[t] > 0) issue_s(t, pos, nk[t] == 1);
@@ -266,25 +235,34 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     bool have_v = false, have_k = false;
                     for (int t = 0; t < 2 && ok; ++t) {
                         if (j >= nk[t]) continue;
+                        PROF_LAP(0);
                         if (j == 0) {                       // the previous item's O_t has been read out
                             if (!(ok = wait_or(TO_EMPTY + t, o_phase[t], 102u))) break;
                             o_phase[t] ^= 1;
+                            PROF_LAP(3);
                         }
                         if (!(ok = wait_or(TP_FULL + t, p_phase[t], 103u))) break;
                         p_phase[t] ^= 1;
+                        PROF_LAP(4 + t);
                         if (!have_v) {
                             if (!(ok = wait_ring(at_v, 104u))) break;
                             have_v = true;
+                            PROF_LAP(6);
                         }
                         tc_fence_after();
+                        PROF_LAP(0);
                         issue_pv(t, at_v, j == 0, j == nk[t] - 1);
+                        PROF_LAP(8);
                         if (j + 1 < nk[t]) {
                             if (!have_k) {
                                 if (!(ok = wait_ring(at_k, 105u))) break;
                                 have_k = true;
+                                PROF_LAP(7);
                                 tc_fence_after();
                             }
+                            PROF_LAP(0);
                             issue_s(t, at_k, j + 1 == nk[t] - 1);
+                            PROF_LAP(9);
                         }
                     }
                     if (!ok) break;
@@ -293,6 +271,8 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 pos += 2u * (unsigned)n_max;
             }
+            PROF_LAP(0);
+            PROF_FLUSH(0, 10);
         }
     } else {
         // ------------------------------------------------------------------ softmax (warps 2-5: tile 0, warps 6-9: tile 1)
@@ -303,6 +283,7 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const unsigned s_addr = lane_base + (unsigned)t * AT_S_COLS, o_addr = lane_base + AT_O_COL0 + (unsigned)t * 128u;
         unsigned s_phase = 0, o_phase = 0;
         bool ok = true;
+        PROF_DECL(8);   // 0 other, 1 wait S, 2 loads + maximum, 3 rescale, 4 exponentials + stores, 5 hand-over, 6 wait O, 7 write-out
         auto wait_all = [&](int which, unsigned parity, unsigned code) -> bool {
             bool got = mbar_wait(bar(which), parity);
             got = __all_sync(0xffffffffu, got);
@@ -317,8 +298,10 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int qt = 2 * pt + t;
             float l_run = 0.f, ref = 0.f;
             for (int j = 0; j < n_kv && ok; ++j) {
+                PROF_LAP(0);
                 if (!(ok = wait_all(TS_FULL + t, s_phase, 110u))) break;
                 s_phase ^= 1;
+                PROF_LAP(1);
                 tc_fence_after();
                 float alpha = 1.f;
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -375,6 +358,7 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     alpha = ex2_approx(ref - mt);
                     ref = mt;
                 }
+                PROF_LAP(2);
                 if (__any_sync(0xffffffffu, grow)) {
                     // S_t(j) is complete, so P V_t(j-1) is too: O_t is at rest.  Rescale this warp's 32
                     // rows (lanes whose maximum did not grow multiply by 1).
@@ -388,6 +372,7 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         tmem_st_32x32(o_addr + (unsigned)c * 32u, o);
                     }
                 }
+                PROF_LAP(3);
                 // P = exp2(s * c - ref), packed two per column over the columns the scores came from
                 // (chunk c of 32 scores becomes columns 16 c .. 16 c + 15: always behind the loads)
                 const float nref = -ref;
@@ -399,16 +384,11 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         if (MODE != 0 && diag && c * 32 + i > r) s0 = -INFINITY;
                         if (MODE != 0 && diag && c * 32 + i + 1 > r) s1 = -INFINITY;
                         const float x0 = fmaf(s0, p.scale_log2e, nref), x1 = fmaf(s1, p.scale_log2e, nref);
-                        if constexpr (MODE == 2) {
-                            pk[i >> 1] = ex2_pair<T>(x0, x1);
-                        } else {
-                            const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
-                            l4[i & 2] += e0;
-                            l4[(i & 2) + 1] += e1;
-                            pk[i >> 1] = pack2<T>(e0, e1);
-                        }
+                        const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                        l4[i & 2] += e0;
+                        l4[(i & 2) + 1] += e1;
+                        pk[i >> 1] = pack2<T>(e0, e1);
                     }
-                    if constexpr (MODE == 2) l4[c] += sum_packed32<T>(pk);
                     tmem_st_32x16(s_addr + (unsigned)c * 16u, pk);
                 };
                 if constexpr (MODE == 0) {
@@ -430,15 +410,18 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     probabilities(vb, 3);
                 }
                 l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+                PROF_LAP(4);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(TP_FULL + t));
+                PROF_LAP(5);
             }
             if (!ok) break;
             // ---- O / l -> global memory
             if (!(ok = wait_all(TO_FULL + t, o_phase, 111u))) break;
             o_phase ^= 1;
+            PROF_LAP(6);
             tc_fence_after();
             const float inv = 1.0f / l_run;
             T* orow = O + (long long)(b / p.heads) * p.o_bs + (long long)(b % p.heads) * p.o_hs + ((long long)qt * 128 + r) * p.o_rs;
@@ -460,7 +443,9 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(TO_EMPTY + t));
+            PROF_LAP(7);
         }
+        if (lane == 0 && quarter == 0) PROF_FLUSH(10 + 8 * t, 8);
     }
     tc_fence_before();
     __syncthreads();
