@@ -344,7 +344,7 @@ def matmul_record(wgf, dev, torch, stream, barrier, launches=60):
 
 
 def llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=2048, masked=False, steps=10, warmup=3,
-                 check=True):
+                 check=True, breakdown=False):
     blk = LlamaBlock(wgf, dev, world, rank, seq, masked)
     for _ in range(warmup):
         blk.step()
@@ -354,6 +354,18 @@ def llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=2048, 
     launches = dev.launch_count - before
     clocks = sampler.stop() if sampler else None
     err = blk.check() if check else None
+    # device time of every kernel of one step (event pair around each launch), after the timed region
+    kernels = None
+    if breakdown and blk.x is not None:
+        dev.set_timing(True)
+        for _ in range(2):
+            seen = len(blk.x.all_timing_information())
+            out = blk.request().materialize()
+            dev.sync()
+            ns, labels = blk.x.all_timing_information()[seen:], blk.x.timing_labels()[seen:]
+            del out
+        dev.set_timing(False)
+        kernels = [{"kernel": name, "us": round(t / 1e3, 1)} for name, t in zip(labels, ns)]
     vals = torch.tensor([ms, float(launches), err if err is not None else 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         mx, sm = vals.clone(), vals.clone()
@@ -369,6 +381,8 @@ def llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=2048, 
            "attention": "matmul + masked softmax + matmul" if masked else "fused tcgen05 kernel", "clocks": clocks}
     if err is not None:
         rec["check"] = {"sampled_tokens_rel": err, "ok": bool(err <= 2e-2)}
+    if kernels is not None:
+        rec["kernels_of_one_step"] = kernels
     return rec
 
 
@@ -686,7 +700,7 @@ def run_llama(args):
         torch.cuda.synchronize()
 
     rec = llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=args.seq, masked=args.separate_kernels,
-                       steps=args.steps, warmup=max(args.warmup, 3), check=not args.no_cpu)
+                       steps=args.steps, warmup=max(args.warmup, 3), check=not args.no_cpu, breakdown=args.breakdown)
     if rank == 0:
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
@@ -698,7 +712,7 @@ def run_llama(args):
                        "head_dim": rec["hidden"] // rec["heads"], "mlp": rec["mlp"], "global_batch": rec["global_batch"],
                        "seq_len": rec["seq_len"], "sharding": rec["sharding"], "attention": rec["attention"]},
             "tflops_nominal": rec["tflops_nominal"], "gpu_launches": rec["gpu_launches"], "check": rec.get("check"),
-            "clocks": rec["clocks"],
+            "kernels_of_one_step": rec.get("kernels_of_one_step"), "clocks": rec["clocks"],
         }))
     if world > 1:
         dist.barrier()
@@ -732,6 +746,7 @@ def main():
     ap.add_argument("--workload", default="fused_chain", choices=["fused_chain", "llama_block", "configs"])
     ap.add_argument("--seq", type=int, default=2048, help="sequence length of the llama_block workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (llama_block: the float64 check)")
+    ap.add_argument("--breakdown", action="store_true", help="llama_block: also list the device time of every kernel of one step")
     ap.add_argument("--no-extras", action="store_true",
                     help="fused_chain: leave out the long_run, matmul and llama_block records")
     ap.add_argument("--rows", default=None, help="configs workload: only the rows whose name contains this text")
