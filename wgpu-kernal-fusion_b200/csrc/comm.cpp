@@ -53,8 +53,13 @@ Comm::~Comm() {
     if (dev) cudaSetDevice(dev->ordinal);
     for (int r = 0; r < (int)peer_mailbox.size(); ++r)
         if (r != rank && peer_mailbox[r]) cudaIpcCloseMemHandle(peer_mailbox[r]);
+    // Result buffers of earlier exchanges may still name one of these events as what they wait for, so the
+    // events are not destroyed: they go to the device's pool, where they stay valid (a stale waiter then
+    // waits for whatever the event's next user records, or for nothing).
     for (cudaEvent_t e : finished)
-        if (e) cudaEventDestroy(e);
+        if (e && dev) dev->recycle(e);
+    for (cudaEvent_t e : posted)
+        if (e && dev) dev->recycle(e);
     if (peer_table) cudaFree(peer_table);
     if (mailbox) cudaFree(mailbox);
     if (handle) Nccl::get().CommDestroy(handle);
@@ -116,11 +121,13 @@ void setup_mailboxes(Comm& c) {
     }
     if (ok) {
         c.finished.assign(kMailboxSlots, nullptr);
-        for (auto& e : c.finished)
-            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
-                e = nullptr;
-                ok = 0;
-            }
+        c.posted.assign(kMailboxSlots, nullptr);
+        for (auto* ring : {&c.finished, &c.posted})
+            for (auto& e : *ring)
+                if (cudaEventCreate(&e) != cudaSuccess) {   // timing-capable: they end their life in the device pool
+                    e = nullptr;
+                    ok = 0;
+                }
     }
     if (cudaMemcpy(flag.p, &ok, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
     cudaGetLastError();   // a failed mapping is not an error of the library: NCCL takes over
@@ -193,10 +200,9 @@ void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<Peer
     WGF_CHECK(!vals.empty() && vals.size() <= (size_t)kMailboxValues, WGF_ERR_INVALID_ARGUMENT, "exchange of 1..4 values");
     dev.make_current();
     cudaStream_t cs = dev.collective_stream();
-    cudaEvent_t posted = dev.event();
-    WGF_CUDA(cudaEventRecord(posted, dev.stream));
-    WGF_CUDA(cudaStreamWaitEvent(cs, posted, 0));
-    dev.recycle(posted);
+    const uint32_t slot = seq % kMailboxSlots;
+    WGF_CUDA(cudaEventRecord(c.posted[slot], dev.stream));
+    WGF_CUDA(cudaStreamWaitEvent(cs, c.posted[slot], 0));
     dev.launches++;
     launch_peer_combine(cs, c.mailbox, dev.error_word(), c.wait_ns, (uint32_t)c.world, (uint32_t)c.rank, seq, vals);
     cudaError_t e = cudaPeekAtLastError();
@@ -204,12 +210,14 @@ void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<Peer
         cudaGetLastError();
         fail(WGF_ERR_CUDA, std::string("peer_combine launch failed: ") + cudaGetErrorString(e));
     }
-    WGF_CUDA(cudaEventRecord(c.finished[seq % kMailboxSlots], cs));
+    WGF_CUDA(cudaEventRecord(c.finished[slot], cs));
+    // the results wait for that same event (it is recorded again 16 exchanges later: a reader that comes
+    // after that waits a little longer than it has to, never too little)
     for (const PeerValue& v : vals) {
         Buffer& b = *v.out.buf;
-        if (b.pending) dev.recycle(b.pending);   // written by the posting kernel on the device stream only
-        b.pending = dev.event();
-        WGF_CUDA(cudaEventRecord(b.pending, cs));
+        if (b.pending && !b.pending_shared) dev.recycle(b.pending);   // written by the posting kernel on the device stream only
+        b.pending = c.finished[slot];
+        b.pending_shared = true;
     }
 }
 

@@ -32,7 +32,8 @@ struct Comm {
     uint32_t seq = 0;                     // sequence number of the last exchange
     bool peer_ok = false;                 // every rank mapped every peer
     uint64_t wait_ns = 5000000000ull;     // limit of the combine kernel's wait (WGF_PEER_WAIT_MS)
-    std::vector<cudaEvent_t> finished;    // [kMailboxSlots] completion events of the combine kernels
+    std::vector<cudaEvent_t> finished;    // [kMailboxSlots] completion events of the combine kernels (also the results' Buffer::pending)
+    std::vector<cudaEvent_t> posted;      // [kMailboxSlots] "the posting kernel is queued" events
     ~Comm();
 };
 constexpr int kMailboxValues = 4;

@@ -179,20 +179,20 @@ Buffer::~Buffer() {
             // a block of a recorded schedule stays with the schedule while that one lives
             std::lock_guard<std::mutex> g(arena->mu);
             if (!arena->closed) {
-                if (pending) dev->recycle(pending);
+                if (pending && !pending_shared) dev->recycle(pending);
                 arena->free.emplace(block, ptr);
                 return;
             }
         }
         // a collective may still touch the block: it goes back to the pool once that is over
-        if (pending) dev->release_block_after(ptr, block, pending);
+        if (pending) dev->release_block_after(ptr, block, pending, pending_shared);
         else dev->release_block(ptr, block);
     }
 }
 
-void Device::release_block_after(void* p, size_t block, cudaEvent_t ev) {
+void Device::release_block_after(void* p, size_t block, cudaEvent_t ev, bool shared_event) {
     std::lock_guard<std::mutex> g(mu_);
-    deferred_.push_back({p, block, ev});
+    deferred_.push_back({p, block, ev, shared_event});
 }
 
 // Moves blocks whose collective has finished from the deferred list to the pool.  mu_ held.
@@ -201,7 +201,7 @@ void Device::drain_deferred_locked() {
         if (cudaEventQuery(deferred_[i].ev) == cudaSuccess) {
             free_.emplace(deferred_[i].block, deferred_[i].ptr);
             in_use_ -= deferred_[i].block;
-            event_pool_.push_back(deferred_[i].ev);
+            if (!deferred_[i].shared_event) event_pool_.push_back(deferred_[i].ev);
             deferred_[i] = deferred_.back();
             deferred_.pop_back();
         } else {
@@ -225,8 +225,9 @@ void Device::wait_for(Buffer& b) {
     // an event recorded outside a capture cannot become a dependency inside it: wait on the host
     if (recording()) cudaEventSynchronize(b.pending);
     else cudaStreamWaitEvent(stream, b.pending, 0);
-    recycle(b.pending);
+    if (!b.pending_shared) recycle(b.pending);
     b.pending = nullptr;
+    b.pending_shared = false;
 }
 
 std::shared_ptr<Device> Device::create(int ordinal) {
@@ -387,10 +388,21 @@ BufferRef Device::alloc(size_t bytes, bool zero) {
     }
     if (!p) {
         std::lock_guard<std::mutex> g(mu_);
-        if (!deferred_.empty()) drain_deferred_locked();
-        auto it = free_.lower_bound(block);
-        // reuse a cached block unless it would waste more than a quarter of itself
-        if (it != free_.end() && it->first <= block + block / 4 + 4096) {
+        // Blocks that wait for a collective are looked at only when the pool has nothing that fits (or
+        // when many have piled up): asking the driver about every one of them on every allocation cost
+        // the host several microseconds per step.
+        if (deferred_.size() > 64) drain_deferred_locked();
+        auto fits = [&] {
+            auto it = free_.lower_bound(block);
+            // reuse a cached block unless it would waste more than a quarter of itself
+            return it != free_.end() && it->first <= block + block / 4 + 4096 ? it : free_.end();
+        };
+        auto it = fits();
+        if (it == free_.end() && !deferred_.empty()) {
+            drain_deferred_locked();
+            it = fits();
+        }
+        if (it != free_.end()) {
             p = it->second;
             block = it->first;
             free_.erase(it);

@@ -45,6 +45,9 @@ struct Buffer {
     // buffer.  The device stream waits for it before the next use of the buffer and before
     // the block goes back to the pool (Device::wait_for, ~Buffer).
     cudaEvent_t pending = nullptr;
+    // `pending` belongs to someone else (a communicator's ring of completion events): waited for like
+    // any other, but not returned to the device's event pool afterwards
+    bool pending_shared = false;
     std::shared_ptr<Arena> arena;   // set for buffers allocated while a schedule was being recorded
     ~Buffer();
 };
@@ -113,7 +116,7 @@ struct Device : std::enable_shared_from_this<Device> {
     uint64_t in_use_bytes() const { return in_use_; }
     void release_block(void* p, size_t block);
     // Same, but only once `ev` (recorded on the collective stream) has completed.
-    void release_block_after(void* p, size_t block, cudaEvent_t ev);
+    void release_block_after(void* p, size_t block, cudaEvent_t ev, bool shared_event = false);
     void trim();
 
     // ---- kernels ----
@@ -175,6 +178,7 @@ struct Device : std::enable_shared_from_this<Device> {
         void* ptr;
         size_t block;
         cudaEvent_t ev;
+        bool shared_event;   // not ours to recycle
     };
     std::vector<Deferred> deferred_;
     std::shared_ptr<Arena> arena_;     // non-null while recording
