@@ -286,9 +286,48 @@ class LlamaBlock:
         return tokens * (4 * 2 * self.Hd * self.Hd + 3 * 2 * self.Hd * self.inter + 4 * self.seq * self.Hd)
 
 
+class Barrier:
+    """barrier(): device sync of the library, dist.barrier(), torch.cuda.synchronize().
+    barrier.start() is the barrier that opens a timed region.  Ranks leave a barrier tens of
+    microseconds apart (every host thread wakes up by itself), and a rank that starts early spends
+    that time inside its region waiting for the others' first all-reduce: the maximum over ranks
+    would contain the barrier's own jitter.  The ranks of one node read the same monotonic clock, so
+    after the barrier rank 0 names an instant 2 ms ahead and every rank spins until then; the spread
+    of the instants at which the ranks really started is kept in skew_us()."""
+
+    def __init__(self, dev, dist, torch, world):
+        self.dev, self.dist, self.torch, self.world = dev, dist, torch, world
+        self.started_ns = 0
+
+    def __call__(self):
+        self.dev.sync()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def start(self):
+        self()
+        if self.world > 1:
+            t = self.torch.tensor([time.monotonic_ns() + 2_000_000], dtype=self.torch.int64, device="cuda")
+            self.dist.broadcast(t, 0)
+            deadline = int(t.item())
+            self.torch.cuda.synchronize()
+            while time.monotonic_ns() < deadline:
+                pass
+        self.started_ns = time.monotonic_ns()
+
+    def skew_us(self):
+        """Spread of the ranks' last start() instants (a collective: call outside timed regions)."""
+        if self.world == 1:
+            return 0.0
+        t = self.torch.tensor([self.started_ns, -self.started_ns], dtype=self.torch.int64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(int(t[0]) + int(t[1])) / 1e3
+
+
 def time_region(torch, stream, barrier, fn, steps, close=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    barrier.start()
     e0.record(stream)
     last = None
     for i in range(steps):
@@ -443,18 +482,14 @@ def run_gpu(args):
         return s
 
     def close_region(s):
-        # At N > 1 the ranks' scalars are combined by a small kernel on the library's collective
-        # stream, beside the next step's kernel.  The closing event of a timed region is recorded on
-        # the device stream, so the last step's scalar is consumed there first (one tiny kernel that
-        # waits for the combine): the region then contains every step's all-reduce in full.
+        # At N > 1 the kernel of a step posts this rank's scalar and combines the ranks' scalars of
+        # the step before; the last step's exchange is still open when the loop ends.  Its result is
+        # consumed here, inside the timed region (the library settles it with one small kernel, then
+        # a one-element multiply reads it): the region contains every step's all-reduce in full.
         if comm is not None and s is not None:
             (s * 1.0).materialize()
 
-    def barrier():
-        dev.sync()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    barrier = Barrier(dev, dist, torch, world)
 
     # ---- device-resident timing --------------------------------------------------------------
     sampler = ClockSampler(local) if rank == 0 else None   # sampled from the warm-up on: the timed region is short
@@ -469,18 +504,25 @@ def run_gpu(args):
     dev.set_timing(False)
     launches_before = dev.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    barrier.start()
     e0.record(stream)
     host_t0 = time.perf_counter()
     last = None
+    host_marks = []
     for i in range(args.steps):
         last = step(i)
-    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps   # time the host needs to queue one step
+        host_marks.append(time.perf_counter())
+    host_ms = (host_marks[-1] - host_t0) * 1e3 / args.steps   # time the host needs to queue one step
+    host_first_us = [round((b - a) * 1e6, 1) for a, b in zip([host_t0] + host_marks[:5], host_marks[:6])]
+    e_loop = torch.cuda.Event(enable_timing=True)
+    e_loop.record(stream)
     close_region(last)
     del last
     e1.record(stream)
     barrier()
     ms_total = e0.elapsed_time(e1)
+    start_skew_us = barrier.skew_us()    # how far apart the ranks opened the region
+    close_ms = e_loop.elapsed_time(e1)   # what consuming the last step's all-reduced scalar adds to the region
     launches = dev.launch_count - launches_before
 
     # Region B (the roofline): the same K steps again with an event pair around every launch.
@@ -598,7 +640,7 @@ def run_gpu(args):
         xs.clear()
         dev.set_timing(False)
         if rank == 0:
-            matmul = matmul_record(wgf, dev, torch, stream, lambda: (dev.sync(), torch.cuda.synchronize()))
+            matmul = matmul_record(wgf, dev, torch, stream, Barrier(dev, None, torch, 1))   # this rank alone
         llama = llama_record(wgf, dev, torch, dist, stream, barrier, world, rank)
 
     if rank == 0:
@@ -658,8 +700,13 @@ def run_gpu(args):
             "matmul": matmul,
             "llama_block": llama,
             "host_queue_ms_per_step": host_ms,
+            "region_close_ms": close_ms,
+            "host_queue_first_steps_us": host_first_us,
+            "row_kernel_first_launches_us": [round(t / 1e3, 1) for t in row_ns[:6]],
+            "row_kernel_median_us": (round(float(np.median(row_ns)) / 1e3, 1) if row_ns else None),
+            "region_start_skew_us": start_skew_us,
             "all_reduce": (None if comm is None else
-                           "posted by the reduction kernel over peer memory, combined by a one-CTA kernel on the collective stream"
+                           "posted by the reduction kernel over peer memory; the same kernel combines the ranks' values of the step before"
                            if per_step == kernels_per_step else "NCCL launch"),
             "all_reduce_on_device_stream_ms": ar_ms,
             "clocks": clocks,
@@ -697,12 +744,7 @@ def run_llama(args):
     stream = torch.cuda.ExternalStream(stream_ptr, device=torch.device("cuda", local))
     dev.set_timing(False)
 
-    def barrier():
-        dev.sync()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    barrier = Barrier(dev, dist, torch, world)
     rec = llama_record(wgf, dev, torch, dist, stream, barrier, world, rank, seq=args.seq, masked=args.separate_kernels,
                        steps=args.steps, warmup=max(args.warmup, 3), check=not args.no_cpu, breakdown=args.breakdown)
     if rank == 0:

@@ -2,8 +2,8 @@
 WGF_PEER_WAIT_MS=50 and NVLS off).
 
 Both ranks do one all-reduce over peer memory; then rank 1 sits one exchange out (it is idle, between
-steps, with nothing in flight).  Rank 0's combine kernel must give up after its 50 ms limit and
-return, rank 0's next synchronisation must raise WGF_ERR_TIMEOUT, further all-reduces on that device
+steps, with nothing in flight).  Rank 0's settling kernel (queued by the synchronisation) must give up after its 50 ms
+limit and return, rank 0's next synchronisation must raise WGF_ERR_TIMEOUT, further all-reduces on that device
 must be refused, and both ranks must be able to release the communicator and leave cleanly.  No GPU
 is faulted: the wait is a bounded poll of a word that nobody writes."""
 import datetime

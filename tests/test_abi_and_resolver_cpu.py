@@ -384,3 +384,49 @@ def test_null_chain_with_a_length_is_an_error_not_a_crash(wgf, drydev):
                                C.byref(out), None)
     assert wgf.STATUS[rc] == "INVALID_ARGUMENT"
     lib.wgf_buffer_release(C.c_void_p(d.buf))
+
+
+def test_all_reduce_over_peer_memory_costs_one_launch_per_step(wgf, drydev):
+    """Host side of the scalar all-reduce over peer memory, on the compile-only device (its
+    communicator needs no NCCL and compiles the same kernels).  The kernel of a step posts this
+    rank's values and settles the exchange of the step before: one launch per step, however many
+    values ride along.  A result that is read before the next posting kernel is settled by one
+    small kernel of its own, once; a synchronisation settles what is still open."""
+    d = drydev
+    comm = wgf.Comm(d, 2, 0, bytes(128))
+    x = d.tensor(np.zeros((64, 256), np.float32))
+
+    def step():
+        y = x.softmax_last_dim()
+        s = x.exp().sum(0).sum(0).all_reduce(comm)
+        m = x.max(0).max(0).all_reduce(comm, wgf.OP_MAX)
+        before = d.launch_count
+        wgf.Tensor.materialize_all([y, s, m])
+        return d.launch_count - before, s, m
+
+    n, s, m = step()
+    assert n == 1                                   # posts exchange 1; nothing to settle yet
+    n, s2, m2 = step()
+    assert n == 1                                   # posts 2, settles 1 in the same kernel
+    before = d.launch_count
+    (s * 2.0).materialize()                         # exchange 1 was settled by that kernel: plain read
+    assert d.launch_count - before == 1
+    before = d.launch_count
+    (s2 * 2.0).materialize()                        # exchange 2 is open: settle kernel + the multiply
+    assert d.launch_count - before == 2
+    before = d.launch_count
+    (m2 * 2.0).materialize()                        # same exchange: already settled
+    assert d.launch_count - before == 1
+    # the streaming reduction posts and settles too
+    before = d.launch_count
+    alone = (x * 2.0).exp().sum(0).sum(0).all_reduce(comm)
+    alone.materialize()
+    assert d.launch_count - before == 1
+    before = d.launch_count
+    d.sync()                                        # leaves nothing open ...
+    assert d.launch_count - before == 1
+    before = d.launch_count
+    d.sync()                                        # ... once
+    (alone * 2.0).materialize()
+    assert d.launch_count - before == 1
+    del comm

@@ -37,8 +37,8 @@ def test_all_reduce_inside_the_row_kernel(peer):
 
 
 def test_a_peer_that_sits_an_exchange_out_gives_a_timeout_status():
-    """The combine kernel's wait has a limit (WGF_PEER_WAIT_MS): when a peer never posts, the kernel
-    returns, the next synchronisation reports WGF_ERR_TIMEOUT and the communicator can be released."""
+    """The wait for the peers' values has a limit (WGF_PEER_WAIT_MS): when a peer never posts, the settling
+    kernel returns, the next synchronisation reports WGF_ERR_TIMEOUT and the communicator can be released."""
     if gpu_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ)

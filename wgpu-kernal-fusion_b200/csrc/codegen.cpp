@@ -107,6 +107,16 @@ struct ParamWriter {
     }
 };
 
+// PEER_SETTLE_PARAMS of the templates: the earlier exchange that a posting kernel settles.
+void put_settle(ParamWriter& w, const GrandComm* gc) {
+    w.put<uint64_t>(gc ? (uint64_t)(uintptr_t)gc->mailbox : 0);
+    w.put<uint64_t>(gc ? gc->wait_ns : 0);
+    for (int i = 0; i < 4; ++i) w.put<uint64_t>(gc ? (uint64_t)(uintptr_t)gc->prev_out[i] : 0);
+    for (int i = 0; i < 4; ++i) w.put<uint32_t>(gc ? gc->prev_meta[i] : 0);
+    w.put<uint32_t>(gc ? gc->prev_seq : 0);
+    w.put<uint32_t>(gc ? gc->prev_n : 0);
+}
+
 void magic_for(uint32_t d, uint32_t& m, uint32_t& s) {
     if (d <= 1) {
         m = 0;
@@ -602,6 +612,11 @@ std::string row_source(const Program& prog_in, const RowConfig& c) {
     replace_all(tmpl, "ROW_GRAND_BLOCK", gblock.str());
     replace_all(tmpl, "ROW_GRAND_PUT", gput.str());
     replace_all(tmpl, "ROW_GRAND_FINISH", gfinish.str());
+    bool posts = false;
+    for (const Grand& gr : prog.grands) posts = posts || gr.all_reduce;
+    // a kernel that posts an exchange settles the one before it (every thread of the finishing CTA)
+    replace_all(tmpl, "ROW_GRAND_SETTLE", posts ? "PEER_SETTLE(p);" : "");
+    replace_all(tmpl, "ROW_GRAND_PEEK", posts ? "PEER_PEEK(p)" : "");
     replace_all(tmpl, "ROW_INVARIANT", inv.str());
     replace_all(tmpl, "ROW_NEXT_DECL", decl.str());
     replace_all(tmpl, "ROW_PREFETCH", pre.str());
@@ -1047,8 +1062,10 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
         const JitKernel& k = dev.kernel(key.str(), "wgf_rows", [&] { return row_source(prog, cfg); });
         // persistent CTAs: as many as fit on the machine at once, each walking several rows
         int64_t blocks = (rows + cfg.RPC - 1) / cfg.RPC;
-        if (tune("ROW_PERSIST", 1))
-            blocks = std::min<int64_t>(blocks, (int64_t)dev.sm_count * dev.max_blocks_per_sm(k, cfg.GROUP * cfg.RPC));
+        if (tune("ROW_PERSIST", 1)) {
+            const int64_t slots = (int64_t)dev.sm_count * dev.max_blocks_per_sm(k, cfg.GROUP * cfg.RPC);
+            blocks = std::min<int64_t>(blocks, slots);
+        }
         ParamWriter w;
         put_common(w);
         w.put<uint32_t>((uint32_t)H);
@@ -1075,6 +1092,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             w.put<uint32_t>(gc ? gc->rank : 0);
             w.put<uint32_t>(gc ? gc->seq : 0);
             w.put<uint32_t>(0);
+            put_settle(w, gc);
         }
         put_tail(w);
         dev.launch(k, dim3((unsigned)blocks), dim3(cfg.GROUP * cfg.RPC), 0, w.bytes.data(), "rows");
@@ -1126,6 +1144,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
         w.put<uint32_t>(gc->rank);
         w.put<uint32_t>(gc->seq);
         w.put<uint32_t>(0);
+        put_settle(w, gc);
     }
     put_tail(w);
     dev.launch(k, dim3((unsigned)(rows * split)), dim3(256), 0, w.bytes.data(), "stream_reduce");

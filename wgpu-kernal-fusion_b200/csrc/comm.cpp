@@ -50,16 +50,18 @@ void nccl_check(int r, const char* what) {
 }  // namespace
 
 Comm::~Comm() {
-    if (dev) cudaSetDevice(dev->ordinal);
+    if (dev && !dev->dry) cudaSetDevice(dev->ordinal);
+    if (dev && open_seq) {
+        // the results of the last exchange are still this rank's own values: settle them while the
+        // mailbox exists (the peers' words are in this GPU's memory; no peer is needed for that)
+        try {
+            comm_settle(*this, *dev);
+        } catch (...) {
+        }
+        if (!dev->dry) cudaStreamSynchronize(dev->stream);
+    }
     for (int r = 0; r < (int)peer_mailbox.size(); ++r)
         if (r != rank && peer_mailbox[r]) cudaIpcCloseMemHandle(peer_mailbox[r]);
-    // Result buffers of earlier exchanges may still name one of these events as what they wait for, so the
-    // events are not destroyed: they go to the device's pool, where they stay valid (a stale waiter then
-    // waits for whatever the event's next user records, or for nothing).
-    for (cudaEvent_t e : finished)
-        if (e && dev) dev->recycle(e);
-    for (cudaEvent_t e : posted)
-        if (e && dev) dev->recycle(e);
     if (peer_table) cudaFree(peer_table);
     if (mailbox) cudaFree(mailbox);
     if (handle) Nccl::get().CommDestroy(handle);
@@ -79,8 +81,8 @@ struct DeviceScratch {
 // Between the all-gather and the agreeing all-reduce a local CUDA failure only clears `ok`: a
 // rank that threw there would leave the others waiting inside the collective.
 void setup_mailboxes(Comm& c) {
-    // one warp of the combine kernel reads the ranks' words: 32 lanes x 2 rounds at most
-    if (c.world < 2 || c.world > 64 || getenv("WGF_NO_PEER_ALLREDUCE")) return;
+    // one warp of the settling code holds the ranks' words, one per lane
+    if (c.world < 2 || c.world > 32 || getenv("WGF_NO_PEER_ALLREDUCE")) return;
     Device& dev = *c.dev;
     if (const char* ms = getenv("WGF_PEER_WAIT_MS")) {
         const long long v = atoll(ms);
@@ -119,16 +121,6 @@ void setup_mailboxes(Comm& c) {
             cudaMemcpy(c.peer_table, table.data(), sizeof(uint64_t) * c.world, cudaMemcpyHostToDevice) != cudaSuccess)
             ok = 0;
     }
-    if (ok) {
-        c.finished.assign(kMailboxSlots, nullptr);
-        c.posted.assign(kMailboxSlots, nullptr);
-        for (auto* ring : {&c.finished, &c.posted})
-            for (auto& e : *ring)
-                if (cudaEventCreate(&e) != cudaSuccess) {   // timing-capable: they end their life in the device pool
-                    e = nullptr;
-                    ok = 0;
-                }
-    }
     if (cudaMemcpy(flag.p, &ok, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
     cudaGetLastError();   // a failed mapping is not an error of the library: NCCL takes over
     // every rank must take the same path: minimum of the outcomes (a rank whose copy above failed
@@ -154,7 +146,12 @@ std::shared_ptr<Comm> comm_create(const DeviceRef& dev, int world, int rank, con
     c->dev = dev;
     c->world = world;
     c->rank = rank;
-    WGF_CHECK(!dev->dry, WGF_ERR_NCCL, "compile-only device cannot join a communicator");
+    if (dev->dry) {
+        // Compile-only device: no NCCL, no memory.  The communicator takes the peer-memory path, so that
+        // the kernels of that path are compiled and its host-side bookkeeping runs without a GPU.
+        c->peer_ok = getenv("WGF_NO_PEER_ALLREDUCE") == nullptr;
+        return c;
+    }
     dev->make_current();
     NcclId nid;
     std::memcpy(&nid, id, sizeof nid);
@@ -168,6 +165,10 @@ void comm_all_reduce(Comm& c, Device& dev, Buffer& out, void* data, int64_t coun
     int ndt = dt == DType::F32 ? 7 : dt == DType::F16 ? 6 : 9;
     int nop = op == WGF_OP_SUM ? 0 : op == WGF_OP_PRODUCT ? 1 : op == WGF_OP_MAX ? 2 : 3;
     void* recv = data;
+    if (dev.dry) {
+        dev.launches++;
+        return;
+    }
     dev.make_current();
     dev.wait_for(out);
     cudaStream_t cs = dev.collective_stream();
@@ -187,37 +188,67 @@ void comm_all_reduce(Comm& c, Device& dev, Buffer& out, void* data, int64_t coun
     WGF_CUDA(cudaEventRecord(out.pending, cs));
 }
 
-uint32_t comm_peer_begin(Comm& c, Device& dev) {
-    const uint32_t seq = ++c.seq;
-    if (seq > (uint32_t)kMailboxLag) {
-        dev.make_current();
-        WGF_CUDA(cudaStreamWaitEvent(dev.stream, c.finished[(seq - kMailboxLag) % kMailboxSlots], 0));
+uint32_t peer_value_meta(const PeerValue& v) {
+    const uint32_t op = v.op == WGF_OP_SUM ? 0u : v.op == WGF_OP_PRODUCT ? 1u : v.op == WGF_OP_MAX ? 2u : 3u;
+    return op | ((uint32_t)v.out.dtype << 8) | (v.index << 16);
+}
+
+namespace {
+// The open exchange is over (settled, or about to be by a queued kernel): its results are ordinary buffers again.
+void close_open(Comm& c, Device& dev) {
+    for (const PeerValue& v : c.open_vals)
+        if (v.out.buf->unsettled == &c) v.out.buf->unsettled = nullptr;
+    c.open_vals.clear();
+    c.open_seq = 0;
+    if (dev.unsettled_comm == &c) dev.unsettled_comm = nullptr;
+}
+}  // namespace
+
+GrandComm comm_peer_begin(Comm& c, Device& dev) {
+    // one communicator per device has an open exchange at a time
+    if (dev.unsettled_comm && dev.unsettled_comm != &c) comm_settle(*dev.unsettled_comm, dev);
+    GrandComm g{};
+    g.peer_table = c.peer_table;
+    g.world = (uint32_t)c.world;
+    g.rank = (uint32_t)c.rank;
+    g.seq = ++c.seq;
+    g.mailbox = c.mailbox;
+    g.wait_ns = c.wait_ns;
+    g.prev_seq = c.open_seq;
+    g.prev_n = c.open_seq ? (uint32_t)c.open_vals.size() : 0u;
+    for (uint32_t i = 0; i < g.prev_n; ++i) {
+        g.prev_meta[i] = peer_value_meta(c.open_vals[i]);
+        g.prev_out[i] = c.open_vals[i].out.base_ptr();
     }
-    return seq;
+    return g;
 }
 
 void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<PeerValue>& vals) {
     WGF_CHECK(!vals.empty() && vals.size() <= (size_t)kMailboxValues, WGF_ERR_INVALID_ARGUMENT, "exchange of 1..4 values");
-    dev.make_current();
-    cudaStream_t cs = dev.collective_stream();
-    const uint32_t slot = seq % kMailboxSlots;
-    WGF_CUDA(cudaEventRecord(c.posted[slot], dev.stream));
-    WGF_CUDA(cudaStreamWaitEvent(cs, c.posted[slot], 0));
+    close_open(c, dev);   // the kernel just queued settles it; later work on the device stream sees the results
+    c.open_seq = seq;
+    c.open_vals = vals;
+    for (const PeerValue& v : vals) v.out.buf->unsettled = &c;
+    dev.unsettled_comm = &c;
+}
+
+void comm_settle(Comm& c, Device& dev) {
+    if (!c.open_seq) return;
+    const uint32_t seq = c.open_seq;
+    std::vector<PeerValue> vals;
+    vals.swap(c.open_vals);
+    for (const PeerValue& v : vals)
+        if (v.out.buf->unsettled == &c) v.out.buf->unsettled = nullptr;
+    c.open_seq = 0;
+    if (dev.unsettled_comm == &c) dev.unsettled_comm = nullptr;
     dev.launches++;
-    launch_peer_combine(cs, c.mailbox, dev.error_word(), c.wait_ns, (uint32_t)c.world, (uint32_t)c.rank, seq, vals);
+    if (dev.dry) return;
+    dev.make_current();
+    launch_peer_combine(dev.stream, c.mailbox, dev.error_word(), c.wait_ns, (uint32_t)c.world, (uint32_t)c.rank, seq, vals);
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) {
         cudaGetLastError();
         fail(WGF_ERR_CUDA, std::string("peer_combine launch failed: ") + cudaGetErrorString(e));
-    }
-    WGF_CUDA(cudaEventRecord(c.finished[slot], cs));
-    // the results wait for that same event (it is recorded again 16 exchanges later: a reader that comes
-    // after that waits a little longer than it has to, never too little)
-    for (const PeerValue& v : vals) {
-        Buffer& b = *v.out.buf;
-        if (b.pending && !b.pending_shared) dev.recycle(b.pending);   // written by the posting kernel on the device stream only
-        b.pending = c.finished[slot];
-        b.pending_shared = true;
     }
 }
 

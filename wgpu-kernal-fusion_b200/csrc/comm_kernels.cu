@@ -1,8 +1,8 @@
-// Second half of the all-reduce of a few scalars over peer memory (see Comm): one CTA on the
-// device's collective stream waits for the words that every rank posted into this GPU's
-// mailbox, combines them in rank order (so every rank ends with the same bits) and writes the
-// results.  The kernel that produced this GPU's values posted them and went on; the kernels
-// queued behind it on the device stream run beside this one.
+// Second half of the all-reduce of a few scalars over peer memory (see Comm) as a kernel of its
+// own: one CTA waits for the words that every rank posted into this GPU's mailbox, combines them in
+// rank order (so every rank ends with the same bits) and writes the results.  Used when a result is
+// read before the next posting kernel, which would otherwise do the same in its finishing CTA
+// (peer_settle in jit_templates.hpp), has been queued.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 

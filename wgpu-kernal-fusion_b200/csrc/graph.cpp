@@ -1075,15 +1075,19 @@ TensorData run_region(Node* root, bool allow_fold = true) {
         GrandComm gc{};
         // the exchange carries a sequence number that the host advances per launch
         if (kernel_comm) dev.refuse_while_recording("an all-reduce");
-        if (kernel_comm)
-            gc = GrandComm{kernel_comm->peer_table, (uint32_t)kernel_comm->world, (uint32_t)kernel_comm->rank,
-                           comm_peer_begin(*kernel_comm, dev)};
+        if (kernel_comm) {
+            // an input that is a result of the open exchange is settled first: the kernel then has no
+            // exchange to settle, instead of rewriting a value it also reads
+            for (auto& t : em.slots) dev.wait_for(*t.buf);
+            gc = comm_peer_begin(*kernel_comm, dev);
+        }
         if (rg.row_mode) out = run_rows(dev, em.prog, em.slots, index_shape, rg.out_has_h, inplace, &grand_out, kernel_comm ? &gc : nullptr);
         else out = run_elementwise(dev, em.prog, em.slots, index_shape, inplace);
         if (kernel_comm) {
-            // The kernel has posted this GPU's values to every rank's mailbox.  The other half of the
-            // exchange -- wait for the peers' values, combine in rank order, overwrite the results --
-            // runs on the collective stream beside whatever is queued next on the device stream.
+            // The kernel posts this GPU's values to every rank's mailbox (and settles the exchange
+            // before this one).  The other half of this exchange -- wait for the peers' values, combine
+            // in rank order, overwrite the results -- rides in the next kernel that posts, or runs as
+            // a kernel of its own when a result is read first.
             std::vector<PeerValue> vals;
             if (result_ar) vals.push_back(PeerValue{arq->op, 0u, out});
             for (size_t i = 0; i < companions.size(); ++i)

@@ -208,15 +208,14 @@ template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t)
     return v;
 }
 
-// First half of an all-reduce of one scalar across the GPUs of a communicator, done from inside
-// the kernel that produces the value (one thread): the value is POSTED to every rank's mailbox,
-// this GPU's own included, by one 64-bit store each (over NVLink for the peers), and the kernel
-// goes on.  Mailboxes hold words {sequence << 32 | value bits} at
+// All-reduce of a few scalars across the GPUs of a communicator without a collective launch.
+// Mailboxes hold words {sequence << 32 | value bits} at
 // [sequence % PEER_SLOTS][source rank][value index]; a single 64-bit store is atomic, so a word
-// that carries the expected sequence number carries the value that belongs to it.  The second
-// half -- waiting for the peers' words and combining them in rank order -- is a one-CTA kernel on
-// the device's collective stream (peer_combine_kernel), off the path of the kernels queued behind
-// this one.  Nothing here waits.
+// that carries the expected sequence number carries the value that belongs to it.
+//
+// First half, done by one thread of the kernel that produces the value: the value is POSTED to
+// every rank's mailbox, this GPU's own included, by one 64-bit store each (over NVLink for the
+// peers).  Nothing here waits.
 #define PEER_SLOTS 16u
 DEV void peer_post(float mine, int index, u64 peers, u32 world, u32 rank, u32 seq) {
     const u64* table = (const u64*)peers;
@@ -227,6 +226,69 @@ DEV void peer_post(float mine, int index, u64 peers, u32 world, u32 rank, u32 se
         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(word) : "memory");
     }
 }
+
+// Second half: wait (bounded by wait_ns) until this GPU's own mailbox holds every rank's word of
+// exchange `seq`, combine the words in rank order -- every rank ends with the same bits -- and
+// write the n results.  It is run for the exchange BEFORE the one a kernel posts, by every thread
+// of that kernel's finishing CTA: the ranks run the same program, so the peers' words of the
+// earlier exchange are nearly always there already, and no launch, event or second stream is
+// spent on the exchange.  Warp w serves value w (w + warps, ... if the CTA has fewer warps than
+// there are values); lane l holds rank l's word (at most 32 ranks).  peer_peek issues the loads
+// before the CTA finishes its own reduction, so their latency hides behind that work;
+// peer_settle takes the words, polls for the ones that had not arrived, and combines by shuffles.
+// A wait that runs out sets the error word (51) and leaves this GPU's own value as the result:
+// the kernel always returns and the host sees a timeout status at its next synchronisation.
+// meta[v] = op (0 sum, 1 product, 2 max, 3 min) | dtype << 8 | value index << 16.
+DEV const u64* peer_word(u64 mailbox, u32 world, u32 seq, u32 m, u32 r) {
+    return (const u64*)mailbox + ((u64)((seq % PEER_SLOTS) * world + r)) * 4 + (u64)(m >> 16);
+}
+DEV u64 peer_peek(u64 mailbox, u32 world, u32 seq, u32 n, const u32* meta) {
+    const u32 v = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    u64 w = 0;
+    if (v < n && lane < world)
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(peer_word(mailbox, world, seq, meta[v], lane)) : "memory");
+    return w;
+}
+DEV void peer_settle(u64 peeked, u64 mailbox, u64 err, u64 wait_ns, u32 world, u32 rank, u32 seq, u32 n, const u32* meta, const u64* out) {
+    const u32 first = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    for (u32 v = first; v < n; v += warps) {
+        const u32 m = meta[v], op = m & 255u, dt = (m >> 8) & 255u;
+        u64 w = v == first ? peeked : 0;
+        bool got = lane >= world || (u32)(w >> 32) == seq;
+        if (!got) {
+            const u64* slot = peer_word(mailbox, world, seq, m, lane);
+            u64 start = 0;
+            for (u32 spin = 0; spin < (1u << 30) && !got; ++spin) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
+                got = (u32)(w >> 32) == seq;
+                if (!got && (spin & 63u) == 63u) {
+                    u64 now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (start == 0) start = now;
+                    else if (now - start > wait_ns) break;
+                }
+            }
+        }
+        const bool all_here = __all_sync(0xffffffffu, got);
+        const float x = __uint_as_float((u32)w);
+        float acc = __shfl_sync(0xffffffffu, x, all_here ? 0 : (int)rank);
+        if (all_here)
+            for (u32 r = 1; r < world; ++r) {
+                const float y = __shfl_sync(0xffffffffu, x, (int)r);
+                acc = op == 0 ? acc + y : op == 1 ? acc * y : op == 2 ? fmaxf(acc, y) : fminf(acc, y);
+            }
+        if (lane == 0) {
+            if (!all_here) atomicExch((u32*)err, 51u);
+            if (dt == 0) *(float*)out[v] = acc;
+            else if (dt == 1) *(u16*)out[v] = f2h(acc);
+            else *(u16*)out[v] = f2b(acc);
+        }
+    }
+}
+// The earlier exchange a posting kernel settles (gprev_n == 0: none).
+#define PEER_SETTLE_PARAMS u64 gmailbox; u64 gwait_ns; u64 gprev_out[4]; u32 gprev_meta[4]; u32 gprev_seq, gprev_n;
+#define PEER_PEEK(p) const u64 peeked_ = peer_peek(p.gmailbox, p.gworld, p.gprev_seq, p.gprev_n, p.gprev_meta);
+#define PEER_SETTLE(p) peer_settle(peeked_, p.gmailbox, p.gerr, p.gwait_ns, p.gworld, p.grank, p.gprev_seq, p.gprev_n, p.gprev_meta, p.gprev_out)
 )CUDA";
 
 // ---------------------------------------------------------------------------------------
@@ -407,6 +469,7 @@ struct Params {
     u64 gpeers;         // all-reduce inside this kernel: device array of every rank's mailbox address
     u64 gerr;           // u32 device error word
     u32 gworld, grank, gseq, gpad_;
+    PEER_SETTLE_PARAMS
 #endif
     u32 oshape[RO];
     u32 mm[RO];
@@ -481,9 +544,11 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __gri
     }
     __syncthreads();
     if (!g_last) return;
+    ROW_GRAND_PEEK
     __threadfence();
     ROW_GRAND_FINISH
     if (threadIdx.x == 0) *(u32*)p.gcounter = 0;
+    ROW_GRAND_SETTLE
 #endif
 }
 )CUDA";
@@ -513,6 +578,7 @@ struct Params {
     u64 gpeers;         // all-reduce of the result inside this kernel: the ranks' mailbox addresses
     u64 gerr;           // u32 device error word
     u32 gworld, grank, gseq, gpad_;
+    PEER_SETTLE_PARAMS
 #endif
     u32 oshape[RO];
     u32 mm[RO];
@@ -602,7 +668,13 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(co
         STREAM_BLOCK_REDUCE
         if (t == 0) ((u32*)p.counters)[row] = 0;
     }
+#if STREAM_AR
+    PEER_PEEK(p)
+#endif
     STREAM_POST
+#if STREAM_AR
+    PEER_SETTLE(p);
+#endif
 }
 )CUDA";
 

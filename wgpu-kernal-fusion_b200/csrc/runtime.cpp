@@ -220,6 +220,7 @@ cudaStream_t Device::collective_stream() {
 }
 
 void Device::wait_for(Buffer& b) {
+    if (b.unsettled) comm_settle(*b.unsettled, *this);   // the ranks' values are combined before anyone reads the result
     if (!b.pending) return;
     cudaSetDevice(ordinal);
     // an event recorded outside a capture cannot become a dependency inside it: wait on the host
@@ -302,6 +303,7 @@ void Device::make_current() const {
 
 void Device::sync() {
     refuse_while_recording("wgf_device_sync");
+    if (unsettled_comm) comm_settle(*unsettled_comm, *this);   // after a synchronisation every result is final
     if (dry) return;
     make_current();
     WGF_CUDA(cudaStreamSynchronize(stream));

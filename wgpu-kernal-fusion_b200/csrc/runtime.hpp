@@ -25,6 +25,9 @@ namespace wgf {
     } while (0)
 
 struct Device;
+struct Comm;
+// Settles the communicator's open exchange over peer memory, if it has one (comm.cpp).
+void comm_settle(Comm& c, Device& dev);
 
 // Memory of a recorded schedule (Device::begin_recording).  Blocks handed out while recording
 // come back here instead of to the device pool for as long as the schedule lives, so that a
@@ -48,6 +51,10 @@ struct Buffer {
     // `pending` belongs to someone else (a communicator's ring of completion events): waited for like
     // any other, but not returned to the device's event pool afterwards
     bool pending_shared = false;
+    // Set while the buffer holds this rank's own value of an all-reduce whose ranks have not been
+    // combined yet (see Comm): Device::wait_for settles the exchange before the buffer is read.
+    // The communicator keeps the buffer alive for as long as this is set.
+    Comm* unsettled = nullptr;
     std::shared_ptr<Arena> arena;   // set for buffers allocated while a schedule was being recorded
     ~Buffer();
 };
@@ -108,6 +115,8 @@ struct Device : std::enable_shared_from_this<Device> {
     // code 51): the ranks are out of step from then on, and further all-reduces on this device are
     // refused with WGF_ERR_TIMEOUT until its communicators have been released and made anew.
     std::atomic<bool> exchange_broken{false};
+    // The communicator whose last exchange over peer memory is posted but not settled (see Comm), if any.
+    Comm* unsettled_comm = nullptr;
     // Second stream for collectives, so that an all-reduce overlaps the kernels queued behind it.
     cudaStream_t collective_stream();
     // Orders the device stream behind any collective still using `b` (no-op otherwise).
