@@ -388,10 +388,11 @@ def test_null_chain_with_a_length_is_an_error_not_a_crash(wgf, drydev):
 
 def test_all_reduce_over_peer_memory_costs_one_launch_per_step(wgf, drydev):
     """Host side of the scalar all-reduce over peer memory, on the compile-only device (its
-    communicator needs no NCCL and compiles the same kernels).  The kernel of a step posts this
-    rank's values and settles the exchange of the step before: one launch per step, however many
-    values ride along.  A result that is read before the next posting kernel is settled by one
-    small kernel of its own, once; a synchronisation settles what is still open."""
+    communicator needs no NCCL and compiles the same kernels).  The kernel of a step stores this
+    rank's values, posts the values of the step before and settles the step before that: one launch
+    per step, however many values ride along.  Results that are read before those later kernels
+    have been queued are finished by one small kernel, once for all open exchanges; a
+    synchronisation does the same."""
     d = drydev
     comm = wgf.Comm(d, 2, 0, bytes(128))
     x = d.tensor(np.zeros((64, 256), np.float32))
@@ -404,29 +405,25 @@ def test_all_reduce_over_peer_memory_costs_one_launch_per_step(wgf, drydev):
         wgf.Tensor.materialize_all([y, s, m])
         return d.launch_count - before, s, m
 
-    n, s, m = step()
-    assert n == 1                                   # posts exchange 1; nothing to settle yet
-    n, s2, m2 = step()
-    assert n == 1                                   # posts 2, settles 1 in the same kernel
-    before = d.launch_count
-    (s * 2.0).materialize()                         # exchange 1 was settled by that kernel: plain read
-    assert d.launch_count - before == 1
-    before = d.launch_count
-    (s2 * 2.0).materialize()                        # exchange 2 is open: settle kernel + the multiply
-    assert d.launch_count - before == 2
-    before = d.launch_count
-    (m2 * 2.0).materialize()                        # same exchange: already settled
-    assert d.launch_count - before == 1
-    # the streaming reduction posts and settles too
-    before = d.launch_count
+    def launches_of(fn):
+        before = d.launch_count
+        fn()
+        return d.launch_count - before
+
+    n1, s1, m1 = step()
+    n2, s2, m2 = step()
+    n3, s3, m3 = step()
+    n4, s4, m4 = step()
+    assert (n1, n2, n3, n4) == (1, 1, 1, 1)
+    assert launches_of(lambda: (s1 * 2.0).materialize()) == 1   # settled by the kernel of step 3: a plain read
+    assert launches_of(lambda: (m2 * 2.0).materialize()) == 1   # settled by the kernel of step 4
+    assert launches_of(lambda: (s3 * 2.0).materialize()) == 2   # posted, not settled: one kernel finishes 3 and 4
+    assert launches_of(lambda: (m4 * 2.0).materialize()) == 1   # ... so this one is a plain read
+    assert launches_of(lambda: (m3 * 2.0).materialize()) == 1
+    # the streaming reduction is a kernel of the same path
     alone = (x * 2.0).exp().sum(0).sum(0).all_reduce(comm)
-    alone.materialize()
-    assert d.launch_count - before == 1
-    before = d.launch_count
-    d.sync()                                        # leaves nothing open ...
-    assert d.launch_count - before == 1
-    before = d.launch_count
-    d.sync()                                        # ... once
-    (alone * 2.0).materialize()
-    assert d.launch_count - before == 1
+    assert launches_of(alone.materialize) == 1
+    assert launches_of(d.sync) == 1                             # a synchronisation leaves nothing open ...
+    assert launches_of(d.sync) == 0                             # ... once
+    assert launches_of(lambda: (alone * 2.0).materialize()) == 1
     del comm

@@ -107,14 +107,18 @@ struct ParamWriter {
     }
 };
 
-// PEER_SETTLE_PARAMS of the templates: the earlier exchange that a posting kernel settles.
+// PEER_SETTLE_PARAMS of the templates: the earlier exchanges that a kernel of the all-reduce path posts and settles.
 void put_settle(ParamWriter& w, const GrandComm* gc) {
     w.put<uint64_t>(gc ? (uint64_t)(uintptr_t)gc->mailbox : 0);
     w.put<uint64_t>(gc ? gc->wait_ns : 0);
     for (int i = 0; i < 4; ++i) w.put<uint64_t>(gc ? (uint64_t)(uintptr_t)gc->prev_out[i] : 0);
+    for (int i = 0; i < 4; ++i) w.put<uint64_t>(gc ? (uint64_t)(uintptr_t)gc->post_src[i] : 0);
     for (int i = 0; i < 4; ++i) w.put<uint32_t>(gc ? gc->prev_meta[i] : 0);
+    for (int i = 0; i < 4; ++i) w.put<uint32_t>(gc ? gc->post_meta[i] : 0);
     w.put<uint32_t>(gc ? gc->prev_seq : 0);
     w.put<uint32_t>(gc ? gc->prev_n : 0);
+    w.put<uint32_t>(gc ? gc->post_seq : 0);
+    w.put<uint32_t>(gc ? gc->post_n : 0);
 }
 
 void magic_for(uint32_t d, uint32_t& m, uint32_t& s) {
@@ -599,9 +603,6 @@ std::string row_source(const Program& prog_in, const RowConfig& c) {
                 << ">(a_, __ldcg(gpart + (u64)b_ * NGRAND + " << id << "));\n"
                 << "  __syncthreads();\n  a_ = group_reduce<" << op << ", THREADS>(a_, g_smem[" << id
                 << "], (int)threadIdx.x);\n  if (threadIdx.x == 0) {\n";
-        if (gr.all_reduce)   // the value of this GPU, rounded to the element type, goes to every rank's mailbox;
-                             // a kernel on the collective stream combines the ranks and overwrites gout
-            gfinish << "    peer_post(" << rounded(gr.dtype, "a_") << ", " << id << ", p.gpeers, p.gworld, p.grank, p.gseq);\n";
         gfinish << "    store1<" << (int)gr.dtype << ">((void*)p.gout[" << id << "], 0, a_); } }\n";
     }
     // A group_reduce reuses its shared-memory slot in the next iteration: all reads of this
@@ -614,9 +615,11 @@ std::string row_source(const Program& prog_in, const RowConfig& c) {
     replace_all(tmpl, "ROW_GRAND_FINISH", gfinish.str());
     bool posts = false;
     for (const Grand& gr : prog.grands) posts = posts || gr.all_reduce;
-    // a kernel that posts an exchange settles the one before it (every thread of the finishing CTA)
-    replace_all(tmpl, "ROW_GRAND_SETTLE", posts ? "PEER_SETTLE(p);" : "");
-    replace_all(tmpl, "ROW_GRAND_PEEK", posts ? "PEER_PEEK(p)" : "");
+    // A kernel whose values are all-reduced stores this GPU's values like any other; it posts the
+    // values of the exchange before its own first thing, and its last CTA settles the exchange
+    // before that one around its share of the rows (see Comm).
+    replace_all(tmpl, "ROW_GRAND_POST", posts ? "PEER_POST(p) PEER_PEEK(p)" : "");
+    replace_all(tmpl, "ROW_GRAND_SETTLE", posts ? "PEER_SETTLE(p)" : "");
     replace_all(tmpl, "ROW_INVARIANT", inv.str());
     replace_all(tmpl, "ROW_NEXT_DECL", decl.str());
     replace_all(tmpl, "ROW_PREFETCH", pre.str());
@@ -719,8 +722,6 @@ std::string stream_source(const Program& prog_in, const StreamConfig& c) {
     s << "#define STREAM_LOAD(COL, NV, X) " << load.str() << "\n";
     s << "#define STREAM_AR " << (prog.result_all_reduce ? 1 : 0) << "\n";
     s << "#define STREAM_POST " << post.str() << " if (t == 0) { float r_ = " << vn(prog.result) << "; ";
-    if (prog.result_all_reduce)   // posted to every rank's mailbox; the combine kernel overwrites the result
-        s << "peer_post(" << rounded(prog.out_dtype(), "r_") << ", 0, p.gpeers, p.gworld, p.grank, p.gseq); ";
     s << "store1<" << (int)prog.out_dtype() << ">((void*)p.ptr[NIN], roff[NIN], r_); }\n";
     s << JIT_STREAM_KERNEL;
     return s.str();

@@ -51,9 +51,9 @@ void nccl_check(int r, const char* what) {
 
 Comm::~Comm() {
     if (dev && !dev->dry) cudaSetDevice(dev->ordinal);
-    if (dev && open_seq) {
-        // the results of the last exchange are still this rank's own values: settle them while the
-        // mailbox exists (the peers' words are in this GPU's memory; no peer is needed for that)
+    if (dev && (posted.seq || produced.seq)) {
+        // results of the last exchanges are still this rank's own values: finish them while the
+        // mailboxes exist
         try {
             comm_settle(*this, *dev);
         } catch (...) {
@@ -82,7 +82,9 @@ struct DeviceScratch {
 // rank that threw there would leave the others waiting inside the collective.
 void setup_mailboxes(Comm& c) {
     // one warp of the settling code holds the ranks' words, one per lane
-    if (c.world < 2 || c.world > 32 || getenv("WGF_NO_PEER_ALLREDUCE")) return;
+    // (a communicator of one rank takes this path only when asked to: a way to time the exchange's
+    // code without a second GPU)
+    if ((c.world < 2 && !getenv("WGF_PEER_SINGLE_RANK")) || c.world > 32 || getenv("WGF_NO_PEER_ALLREDUCE")) return;
     Device& dev = *c.dev;
     if (const char* ms = getenv("WGF_PEER_WAIT_MS")) {
         const long long v = atoll(ms);
@@ -194,18 +196,16 @@ uint32_t peer_value_meta(const PeerValue& v) {
 }
 
 namespace {
-// The open exchange is over (settled, or about to be by a queued kernel): its results are ordinary buffers again.
-void close_open(Comm& c, Device& dev) {
-    for (const PeerValue& v : c.open_vals)
+void unmark(Comm& c, Comm::Exchange& e) {
+    for (const PeerValue& v : e.vals)
         if (v.out.buf->unsettled == &c) v.out.buf->unsettled = nullptr;
-    c.open_vals.clear();
-    c.open_seq = 0;
-    if (dev.unsettled_comm == &c) dev.unsettled_comm = nullptr;
+    e.vals.clear();
+    e.seq = 0;
 }
 }  // namespace
 
 GrandComm comm_peer_begin(Comm& c, Device& dev) {
-    // one communicator per device has an open exchange at a time
+    // one communicator per device has open exchanges at a time
     if (dev.unsettled_comm && dev.unsettled_comm != &c) comm_settle(*dev.unsettled_comm, dev);
     GrandComm g{};
     g.peer_table = c.peer_table;
@@ -214,41 +214,49 @@ GrandComm comm_peer_begin(Comm& c, Device& dev) {
     g.seq = ++c.seq;
     g.mailbox = c.mailbox;
     g.wait_ns = c.wait_ns;
-    g.prev_seq = c.open_seq;
-    g.prev_n = c.open_seq ? (uint32_t)c.open_vals.size() : 0u;
+    g.prev_seq = c.posted.seq;
+    g.prev_n = c.posted.seq ? (uint32_t)c.posted.vals.size() : 0u;
     for (uint32_t i = 0; i < g.prev_n; ++i) {
-        g.prev_meta[i] = peer_value_meta(c.open_vals[i]);
-        g.prev_out[i] = c.open_vals[i].out.base_ptr();
+        g.prev_meta[i] = peer_value_meta(c.posted.vals[i]);
+        g.prev_out[i] = c.posted.vals[i].out.base_ptr();
+    }
+    g.post_seq = c.produced.seq;
+    g.post_n = c.produced.seq ? (uint32_t)c.produced.vals.size() : 0u;
+    for (uint32_t i = 0; i < g.post_n; ++i) {
+        g.post_meta[i] = peer_value_meta(c.produced.vals[i]);
+        g.post_src[i] = c.produced.vals[i].out.base_ptr();
     }
     return g;
 }
 
 void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<PeerValue>& vals) {
     WGF_CHECK(!vals.empty() && vals.size() <= (size_t)kMailboxValues, WGF_ERR_INVALID_ARGUMENT, "exchange of 1..4 values");
-    close_open(c, dev);   // the kernel just queued settles it; later work on the device stream sees the results
-    c.open_seq = seq;
-    c.open_vals = vals;
+    unmark(c, c.posted);   // the kernel just queued settles it; later work on the device stream sees the results
+    c.posted = std::move(c.produced);
+    c.produced.seq = seq;
+    c.produced.vals = vals;
     for (const PeerValue& v : vals) v.out.buf->unsettled = &c;
     dev.unsettled_comm = &c;
 }
 
 void comm_settle(Comm& c, Device& dev) {
-    if (!c.open_seq) return;
-    const uint32_t seq = c.open_seq;
-    std::vector<PeerValue> vals;
-    vals.swap(c.open_vals);
-    for (const PeerValue& v : vals)
-        if (v.out.buf->unsettled == &c) v.out.buf->unsettled = nullptr;
-    c.open_seq = 0;
+    if (!c.posted.seq && !c.produced.seq) return;
+    Comm::Exchange posted, produced;
+    std::swap(posted, c.posted);
+    std::swap(produced, c.produced);
+    for (Comm::Exchange* e : {&posted, &produced})
+        for (const PeerValue& v : e->vals)
+            if (v.out.buf->unsettled == &c) v.out.buf->unsettled = nullptr;
     if (dev.unsettled_comm == &c) dev.unsettled_comm = nullptr;
     dev.launches++;
     if (dev.dry) return;
     dev.make_current();
-    launch_peer_combine(dev.stream, c.mailbox, dev.error_word(), c.wait_ns, (uint32_t)c.world, (uint32_t)c.rank, seq, vals);
+    launch_peer_flush(dev.stream, c, dev.error_word(), produced.seq ? &produced : nullptr, posted.seq ? &posted : nullptr,
+                      produced.seq ? &produced : nullptr);
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) {
         cudaGetLastError();
-        fail(WGF_ERR_CUDA, std::string("peer_combine launch failed: ") + cudaGetErrorString(e));
+        fail(WGF_ERR_CUDA, std::string("peer flush launch failed: ") + cudaGetErrorString(e));
     }
 }
 

@@ -20,49 +20,57 @@ struct Comm {
     // All-reduces of a few scalars WITHOUT a collective launch, over peer memory.  Every rank owns
     // a mailbox of 64-bit words {sequence number << 32 | value bits}, laid out
     // [kMailboxSlots][world source ranks][kMailboxValues], and maps the peers' mailboxes through
-    // CUDA IPC.  The exchange has two halves.  (1) The finishing CTA of the kernel that produces
-    // the values POSTS them: one 64-bit store per rank (NVLink stores for the peers, a local one
-    // for itself) into slot `sequence % kMailboxSlots`; it waits for nothing.  The result buffers
-    // hold this rank's own values from then on and are marked Buffer::unsettled; the exchange is
-    // `open`.  (2) SETTLING: wait (bounded: wait_ns) until the own mailbox holds every rank's word
-    // with this sequence number, combine them in rank order -- every rank gets the same bits --
-    // and overwrite the results.  The next kernel that posts on this communicator does it for the
-    // open exchange, in its finishing CTA after its own post: ranks that run the same program have
-    // posted the earlier exchange long before, so a step costs one launch and its stream never
-    // stops for a peer.  If a result is read first (Device::wait_for), the device synchronised or a
-    // schedule recorded, a one-CTA kernel on the device stream settles the open exchange instead.
+    // CUDA IPC.  An exchange goes through three stages, each done by a kernel of this path on the
+    // device stream, so that a step of a loop costs one launch and its stream never stops for a peer:
+    //   produced  kernel k (the one that computes the values) stores this rank's values in the
+    //             result buffers, which are marked Buffer::unsettled from then on;
+    //   posted    kernel k+1 reads them back first thing and stores one word per value into
+    //             slot `k % kMailboxSlots` of every rank's mailbox (NVLink stores for the peers, a
+    //             local one for itself); it waits for nothing;
+    //   settled   one CTA of kernel k+2 waits (bounded: wait_ns) until the own mailbox holds every
+    //             rank's word of exchange k, combines them in rank order -- every rank gets the
+    //             same bits -- and overwrites the results.  Ranks that run the same program posted
+    //             k a whole kernel earlier, so nothing waits: the CTA asks for the words when it
+    //             starts and takes them when it is done with its own rows.
+    // If a result is read first (Device::wait_for), the device synchronised or a schedule recorded,
+    // a one-CTA kernel on the device stream does what is left for the open exchanges (comm_settle).
     //
     // A slot is reused every kMailboxSlots exchanges, with no further gate.  On every rank the
-    // stream order is post(j) < settle(j) < post(j+2) (exchange j is settled by the kernel that
-    // posts j+1 at the latest), and settle(j) ends only after every peer's post(j) has arrived.
-    // When rank A posts k, its settle(k-2) is over, so every peer had posted k-2, so every peer's
-    // kernel of exchange k-3 had ended, and with it the peer's settle(k-4): the peers have read
-    // every exchange up to k-4, and the word of exchange k-16 that post k replaces is long dead.
+    // stream order is produce(j) < post(j) < settle(j), and settle(j) ends before kernel j+2 does;
+    // settle(j) ends only after every peer's post(j) has arrived.  When rank A posts j, its kernel
+    // j has ended, so its settle(j-2) is over, so every peer had posted j-2, so every peer's kernel
+    // j-2 had ended, and with it the peer's settle(j-4): the peers have read every exchange up to
+    // j-4, and the word of exchange j-16 that post j replaces is long dead.
     void* mailbox = nullptr;              // this rank's mailbox (device memory)
     std::vector<void*> peer_mailbox;      // [world]; the own entry is `mailbox`
     void* peer_table = nullptr;           // device array of the world mailbox addresses
     uint32_t seq = 0;                     // sequence number of the last exchange
     bool peer_ok = false;                 // every rank mapped every peer
     uint64_t wait_ns = 5000000000ull;     // limit of a settling wait (WGF_PEER_WAIT_MS)
-    uint32_t open_seq = 0;                // the posted exchange that is not settled yet (0: none) ...
-    std::vector<PeerValue> open_vals;     // ... and its results
+    struct Exchange {
+        uint32_t seq = 0;                 // 0: none
+        std::vector<PeerValue> vals;      // its results (keeps the buffers alive)
+    };
+    Exchange produced;                    // values stored, not posted
+    Exchange posted;                      // posted, not settled (always the one before `produced`)
     ~Comm();
 };
 constexpr int kMailboxValues = 4;
 constexpr int kMailboxSlots = 16;
 static_assert(kMailboxSlots >= 5, "a slot must have been read before it is posted to again");
 
-// Starts the next exchange: the sequence number and mailboxes for the kernel that posts, and the open
-// exchange for it to settle.  Call before launching that kernel.
+// Starts the next exchange: its sequence number, and the two open exchanges that the kernel which
+// produces it posts and settles.  Call before launching that kernel.
 GrandComm comm_peer_begin(Comm& c, Device& dev);
-// After the posting kernel has been queued: the exchange it settled is closed, `vals` (its own results,
-// holding this rank's values for now) become the open one.
+// After that kernel has been queued: the exchange it settled is closed, the one it posted waits to be
+// settled, and `vals` (the kernel's own results, holding this rank's values for now) wait to be posted.
 void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<PeerValue>& vals);
-// Settles the open exchange, if any, with a kernel of its own on the device stream
+// Finishes the open exchanges, if any, with a kernel of its own on the device stream
 // (declared in runtime.hpp too: Device::wait_for and Device::sync call it).
 void comm_settle(Comm& c, Device& dev);
-void launch_peer_combine(cudaStream_t stream, const void* mailbox, unsigned* err, uint64_t wait_ns, uint32_t world,
-                         uint32_t rank, uint32_t seq, const std::vector<PeerValue>& vals);
+// The kernel of comm_settle: posts `post` (if it has values), then settles `first` and `second`.
+void launch_peer_flush(cudaStream_t stream, const Comm& c, unsigned* err, const Comm::Exchange* post,
+                       const Comm::Exchange* first, const Comm::Exchange* second);
 // op | dtype << 8 | value index << 16, as the settling code reads it
 uint32_t peer_value_meta(const PeerValue& v);
 

@@ -1,8 +1,9 @@
-// Second half of the all-reduce of a few scalars over peer memory (see Comm) as a kernel of its
-// own: one CTA waits for the words that every rank posted into this GPU's mailbox, combines them in
-// rank order (so every rank ends with the same bits) and writes the results.  Used when a result is
-// read before the next posting kernel, which would otherwise do the same in its finishing CTA
-// (peer_settle in jit_templates.hpp), has been queued.
+// The all-reduce of a few scalars over peer memory (see Comm) as a kernel of its own: one CTA
+// does whatever is left of the communicator's open exchanges -- posts this GPU's values of the one
+// that is only produced, then waits for the words that every rank posted into this GPU's mailbox,
+// combines them in rank order (so every rank ends with the same bits) and writes the results.
+// Used when a result is read before the kernels of the following steps, which would otherwise do the
+// same work on their way (peer_post / peer_settle in jit_templates.hpp), have been queued.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -11,42 +12,46 @@
 namespace wgf {
 namespace {
 
-struct CombineParams {
+struct ExchangeParams {
+    unsigned seq, n;                     // n == 0: nothing to do
+    unsigned meta[kMailboxValues];       // op code | dtype << 8 | word of the slot << 16 (peer_value_meta)
+    void* buf[kMailboxValues];           // the result buffers
+};
+struct FlushParams {
     const unsigned long long* mailbox;   // this GPU's mailbox
+    const unsigned long long* peers;     // device array of every rank's mailbox address
     unsigned* err;                       // device error word
     unsigned long long wait_ns;          // limit of the wait for a peer's word
-    unsigned world, rank, seq, nvals;
-    unsigned index[kMailboxValues];      // word of the slot that holds this value
-    unsigned op[kMailboxValues];         // WGF_OP_SUM / MAX / MIN / PRODUCT
-    unsigned dtype[kMailboxValues];      // 0 f32, 1 f16, 2 bf16
-    void* out[kMailboxValues];
+    unsigned world, rank;
+    ExchangeParams post, settle[2];
 };
 
 __device__ __forceinline__ float combine(unsigned op, float a, float b) {
-    switch (op) {
-        case WGF_OP_SUM: return a + b;
-        case WGF_OP_PRODUCT: return a * b;
-        case WGF_OP_MAX: return fmaxf(a, b);
-        default: return fminf(a, b);
-    }
+    return op == 0 ? a + b : op == 1 ? a * b : op == 2 ? fmaxf(a, b) : fminf(a, b);
+}
+__device__ __forceinline__ float read_as(unsigned dt, const void* p) {
+    return dt == 0 ? *(const float*)p : dt == 1 ? __half2float(*(const __half*)p) : __bfloat162float(*(const __nv_bfloat16*)p);
+}
+__device__ __forceinline__ unsigned long long word_at(unsigned seq, unsigned world, unsigned r, unsigned index) {
+    return (unsigned long long)((seq % kMailboxSlots) * world + r) * kMailboxValues + index;
 }
 
-// Warp w serves value w; lane l waits for the words of ranks l, l + 32, ...  A wait that runs
+// Warp w settles value w; lane l waits for the words of ranks l, l + 32, ...  A wait that runs
 // out sets the error word (51) and leaves this GPU's own value as the result: the kernel always
 // returns, and the host sees WGF_ERR_TIMEOUT at its next synchronisation.
-__global__ void __launch_bounds__(32 * kMailboxValues) peer_combine_kernel(const CombineParams p) {
+__device__ void settle(const FlushParams& p, const ExchangeParams& e) {
     const unsigned v = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (v >= p.nvals) return;
-    const unsigned long long* base = p.mailbox + (unsigned long long)((p.seq % kMailboxSlots) * p.world) * kMailboxValues + p.index[v];
+    if (v >= e.n) return;
+    const unsigned op = e.meta[v] & 255u, dt = (e.meta[v] >> 8) & 255u, index = e.meta[v] >> 16;
     bool all_here = true;
     unsigned long long start = 0;
     for (unsigned r = lane; r < p.world; r += 32) {
-        const unsigned long long* slot = base + (unsigned long long)r * kMailboxValues;
+        const unsigned long long* slot = p.mailbox + word_at(e.seq, p.world, r, index);
         unsigned long long w = 0;
         bool got = false;
         for (unsigned spin = 0; spin < (1u << 30) && !got; ++spin) {
             asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
-            got = (unsigned)(w >> 32) == p.seq;
+            got = (unsigned)(w >> 32) == e.seq;
             if (!got && (spin & 63u) == 63u) {
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
@@ -57,48 +62,64 @@ __global__ void __launch_bounds__(32 * kMailboxValues) peer_combine_kernel(const
         all_here = all_here && got;
     }
     all_here = __all_sync(0xffffffffu, all_here);
+    if (lane != 0) return;
+    if (!all_here) {          // the buffer keeps this GPU's own value
+        atomicExch(p.err, 51u);
+        return;
+    }
+    // every word is in this GPU's memory now: read them in rank order
     float acc = 0.f;
-    if (lane == 0) {
-        // every word is in this GPU's memory now (or the wait ran out): read them in rank order
-        const unsigned long long mine = base[(unsigned long long)p.rank * kMailboxValues];
-        if (!all_here) {
-            atomicExch(p.err, 51u);
-            acc = __uint_as_float((unsigned)mine);
-        } else {
-            for (unsigned r = 0; r < p.world; ++r) {
-                unsigned long long w;
-                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(base + (unsigned long long)r * kMailboxValues) : "memory");
-                const float x = __uint_as_float((unsigned)w);
-                acc = r == 0 ? x : combine(p.op[v], acc, x);
-            }
-        }
-        switch (p.dtype[v]) {
-            case 0: *(float*)p.out[v] = acc; break;
-            case 1: *(__half*)p.out[v] = __float2half_rn(acc); break;
-            default: *(__nv_bfloat16*)p.out[v] = __float2bfloat16_rn(acc); break;
-        }
+    for (unsigned r = 0; r < p.world; ++r) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p.mailbox + word_at(e.seq, p.world, r, index)) : "memory");
+        const float x = __uint_as_float((unsigned)w);
+        acc = r == 0 ? x : combine(op, acc, x);
+    }
+    if (dt == 0) *(float*)e.buf[v] = acc;
+    else if (dt == 1) *(__half*)e.buf[v] = __float2half_rn(acc);
+    else *(__nv_bfloat16*)e.buf[v] = __float2bfloat16_rn(acc);
+}
+
+__global__ void __launch_bounds__(32 * kMailboxValues) peer_flush_kernel(const FlushParams p) {
+    if (threadIdx.x < p.post.n) {
+        const unsigned m = p.post.meta[threadIdx.x];
+        const float mine = read_as((m >> 8) & 255u, p.post.buf[threadIdx.x]);
+        const unsigned long long word = ((unsigned long long)p.post.seq << 32) | (unsigned long long)__float_as_uint(mine);
+        const unsigned long long at = word_at(p.post.seq, p.world, p.rank, m >> 16);
+        for (unsigned r = 0; r < p.world; ++r)
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"((unsigned long long*)p.peers[r] + at), "l"(word) : "memory");
+    }
+    __syncthreads();   // the values have been read before a settle below overwrites them
+    settle(p, p.settle[0]);
+    settle(p, p.settle[1]);
+}
+
+void fill(ExchangeParams& e, const Comm::Exchange* x) {
+    e = ExchangeParams{};
+    if (!x) return;
+    e.seq = x->seq;
+    e.n = (unsigned)x->vals.size();
+    for (size_t i = 0; i < x->vals.size(); ++i) {
+        e.meta[i] = peer_value_meta(x->vals[i]);
+        e.buf[i] = x->vals[i].out.base_ptr();
     }
 }
 
 }  // namespace
 
-void launch_peer_combine(cudaStream_t stream, const void* mailbox, unsigned* err, uint64_t wait_ns, uint32_t world,
-                         uint32_t rank, uint32_t seq, const std::vector<PeerValue>& vals) {
-    CombineParams p{};
-    p.mailbox = (const unsigned long long*)mailbox;
+void launch_peer_flush(cudaStream_t stream, const Comm& c, unsigned* err, const Comm::Exchange* post,
+                       const Comm::Exchange* first, const Comm::Exchange* second) {
+    FlushParams p{};
+    p.mailbox = (const unsigned long long*)c.mailbox;
+    p.peers = (const unsigned long long*)c.peer_table;
     p.err = err;
-    p.wait_ns = wait_ns;
-    p.world = world;
-    p.rank = rank;
-    p.seq = seq;
-    p.nvals = (unsigned)vals.size();
-    for (size_t i = 0; i < vals.size(); ++i) {
-        p.index[i] = vals[i].index;
-        p.op[i] = vals[i].op;
-        p.dtype[i] = (unsigned)vals[i].out.dtype;
-        p.out[i] = vals[i].out.base_ptr();
-    }
-    peer_combine_kernel<<<1, 32 * kMailboxValues, 0, stream>>>(p);
+    p.wait_ns = c.wait_ns;
+    p.world = (unsigned)c.world;
+    p.rank = (unsigned)c.rank;
+    fill(p.post, post);
+    fill(p.settle[0], first);
+    fill(p.settle[1], second);
+    peer_flush_kernel<<<1, 32 * kMailboxValues, 0, stream>>>(p);
 }
 
 }  // namespace wgf

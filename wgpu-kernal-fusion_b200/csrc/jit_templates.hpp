@@ -208,34 +208,43 @@ template <int OP, int GROUP> DEV float group_reduce(float v, float* slot, int t)
     return v;
 }
 
-// All-reduce of a few scalars across the GPUs of a communicator without a collective launch.
+// All-reduce of a few scalars across the GPUs of a communicator without a collective launch, as
+// a pipeline over three kernels of the same stream that all belong to this path (see Comm).
 // Mailboxes hold words {sequence << 32 | value bits} at
 // [sequence % PEER_SLOTS][source rank][value index]; a single 64-bit store is atomic, so a word
 // that carries the expected sequence number carries the value that belongs to it.
 //
-// First half, done by one thread of the kernel that produces the value: the value is POSTED to
-// every rank's mailbox, this GPU's own included, by one 64-bit store each (over NVLink for the
-// peers).  Nothing here waits.
+// The kernel that PRODUCES exchange k only stores this GPU's values to the result buffers.
+// The next such kernel POSTS them first thing (one thread per value of its last CTA): it reads
+// the value back from the result buffer and sends it to every rank's mailbox, this GPU's own
+// included, by one 64-bit store each (over NVLink for the peers).  Nothing here waits.  Stores
+// to memory that peers have mapped delay the end of the kernel that issues them by about 2 us
+// when they are its last instructions; issued at the start they cost nothing.
 #define PEER_SLOTS 16u
-DEV void peer_post(float mine, int index, u64 peers, u32 world, u32 rank, u32 seq) {
+#define PEER_ST(ptr, v) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory")
+#define PEER_LD(w, ptr) asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(ptr) : "memory")
+// meta = dtype << 8 | value index << 16 (the low byte, the settling side's op code, is not used here)
+DEV void peer_post(u64 src, u32 meta, u64 peers, u32 world, u32 rank, u32 seq) {
+    const u32 dt = (meta >> 8) & 255u;
+    const float mine = dt == 0 ? *(const float*)src : dt == 1 ? h2f(*(const u16*)src) : b2f(*(const u16*)src);
     const u64* table = (const u64*)peers;
     const u64 word = ((u64)seq << 32) | (u64)__float_as_uint(mine);
-    const u64 at = ((u64)((seq % PEER_SLOTS) * world + rank)) * 4 + (u64)index;
+    const u64 at = ((u64)((seq % PEER_SLOTS) * world + rank)) * 4 + (u64)(meta >> 16);
     for (u32 r = 0; r < world; ++r) {
         u64* slot = (u64*)table[r] + at;
-        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(word) : "memory");
+        PEER_ST(slot, word);
     }
 }
 
-// Second half: wait (bounded by wait_ns) until this GPU's own mailbox holds every rank's word of
-// exchange `seq`, combine the words in rank order -- every rank ends with the same bits -- and
-// write the n results.  It is run for the exchange BEFORE the one a kernel posts, by every thread
-// of that kernel's finishing CTA: the ranks run the same program, so the peers' words of the
-// earlier exchange are nearly always there already, and no launch, event or second stream is
-// spent on the exchange.  Warp w serves value w (w + warps, ... if the CTA has fewer warps than
-// there are values); lane l holds rank l's word (at most 32 ranks).  peer_peek issues the loads
-// before the CTA finishes its own reduction, so their latency hides behind that work;
-// peer_settle takes the words, polls for the ones that had not arrived, and combines by shuffles.
+// SETTLING exchange k: wait (bounded by wait_ns) until this GPU's own mailbox holds every rank's
+// word of it, combine the words in rank order -- every rank ends with the same bits -- and write
+// the n results over this GPU's own values.  The kernel that produces exchange k + 2 does it: the
+// peers posted k at the start of their kernel k + 1, a whole kernel earlier for ranks that run
+// the same program, so nothing waits, and no launch, event or second stream is spent on the
+// exchange.  All threads of the kernel's LAST CTA take part: peer_peek issues the loads when the
+// CTA starts, peer_settle takes the words when the CTA is done with its own rows, polls for the
+// ones that had not arrived, and combines by shuffles.  Warp w serves value w (w + warps, ... if
+// the CTA has fewer warps than there are values); lane l holds rank l's word (at most 32 ranks).
 // A wait that runs out sets the error word (51) and leaves this GPU's own value as the result:
 // the kernel always returns and the host sees a timeout status at its next synchronisation.
 // meta[v] = op (0 sum, 1 product, 2 max, 3 min) | dtype << 8 | value index << 16.
@@ -246,7 +255,7 @@ DEV u64 peer_peek(u64 mailbox, u32 world, u32 seq, u32 n, const u32* meta) {
     const u32 v = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     u64 w = 0;
     if (v < n && lane < world)
-        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(peer_word(mailbox, world, seq, meta[v], lane)) : "memory");
+        PEER_LD(w, peer_word(mailbox, world, seq, meta[v], lane));
     return w;
 }
 DEV void peer_settle(u64 peeked, u64 mailbox, u64 err, u64 wait_ns, u32 world, u32 rank, u32 seq, u32 n, const u32* meta, const u64* out) {
@@ -259,7 +268,7 @@ DEV void peer_settle(u64 peeked, u64 mailbox, u64 err, u64 wait_ns, u32 world, u
             const u64* slot = peer_word(mailbox, world, seq, m, lane);
             u64 start = 0;
             for (u32 spin = 0; spin < (1u << 30) && !got; ++spin) {
-                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(slot) : "memory");
+                PEER_LD(w, slot);
                 got = (u32)(w >> 32) == seq;
                 if (!got && (spin & 63u) == 63u) {
                     u64 now;
@@ -285,10 +294,16 @@ DEV void peer_settle(u64 peeked, u64 mailbox, u64 err, u64 wait_ns, u32 world, u
         }
     }
 }
-// The earlier exchange a posting kernel settles (gprev_n == 0: none).
-#define PEER_SETTLE_PARAMS u64 gmailbox; u64 gwait_ns; u64 gprev_out[4]; u32 gprev_meta[4]; u32 gprev_seq, gprev_n;
-#define PEER_PEEK(p) const u64 peeked_ = peer_peek(p.gmailbox, p.gworld, p.gprev_seq, p.gprev_n, p.gprev_meta);
-#define PEER_SETTLE(p) peer_settle(peeked_, p.gmailbox, p.gerr, p.gwait_ns, p.gworld, p.grank, p.gprev_seq, p.gprev_n, p.gprev_meta, p.gprev_out)
+// The two earlier exchanges a kernel of this path works on: the one it posts (gpost_n == 0: none)
+// and the one it settles (gprev_n == 0: none).
+#define PEER_SETTLE_PARAMS u64 gmailbox; u64 gwait_ns; u64 gprev_out[4]; u64 gpost_src[4]; u32 gprev_meta[4]; u32 gpost_meta[4]; u32 gprev_seq, gprev_n, gpost_seq, gpost_n;
+#define PEER_POST(p) if (blockIdx.x == gridDim.x - 1 && threadIdx.x < p.gpost_n) peer_post(p.gpost_src[threadIdx.x], p.gpost_meta[threadIdx.x], p.gpeers, p.gworld, p.grank, p.gpost_seq);
+// One CTA does both, and the settling around its own share of the work: the loads of the peers'
+// words are issued when it starts and consumed when it is done with its rows, so their latency is
+// hidden and the end of the kernel is not held up.  It is the LAST CTA of the grid: when the rows do
+// not divide evenly over the CTAs it is the one with a round less to do, which gives it the time.
+#define PEER_PEEK(p) u64 peeked_ = 0; if (blockIdx.x == gridDim.x - 1) peeked_ = peer_peek(p.gmailbox, p.gworld, p.gprev_seq, p.gprev_n, p.gprev_meta);
+#define PEER_SETTLE(p) if (blockIdx.x == gridDim.x - 1) peer_settle(peeked_, p.gmailbox, p.gerr, p.gwait_ns, p.gworld, p.grank, p.gprev_seq, p.gprev_n, p.gprev_meta, p.gprev_out);
 )CUDA";
 
 // ---------------------------------------------------------------------------------------
@@ -468,7 +483,7 @@ struct Params {
     u64 gout[NGRAND];   // one scalar each
     u64 gpeers;         // all-reduce inside this kernel: device array of every rank's mailbox address
     u64 gerr;           // u32 device error word
-    u32 gworld, grank, gseq, gpad_;
+    u32 gworld, grank, gseq, gpad_;   // gseq: number of the exchange this kernel produces (for inspection; the kernel does not use it)
     PEER_SETTLE_PARAMS
 #endif
     u32 oshape[RO];
@@ -500,6 +515,7 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __gri
     __shared__ __align__(16) float red_smem[NRED][RPC][GROUP / 32];
 #endif
     const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
+    ROW_GRAND_POST
     const float* imm = p.imm;
     bool cv[NCH];
 #pragma unroll
@@ -529,6 +545,7 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __gri
         ROW_PREFETCH
         ROW_BODY
     }
+    ROW_GRAND_SETTLE
 #if NGRAND > 0
     // Companion whole-tensor reductions: CTA partial -> scratch; the last CTA to arrive
     // (ticket) combines all partials in index order and stores the scalars.
@@ -544,11 +561,9 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_rows(const __gri
     }
     __syncthreads();
     if (!g_last) return;
-    ROW_GRAND_PEEK
     __threadfence();
     ROW_GRAND_FINISH
     if (threadIdx.x == 0) *(u32*)p.gcounter = 0;
-    ROW_GRAND_SETTLE
 #endif
 }
 )CUDA";
@@ -577,7 +592,7 @@ struct Params {
 #if STREAM_AR
     u64 gpeers;         // all-reduce of the result inside this kernel: the ranks' mailbox addresses
     u64 gerr;           // u32 device error word
-    u32 gworld, grank, gseq, gpad_;
+    u32 gworld, grank, gseq, gpad_;   // gseq: number of the exchange this kernel produces (for inspection; the kernel does not use it)
     PEER_SETTLE_PARAMS
 #endif
     u32 oshape[RO];
@@ -606,6 +621,10 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(co
     __shared__ __align__(16) float red_smem[NRED][THREADS / 32];
     __shared__ u32 is_last;
     const int t = threadIdx.x;
+#if STREAM_AR
+    PEER_POST(p)
+    PEER_PEEK(p)
+#endif
     const u32 sp = blockIdx.x % p.split;
     const u64 row = blockIdx.x / p.split;
     i64 roff[NIN + 1];
@@ -647,6 +666,9 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(co
         for (int u = 0; u < U; ++u) elem_phase(xb[u], rowv, imm, nb[u], acc);
         base += step;
     }
+#if STREAM_AR
+    PEER_SETTLE(p)
+#endif
     STREAM_BLOCK_REDUCE
     if (p.split > 1) {
         float* part = (float*)p.partials + (row * p.split) * NRED;
@@ -668,13 +690,7 @@ extern "C" __global__ void __launch_bounds__(THREADS, MINB) wgf_stream_reduce(co
         STREAM_BLOCK_REDUCE
         if (t == 0) ((u32*)p.counters)[row] = 0;
     }
-#if STREAM_AR
-    PEER_PEEK(p)
-#endif
     STREAM_POST
-#if STREAM_AR
-    PEER_SETTLE(p);
-#endif
 }
 )CUDA";
 

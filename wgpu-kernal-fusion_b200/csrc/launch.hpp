@@ -17,17 +17,20 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
 // `out_has_h` says whether the result keeps the last axis (a Row-kind result is then written
 // to every column of its row).  A program with companion reductions (`prog.grands`) needs
 // `out_has_h` and a non-empty index space; their rank-0 results are returned in `grand_out`.
-// Companion reductions marked `all_reduce` post their values to the mailboxes of `gc` (see Comm)
-// with sequence number gc->seq; the same kernel then settles the exchange before it (prev_*), if
-// that one is still open.
+// Companion reductions marked `all_reduce` are exchanged through the mailboxes of a communicator
+// (see Comm): the kernel stores this GPU's values of exchange `seq`, posts the values of the
+// exchange before it (post_*) and settles the one before that (prev_*), where those are still open.
 struct GrandComm {
     const void* peer_table;   // device array of the ranks' mailbox addresses
     uint32_t world, rank, seq;
-    const void* mailbox;      // this rank's own mailbox: where the earlier exchange is read
+    const void* mailbox;      // this rank's own mailbox: where the settled exchange is read
     uint64_t wait_ns;         // limit of the wait for a peer's word
     uint32_t prev_seq, prev_n;   // prev_n == 0: nothing to settle
     uint32_t prev_meta[4];    // op code (0 sum, 1 product, 2 max, 3 min) | dtype << 8 | value index << 16
     void* prev_out[4];
+    uint32_t post_seq, post_n;   // post_n == 0: nothing to post
+    uint32_t post_meta[4];    // same encoding
+    void* post_src[4];        // result buffers that hold this GPU's values of exchange post_seq
 };
 TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorData>& in,
                     const std::vector<int64_t>& shape, bool out_has_h, int inplace_slot,
