@@ -321,8 +321,14 @@ int32_t wgf_comm_unique_id(uint8_t id[WGF_COMM_ID_BYTES]);
 int32_t wgf_comm_create(wgf_device* dev, int32_t world, int32_t rank,
                         const uint8_t id[WGF_COMM_ID_BYTES], wgf_comm** out);
 int32_t wgf_comm_release(wgf_comm* comm);
-/* Lazy node: all-reduce (WGF_OP_SUM / MAX / MIN / PRODUCT) of `t` over the communicator,
- * queued on the device stream directly behind the kernel that produces `t`. */
+/* Lazy node: all-reduce (WGF_OP_SUM / MAX / MIN / PRODUCT) of `t` over the communicator.
+ * Every rank must request the same all-reduces in the same order.  When `t` is a whole-tensor
+ * reduction, the exchange is done over peer memory by the kernels of this and the following
+ * steps (no collective launch); the result is final for every reader that goes through this
+ * library, and after wgf_device_sync.  A peer that does not take part within the limit
+ * (environment WGF_PEER_WAIT_MS, default 5000) makes the next synchronisation return
+ * WGF_ERR_TIMEOUT; later all-reduces on that device are refused until a new communicator
+ * has been created. */
 int32_t wgf_tensor_all_reduce(wgf_tensor* t, wgf_comm* comm, uint32_t opcode, wgf_tensor** out);
 
 /* ======================================================================================

@@ -287,6 +287,9 @@ int32_t wgf_buffer_upload_async(wgf_buffer* buf, uint64_t offset_bytes, const vo
 int32_t wgf_buffer_device_ptr(wgf_buffer* buf, void** ptr, uint64_t* bytes) {
     return guard([&] {
         REQUIRE(buf);
+        // whoever uses the address works outside this library: what other streams still do to the
+        // buffer is ordered before the device stream's next work, and an open all-reduce is finished
+        if (buf->ref->dev && !buf->ref->dev->recording()) buf->ref->dev->wait_for(*buf->ref);
         if (ptr) *ptr = buf->ref->ptr;
         if (bytes) *bytes = buf->ref->bytes;
     });
