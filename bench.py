@@ -660,7 +660,13 @@ def run_gpu(args):
         # bytes the dominant kernel has to move per launch: x, w in, y out (+ the 4-byte scalar when
         # the reduction rides along)
         kernel_bytes = BYTES_CHAIN + (4 if fused else 0)
-        achieved = kernel_bytes / (row_ms * 1e-3) / 1e9
+        # Average duration of a launch: with one kernel per step the timed region IS K launches of that
+        # kernel between one event pair, so its average is region A's; an event pair around every
+        # single launch (region B) adds about 2.5 us of event handling to each and is reported beside it
+        # (ncu's gpu__time_duration of the same launches, serialised and cold: 46.3 us).  With two kernels
+        # per step only the event pairs can tell them apart.
+        launch_ms = ms_step if fused and world == 1 else row_ms
+        achieved = kernel_bytes / (launch_ms * 1e-3) / 1e9
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
         # the ncu captures summarised under profiles/ (134.26 MB read + 85.19 MB written with the
         # reduction riding along; 134.25 + 84.19 without); the rest of the 134 MB output is still
@@ -696,7 +702,8 @@ def run_gpu(args):
             "roofline": {"bound": "hbm",
                          "kernel": "fused rmsnorm->softmax row kernel" + (" with sum(exp(x)) riding along" if fused else ""),
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic, "launch_ms": row_ms,
+                         "frac": achieved / peak, "traffic": traffic, "launch_ms": launch_ms,
+                         "launch_ms_with_event_pair_per_launch": row_ms,
                          "bytes_per_launch": kernel_bytes, "sum_exp_kernel": sum_exp},
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": bytes_step * world / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,

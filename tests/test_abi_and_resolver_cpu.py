@@ -427,3 +427,35 @@ def test_all_reduce_over_peer_memory_costs_one_launch_per_step(wgf, drydev):
     assert launches_of(d.sync) == 0                             # ... once
     assert launches_of(lambda: (alone * 2.0).materialize()) == 1
     del comm
+
+
+def test_sine_and_cosine_of_bounded_values_skip_the_range_reduction(tmp_path):
+    """Generated source: a sine or cosine whose argument is itself a sine, cosine or tanh (also
+    through neg / abs / sqr / products of such values) uses the polynomial for [-1, 1]; any other
+    argument keeps the full-range function."""
+    import subprocess
+    import sys
+    script = tmp_path / "dump.py"
+    script.write_text(
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {os.path.join(ROOT, 'tests')!r})\n"
+        "from conftest import load_package\n"
+        "wgf = load_package(); d = wgf.Device(-1)\n"
+        "x = d.tensor(np.zeros((64, 512), np.float32))\n"
+        "for name, t in (('CHAIN', lambda: (x * 2.0 + 1.0).sin().cos() * 0.5 + (-(x * x)).exp()),\n"
+        "                ('TANH', lambda: (-x.tanh()).sin()), ('PRODUCT', lambda: (x.sin() * x.cos()).cos()),\n"
+        "                ('SCALED', lambda: (x.sin() * 2.0).cos()), ('PLAIN', lambda: x.cos())):\n"
+        "    print('@@', name, file=sys.stderr, flush=True); t().materialize()\n")
+    env = dict(os.environ, WGF_KERNEL_CACHE=str(tmp_path / "cache"), WGF_JIT_VERBOSE="1", WGF_DUMP_SOURCE="1")
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    uses = {}
+    for chunk in r.stderr.split("@@ ")[1:]:
+        name, _, text = chunk.partition("\n")
+        body = text.split("DEV float prog(")[-1] if "DEV float prog(" in text else text.split("op_tan(float x)")[-1]
+        uses[name.strip()] = sorted(c for c in ("op_sin_unit(", "op_cos_unit(", "op_sin(", "op_cos(") if c in body)
+    assert uses["CHAIN"] == ["op_cos_unit(", "op_sin("], uses
+    assert uses["TANH"] == ["op_sin_unit("], uses
+    assert uses["PRODUCT"] == ["op_cos(", "op_cos_unit(", "op_sin("], uses
+    assert uses["SCALED"] == ["op_cos(", "op_sin("], uses          # 2 sin(x) leaves [-1, 1]
+    assert uses["PLAIN"] == ["op_cos("], uses

@@ -543,3 +543,32 @@ def test_exp_that_only_feeds_a_sum_stays_inside_the_reduction_bound(lo, hi, wgf,
     tot = both.sum(1)
     wgf.Tensor.materialize_all([both, tot])
     assert np.array_equal(both.as_slice(), dev.tensor(x).exp().as_slice())
+
+
+@pytest.mark.parametrize("inner", ["tanh", "sin", "cos"])
+def test_sine_and_cosine_of_bounded_values(inner, dev, orc):
+    """sin / cos whose argument is a tanh, sine or cosine use the polynomial for [-1, 1] (no range
+    reduction).  4 Mi arguments per inner function -- every binade down to 1e-30 on both sides, the
+    values that saturate tanh, a dense stretch around the ends of the interval -- checked against
+    float64 applied to the VERY float the fused kernel saw (the inner function materialised on its
+    own is the same code): 2 ulp, the bound of every transcendental here."""
+    g = seeded(1, 40)
+    mant = g.random(1 << 21, dtype=np.float32) + 1
+    expo = g.integers(-100, 5, 1 << 21).astype(np.float32)
+    x = np.concatenate([mant * np.exp2(expo), -(mant * np.exp2(expo)),
+                        g.uniform(-1.6, 1.6, 1 << 19).astype(np.float32),
+                        np.array([0.0, -0.0, 1.0, -1.0, 20.0, -20.0, np.pi / 2, -np.pi / 2, np.inf, -np.inf, np.nan], np.float32)])
+    t = dev.tensor(x)
+    u = getattr(t, inner)().as_slice()                       # the bounded value, as the fused kernel computes it
+    assert np.all((np.abs(u) <= 1) | np.isnan(u))
+    for outer in ("sin", "cos"):
+        before = dev.launch_count
+        got = getattr(getattr(t, inner)(), outer)().as_slice()
+        assert dev.launch_count - before == 1
+        want = getattr(np, outer)(u.astype(np.float64)).astype(np.float32)
+        ok = ~np.isnan(want)
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert_ulp(orc, got[ok], want[ok], tol=2)
+        # and against the full-range function on the same values (a separate, unfused graph)
+        plain = getattr(dev.tensor(u), outer)().as_slice()
+        assert_ulp(orc, got[ok], plain[ok], tol=2)

@@ -56,6 +56,9 @@ std::string instr_expr(const Instr& in, const std::string& a, const std::string&
             // form (error about 1e-6 relative) gives the same 16-bit value as expf except where the
             // exact result lies within that distance of a rounding boundary
             if (in.op == WGF_OP_EXP && (in.dtype != DType::F32 || in.approx)) return rounded(in.dtype, "op_exp_sfu(" + a + ")");
+            // an argument known to lie in [-1, 1] needs no range reduction
+            if (in.arg_unit && in.op == WGF_OP_SIN) return rounded(in.dtype, "op_sin_unit(" + a + ")");
+            if (in.arg_unit && in.op == WGF_OP_COS) return rounded(in.dtype, "op_cos_unit(" + a + ")");
             return rounded(in.dtype, std::string(unary_fn(in.op)) + "(" + a + ")");
         case IKind::Scalar: {
             std::string c = "imm[" + std::to_string(in.slot) + "]";

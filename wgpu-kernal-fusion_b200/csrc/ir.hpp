@@ -35,6 +35,11 @@ struct Instr {
     // follow from the instructions, so they need no place in the signature.
     bool inexact = false;
     bool fast_div = false;
+    // `unit`: the value lies in [-1, 1] (or is NaN) whatever the inputs are -- a sine, cosine or tanh,
+    // and what abs / neg / sqr / products / casts make of such values.  `arg_unit`: operand `a` is such
+    // a value: a sine or cosine of it needs no range reduction (op_sin_unit / op_cos_unit).
+    bool unit = false;
+    bool arg_unit = false;
 };
 
 inline bool op_is_exact_unary(uint16_t op) { return op == WGF_OP_SQR || op == WGF_OP_SQRT || op == WGF_OP_ABS || op == WGF_OP_NEG; }
@@ -114,6 +119,9 @@ struct Program {
         in.dtype = ins[a].dtype;
         in.vk = ins[a].vk;
         in.inexact = ins[a].inexact || !op_is_exact_unary(op);
+        in.arg_unit = ins[a].unit;
+        in.unit = op == WGF_OP_SIN || op == WGF_OP_COS || op == WGF_OP_TANH ||
+                  (ins[a].unit && (op == WGF_OP_ABS || op == WGF_OP_NEG || op == WGF_OP_SQR));
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
@@ -137,6 +145,7 @@ struct Program {
         in.dtype = to;
         in.vk = ins[a].vk;
         in.inexact = ins[a].inexact;
+        in.unit = ins[a].unit;   // rounding to a narrower type keeps |v| <= 1
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
@@ -149,6 +158,7 @@ struct Program {
         in.vk = (ins[a].vk == VKind::Row && ins[b].vk == VKind::Row) ? VKind::Row : VKind::Elem;
         in.inexact = ins[a].inexact || ins[b].inexact || op == WGF_OP_POW;
         in.fast_div = op == WGF_OP_DIV && ins[b].inexact;
+        in.unit = op == WGF_OP_MUL && ins[a].unit && ins[b].unit;
         ins.push_back(in);
         return (int)ins.size() - 1;
     }
