@@ -785,15 +785,19 @@ def run_configs(args):
     wgf = load("wgf_b200", os.path.join(ROOT, "wgpu-kernal-fusion_b200", "__init__.py"))
     sweep = load("wgf_b200_bench_configs", os.path.join(ROOT, "bench_configs.py"))
     peak_gbs, which = measured_peak()
-    peak_tf = 1590.0
+    peak_tf, peak_tf_sustained = 1590.0, 1400.0
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            peak_tf = float(json.load(f).get("bf16_tflops", peak_tf))
+            peaks = json.load(f)
+        peak_tf = float(peaks.get("bf16_tflops", peak_tf))
+        peak_tf_sustained = float(peaks.get("bf16_tflops_sustained", peak_tf_sustained))
     dev = wgf.Device(int(os.environ.get("LOCAL_RANK", "0")))
     sampler = ClockSampler(0)
-    rows = sweep.run(wgf, dev, peak_gbs, peak_tf, iters=args.steps, warmup=max(args.warmup, 3), only=args.rows)
+    rows = sweep.run(wgf, dev, peak_gbs, peak_tf, iters=args.steps, warmup=max(args.warmup, 3), only=args.rows,
+                     peak_tflops_sustained=peak_tf_sustained)
     print(json.dumps({"workload": "configs", "rows": len(rows), "peak_hbm_gbs": peak_gbs, "peak_bf16_tflops": peak_tf,
+                      "peak_bf16_tflops_sustained": peak_tf_sustained,
                       "peaks": which, "clocks": sampler.stop()}))
 
 

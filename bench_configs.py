@@ -7,7 +7,8 @@ around each dispatch, benches/elementwise.rs:42-43) and reports, per iteration, 
 iterations of the summed kernel times.  Inputs larger than the 126 MB L2 are reused as they are;
 smaller inputs rotate through enough copies to exceed L2 ("cold") and are also timed on one copy
 ("warm").  `bytes` / `flop` are the algorithmic figures of the row, so GB/s and TFLOP/s are
-algorithmic too.
+algorithmic too.  Beside that, `back_to_back_us` is the time per materialisation when the same
+launches follow one another with nothing between them (stream_time_row).
 """
 import collections
 import json
@@ -59,6 +60,45 @@ def time_row(dev, row, iters, warmup):
         t.release()
     per_iter.sort()
     return per_iter[len(per_iter) // 2] * 1e-3, per_iter[0] * 1e-3, labels
+
+
+def stream_time_row(dev, row, budget_s=0.03):
+    """The same materialisation as a STREAM of launches with nothing between them: `reps` of them
+    recorded once as a schedule (one CUDA graph) and replayed until about `budget_s` of device time
+    has passed; wall clock around the replays with the device drained on both sides, divided by the
+    number of materialisations.  An event pair around a single launch adds about 2.5 us of event
+    handling to it (10 % of a 25 us kernel); back to back that cost is not there, and neither is the
+    host's (a replay costs the host one graph launch per `reps` materialisations).  Returns
+    microseconds per materialisation, or None where the row cannot be recorded."""
+    import time
+    reps = max(row.variants, 8)
+    dev.set_timing(False)
+    sched = None
+    try:
+        with dev.record() as sched:
+            for k in range(reps):
+                t = row.build(k % row.variants)
+                t.materialize()
+                t.release()
+        dev.sync()
+        sched.launch()
+        dev.sync()
+        t0 = time.perf_counter()
+        sched.launch()
+        dev.sync()
+        once = max(time.perf_counter() - t0, 1e-6)
+        n = max(3, min(400, int(budget_s / once)))
+        t0 = time.perf_counter()
+        for _ in range(n):
+            sched.launch()
+        dev.sync()
+        return (time.perf_counter() - t0) / (n * reps) * 1e6
+    except Exception:
+        return None
+    finally:
+        if sched is not None and getattr(sched, "h", None):
+            sched.destroy()
+        dev.set_timing(True)
 
 
 # Each group allocates its inputs only when one of its rows is wanted.
@@ -220,7 +260,7 @@ def group_c5(wgf, dev):
 GROUPS = [("C1", group_c1), ("C2", group_c2), ("C3", group_c3), ("C4", group_c4), ("C5", group_c5)]
 
 
-def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, only=None, emit=print):
+def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, only=None, emit=print, stream=True, peak_tflops_sustained=None):
     dev.set_timing(True)
     results = []
     for prefix, make in GROUPS:
@@ -236,6 +276,18 @@ def run(wgf, dev, peak_gbs, peak_tflops, iters=30, warmup=5, only=None, emit=pri
             med, best, labels = time_row(dev, row, iters, warmup)
             med = max(med, 1e-9)          # the compile-only device records no time
             r = {"row": row.name, "kernels": labels, "median_us": round(med, 2), "best_us": round(best, 2)}
+            stream_us = stream_time_row(dev, row) if stream else None
+            if stream_us:
+                r["back_to_back_us"] = round(stream_us, 2)
+                if row.nbytes:
+                    r["back_to_back_frac_hbm"] = round(row.nbytes / stream_us / 1e3 / peak_gbs, 3)
+                elif row.flop and "f32" in row.name:
+                    r["back_to_back_frac_ffma_peak"] = round(row.flop / stream_us / 1e6 / 74.5, 3)
+                elif row.flop:
+                    # tensor-core kernels launched back to back for tens of milliseconds run under the
+                    # power cap: the denominator is the cuBLAS figure measured the same way
+                    r["back_to_back_tflops"] = round(row.flop / stream_us / 1e6, 1)
+                    r["back_to_back_frac_bf16_sustained"] = round(row.flop / stream_us / 1e6 / (peak_tflops_sustained or peak_tflops), 3)
             if row.nbytes:
                 r["gbs"] = round(row.nbytes / med / 1e3, 1)
                 r["frac_hbm"] = round(row.nbytes / med / 1e3 / peak_gbs, 3)

@@ -230,3 +230,25 @@ def test_matmul_epilogues_batched_row_major_and_views(wgf, dev, monkeypatch):
     assert dev.launch_count - before == 2
     np.testing.assert_array_equal(both.as_slice().view(np.uint16), apart.view(np.uint16))
     assert normwise(prod.as_slice(), ra @ rb) <= 1e-2
+
+
+def test_two_devices_in_one_process_each_run_the_tcgen05_kernels(wgf, dev):
+    """Function attributes (the opt-in to large dynamic shared memory) and the occupancy figures the
+    launchers keep are per GPU: a second wgf_device in the same process must set up its own.  The
+    pair kernel, the single-CTA kernel and the fused attention run on GPU 0, GPU 1 and GPU 0 again."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import dense_ref
+    g = seeded(4, 90)
+    a = (g.random((512, 384)) * 2 - 1).astype(np.float16)
+    b = (g.random((384, 640)) * 2 - 1).astype(np.float16)
+    small_a = a[:96, :64].copy()                      # below the pair kernel's shape: the single-CTA kernel
+    q, k, v = [(g.standard_normal((2, 256, 128)) * 0.5).astype(np.float16) for _ in range(3)]
+    for d in (dev, wgf.Device(1), dev):
+        got = d.tensor(a).mat_mul(d.tensor(b)).as_slice()
+        assert normwise(got, a.astype(np.float64) @ b.astype(np.float64)) <= 1e-2
+        got = d.tensor(small_a).mat_mul(d.tensor(b[:64])).as_slice()
+        assert normwise(got, small_a.astype(np.float64) @ b[:64].astype(np.float64)) <= 1e-2
+        got = d.tensor(q).attention(d.tensor(k), d.tensor(v), causal=True).as_slice()
+        assert normwise(got, dense_ref.attention(q, k, v, True, 128 ** -0.5)) <= 2e-2
