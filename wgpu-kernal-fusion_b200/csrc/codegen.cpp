@@ -144,6 +144,16 @@ int tune(const char* name, int dflt) {
     return v ? atoi(v) : dflt;
 }
 
+// Checked build: names the buffers of the launch that follows (Device::chk_bind); the result last.
+static void bind_checked(Device& dev, const std::vector<TensorData>& in, const TensorData& out,
+                         const std::vector<TensorData>* more = nullptr) {
+    if (!dev.checked) return;
+    for (const TensorData& t : in) dev.chk_bind(t.buf.get());
+    if (more)
+        for (const TensorData& t : *more) dev.chk_bind(t.buf.get());
+    dev.chk_bind(out.buf.get());
+}
+
 // The helpers every generated kernel starts with.
 std::string prelude() {
     // warp-wide max / min through redux.sync (f32 form of sm_100a)
@@ -406,7 +416,7 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
                 if (sidx[t] >= 0)
                     s << "    { float4 v_[4]; \\\n"
                       << "      for (int i = 0; i < 4; ++i) { const u32 ll = l0 + r16 + 16 * i; \\\n"
-                      << "        v_[i] = (pp < P && ll < L) ? *(const float4*)((const float*)p.ptr[" << t << "] + base[" << t
+                      << "        v_[i] = (pp < P && ll < L) ? load_f4((const void*)p.ptr[" << t << "], base[" << t
                       << "] + (i64)pp + (i64)ll * p.stride[" << t << " * R + R - 1]) : make_float4(0.f, 0.f, 0.f, 0.f); } \\\n"
                       << "      for (int i = 0; i < 4; ++i) { const int li = r16 + 16 * i; \\\n"
                       << "        stage[" << sidx[t] << "][4 * c16 + 0][li] = v_[i].x; stage[" << sidx[t] << "][4 * c16 + 1][li] = v_[i].y; \\\n"
@@ -435,6 +445,7 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
         for (float f : prog.imms) w.put<float>(f);
         if (prog.imms.empty()) w.put<float>(0.f);
         w.finish();
+        bind_checked(dev, in, out);
         dev.launch(k, dim3((unsigned)tiles), dim3(256), 0, w.bytes.data(), "elementwise_tiled");
         return out;
     }
@@ -471,6 +482,7 @@ static TensorData run_elementwise_impl(Device& dev, const Program& prog, const s
 
     int64_t blocks = (nchunks + 256ll * cfg.U - 1) / (256ll * cfg.U);
     WGF_CHECK(blocks < (1ll << 31), WGF_ERR_UNSUPPORTED, "tensor too large for one launch");
+    bind_checked(dev, in, out);
     dev.launch(k, dim3((unsigned)blocks), dim3(256), 0, w.bytes.data(), "elementwise");
     return out;
 }
@@ -985,6 +997,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             for (float f : prog.imms) w.put<float>(f);
             if (prog.imms.empty()) w.put<float>(0.f);
             w.finish();
+            bind_checked(dev, in, out);
             dev.launch(k, dim3((unsigned)tiles, (unsigned)split, (unsigned)O), dim3(cfg.TX, 256 / cfg.TX), 0, w.bytes.data(), "col_reduce");
             return out;
         }
@@ -1099,6 +1112,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
             put_settle(w, gc);
         }
         put_tail(w);
+        bind_checked(dev, in, out, grand_out);
         dev.launch(k, dim3((unsigned)blocks), dim3(cfg.GROUP * cfg.RPC), 0, w.bytes.data(), "rows");
         return out;
     }
@@ -1151,6 +1165,7 @@ TensorData run_rows(Device& dev, const Program& prog, const std::vector<TensorDa
         put_settle(w, gc);
     }
     put_tail(w);
+    bind_checked(dev, in, out);
     dev.launch(k, dim3((unsigned)(rows * split)), dim3(256), 0, w.bytes.data(), "stream_reduce");
     return out;
 }

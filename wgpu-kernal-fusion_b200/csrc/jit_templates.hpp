@@ -16,6 +16,34 @@ typedef long long i64;
 typedef unsigned long long u64;
 #define DEV __device__ __forceinline__
 
+// Checked build (environment WGF_CHECKED=1; the device puts the three defines in front of this
+// text): every access of a generated kernel to tensor memory is tested against the extents of the
+// buffers that the host bound to the launch.  An access outside all of them is NOT made: the first
+// one is recorded (error word = 61, then the address and the byte count) and the host reports it
+// at its next synchronisation.  The stand-in for a memory checker where none can be run; several
+// times slower than the normal build.
+#ifndef WGF_CHECKED
+#define WGF_CHECKED 0
+#endif
+#if WGF_CHECKED
+struct ChkTable { u64 n; u64 lo[24]; u64 hi[24]; };
+__device__ __noinline__ bool chk(const void* base, i64 elem, int esize, int n) {
+    const ChkTable* t = (const ChkTable*)WGF_CHK_TABLE;
+    const u64 a = (u64)base + (u64)(elem * esize), e = a + (u64)(n * esize);
+    for (u64 k = 0; k < t->n; ++k)
+        if (a >= t->lo[k] && e <= t->hi[k]) return true;
+    u32* err = (u32*)WGF_CHK_ERR;
+    if (atomicCAS(err, 0u, 61u) == 0u) {
+        ((u64*)err)[1] = a;
+        ((u64*)err)[2] = e - a;
+    }
+    return false;
+}
+#define CHK_FAILS(base, i, esize, n) (!chk(base, i, esize, n))
+#else
+#define CHK_FAILS(base, i, esize, n) false
+#endif
+
 DEV float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
 DEV float b2f(u16 b) { return __uint_as_float(((u32)b) << 16); }
 // two floats -> packed pair of 16-bit values (lo in bits 0-15), round to nearest even
@@ -79,13 +107,20 @@ DEV float op_pow(float a, float b) { return (float)pow((double)a, (double)b); }
 DEV u32 fastdiv(u32 n, u32 m, u32 s) { return m ? (__umulhi(n, m) >> s) : n; }
 
 template <int DT> DEV float load1(const void* base, i64 i) {
+    if (CHK_FAILS(base, i, DT == 0 ? 4 : 2, 1)) return 0.f;
     if (DT == 0) return ((const float*)base)[i];
     u16 v = ((const u16*)base)[i];
     return DT == 1 ? h2f(v) : b2f(v);
 }
 template <int DT> DEV void store1(void* base, i64 i, float v) {
+    if (CHK_FAILS(base, i, DT == 0 ? 4 : 2, 1)) return;
     if (DT == 0) ((float*)base)[i] = v;
     else ((u16*)base)[i] = DT == 1 ? f2h(v) : f2b(v);
+}
+// four consecutive f32 at element index i (16-byte aligned), zeros where the checked build refuses
+DEV float4 load_f4(const void* base, i64 i) {
+    if (CHK_FAILS(base, i, 4, 4)) return make_float4(0.f, 0.f, 0.f, 0.f);
+    return *(const float4*)((const float*)base + i);
 }
 template <int DT> DEV float cvt16(u16 v) { return DT == 1 ? h2f(v) : b2f(v); }
 template <int DT> DEV u32 pack16(float lo, float hi) {
@@ -94,6 +129,11 @@ template <int DT> DEV u32 pack16(float lo, float hi) {
 
 // C consecutive elements starting at element index i; (base + i) is aligned to the vector.
 template <int DT, int C> DEV void load_vec(const void* base, i64 i, float* out) {
+    if (CHK_FAILS(base, i, DT == 0 ? 4 : 2, C)) {
+#pragma unroll
+        for (int j = 0; j < C; ++j) out[j] = 0.f;
+        return;
+    }
     if (DT == 0) {
         if (C % 4 == 0) {
             const float4* p = (const float4*)((const float*)base + i);
@@ -126,6 +166,7 @@ template <int DT, int C> DEV void load_vec(const void* base, i64 i, float* out) 
     }
 }
 template <int DT, int C> DEV void store_vec(void* base, i64 i, const float* v) {
+    if (CHK_FAILS(base, i, DT == 0 ? 4 : 2, C)) return;
     if (DT == 0) {
         if (C % 4 == 0) {
             float4* p = (float4*)((float*)base + i);

@@ -238,6 +238,7 @@ std::shared_ptr<Device> Device::create(int ordinal) {
         d->dry = true;
         d->timing = false;
         d->sm_count = 148;
+        d->checked = getenv("WGF_CHECKED") != nullptr;   // compiles the checked kernels (nothing runs)
         return d;
     }
     int count = 0;
@@ -258,6 +259,7 @@ std::shared_ptr<Device> Device::create(int ordinal) {
     d->sm_count = prop.multiProcessorCount;
     WGF_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
     DriverApi::get();
+    d->checked = getenv("WGF_CHECKED") != nullptr;
     return d;
 }
 
@@ -282,6 +284,7 @@ Device::~Device() {
     for (auto e : event_pool_) cudaEventDestroy(e);
     if (counters_) cudaFree(counters_);
     if (error_word_) cudaFree(error_word_);
+    if (chk_table_) cudaFree(chk_table_);
     if (collective_stream_) {
         cudaStreamSynchronize(collective_stream_);
         cudaStreamDestroy(collective_stream_);
@@ -316,6 +319,10 @@ void Device::sync() {
     check_error_word();
 }
 
+void Device::chk_bind(const Buffer* b) {
+    if (checked && b && b->ptr) chk_bound_.emplace_back((uint64_t)(uintptr_t)b->ptr, (uint64_t)(uintptr_t)b->ptr + b->bytes);
+}
+
 unsigned* Device::error_word() {
     if (dry) return nullptr;
     if (!error_word_) {
@@ -331,6 +338,15 @@ void Device::check_error_word() {
     if (!error_word_) return;
     unsigned v = 0;
     WGF_CUDA(cudaMemcpy(&v, error_word_, sizeof v, cudaMemcpyDeviceToHost));
+    if (v == 61) {
+        uint64_t detail[3] = {0, 0, 0};
+        cudaMemcpy(detail, error_word_, sizeof detail, cudaMemcpyDeviceToHost);
+        cudaMemset(error_word_, 0, sizeof detail);
+        char msg[224];
+        snprintf(msg, sizeof msg, "checked build: a generated kernel asked for %llu bytes at device address 0x%llx, outside every "
+                 "buffer bound to its launch; the access was not made", (unsigned long long)detail[2], (unsigned long long)detail[1]);
+        fail(WGF_ERR_CUDA, msg);
+    }
     if (v) {
         cudaMemset(error_word_, 0, sizeof v);
         if (v == 51) exchange_broken = true;
@@ -535,6 +551,16 @@ const JitKernel& Device::kernel(const std::string& key, const char* entry, const
     }
     make_current();
     std::string src = source();
+    if (checked) {
+        char defs[192];
+        if (!dry && !chk_table_) {
+            WGF_CUDA(cudaMalloc(&chk_table_, 512));
+            WGF_CUDA(cudaMemset(chk_table_, 0, 512));
+        }
+        snprintf(defs, sizeof defs, "#define WGF_CHECKED 1\n#define WGF_CHK_TABLE 0x%llxull\n#define WGF_CHK_ERR 0x%llxull\n",
+                 (unsigned long long)(uintptr_t)chk_table_, (unsigned long long)(uintptr_t)error_word());
+        src = defs + src;
+    }
     std::vector<char> cubin = compile_to_cubin(src, entry);
     compiles++;
     if (dry) {
@@ -594,6 +620,24 @@ void Device::launch(const JitKernel& k, dim3 grid, dim3 block, size_t smem, cons
         end_launch();
         return;
     }
+    if (checked) {
+        // the extents of this launch's buffers, stream-ordered between the previous kernel and this one
+        struct {
+            uint64_t n, lo[24], hi[24];
+        } t{};
+        WGF_CHECK(chk_bound_.size() <= 24, WGF_ERR_UNSUPPORTED, "checked build: more than 24 buffers in one launch");
+        t.n = chk_bound_.size();
+        for (size_t i = 0; i < chk_bound_.size(); ++i) {
+            t.lo[i] = chk_bound_[i].first;
+            t.hi[i] = chk_bound_[i].second;
+        }
+        static const long shrink = getenv("WGF_CHECKED_SHRINK") ? atol(getenv("WGF_CHECKED_SHRINK")) : 0;   // test hook:
+        // the last buffer bound (the result) is declared this many bytes shorter than it is, so that
+        // accesses that are in fact valid are refused and reported
+        if (shrink > 0 && t.n) t.hi[t.n - 1] -= std::min<uint64_t>((uint64_t)shrink, t.hi[t.n - 1] - t.lo[t.n - 1]);
+        chk_bound_.clear();
+        WGF_CUDA(cudaMemcpyAsync(chk_table_, &t, sizeof t, cudaMemcpyHostToDevice, stream));
+    }
     void* args[] = {const_cast<void*>(params)};
     CUresult r = DriverApi::get().LaunchKernel(k.fn, grid.x, grid.y, grid.z, block.x, block.y, block.z,
                                                (unsigned)smem, (CUstream)stream, args, nullptr);
@@ -612,6 +656,7 @@ void Device::refuse_while_recording(const char* what) const {
 
 void Device::begin_recording() {
     WGF_CHECK(!recording(), WGF_ERR_INVALID_ARGUMENT, "a schedule is already being recorded on this device");
+    WGF_CHECK(!checked, WGF_ERR_UNSUPPORTED, "the checked build (WGF_CHECKED) uploads a table before every launch and cannot record schedules");
     if (!dry) {
         make_current();
         // everything the capture must not contain happens now: the one-time set-up of the

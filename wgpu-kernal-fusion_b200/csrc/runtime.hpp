@@ -110,6 +110,12 @@ struct Device : std::enable_shared_from_this<Device> {
     // A device word that kernels with bounded waits set when a wait gives up (0 = fine).
     // sync() and download() read it after the stream has drained and raise WGF_ERR_TIMEOUT.
     unsigned* error_word();
+    // Checked build (environment WGF_CHECKED=1, read when the device is created): generated kernels
+    // test every tensor access against the extents bound here (see CHK_FAILS in jit_templates.hpp).
+    // A launcher of a generated kernel names the buffers of its launch with chk_bind before
+    // Device::launch, which uploads the table on the device stream.  Schedules cannot be recorded.
+    bool checked = false;
+    void chk_bind(const Buffer* b);
     void check_error_word();
     // Set once a combine kernel of an all-reduce over peer memory gave up waiting for a peer (error
     // code 51): the ranks are out of step from then on, and further all-reduces on this device are
@@ -181,6 +187,8 @@ struct Device : std::enable_shared_from_this<Device> {
     TimingRecord pending_;
     void* counters_ = nullptr;
     unsigned* error_word_ = nullptr;
+    void* chk_table_ = nullptr;                               // device copy of the extents of the current launch
+    std::vector<std::pair<uint64_t, uint64_t>> chk_bound_;    // [lo, hi) of the buffers named since the last launch
     cudaStream_t collective_stream_ = nullptr;
     cudaStream_t upload_stream_ = nullptr;
     struct Deferred {
