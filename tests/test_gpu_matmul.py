@@ -252,3 +252,25 @@ def test_two_devices_in_one_process_each_run_the_tcgen05_kernels(wgf, dev):
         assert normwise(got, small_a.astype(np.float64) @ b[:64].astype(np.float64)) <= 1e-2
         got = d.tensor(q).attention(d.tensor(k), d.tensor(v), causal=True).as_slice()
         assert normwise(got, dense_ref.attention(q, k, v, True, 128 ** -0.5)) <= 2e-2
+
+
+@pytest.mark.parametrize("shape", [(2100, 4420, 260), (4096, 2560, 512), (2, 2100, 2304, 264)])
+def test_f32_wide_tile_kernel_on_ragged_shapes(shape, wgf, dev):
+    """Large f32 products take the 128x256-tile kernel (cp.async ring); M, N and K that are not
+    multiples of the tile (zero-filled pieces on three edges, a short last k tile) and a batch."""
+    g = seeded(4, 70)
+    if len(shape) == 4:
+        B, M, N, K = shape
+        a = (g.random((B, M, K), dtype=np.float32) * 2 - 1)
+        b = (g.random((B, K, N), dtype=np.float32) * 2 - 1)
+    else:
+        M, N, K = shape
+        a = (g.random((M, K), dtype=np.float32) * 2 - 1)
+        b = (g.random((K, N), dtype=np.float32) * 2 - 1)
+    dev.set_timing(True)
+    t = dev.tensor(a).mat_mul(dev.tensor(b))
+    got = t.as_slice()
+    assert "sgemm_wide" in t.timing_labels()
+    dev.set_timing(False)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    assert normwise(got, ref) <= 1e-5

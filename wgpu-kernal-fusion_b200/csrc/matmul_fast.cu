@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "matmul.hpp"
 
@@ -365,12 +366,205 @@ bool run_gemv(Device& dev, const void* a, const void* b, void* c, const MatmulDi
     return false;
 }
 
+// ---------------------------------------------------------------------------------------
+// f32 SGEMM for large problems with B stored [K,N]: 128x256x16 tiles, 8x16 register tile per
+// thread, one CTA of 256 threads per SM, tiles brought into a 4-stage shared-memory ring with
+// cp.async (no staging registers, no shared-memory stores, one barrier per k-tile).
+// Why this shape: an FFMA kernel on this SM (128 fp32 lanes, 128 bytes of shared memory per clock)
+// with an 8x8 register tile needs a byte of shared memory per FFMA lane -- exactly all there is --
+// so fragment loads and FFMAs have to overlap perfectly; 8x16 needs 0.75.  A is kept [m][k] in
+// shared memory as it comes from global memory (rows of 16 floats padded to 20: the two rows a
+// warp reads are broadcast), and a thread takes four k steps of a row with one 16-byte load.
+// ---------------------------------------------------------------------------------------
+constexpr int SW_BM = 128, SW_BN = 256, SW_BK = 16, SW_STAGES = 4, SW_LDA = SW_BK + 4;
+constexpr int SW_A_FLOATS = SW_BM * SW_LDA, SW_B_FLOATS = SW_BK * SW_BN;
+constexpr size_t SW_SMEM = (size_t)SW_STAGES * (SW_A_FLOATS + SW_B_FLOATS) * sizeof(float);
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+
+// Two fp32 FMAs in one instruction on a register pair (fma.rn.f32x2, sm_100): the FMA pipe does the
+// same work per clock, but the scheduler dispatches half as many instructions, and what limited
+// the scalar form of this kernel were dispatch stalls (66 % of the pipe at 0.5 stalls per issue).
+// Every lane rounds like a scalar fmaf.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void ffma2(unsigned long long& d, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+
+// Work items: tile t (0 <= t < tiles) in full for CTAs below `whole`; the remaining tiles -- the part
+// of the last wave that would leave most SMs idle -- are computed as two halves of the k range by
+// two CTAs each, which add their halves to a zeroed C with atomics (x + y on 0 is the same bits in
+// either order, so the result does not depend on which half arrives first).
+struct WideSplit {
+    int tn, tm;        // tiles along N and M
+    int whole;         // CTAs [0, whole) own a full tile; CTA whole + 2 i + h owns half h of tile whole + i
+};
+
+__global__ void __launch_bounds__(256, 1)
+sgemm_wide_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                  const __grid_constant__ MatmulDims d, const WideSplit ws) {
+    extern __shared__ __align__(16) float sw_smem[];
+    float* As = sw_smem;                                   // [stage][128][20]
+    float* Bs = sw_smem + SW_STAGES * SW_A_FLOATS;         // [stage][16][256]
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const bool halved = (int)blockIdx.x >= ws.whole;
+    const int tile = halved ? ws.whole + ((int)blockIdx.x - ws.whole) / 2 : (int)blockIdx.x;
+    const int bx = tile % ws.tn, by = (tile / ws.tn) % ws.tm, bz = tile / (ws.tn * ws.tm);
+    const long long m0 = (long long)by * SW_BM, n0 = (long long)bx * SW_BN;
+    const float* Ab = A + (long long)bz * d.a_bs;
+    const float* Bb = B + (long long)bz * d.b_bs;
+    float* Cb = C + (long long)bz * d.c_bs;
+    const long long lda = d.a_rs, ldb = d.b_rs;
+    const int all_tiles = (int)((d.K + SW_BK - 1) / SW_BK);
+    // k tiles [kt0, kt0 + n_tiles) of this work item
+    const int kt0 = halved && (((int)blockIdx.x - ws.whole) & 1) ? all_tiles / 2 : 0;
+    const int n_tiles = !halved ? all_tiles : kt0 ? all_tiles - all_tiles / 2 : all_tiles / 2;
+
+    // K, N, lda, ldb are multiples of 4 and the bases 16-byte aligned (the launcher checks), so a
+    // 16-byte piece is either wholly inside the matrix or wholly outside (then zero-filled; the
+    // source address of such a piece is the matrix base, never dereferenced)
+    auto load_tile = [&](int kt, int stage) {
+        const long long k0 = (long long)(kt0 + kt) * SW_BK;
+        float* as = As + stage * SW_A_FLOATS;
+        float* bs = Bs + stage * SW_B_FLOATS;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {          // A: 128 rows x 4 pieces
+            const int idx = tid + i * 256, r = idx / 4, c4 = idx % 4;
+            const long long m = m0 + r, k = k0 + c4 * 4;
+            const bool in = m < d.M && k < d.K;
+            cp_async16(as + r * SW_LDA + c4 * 4, in ? Ab + m * lda + k : Ab, in ? 16 : 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {          // B: 16 k-rows x 64 pieces
+            const int idx = tid + i * 256, kr = idx / 64, c4 = idx % 64;
+            const long long k = k0 + kr, n = n0 + c4 * 4;
+            const bool in = k < d.K && n < d.N;
+            cp_async16(bs + kr * SW_BN + c4 * 4, in ? Bb + k * ldb + n : Bb, in ? 16 : 0);
+        }
+    };
+
+    unsigned long long acc[8][8];   // acc[i][jj] = columns 2 jj, 2 jj + 1 of row i of the thread's 8 x 16 tile
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
+
+#pragma unroll
+    for (int s = 0; s < SW_STAGES - 1; ++s) {
+        if (s < n_tiles) load_tile(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < n_tiles; ++kt) {
+        // tile kt has landed (all but the newest STAGES-2 groups are complete) and every thread is
+        // done with the stage that the load below overwrites (tile kt-1's)
+        asm volatile("cp.async.wait_group %0;" ::"n"(SW_STAGES - 2) : "memory");
+        __syncthreads();
+        if (kt + SW_STAGES - 1 < n_tiles) load_tile(kt + SW_STAGES - 1, (kt + SW_STAGES - 1) % SW_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const float* as = As + (kt % SW_STAGES) * SW_A_FLOATS;
+        const float* bs = Bs + (kt % SW_STAGES) * SW_B_FLOATS;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float4 av[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = (i < 4 ? 0 : 64) + ty * 4 + (i & 3);
+                av[i] = *reinterpret_cast<const float4*>(as + r * SW_LDA + g * 4);
+            }
+#pragma unroll
+            for (int kq = 0; kq < 4; ++kq) {
+                unsigned long long b[8];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const float4 t = *reinterpret_cast<const float4*>(bs + (g * 4 + kq) * SW_BN + h * 64 + tx * 4);
+                    b[h * 2] = pack2(t.x, t.y);
+                    b[h * 2 + 1] = pack2(t.z, t.w);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float a = kq == 0 ? av[i].x : kq == 1 ? av[i].y : kq == 2 ? av[i].z : av[i].w;
+                    const unsigned long long aa = pack2(a, a);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ffma2(acc[i][j], aa, b[j]);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const bool vec_ok = (d.c_rs % 4 == 0) && ((reinterpret_cast<uintptr_t>(Cb) & 15) == 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long m = m0 + (i < 4 ? 0 : 64) + ty * 4 + (i & 3);
+        if (m >= d.M) continue;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const long long n = n0 + h * 64 + tx * 4;
+            float v[4];
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(v[0]), "=f"(v[1]) : "l"(acc[i][h * 2]));
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(v[2]), "=f"(v[3]) : "l"(acc[i][h * 2 + 1]));
+            if (halved) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (n + j < d.N) atomicAdd(Cb + m * d.c_rs + n + j, v[j]);
+            } else if (vec_ok && n + 3 < d.N) {
+                *reinterpret_cast<float4*>(Cb + m * d.c_rs + n) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (n + j < d.N) Cb[m * d.c_rs + n + j] = v[j];
+            }
+        }
+    }
+}
+
 bool run_sgemm(Device& dev, const void* a, const void* b, void* c, const MatmulDims& d) {
     if (d.a_cs != 1 || d.a_rs % 4 || d.K % 4 || !aligned16(a) || !aligned16(b)) return false;
     if (d.a_bs % 4 || d.b_bs % 4) return false;
     const bool b_kn = d.b_cs == 1 && d.b_rs % 4 == 0 && d.N % 4 == 0;
     const bool b_nk = d.b_rs == 1 && d.b_cs % 4 == 0;
     if (!b_kn && !b_nk) return false;
+    // the wide kernel pays where its 128x256 tiles fill the machine more than once
+    static const bool no_wide = getenv("WGF_SGEMM_NO_WIDE") != nullptr;   // diagnostic switch, read once
+    const long long wide_tiles = ((d.M + SW_BM - 1) / SW_BM) * ((d.N + SW_BN - 1) / SW_BN) * d.batch;
+    // C as one dense block [batch, M, N]: what the memset before a split launch assumes
+    const bool wide_rows_dense = d.c_rs == d.N && (d.batch == 1 || d.c_bs == d.M * d.N);
+    if (b_kn && !no_wide && d.M >= 512 && d.N >= 512 && d.K >= 256 && wide_tiles >= 2ll * dev.sm_count &&
+        wide_tiles < (1ll << 30)) {
+        dev.begin_launch("sgemm_wide");
+        if (!dev.dry) {
+            static std::mutex mu;
+            static bool attr_set[64] = {};
+            {
+                std::lock_guard<std::mutex> g(mu);
+                if (dev.ordinal >= 0 && dev.ordinal < 64 && !attr_set[dev.ordinal]) {
+                    cudaFuncSetAttribute(sgemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SW_SMEM);
+                    attr_set[dev.ordinal] = true;
+                }
+            }
+            WideSplit ws;
+            ws.tn = (int)((d.N + SW_BN - 1) / SW_BN);
+            ws.tm = (int)((d.M + SW_BM - 1) / SW_BM);
+            const long long tail = wide_tiles % dev.sm_count;
+            const bool split = tail > 0 && 2 * tail <= dev.sm_count && d.K >= 4 * SW_BK && wide_rows_dense;
+            ws.whole = (int)(split ? wide_tiles - tail : wide_tiles);
+            if (split) {
+                // the halved tiles are added into C: rows of C are dense here, so one memset covers it
+                WGF_CUDA(cudaMemsetAsync(c, 0, (size_t)d.batch * d.M * d.N * sizeof(float), dev.stream));
+            }
+            const unsigned ctas = (unsigned)(ws.whole + (split ? 2 * tail : 0));
+            sgemm_wide_kernel<<<ctas, 256, SW_SMEM, dev.stream>>>((const float*)a, (const float*)b, (float*)c, d, ws);
+        }
+        dev.end_launch();
+        return true;
+    }
     dim3 grid((unsigned)((d.N + SG_BN - 1) / SG_BN), (unsigned)((d.M + SG_BM - 1) / SG_BM), (unsigned)d.batch);
     if (grid.y > 65535) return false;
     dev.begin_launch("sgemm");
