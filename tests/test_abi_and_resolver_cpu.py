@@ -459,3 +459,25 @@ def test_sine_and_cosine_of_bounded_values_skip_the_range_reduction(tmp_path):
     assert uses["PRODUCT"] == ["op_cos(", "op_cos_unit(", "op_sin("], uses
     assert uses["SCALED"] == ["op_cos(", "op_sin("], uses          # 2 sin(x) leaves [-1, 1]
     assert uses["PLAIN"] == ["op_cos("], uses
+
+
+def test_library_runs_with_nvtx_ranges_on(tmp_path):
+    """WGF_NVTX=1 wraps every materialisation and launch in an NVTX range; without a profiler attached
+    the calls are no-ops, and the library must behave exactly as without them."""
+    import subprocess
+    import sys
+    script = tmp_path / "nvtx.py"
+    script.write_text(
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {os.path.join(ROOT, 'tests')!r})\n"
+        "from conftest import load_package\n"
+        "wgf = load_package(); d = wgf.Device(-1)\n"
+        "x = d.tensor(np.zeros((64, 512), np.float32))\n"
+        "before = d.launch_count\n"
+        "wgf.Tensor.materialize_all([x.softmax_last_dim(), x.exp().sum(0).sum(0)])\n"
+        "(x * 2.0).materialize()\n"
+        "print('LAUNCHES', d.launch_count - before)\n")
+    env = dict(os.environ, WGF_NVTX="1", WGF_KERNEL_CACHE=str(tmp_path / "cache"))
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "LAUNCHES 2" in r.stdout

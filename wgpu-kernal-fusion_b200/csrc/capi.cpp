@@ -1,5 +1,6 @@
 // extern "C" boundary (include/wgf.h).  Handles are small heap objects around the C++
 // objects; every entry point converts exceptions into status codes.
+#include <nvtx3/nvToolsExt.h>
 #include <mutex>
 
 #include "comm.hpp"
@@ -820,7 +821,23 @@ int32_t wgf_tensor_attention(wgf_tensor* q, wgf_tensor* k, wgf_tensor* v, wgf_te
     })
 }
 
+namespace {
+// WGF_NVTX=1: one range per materialisation request around the ranges of its kernels.
+struct NvtxRange {
+    bool on;
+    explicit NvtxRange(const char* name) {
+        static const bool enabled = getenv("WGF_NVTX") != nullptr;
+        on = enabled;
+        if (on) nvtxRangePushA(name);
+    }
+    ~NvtxRange() {
+        if (on) nvtxRangePop();
+    }
+};
+}  // namespace
+
 int32_t wgf_tensor_materialize(wgf_tensor* t) {
+    NvtxRange range("wgf materialize");
     GRAPH_GUARD({
         REQUIRE(t);
         resolve(t->node);
@@ -828,6 +845,7 @@ int32_t wgf_tensor_materialize(wgf_tensor* t) {
 }
 
 int32_t wgf_tensor_materialize_many(wgf_tensor* const* tensors, uint32_t n) {
+    NvtxRange range("wgf materialize_many");
     GRAPH_GUARD({
         if (n > 0) REQUIRE(tensors);
         std::vector<NodeRef> nodes;

@@ -1,3 +1,4 @@
+#include <nvtx3/nvToolsExt.h>   // header-only: ranges cost nothing unless a profiler is attached
 #include "runtime.hpp"
 
 #include <dlfcn.h>
@@ -589,6 +590,13 @@ int Device::max_blocks_per_sm(const JitKernel& k, int threads) {
 void Device::begin_launch(const char* what) {
     static const bool trace = getenv("WGF_TRACE_LAUNCHES") != nullptr;   // diagnostic: one line per kernel queued
     if (trace) fprintf(stderr, "[wgf] launch %s\n", what);
+    // WGF_NVTX=1: every kernel the library queues sits in a named range on the host time line (a
+    // profiler that follows NVTX shows which part of a materialisation each launch belongs to)
+    static const bool nvtx = getenv("WGF_NVTX") != nullptr;
+    if (nvtx) {
+        nvtxRangePushA(what);
+        nvtx_open_ = true;
+    }
     launches++;
     if (timing && sink && !dry && !recording()) {
         pending_.start = event();
@@ -599,6 +607,10 @@ void Device::begin_launch(const char* what) {
 }
 
 void Device::end_launch() {
+    if (nvtx_open_) {
+        nvtxRangePop();
+        nvtx_open_ = false;
+    }
     if (pending_.start) {
         WGF_CUDA(cudaEventRecord(pending_.stop, stream));
         if (sink) sink->push_back(pending_);

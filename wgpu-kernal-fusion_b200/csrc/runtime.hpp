@@ -187,6 +187,7 @@ struct Device : std::enable_shared_from_this<Device> {
     TimingRecord pending_;
     void* counters_ = nullptr;
     unsigned* error_word_ = nullptr;
+    bool nvtx_open_ = false;                                  // a range of begin_launch waits for its end_launch
     void* chk_table_ = nullptr;                               // device copy of the extents of the current launch
     std::vector<std::pair<uint64_t, uint64_t>> chk_bound_;    // [lo, hi) of the buffers named since the last launch
     cudaStream_t collective_stream_ = nullptr;
