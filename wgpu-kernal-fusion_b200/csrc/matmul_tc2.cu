@@ -10,7 +10,7 @@
 //
 // Roles per CTA: warp 0 = TMA producer (both CTAs load their halves; all loads of a stage
 // complete on the LEADER's "full" barrier), warp 1 = MMA issuer (leader only; its commits
-// arrive on both CTAs' barriers), warps 2-5 = epilogue (each CTA drains its own tensor memory
+// arrive on both CTAs' barriers), warps 2-9 = epilogue (each CTA drains its own tensor memory
 // and tells the leader when an accumulator is free).  No TMA load uses multicast.  Every wait
 // is bounded and reports through the device error word.
 //
@@ -43,9 +43,10 @@ constexpr int P_A_BYTES = P_BM * P_BK * 2;            // 16 KiB
 constexpr int P_B_BYTES = P_BNH * P_BK * 2;           // 16 KiB
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // per CTA; a stage of the pair is twice that
 constexpr int P_EPI_TILE_BYTES = 32 * 128;
-constexpr int P_EPI_BYTES = 4 * 2 * P_EPI_TILE_BYTES;
+constexpr int P_EPI_WARPS = 8;             // per CTA: two per quarter of the accumulator's rows, each half of the columns
+constexpr int P_EPI_BYTES = P_EPI_WARPS * P_EPI_TILE_BYTES;   // one staging tile per warp
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int P_THREADS = 192;
+constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;
 constexpr unsigned PEER_BIT_MASK = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared-memory address: the even CTA of the pair
 
 struct PairParams {
@@ -205,7 +206,7 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full_bar(a), 1);
-            mbar_init(acc_empty_bar(a), 8);             // one arrival per epilogue warp of either CTA
+            mbar_init(acc_empty_bar(a), 2 * P_EPI_WARPS);   // one arrival per epilogue warp of either CTA
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -309,11 +310,15 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+        // Warps w and w + 4 read the same quarter of the accumulator's rows (tensor-memory lanes
+        // 32 (w mod 4) ..) and take one half of its columns each: with short K (two k-blocks per
+        // tile, the batched [1024,128] x [128,1024] products) and with the heavier fused epilogues,
+        // draining the accumulator sets the pace, and eight warps drain it twice as fast as four.
         const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
         int acc = 0;
         unsigned acc_phase = 0;
-        int epi_buf = 0;
         const bool vec_ok = (p.c_rs % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.c_bs % 8 == 0);
         Unit u;
         for (int it = 0; next_unit(p, cluster, clusters, it, u); ++it) {
@@ -376,11 +381,16 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                 }
             };
+            // this warp's columns [c_lo, c_hi): half of the unit's, or (a width that does not split
+            // into two multiples of 64) all of them for the first warp of the pair and none for the other
+            const bool halves = out_w % 128 == 0;
+            const int c_lo = halves ? col_half * (out_w / 2) : 0;
+            const int c_hi = halves ? c_lo + out_w / 2 : (col_half == 0 ? out_w : 0);
             if (p.use_tma_store) {
 #pragma unroll 1
-                for (int c = 0; c < out_w; c += 64) {
-                    unsigned char* tile_smem = epi_smem + ((warp - 2) * 2 + epi_buf) * P_EPI_TILE_BYTES;
-                    if (lane == 0) bulk_wait_read<1>();
+                for (int c = c_lo; c < c_hi; c += 64) {
+                    unsigned char* tile_smem = epi_smem + (warp - 2) * P_EPI_TILE_BYTES;
+                    if (lane == 0) bulk_wait_read<0>();    // the store before this one has read the staging tile
                     __syncwarp();
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
@@ -404,11 +414,10 @@ matmul_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         tma_store_3d(&map_c, smem_u32(tile_smem), (int)ncol, (int)mrow, b);
                         bulk_commit();
                     }
-                    epi_buf ^= 1;
                 }
             } else {
 #pragma unroll 1
-                for (int c = 0; c < out_w; c += 32) {
+                for (int c = c_lo; c < c_hi; c += 32) {
                     unsigned v[32];
                     finished(c, v);
                     const long long n = n0 + c;
