@@ -325,7 +325,10 @@ int32_t wgf_comm_release(wgf_comm* comm);
  * Every rank must request the same all-reduces in the same order.  When `t` is a whole-tensor
  * reduction, the exchange is done over peer memory by the kernels of this and the following
  * steps (no collective launch); the result is final for every reader that goes through this
- * library, and after wgf_device_sync.  A peer that does not take part within the limit
+ * library, and after wgf_device_sync.  The exchange makes progress on a rank when that rank
+ * queues its next all-reduce of this kind, reads a result or synchronises: a rank that has
+ * requested an all-reduce must not block on its peers by other means before it has done one of
+ * these.  A peer that does not take part within the limit
  * (environment WGF_PEER_WAIT_MS, default 5000) makes the next synchronisation return
  * WGF_ERR_TIMEOUT; later all-reduces on that device are refused until a new communicator
  * has been created. */
