@@ -267,10 +267,8 @@ def test_f32_wide_tile_kernel_on_ragged_shapes(shape, wgf, dev):
         M, N, K = shape
         a = (g.random((M, K), dtype=np.float32) * 2 - 1)
         b = (g.random((K, N), dtype=np.float32) * 2 - 1)
-    dev.set_timing(True)
-    t = dev.tensor(a).mat_mul(dev.tensor(b))
+    t = dev.tensor(a).mat_mul(dev.tensor(b))       # per-kernel timing is on by default: the labels name the kernel
     got = t.as_slice()
     assert "sgemm_wide" in t.timing_labels()
-    dev.set_timing(False)
     ref = a.astype(np.float64) @ b.astype(np.float64)
     assert normwise(got, ref) <= 1e-5
