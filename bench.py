@@ -71,38 +71,44 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs.
+    nvidia-smi writes to a file that is read when the sampling stops: no thread of this process
+    wakes up while a timed region runs (a reader thread would take the interpreter lock from the
+    thread that queues the steps every time a line arrives).  The timed region of the headline is
+    about a millisecond long, so its sampler runs at a slow rate from the warm-up on (each sample is a
+    driver query on a machine whose other GPUs are busy too); the 0.25 s long run is sampled densely."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
+    def __init__(self, index, period_ms=20):
         self.proc = None
-        self.lines = []
+        self.out = None
         try:
+            import tempfile
+            self.out = tempfile.NamedTemporaryFile(mode="w+", prefix="wgf_clocks_", suffix=".csv")
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "20"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
+                                          "--format=csv,noheader,nounits", "-lms", str(period_ms)],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+            self.period_ms = period_ms
         except OSError:
             self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
 
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.15 + self.period_ms / 1000.0)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        self.out.flush()
+        self.out.seek(0)
+        lines = [line.strip() for line in self.out.read().splitlines()]
+        self.out.close()
         mhz, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -493,7 +499,7 @@ def run_gpu(args):
     barrier = Barrier(dev, dist, torch, world)
 
     # ---- device-resident timing --------------------------------------------------------------
-    sampler = ClockSampler(local) if rank == 0 else None   # sampled from the warm-up on: the timed region is short
+    sampler = ClockSampler(local, period_ms=100) if rank == 0 else None   # sampled from the warm-up on: the timed region is short
     last = None
     for i in range(max(args.warmup, 3)):
         last = step(i)
