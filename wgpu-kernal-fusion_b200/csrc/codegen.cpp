@@ -2,6 +2,8 @@
 // first use (cached per device) and launches it.  Replaces the WGSL text generation of
 // src/element_wise.rs:64-130, src/pair_wise.rs:112-159, src/reduce.rs:83-281 and the launch
 // arithmetic of src/visit_tiled.rs:149-193 / src/reduce.rs:321-386.
+#include <map>
+#include <mutex>
 #include <algorithm>
 #include <sstream>
 
@@ -137,11 +139,24 @@ void magic_for(uint32_t d, uint32_t& m, uint32_t& s) {
     s = p - 32;
 }
 
-// Tuning overrides read from the environment (WGF_TUNE_<NAME>=int); absent = `dflt`.
+// Tuning overrides read from the environment (WGF_TUNE_<NAME>=int); absent = `dflt`.  Each name is
+// looked up once per process (a launch asks for half a dozen of them, and a scan of the environment
+// costs about as much as everything else the launcher does for a small kernel).
 int tune(const char* name, int dflt) {
-    std::string key = std::string("WGF_TUNE_") + name;
-    const char* v = getenv(key.c_str());
-    return v ? atoi(v) : dflt;
+    struct Entry {
+        bool set;
+        int value;
+    };
+    static std::mutex mu;
+    static std::map<std::string, Entry> seen;
+    std::lock_guard<std::mutex> g(mu);
+    auto it = seen.find(name);
+    if (it == seen.end()) {
+        const std::string key = std::string("WGF_TUNE_") + name;
+        const char* v = getenv(key.c_str());
+        it = seen.emplace(name, Entry{v != nullptr, v ? atoi(v) : 0}).first;
+    }
+    return it->second.set ? it->second.value : dflt;
 }
 
 // Checked build: names the buffers of the launch that follows (Device::chk_bind); the result last.
