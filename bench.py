@@ -331,18 +331,35 @@ class Barrier:
         return float(int(t[0]) + int(t[1])) / 1e3
 
 
+class NoCollections:
+    """The interpreter's cyclic garbage collector stays off inside a timed region (as `timeit` keeps
+    it): a collection that falls into a millisecond-long region of one rank holds up every rank."""
+
+    def __enter__(self):
+        import gc
+        self.was_on = gc.isenabled()
+        gc.disable()          # (no collection here: a full one right before the region leaves the caches cold)
+
+    def __exit__(self, *exc):
+        import gc
+        if self.was_on:
+            gc.enable()
+        return False
+
+
 def time_region(torch, stream, barrier, fn, steps, close=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier.start()
-    e0.record(stream)
-    last = None
-    for i in range(steps):
-        last = fn(i)
-    if close is not None:
-        close(last)
-    del last
-    e1.record(stream)
-    barrier()
+    with NoCollections():
+        barrier.start()
+        e0.record(stream)
+        last = None
+        for i in range(steps):
+            last = fn(i)
+        if close is not None:
+            close(last)
+        del last
+        e1.record(stream)
+        barrier()
     return e0.elapsed_time(e1) / steps
 
 
@@ -489,9 +506,9 @@ def run_gpu(args):
 
     def close_region(s):
         # At N > 1 the kernel of a step stores this rank's scalar, posts the scalar of the step
-        # before to the other ranks and combines the ranks' scalars of the step before that; the
-        # last two steps' exchanges are still open when the loop ends.  The last result is consumed
-        # here, inside the timed region (the library finishes both with one small kernel, then a
+        # before to the other ranks and combines the ranks' scalars of the step six before; the
+        # last six steps' exchanges are still open when the loop ends.  The last result is consumed
+        # here, inside the timed region (the library finishes them with one small kernel, then a
         # one-element multiply reads it): the region contains every step's all-reduce in full.
         if comm is not None and s is not None:
             (s * 1.0).materialize()
@@ -517,6 +534,8 @@ def run_gpu(args):
     dev.set_timing(False)
     launches_before = dev.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    no_collections = NoCollections()
+    no_collections.__enter__()
     barrier.start()
     e0.record(stream)
     host_t0 = time.perf_counter()
@@ -533,6 +552,7 @@ def run_gpu(args):
     del last
     e1.record(stream)
     barrier()
+    no_collections.__exit__(None, None, None)
     ms_total = e0.elapsed_time(e1)
     start_skew_us = barrier.skew_us()    # how far apart the ranks opened the region
     close_ms = e_loop.elapsed_time(e1)   # what consuming the last step's all-reduced scalar adds to the region
@@ -726,7 +746,7 @@ def run_gpu(args):
             "row_kernel_median_us": (round(float(np.median(row_ns)) / 1e3, 1) if row_ns else None),
             "region_start_skew_us": start_skew_us,
             "all_reduce": (None if comm is None else
-                           "over peer memory, inside the steps' own kernels: the kernel of step k stores this rank's value, posts the value of step k-1 and combines the ranks' values of step k-2"
+                           "over peer memory, inside the steps' own kernels: the kernel of step k stores this rank's value, posts the value of step k-1 and combines the ranks' values of step k-6"
                            if per_step == kernels_per_step else "NCCL launch"),
             "all_reduce_on_device_stream_ms": ar_ms,
             "clocks": clocks,

@@ -3,7 +3,7 @@
 Each rank owns a shard x_r of f32 [1024,512].  One request asks for the softmax rows of the shard and
 three all-reduced whole-tensor reductions of it (sum of exp, max, sum of squares): one kernel per rank
 computes all four and posts the three scalars to the other ranks over peer memory (no NCCL launch);
-the kernel of the next such step posts them, the one after that combines what the ranks posted, and one
+the kernel of the next such step posts them, the kernel six steps on combines what the ranks posted, and one
 small kernel does both when a result is read first.  Checked against float64 numpy over all shards, for 40 steps of two exchanges each
 (sequence numbers wrap the mailbox slots five times), and that every rank holds identical bits.  With
 WGF_NO_PEER_ALLREDUCE=1 the same script checks the NCCL path (four launches per step)."""
@@ -73,8 +73,8 @@ for step in range(40):
         print(f"rank {rank} step {step}: the ranks hold different bits", flush=True)
         bad += 1
 # Second phase: 100 exchanges queued without reading anything back, rank 1 starting late: the kernel
-# of exchange k settles exchange k - 2, so the other ranks' streams stop two exchanges ahead of rank 1
-# until it arrives (well inside the wait limit); then every result is read, the last two through a
+# of exchange k settles exchange k - 6, so the other ranks' streams stop six exchanges ahead of rank 1
+# until it arrives (well inside the wait limit); then every result is read, the last six through a
 # kernel of their own.
 import time  # noqa: E402
 

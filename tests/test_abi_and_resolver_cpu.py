@@ -389,7 +389,7 @@ def test_null_chain_with_a_length_is_an_error_not_a_crash(wgf, drydev):
 def test_all_reduce_over_peer_memory_costs_one_launch_per_step(wgf, drydev):
     """Host side of the scalar all-reduce over peer memory, on the compile-only device (its
     communicator needs no NCCL and compiles the same kernels).  The kernel of a step stores this
-    rank's values, posts the values of the step before and settles the step before that: one launch
+    rank's values, posts the values of the step before and settles the step six before: one launch
     per step, however many values ride along.  Results that are read before those later kernels
     have been queued are finished by one small kernel, once for all open exchanges; a
     synchronisation does the same."""
@@ -410,16 +410,15 @@ def test_all_reduce_over_peer_memory_costs_one_launch_per_step(wgf, drydev):
         fn()
         return d.launch_count - before
 
-    n1, s1, m1 = step()
-    n2, s2, m2 = step()
-    n3, s3, m3 = step()
-    n4, s4, m4 = step()
-    assert (n1, n2, n3, n4) == (1, 1, 1, 1)
-    assert launches_of(lambda: (s1 * 2.0).materialize()) == 1   # settled by the kernel of step 3: a plain read
-    assert launches_of(lambda: (m2 * 2.0).materialize()) == 1   # settled by the kernel of step 4
-    assert launches_of(lambda: (s3 * 2.0).materialize()) == 2   # posted, not settled: one kernel finishes 3 and 4
-    assert launches_of(lambda: (m4 * 2.0).materialize()) == 1   # ... so this one is a plain read
-    assert launches_of(lambda: (m3 * 2.0).materialize()) == 1
+    steps = [step() for _ in range(8)]
+    assert [n for n, _, _ in steps] == [1] * 8
+    s = [None] + [t[1] for t in steps]
+    m = [None] + [t[2] for t in steps]
+    assert launches_of(lambda: (s[1] * 2.0).materialize()) == 1   # settled by the kernel of step 7: a plain read
+    assert launches_of(lambda: (m[2] * 2.0).materialize()) == 1   # settled by the kernel of step 8
+    assert launches_of(lambda: (s[3] * 2.0).materialize()) == 2   # posted, not settled: one kernel finishes 3 .. 8
+    assert launches_of(lambda: (m[8] * 2.0).materialize()) == 1   # ... so these are plain reads
+    assert launches_of(lambda: (m[5] * 2.0).materialize()) == 1
     # the streaming reduction is a kernel of the same path
     alone = (x * 2.0).exp().sum(0).sum(0).all_reduce(comm)
     assert launches_of(alone.materialize) == 1

@@ -51,7 +51,7 @@ void nccl_check(int r, const char* what) {
 
 Comm::~Comm() {
     if (dev && !dev->dry) cudaSetDevice(dev->ordinal);
-    if (dev && (posted.seq || produced.seq)) {
+    if (dev && (!posted.empty() || produced.seq)) {
         // results of the last exchanges are still this rank's own values: finish them while the
         // mailboxes exist
         try {
@@ -214,11 +214,15 @@ GrandComm comm_peer_begin(Comm& c, Device& dev) {
     g.seq = ++c.seq;
     g.mailbox = c.mailbox;
     g.wait_ns = c.wait_ns;
-    g.prev_seq = c.posted.seq;
-    g.prev_n = c.posted.seq ? (uint32_t)c.posted.vals.size() : 0u;
-    for (uint32_t i = 0; i < g.prev_n; ++i) {
-        g.prev_meta[i] = peer_value_meta(c.posted.vals[i]);
-        g.prev_out[i] = c.posted.vals[i].out.base_ptr();
+    // the oldest posted exchange is settled by this kernel once it is kMailboxLag kernels old
+    if ((int)c.posted.size() >= kMailboxLag - 1) {
+        const Comm::Exchange& old = c.posted.front();
+        g.prev_seq = old.seq;
+        g.prev_n = (uint32_t)old.vals.size();
+        for (uint32_t i = 0; i < g.prev_n; ++i) {
+            g.prev_meta[i] = peer_value_meta(old.vals[i]);
+            g.prev_out[i] = old.vals[i].out.base_ptr();
+        }
     }
     g.post_seq = c.produced.seq;
     g.post_n = c.produced.seq ? (uint32_t)c.produced.vals.size() : 0u;
@@ -231,8 +235,12 @@ GrandComm comm_peer_begin(Comm& c, Device& dev) {
 
 void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<PeerValue>& vals) {
     WGF_CHECK(!vals.empty() && vals.size() <= (size_t)kMailboxValues, WGF_ERR_INVALID_ARGUMENT, "exchange of 1..4 values");
-    unmark(c, c.posted);   // the kernel just queued settles it; later work on the device stream sees the results
-    c.posted = std::move(c.produced);
+    if ((int)c.posted.size() >= kMailboxLag - 1) {
+        unmark(c, c.posted.front());   // the kernel just queued settles it; later work on the device stream sees the results
+        c.posted.pop_front();
+    }
+    if (c.produced.seq) c.posted.push_back(std::move(c.produced));
+    c.produced = Comm::Exchange{};
     c.produced.seq = seq;
     c.produced.vals = vals;
     for (const PeerValue& v : vals) v.out.buf->unsettled = &c;
@@ -240,19 +248,22 @@ void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<Peer
 }
 
 void comm_settle(Comm& c, Device& dev) {
-    if (!c.posted.seq && !c.produced.seq) return;
-    Comm::Exchange posted, produced;
-    std::swap(posted, c.posted);
+    if (c.posted.empty() && !c.produced.seq) return;
+    std::deque<Comm::Exchange> posted;
+    Comm::Exchange produced;
+    posted.swap(c.posted);
     std::swap(produced, c.produced);
-    for (Comm::Exchange* e : {&posted, &produced})
+    std::vector<const Comm::Exchange*> todo;
+    for (const Comm::Exchange& e : posted) todo.push_back(&e);
+    if (produced.seq) todo.push_back(&produced);
+    for (const Comm::Exchange* e : todo)
         for (const PeerValue& v : e->vals)
             if (v.out.buf->unsettled == &c) v.out.buf->unsettled = nullptr;
     if (dev.unsettled_comm == &c) dev.unsettled_comm = nullptr;
     dev.launches++;
     if (dev.dry) return;
     dev.make_current();
-    launch_peer_flush(dev.stream, c, dev.error_word(), produced.seq ? &produced : nullptr, posted.seq ? &posted : nullptr,
-                      produced.seq ? &produced : nullptr);
+    launch_peer_flush(dev.stream, c, dev.error_word(), produced.seq ? &produced : nullptr, todo.data(), (int)todo.size());
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) {
         cudaGetLastError();

@@ -1,6 +1,8 @@
 // NCCL communicator for the one exchange the path has: the all-reduce that closes a
 // full-tensor reduction whose rows are sharded over GPUs.  libnccl is loaded at run time.
 #pragma once
+#include <deque>
+
 #include "launch.hpp"
 #include "runtime.hpp"
 
@@ -21,26 +23,31 @@ struct Comm {
     // a mailbox of 64-bit words {sequence number << 32 | value bits}, laid out
     // [kMailboxSlots][world source ranks][kMailboxValues], and maps the peers' mailboxes through
     // CUDA IPC.  An exchange goes through three stages, each done by a kernel of this path on the
-    // device stream, so that a step of a loop costs one launch and its stream never stops for a peer:
+    // device stream, so that a step of a loop costs one launch and its stream never stops for a peer
+    // that is less than kMailboxLag - 1 kernels behind:
     //   produced  kernel k (the one that computes the values) stores this rank's values in the
     //             result buffers, which are marked Buffer::unsettled from then on;
     //   posted    kernel k+1 reads them back first thing and stores one word per value into
     //             slot `k % kMailboxSlots` of every rank's mailbox (NVLink stores for the peers, a
     //             local one for itself); it waits for nothing;
-    //   settled   one CTA of kernel k+2 waits (bounded: wait_ns) until the own mailbox holds every
-    //             rank's word of exchange k, combines them in rank order -- every rank gets the
-    //             same bits -- and overwrites the results.  Ranks that run the same program posted
-    //             k a whole kernel earlier, so nothing waits: the CTA asks for the words when it
-    //             starts and takes them when it is done with its own rows.
+    //   settled   one CTA of kernel k+kMailboxLag waits (bounded: wait_ns) until the own mailbox
+    //             holds every rank's word of exchange k, combines them in rank order -- every rank
+    //             gets the same bits -- and overwrites the results.  Ranks that run the same
+    //             program posted k several kernels earlier, so nothing waits: the CTA asks for the
+    //             words when it starts and takes them when it is done with its own rows.  The lag
+    //             is what lets ranks drift apart: a rank whose host stalls for a moment holds the
+    //             others up only once they are kMailboxLag - 1 kernels ahead of it, so stalls of
+    //             different ranks overlap instead of adding up.
     // If a result is read first (Device::wait_for), the device synchronised or a schedule recorded,
     // a one-CTA kernel on the device stream does what is left for the open exchanges (comm_settle).
     //
     // A slot is reused every kMailboxSlots exchanges, with no further gate.  On every rank the
-    // stream order is produce(j) < post(j) < settle(j), and settle(j) ends before kernel j+2 does;
-    // settle(j) ends only after every peer's post(j) has arrived.  When rank A posts j, its kernel
-    // j has ended, so its settle(j-2) is over, so every peer had posted j-2, so every peer's kernel
-    // j-2 had ended, and with it the peer's settle(j-4): the peers have read every exchange up to
-    // j-4, and the word of exchange j-16 that post j replaces is long dead.
+    // stream order is produce(j) < post(j) < settle(j), and settle(j) ends before kernel j+Lag
+    // does; settle(j) ends only after every peer's post(j) has arrived.  When rank A posts j, its
+    // kernel j has ended, so its settle(j-Lag) is over, so every peer had posted j-Lag, so every
+    // peer's kernel j-Lag had ended, and with it the peer's settle(j-2 Lag): the peers have read
+    // every exchange up to j-2 Lag, and with kMailboxSlots >= 2 kMailboxLag + 1 the word of
+    // exchange j-kMailboxSlots that post j replaces is dead.
     void* mailbox = nullptr;              // this rank's mailbox (device memory)
     std::vector<void*> peer_mailbox;      // [world]; the own entry is `mailbox`
     void* peer_table = nullptr;           // device array of the world mailbox addresses
@@ -52,12 +59,13 @@ struct Comm {
         std::vector<PeerValue> vals;      // its results (keeps the buffers alive)
     };
     Exchange produced;                    // values stored, not posted
-    Exchange posted;                      // posted, not settled (always the one before `produced`)
+    std::deque<Exchange> posted;          // posted, not settled, oldest first (at most kMailboxLag - 1)
     ~Comm();
 };
 constexpr int kMailboxValues = 4;
 constexpr int kMailboxSlots = 16;
-static_assert(kMailboxSlots >= 5, "a slot must have been read before it is posted to again");
+constexpr int kMailboxLag = 6;
+static_assert(kMailboxSlots >= 2 * kMailboxLag + 1, "a slot must have been read before it is posted to again");
 
 // Starts the next exchange: its sequence number, and the two open exchanges that the kernel which
 // produces it posts and settles.  Call before launching that kernel.
@@ -68,9 +76,9 @@ void comm_peer_finish(Comm& c, Device& dev, uint32_t seq, const std::vector<Peer
 // Finishes the open exchanges, if any, with a kernel of its own on the device stream
 // (declared in runtime.hpp too: Device::wait_for and Device::sync call it).
 void comm_settle(Comm& c, Device& dev);
-// The kernel of comm_settle: posts `post` (if it has values), then settles `first` and `second`.
+// The kernel of comm_settle: posts `post` (if not null), then settles the `n` exchanges of `settle` in order.
 void launch_peer_flush(cudaStream_t stream, const Comm& c, unsigned* err, const Comm::Exchange* post,
-                       const Comm::Exchange* first, const Comm::Exchange* second);
+                       const Comm::Exchange* const* settle, int n);
 // op | dtype << 8 | value index << 16, as the settling code reads it
 uint32_t peer_value_meta(const PeerValue& v);
 

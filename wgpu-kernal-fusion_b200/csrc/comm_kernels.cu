@@ -23,7 +23,8 @@ struct FlushParams {
     unsigned* err;                       // device error word
     unsigned long long wait_ns;          // limit of the wait for a peer's word
     unsigned world, rank;
-    ExchangeParams post, settle[2];
+    unsigned n_settle;
+    ExchangeParams post, settle[kMailboxLag];
 };
 
 __device__ __forceinline__ float combine(unsigned op, float a, float b) {
@@ -90,8 +91,7 @@ __global__ void __launch_bounds__(32 * kMailboxValues) peer_flush_kernel(const F
             asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"((unsigned long long*)p.peers[r] + at), "l"(word) : "memory");
     }
     __syncthreads();   // the values have been read before a settle below overwrites them
-    settle(p, p.settle[0]);
-    settle(p, p.settle[1]);
+    for (unsigned i = 0; i < p.n_settle; ++i) settle(p, p.settle[i]);
 }
 
 void fill(ExchangeParams& e, const Comm::Exchange* x) {
@@ -108,7 +108,7 @@ void fill(ExchangeParams& e, const Comm::Exchange* x) {
 }  // namespace
 
 void launch_peer_flush(cudaStream_t stream, const Comm& c, unsigned* err, const Comm::Exchange* post,
-                       const Comm::Exchange* first, const Comm::Exchange* second) {
+                       const Comm::Exchange* const* settle_list, int n) {
     FlushParams p{};
     p.mailbox = (const unsigned long long*)c.mailbox;
     p.peers = (const unsigned long long*)c.peer_table;
@@ -117,8 +117,8 @@ void launch_peer_flush(cudaStream_t stream, const Comm& c, unsigned* err, const 
     p.world = (unsigned)c.world;
     p.rank = (unsigned)c.rank;
     fill(p.post, post);
-    fill(p.settle[0], first);
-    fill(p.settle[1], second);
+    p.n_settle = (unsigned)(n < kMailboxLag ? n : kMailboxLag);   // never more: kMailboxLag - 1 posted + 1 produced
+    for (unsigned i = 0; i < p.n_settle; ++i) fill(p.settle[i], settle_list[i]);
     peer_flush_kernel<<<1, 32 * kMailboxValues, 0, stream>>>(p);
 }
 
