@@ -646,8 +646,8 @@ std::string row_source(const Program& prog_in, const RowConfig& c) {
     bool posts = false;
     for (const Grand& gr : prog.grands) posts = posts || gr.all_reduce;
     // A kernel whose values are all-reduced stores this GPU's values like any other; it posts the
-    // values of the exchange before its own first thing, and its last CTA settles the exchange
-    // before that one around its share of the rows (see Comm).
+    // values of the exchange before its own first thing, and its last CTA settles the oldest open
+    // exchange around its share of the rows (see Comm).
     replace_all(tmpl, "ROW_GRAND_POST", posts ? "PEER_POST(p) PEER_PEEK(p)" : "");
     replace_all(tmpl, "ROW_GRAND_SETTLE", posts ? "PEER_SETTLE(p)" : "");
     replace_all(tmpl, "ROW_INVARIANT", inv.str());

@@ -300,9 +300,10 @@ DEV void peer_post(u64 src, u32 meta, u64 peers, u32 world, u32 rank, u32 seq) {
 
 // SETTLING exchange k: wait (bounded by wait_ns) until this GPU's own mailbox holds every rank's
 // word of it, combine the words in rank order -- every rank ends with the same bits -- and write
-// the n results over this GPU's own values.  The kernel that produces exchange k + 2 does it: the
-// peers posted k at the start of their kernel k + 1, a whole kernel earlier for ranks that run
-// the same program, so nothing waits, and no launch, event or second stream is spent on the
+// the n results over this GPU's own values.  The kernel that produces exchange k + 6 does it (the
+// lag of the pipeline, see Comm): the peers posted k at the start of their kernel k + 1, several
+// kernels earlier for ranks that run the same program, so nothing waits even when the ranks have
+// drifted apart by a few kernels, and no launch, event or second stream is spent on the
 // exchange.  All threads of the kernel's LAST CTA take part: peer_peek issues the loads when the
 // CTA starts, peer_settle takes the words when the CTA is done with its own rows, polls for the
 // ones that had not arrived, and combines by shuffles.  Warp w serves value w (w + warps, ... if

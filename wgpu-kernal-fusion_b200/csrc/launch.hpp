@@ -19,7 +19,7 @@ TensorData run_elementwise(Device& dev, const Program& prog, const std::vector<T
 // `out_has_h` and a non-empty index space; their rank-0 results are returned in `grand_out`.
 // Companion reductions marked `all_reduce` are exchanged through the mailboxes of a communicator
 // (see Comm): the kernel stores this GPU's values of exchange `seq`, posts the values of the
-// exchange before it (post_*) and settles the one before that (prev_*), where those are still open.
+// exchange before it (post_*) and settles the oldest open one once that is kMailboxLag kernels old (prev_*).
 struct GrandComm {
     const void* peer_table;   // device array of the ranks' mailbox addresses
     uint32_t world, rank, seq;
