@@ -37,3 +37,31 @@ def test_facade_on_gpu(facade_binary):
     r = subprocess.run([facade_binary], capture_output=True, text=True, env=_env())
     assert r.returncode == 0, r.stderr
     assert "facade ok" in r.stdout
+
+
+@pytest.fixture(scope="module")
+def host_cost_binary(tmp_path_factory, wgf):
+    wgf.lib()
+    exe = str(tmp_path_factory.mktemp("cpp") / "host_cost")
+    subprocess.run(["g++", "-std=c++17", "-O2", "-Wall", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "host_cost.cpp"), "-o", exe, "-L", PKG, "-lwgf",
+                    f"-Wl,-rpath,{PKG}"], check=True)
+    return exe
+
+
+def test_host_cost_of_a_materialisation_through_the_c_abi(host_cost_binary):
+    """tests/cpp/host_cost.cpp: the nine-op chain built, resolved and released 20 000 times through the
+    C ABI alone (no binding on top), on the compile-only device.  The figure is printed, not asserted
+    on (a busy host would fail a bound); what is checked is that nothing leaks or fails on the way."""
+    r = subprocess.run([host_cost_binary, "--compile-only-device"], capture_output=True, text=True, env=_env(), timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "host cost ok" in r.stdout and "build + materialise + release" in r.stdout
+    print(r.stdout.strip())
+
+
+@pytest.mark.gpu
+def test_host_cost_on_gpu(host_cost_binary):
+    r = subprocess.run([host_cost_binary], capture_output=True, text=True, env=_env(), timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "host cost ok" in r.stdout
+    print(r.stdout.strip())
