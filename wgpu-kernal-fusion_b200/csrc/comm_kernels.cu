@@ -37,12 +37,11 @@ __device__ __forceinline__ unsigned long long word_at(unsigned seq, unsigned wor
     return (unsigned long long)((seq % kMailboxSlots) * world + r) * kMailboxValues + index;
 }
 
-// Warp w settles value w; lane l waits for the words of ranks l, l + 32, ...  A wait that runs
-// out sets the error word (51) and leaves this GPU's own value as the result: the kernel always
-// returns, and the host sees WGF_ERR_TIMEOUT at its next synchronisation.
-__device__ void settle(const FlushParams& p, const ExchangeParams& e) {
-    const unsigned v = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (v >= e.n) return;
+// One warp settles value v of exchange e; lane l waits for the words of ranks l, l + 32, ...  A
+// wait that runs out sets the error word (51) and leaves this GPU's own value as the result: the
+// kernel always returns, and the host sees WGF_ERR_TIMEOUT at its next synchronisation.
+__device__ void settle(const FlushParams& p, const ExchangeParams& e, unsigned v) {
+    const unsigned lane = threadIdx.x & 31;
     const unsigned op = e.meta[v] & 255u, dt = (e.meta[v] >> 8) & 255u, index = e.meta[v] >> 16;
     bool all_here = true;
     unsigned long long start = 0;
@@ -91,7 +90,12 @@ __global__ void __launch_bounds__(32 * kMailboxValues) peer_flush_kernel(const F
             asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"((unsigned long long*)p.peers[r] + at), "l"(word) : "memory");
     }
     __syncthreads();   // the values have been read before a settle below overwrites them
-    for (unsigned i = 0; i < p.n_settle; ++i) settle(p, p.settle[i]);
+    // the (exchange, value) pairs go round the four warps: they are independent of one another
+    const unsigned warp = threadIdx.x >> 5;
+    unsigned q = 0;
+    for (unsigned i = 0; i < p.n_settle; ++i)
+        for (unsigned v = 0; v < p.settle[i].n; ++v, ++q)
+            if (q % kMailboxValues == warp) settle(p, p.settle[i], v);
 }
 
 void fill(ExchangeParams& e, const Comm::Exchange* x) {
