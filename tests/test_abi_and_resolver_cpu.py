@@ -480,3 +480,38 @@ def test_library_runs_with_nvtx_ranges_on(tmp_path):
     r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "LAUNCHES 2" in r.stdout
+
+
+def test_f32_matmul_dispatch_between_the_two_ffma_kernels(tmp_path):
+    """Which f32 products take the 128x256-tile kernel: B stored [K,N], M and N at least 512, K at least
+    256 and enough tiles to fill the machine twice; everything else (a transposed view of B, small or
+    few-tile problems) keeps the 128x128 kernel.  Read from the launch trace on the compile-only device."""
+    import subprocess
+    import sys
+    script = tmp_path / "dispatch.py"
+    script.write_text(
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {os.path.join(ROOT, 'tests')!r})\n"
+        "from conftest import load_package\n"
+        "wgf = load_package(); d = wgf.Device(-1)\n"
+        "z = lambda *s: d.tensor(np.zeros(s, np.float32))\n"
+        "cases = {'BIG': (z(2048, 512), z(512, 4864)), 'FEWTILES': (z(1024, 512), z(512, 1024)),\n"
+        "         'SHORTK': (z(2048, 128), z(128, 4864)), 'SMALL': (z(100, 100), z(100, 100)),\n"
+        "         'BATCH': (z(2, 2048, 512), z(2, 512, 2560))}\n"
+        "for name, (a, b) in cases.items():\n"
+        "    print('@@', name, file=sys.stderr, flush=True); a.mat_mul(b).materialize()\n"
+        "a, bt = z(2048, 512), z(4864, 512)\n"
+        "print('@@ TRANSPOSED', file=sys.stderr, flush=True); a.mat_mul(bt.transpose(0, 1)).materialize()\n")
+    env = dict(os.environ, WGF_TRACE_LAUNCHES="1", WGF_KERNEL_CACHE=str(tmp_path / "cache"))
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    seen = {}
+    for chunk in r.stderr.split("@@ ")[1:]:
+        name, _, text = chunk.partition("\n")
+        seen[name.strip()] = [line.split("launch ", 1)[1].strip() for line in text.splitlines() if "[wgf] launch " in line]
+    assert seen["BIG"] == ["sgemm_wide"], seen              # 16 x 19 = 304 tiles
+    assert seen["BATCH"] == ["sgemm_wide"], seen            # 2 x 16 x 10 = 320 tiles
+    assert seen["FEWTILES"] == ["sgemm"], seen              # 8 x 4 tiles: less than two per SM
+    assert seen["SHORTK"] == ["sgemm"], seen
+    assert seen["SMALL"] == ["sgemm"], seen
+    assert seen["TRANSPOSED"] == ["sgemm"], seen            # B as an [N,K] view: the 128x128 kernel reads it in place
