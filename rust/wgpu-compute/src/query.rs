@@ -32,11 +32,22 @@ pub struct PerformanceQueries {
 }
 
 impl PerformanceQueries {
+    /// An empty query set for a kernel-level call to fill (`PerformanceQueries::new`,
+    /// `src/query.rs:51-76`; the device argument is kept for the signature, the handle is created by
+    /// the launch that receives `&mut self.raw`).  The wgpu-specific `resolve` and
+    /// `compute_timestamp_writes` of the original have no counterpart: the library records its event
+    /// pair inside the launch.
+    pub fn new(_device: &crate::Device) -> Self {
+        PerformanceQueries { raw: std::ptr::null_mut() }
+    }
+
     /// Waits for the kernels of the call and returns their summed device time
     /// (`PerformanceQueries::wait_for_results`, `src/query.rs:78-112`).
     pub async fn wait_for_results(&self) -> QueryResults {
         let mut ns = 0u64;
-        crate::error::expect(unsafe { wgf_sys::wgf_timing_elapsed_ns(self.raw, &mut ns) });
+        if !self.raw.is_null() {
+            crate::error::expect(unsafe { wgf_sys::wgf_timing_elapsed_ns(self.raw, &mut ns) });
+        }
         QueryResults::from_nanos(ns)
     }
 }

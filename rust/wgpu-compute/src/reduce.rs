@@ -7,20 +7,33 @@ use wgf_sys as sys;
 /// name it but not build one.  Kept for that; it names one of the four reductions.
 #[derive(Clone, Debug, PartialEq, Eq)]
 pub struct ReduceFunction {
-    name: &'static str,
+    name: Option<String>,
+    builtin: &'static str,
     pub(crate) opcode: u32,
 }
 
 impl ReduceFunction {
+    const fn builtin(builtin: &'static str, opcode: u32) -> Self {
+        ReduceFunction { name: None, builtin, opcode }
+    }
+
+    /// The name given with `with_name`, else the reduction's own (the original answers "reduce" for
+    /// an unnamed function, `src/reduce.rs:407-409`; here the four reductions are told apart).
     pub fn name(&self) -> &str {
-        self.name
+        self.name.as_deref().unwrap_or(self.builtin)
+    }
+
+    /// A label for traces and timing records (`src/reduce.rs:411-414`); the arithmetic is unchanged.
+    pub fn with_name(mut self, name: impl ToString) -> Self {
+        self.name = Some(name.to_string());
+        self
     }
 }
 
-pub(crate) const SUM: ReduceFunction = ReduceFunction { name: "sum", opcode: sys::WGF_OP_SUM };
-pub(crate) const MAX: ReduceFunction = ReduceFunction { name: "max", opcode: sys::WGF_OP_MAX };
-pub(crate) const MIN: ReduceFunction = ReduceFunction { name: "min", opcode: sys::WGF_OP_MIN };
-pub(crate) const PRODUCT: ReduceFunction = ReduceFunction { name: "product", opcode: sys::WGF_OP_PRODUCT };
+pub(crate) const SUM: ReduceFunction = ReduceFunction::builtin("sum", sys::WGF_OP_SUM);
+pub(crate) const MAX: ReduceFunction = ReduceFunction::builtin("max", sys::WGF_OP_MAX);
+pub(crate) const MIN: ReduceFunction = ReduceFunction::builtin("min", sys::WGF_OP_MIN);
+pub(crate) const PRODUCT: ReduceFunction = ReduceFunction::builtin("product", sys::WGF_OP_PRODUCT);
 
 impl<const R: usize, D: DataType> Tensor<R, D> {
     pub(crate) fn reduce<const OUT: usize>(&self, function: &ReduceFunction, dim: usize) -> Tensor<OUT, D> {
