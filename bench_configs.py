@@ -92,7 +92,11 @@ def stream_time_row(dev, row, budget_s=0.03):
         for _ in range(n):
             sched.launch()
         dev.sync()
-        return (time.perf_counter() - t0) / (n * reps) * 1e6
+        us = (time.perf_counter() - t0) / (n * reps) * 1e6
+        # tens of milliseconds of tensor-core work back to back leave the GPU at its power cap: give it a
+        # moment, or the next row's single launches are timed at the clocks this row ended with
+        time.sleep(0.3)
+        return us
     except Exception:
         return None
     finally:
