@@ -75,3 +75,25 @@ def test_gpu_arm_fails_without_a_gpu():
                        capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode != 0
     assert '"value"' not in r.stdout
+
+
+def test_config_sweep_runs_on_the_compile_only_device():
+    """bench_configs.py end to end without a GPU: the rows of the first group are built, resolved and
+    recorded as schedules on the compile-only device (no times come out of it, only the structure)."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from conftest import load_package
+    wgf = load_package()
+    spec = importlib.util.spec_from_file_location("wgf_bench_configs_under_test", os.path.join(ROOT, "bench_configs.py"))
+    sweep = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sweep)
+    dev = wgf.Device(-1)
+    lines = []
+    rows = sweep.run(wgf, dev, 6543.4, 1668.8, iters=2, warmup=1, only="C1", emit=lines.append, peak_tflops_sustained=1376.9)
+    assert len(rows) == 5 and len(lines) == 5
+    names = [r["row"] for r in rows]
+    assert any("wall clock per pass" in n for n in names) and any(n.startswith("C1' chain") for n in names)
+    for r in rows:
+        json.dumps(r)                                    # every row is a JSON object
+        if "median_us" in r:
+            assert "back_to_back_us" in r                # the recorded-schedule path ran too
